@@ -1,0 +1,81 @@
+"""The library's engine, cache and batching driven on the CPU (kernels replaced by the
+torch stand-ins of tests/cpu_kernels.py) against the plain implementation: whole
+prompts, the last tokens one by one, and unequal batches one after another."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import cpu_kernels
+from conftest import TINY, prompts_for
+from plain import qwen3_plain as plain
+from toyinfer_b200.engine import Engine
+
+
+@pytest.fixture()
+def cpu_engine(monkeypatch, model_folders):
+    cpu_kernels.install(monkeypatch)
+
+    def make(name, **kw):
+        kw.setdefault("max_tokens", 2048)
+        kw.setdefault("max_batch", 8)
+        return Engine.from_folder(model_folders[name], dtype="float32", device="cpu", **kw)
+
+    return make
+
+
+def _plain_logits(folder, ids):
+    return plain.forward(plain.read_weights(folder), plain.read_config(folder), ids).float()
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole_prompt_matches_plain(cpu_engine, model_folders, name):
+    eng = cpu_engine(name)
+    ids = prompts_for(name, [90 if name == "C" else 37])[0]
+    slot = eng.new_sequence()
+    got = eng.step([(slot, ids)], [list(range(len(ids)))])
+    want = _plain_logits(model_folders[name], ids)
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
+    eng.end_sequence(slot)
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_last_tokens_one_by_one(cpu_engine, model_folders, name):
+    eng = cpu_engine(name)
+    n = 150 if name == "C" else 60
+    ids = prompts_for(name, [n], seed=1)[0]
+    want = _plain_logits(model_folders[name], ids)
+    slot = eng.new_sequence()
+    head = n - 32
+    got = [eng.step([(slot, ids[:head])], [[head - 1]])]
+    for t in range(head, n):
+        got.append(eng.step([(slot, [ids[t]])], [[0]]).clone())
+    got = torch.cat(got)
+    torch.testing.assert_close(got, want[head - 1:], rtol=1e-4, atol=1e-5)
+
+
+def test_unequal_batches_reuse_slots(cpu_engine, model_folders):
+    name = "C"
+    eng = cpu_engine(name, max_tokens=64 * 8)
+    for round_ in range(3):
+        lens = [70, 3, 130, 41][: 4 - round_ % 2]
+        dec = [5, 9, 2, 7]
+        seqs = prompts_for(name, [n + d for n, d in zip(lens, dec)], seed=10 + round_)
+        want = [_plain_logits(model_folders[name], s) for s in seqs]
+        slots = [eng.new_sequence() for _ in seqs]
+        logits = eng.step([(sl, s[:n]) for sl, s, n in zip(slots, seqs, lens)], None)
+        for i, n in enumerate(lens):
+            torch.testing.assert_close(logits[i], want[i][n - 1], rtol=1e-4, atol=1e-5)
+        live = list(range(len(seqs)))
+        t = 0
+        while live:
+            logits = eng.step([(slots[i], [seqs[i][lens[i] + t]]) for i in live], None)
+            for r, i in enumerate(live):
+                torch.testing.assert_close(logits[r], want[i][lens[i] + t], rtol=1e-4, atol=1e-5)
+            t += 1
+            for i in [i for i in live if t >= dec[i]]:
+                eng.end_sequence(slots[i])
+            live = [i for i in live if t < dec[i]]
+        assert eng.cache.slots.n_free == eng.cache.n_slots
+        for g in eng.cache.kv_groups:
+            assert g.pool.n_free == g.pool.n_pages

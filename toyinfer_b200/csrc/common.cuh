@@ -1,0 +1,96 @@
+// Shared device helpers and the error convention of the C entry points.
+//
+// Every entry point is `extern "C" int ti_<name>(..., cudaStream_t stream)`; it
+// returns 0 on success and otherwise a non-zero code after storing a message that
+// `ti_last_error()` returns.  Nothing here allocates device memory or synchronises.
+// Element types are passed as codes: 0 = float32, 1 = bfloat16.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TI_F32 0
+#define TI_BF16 1
+
+void ti_set_error(const char* fmt, ...);
+
+#define TI_FAIL(...)                \
+    do {                            \
+        ti_set_error(__VA_ARGS__);  \
+        return 1;                   \
+    } while (0)
+
+#define TI_REQUIRE(cond, ...)           \
+    do {                                \
+        if (!(cond)) {                  \
+            ti_set_error(__VA_ARGS__);  \
+            return 1;                   \
+        }                               \
+    } while (0)
+
+#define TI_CHECK_LAUNCH(name)                                                          \
+    do {                                                                               \
+        cudaError_t e__ = cudaGetLastError();                                          \
+        if (e__ != cudaSuccess) {                                                      \
+            ti_set_error("%s: launch failed: %s", name, cudaGetErrorString(e__));      \
+            return 2;                                                                  \
+        }                                                                              \
+    } while (0)
+
+#define TI_CUDA(call)                                                                  \
+    do {                                                                               \
+        cudaError_t e__ = (call);                                                      \
+        if (e__ != cudaSuccess) {                                                      \
+            ti_set_error("%s failed: %s", #call, cudaGetErrorString(e__));             \
+            return 2;                                                                  \
+        }                                                                              \
+    } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `red` is shared memory for 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // protects `red` against a previous use
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+    if (warp == 0) {
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+template <typename F>
+static inline int ti_dispatch_dtype(int dtype, F&& f) {
+    // f is called with a value of the element type
+    if (dtype == TI_F32) return f(float());
+    if (dtype == TI_BF16) return f(bf16());
+    ti_set_error("unknown element type code %d", dtype);
+    return 1;
+}

@@ -1,0 +1,156 @@
+// Per-head RMS norm of q and k, rotary encoding, and the store of k and v into the
+// paged cache, in one pass over the projection's output.  Each stage is optional:
+// a null norm weight skips the norm, null tables skip the rotation, null pages skip
+// the store, a null q/k/v pointer skips that tensor.
+//
+// Reference formulas: per-head norm src/decode.cu:144-187 (one [head_dim] weight for
+// all heads, rounded to the storage type before the rotation, as its in-place kernel
+// does); rotation src/decode.cu:301-324 (pairs i, i + head_dim/2); cache row write
+// src/decode.cu:374-386.  The reference runs these as five launches plus two copies
+// per layer (src/transformer.cpp:380-398, :535-552).
+//
+// One warp handles one (token, head).  The cache position of a token:
+//   row  = pos                    (ring_rows == 0)
+//   row  = pos mod ring_rows      (windowed group; tokens older than the ring are not stored)
+//   page = page_table[slot][row / page_size], line row % page_size
+#include "common.cuh"
+
+struct RopeStoreArgs {
+    void* q; void* k; void* v;
+    long long q_stride, k_stride, v_stride;   // elements between consecutive tokens
+    int n_heads, n_kv_heads, head_dim;
+    const void* q_w; const void* k_w; int w_is_f32; float eps;
+    const float* cos_t; const float* sin_t; int max_pos;
+    const int* tok_pos; const int* tok_seq; const int* seq_slot; const int* seq_len;
+    void* k_pages; void* v_pages; const int* page_table; int table_width; int page_size;
+    int ring_rows; int n_pages;
+    int M;
+};
+
+template <typename T>
+__global__ void rope_store_kernel(RopeStoreArgs a) {
+    const int warps_per_block = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int heads_q = a.q ? a.n_heads : 0;
+    const int heads_k = a.k ? a.n_kv_heads : 0;
+    const int heads_v = a.v ? a.n_kv_heads : 0;
+    const int per_tok = heads_q + heads_k + heads_v;
+    const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    if (item >= (long long)a.M * per_tok) return;
+    const int m = (int)(item / per_tok);
+    int h = (int)(item - (long long)m * per_tok);
+    int kind;  // 0 q, 1 k, 2 v
+    if (h < heads_q) kind = 0;
+    else if (h < heads_q + heads_k) { kind = 1; h -= heads_q; }
+    else { kind = 2; h -= heads_q + heads_k; }
+
+    const int hd = a.head_dim, half = hd >> 1;
+    T* x = kind == 0 ? (T*)a.q + (size_t)m * a.q_stride + (size_t)h * hd
+         : kind == 1 ? (T*)a.k + (size_t)m * a.k_stride + (size_t)h * hd
+                     : (T*)a.v + (size_t)m * a.v_stride + (size_t)h * hd;
+    int pos = a.tok_pos[m];
+
+    // where the cache keeps this token, if it does
+    T* dst = nullptr;
+    if (kind != 0 && a.k_pages) {
+        const int seq = a.tok_seq[m];
+        const int slot = a.seq_slot[seq];
+        int row = pos;
+        bool keep = pos >= 0;
+        if (a.ring_rows > 0) {
+            keep = keep && pos >= a.seq_len[seq] - a.ring_rows;
+            row = pos % a.ring_rows;
+        }
+        const int pidx = row / a.page_size;
+        if (keep && pidx < a.table_width) {
+            const int page = a.page_table[(size_t)slot * a.table_width + pidx];
+            if (page >= 0 && page < a.n_pages) {
+                T* base = (T*)(kind == 1 ? a.k_pages : a.v_pages);
+                dst = base + (((size_t)page * a.n_kv_heads + h) * a.page_size + (row % a.page_size)) * hd;
+            }
+        }
+    }
+
+    if (kind == 2) {  // values: copy only
+        if (dst)
+            for (int i = lane; i < hd; i += 32) dst[i] = x[i];
+        return;
+    }
+
+    const void* wv = kind == 0 ? a.q_w : a.k_w;
+    float r = 1.f;
+    if (wv) {
+        float ss = 0.f;
+        for (int i = lane; i < hd; i += 32) {
+            const float t = to_f32(x[i]);
+            ss = fmaf(t, t, ss);
+        }
+        ss = warp_sum(ss);
+        r = rsqrtf(fmaf(ss, 1.0f / (float)hd, a.eps));
+    }
+    if (pos < 0) pos = 0;
+    if (pos >= a.max_pos) pos = a.max_pos - 1;
+    const float* cs = a.cos_t ? a.cos_t + (size_t)pos * half : nullptr;
+    const float* sn = a.sin_t ? a.sin_t + (size_t)pos * half : nullptr;
+    for (int i = lane; i < half; i += 32) {
+        float lo = to_f32(x[i]), hi = to_f32(x[i + half]);
+        if (wv) {
+            const float wl = a.w_is_f32 ? ((const float*)wv)[i] : to_f32(((const T*)wv)[i]);
+            const float wh = a.w_is_f32 ? ((const float*)wv)[i + half] : to_f32(((const T*)wv)[i + half]);
+            lo = to_f32(from_f32<T>(lo * r * wl));
+            hi = to_f32(from_f32<T>(hi * r * wh));
+        }
+        if (cs) {
+            const float c = cs[i], s = sn[i];
+            const float nlo = lo * c - hi * s;
+            const float nhi = hi * c + lo * s;
+            lo = nlo; hi = nhi;
+        }
+        const T tlo = from_f32<T>(lo), thi = from_f32<T>(hi);
+        x[i] = tlo; x[i + half] = thi;
+        if (dst) { dst[i] = tlo; dst[i + half] = thi; }
+    }
+}
+
+extern "C" int ti_qk_norm_rope_store(
+    void* q, void* k, void* v, long long q_stride, long long k_stride, long long v_stride,
+    int n_heads, int n_kv_heads, int head_dim,
+    const void* q_w, const void* k_w, int w_is_f32, float eps,
+    const float* cos_t, const float* sin_t, int rot_dim, int max_pos,
+    const int* tok_pos, const int* tok_seq, const int* seq_slot, const int* seq_len,
+    void* k_pages, void* v_pages, const int* page_table, int table_width, int page_size,
+    int ring_rows, int n_pages, int M, int dtype, cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(head_dim > 0 && head_dim % 2 == 0, "qk_norm_rope_store: head size %d must be even", head_dim);
+    TI_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "qk_norm_rope_store: cos and sin tables go together");
+    TI_REQUIRE(!cos_t || rot_dim == head_dim,
+               "qk_norm_rope_store: rotation over %d of %d elements is not implemented (the whole head only)",
+               rot_dim, head_dim);
+    TI_REQUIRE(!cos_t || max_pos > 0, "qk_norm_rope_store: empty rotary tables");
+    TI_REQUIRE((k_pages == nullptr) == (v_pages == nullptr), "qk_norm_rope_store: k and v pages go together");
+    TI_REQUIRE(!k_pages || (page_table && page_size > 0 && table_width > 0 && n_pages > 0 && tok_seq && seq_slot),
+               "qk_norm_rope_store: incomplete cache description");
+    TI_REQUIRE(ring_rows == 0 || (ring_rows % page_size == 0 && seq_len),
+               "qk_norm_rope_store: ring of %d rows is not a multiple of the page size %d", ring_rows, page_size);
+    RopeStoreArgs a;
+    a.q = q; a.k = k; a.v = k_pages ? v : nullptr;   // values are only ever copied to the cache
+    a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim;
+    a.q_w = q_w; a.k_w = k_w; a.w_is_f32 = w_is_f32; a.eps = eps;
+    a.cos_t = cos_t; a.sin_t = sin_t; a.max_pos = max_pos > 0 ? max_pos : 1;
+    a.tok_pos = tok_pos; a.tok_seq = tok_seq; a.seq_slot = seq_slot; a.seq_len = seq_len;
+    a.k_pages = k_pages; a.v_pages = v_pages; a.page_table = page_table; a.table_width = table_width;
+    a.page_size = page_size; a.ring_rows = ring_rows; a.n_pages = n_pages; a.M = M;
+    const int per_tok = (a.q ? n_heads : 0) + (a.k ? n_kv_heads : 0) + (a.v ? n_kv_heads : 0);
+    if (per_tok == 0) return 0;
+    const long long items = (long long)M * per_tok;
+    const int warps = 4;
+    const long long blocks = (items + warps - 1) / warps;
+    TI_REQUIRE(blocks < 2147483647LL, "qk_norm_rope_store: too many heads x tokens (%lld)", items);
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        rope_store_kernel<T><<<(unsigned)blocks, warps * 32, 0, stream>>>(a);
+        TI_CHECK_LAUNCH("qk_norm_rope_store");
+        return 0;
+    });
+}

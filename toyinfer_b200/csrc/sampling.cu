@@ -1,0 +1,312 @@
+// Choosing the next token from float32 logits: argmax, and temperature sampling with
+// top-k and top-p.
+//
+// The reference samples on the CPU (src/sampler.cpp:18-69): greedy when
+// |temperature| < 1e-3 or top_k == 1 (first maximum wins, :71-81); otherwise
+// x = logit / temperature, the k largest are kept, p = softmax over them, sorted
+// descending, the list is cut after the first entry at which the running sum exceeds
+// top_p, and a uniform draw times that sum picks the first entry whose running sum
+// exceeds it.  It divides by the temperature a second time inside the exponent
+// (:38) and seeds its generator from the clock (:57-60); here the temperature
+// applies once and the uniform number is a pure function of (seed, sequence key,
+// step), so a sequence draws the same numbers in any batch.
+//
+// One block of 1024 threads per row.  Which of the two rules applies is the host's
+// decision; this file only refuses combinations it cannot run.
+#include "common.cuh"
+
+#include <climits>
+
+namespace {
+constexpr int SB = 1024;      // threads per block
+constexpr int MAXK = 1024;    // candidates the top-k path can sort
+
+__device__ __forceinline__ unsigned order_key(float x) {
+    const unsigned u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);   // larger float <=> larger key
+}
+
+// uniform in [0, 1) with 24 bits, from (seed, key, step)
+__host__ __device__ __forceinline__ float uniform_from(unsigned long long seed, unsigned long long key,
+                                                       unsigned long long step) {
+    unsigned long long x = seed * 0x9E3779B97F4A7C15ull + key * 0xBF58476D1CE4E5B9ull +
+                           step * 0x94D049BB133111EBull + 0x2545F4914F6CDD1Dull;
+    x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull;
+    x ^= x >> 27; x *= 0x94D049BB133111EBull;
+    x ^= x >> 31;
+    return (float)(x >> 40) * (1.0f / 16777216.0f);
+}
+
+// exclusive prefix sums over the block's threads in thread order; returns the total
+template <typename V>
+__device__ V block_exclusive_scan(V v, V* total, V* sm /* 33 entries */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    V inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const V n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += n;
+    }
+    __syncthreads();
+    if (lane == 31) sm[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        V w = lane < (blockDim.x >> 5) ? sm[lane] : V(0);
+        V winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const V n = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += n;
+        }
+        sm[lane] = winc - w;
+        if (lane == 31) sm[32] = winc;
+    }
+    __syncthreads();
+    *total = sm[32];
+    return sm[warp] + inc - v;
+}
+
+__global__ void __launch_bounds__(SB) argmax_kernel(const float* __restrict__ logits, long long ld, int V,
+                                                    int* __restrict__ out) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const float* x = logits + (size_t)blockIdx.x * ld;
+    float best = -INFINITY;
+    int idx = INT_MAX;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = x[i];
+        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    }
+    auto better = [](float v, int i, float w, int j) { return v > w || (v == w && i < j); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float w = __shfl_xor_sync(0xffffffffu, best, o);
+        const int j = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (better(w, j, best, idx)) { best = w; idx = j; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < (blockDim.x >> 5) ? bv[lane] : -INFINITY;
+        idx = lane < (blockDim.x >> 5) ? bi[lane] : INT_MAX;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float w = __shfl_xor_sync(0xffffffffu, best, o);
+            const int j = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (better(w, j, best, idx)) { best = w; idx = j; }
+        }
+        if (lane == 0) out[blockIdx.x] = idx == INT_MAX ? 0 : idx;
+    }
+}
+
+struct SampleArgs {
+    const float* logits; long long ld; int V;
+    float temperature; int top_k; float top_p;
+    unsigned long long seed; const long long* keys; const int* steps;
+    int* out;
+};
+
+// top_k in [1, MAXK], top_k < V.  Keeps exactly top_k entries (ties at the k-th value
+// go to the lowest indices), then applies top_p on the sorted list.
+__global__ void __launch_bounds__(SB) sample_topk_kernel(SampleArgs a) {
+    __shared__ int hist[256];
+    __shared__ float cval[MAXK];
+    __shared__ int cidx[MAXK];
+    __shared__ int scan_i[33];
+    __shared__ unsigned s_prefix;
+    __shared__ int s_rem, s_count;
+    const int t = threadIdx.x, V = a.V, k = a.top_k;
+    const float* x = a.logits + (size_t)blockIdx.x * a.ld;
+    const float temp = a.temperature;
+
+    // --- the key of the k-th largest value, by radix selection from the top byte down
+    unsigned prefix = 0, mask = 0;
+    int rem = k;
+    for (int pass = 3; pass >= 0; pass--) {
+        if (t < 256) hist[t] = 0;
+        __syncthreads();
+        for (int i = t; i < V; i += SB) {
+            const unsigned key = order_key(x[i] / temp);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> (8 * pass)) & 255], 1);
+        }
+        __syncthreads();
+        if (t == 0) {
+            int above = 0, bin = 255;
+            for (; bin > 0; bin--) {
+                if (above + hist[bin] >= rem) break;
+                above += hist[bin];
+            }
+            s_prefix = prefix | ((unsigned)bin << (8 * pass));
+            s_rem = rem - above;
+        }
+        __syncthreads();
+        prefix = s_prefix;
+        rem = s_rem;
+        mask |= 0xFFu << (8 * pass);
+        __syncthreads();
+    }
+    const unsigned thr = prefix;   // rem = how many entries equal to thr are kept
+
+    // --- gather: everything above thr, then the `rem` lowest-index entries equal to thr
+    if (t == 0) s_count = 0;
+    __syncthreads();
+    const int chunk = (V + SB - 1) / SB;
+    const int lo = min(V, t * chunk), hi = min(V, lo + chunk);
+    int ties = 0;
+    for (int i = lo; i < hi; i++) {
+        const float v = x[i] / temp;
+        const unsigned key = order_key(v);
+        if (key > thr) {
+            const int p = atomicAdd(&s_count, 1);
+            if (p < MAXK) { cval[p] = v; cidx[p] = i; }
+        } else if (key == thr) {
+            ties++;
+        }
+    }
+    int total_ties;
+    int rank = block_exclusive_scan<int>(ties, &total_ties, scan_i);
+    __syncthreads();
+    const int n_gt = s_count;     // < k
+    for (int i = lo; i < hi && rank < rem; i++) {
+        const float v = x[i] / temp;
+        if (order_key(v) == thr) {
+            const int p = n_gt + rank;
+            if (p < MAXK) { cval[p] = v; cidx[p] = i; }
+            rank++;
+        }
+    }
+    __syncthreads();
+    const int n = min(k, MAXK);
+
+    // --- sort descending by value, ascending index on ties (bitonic, padded to a power of two)
+    int n2 = 1;
+    while (n2 < n) n2 <<= 1;
+    for (int i = n + t; i < n2; i += SB) { cval[i] = -INFINITY; cidx[i] = INT_MAX; }
+    __syncthreads();
+    for (int size = 2; size <= n2; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = t; i < n2; i += SB) {
+                const int j = i ^ stride;
+                if (j > i) {
+                    const bool desc = (i & size) == 0;
+                    const float vi = cval[i], vj = cval[j];
+                    const int ii = cidx[i], ij = cidx[j];
+                    const bool i_first = vi > vj || (vi == vj && ii < ij);   // i belongs before j
+                    if (desc != i_first) { cval[i] = vj; cval[j] = vi; cidx[i] = ij; cidx[j] = ii; }
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    // --- softmax over the kept entries, top-p cut, draw
+    const float mx = cval[0];
+    for (int i = t; i < n; i += SB) cval[i] = expf(cval[i] - mx);
+    __syncthreads();
+    if (t == 0) {
+        float sum = 0.f;
+        for (int i = 0; i < n; i++) sum += cval[i];
+        float acc = 0.f;
+        int kept = n;
+        for (int i = 0; i < n; i++) {
+            acc += cval[i] / sum;
+            if (acc > a.top_p) { kept = i + 1; break; }
+        }
+        const float u = uniform_from(a.seed, (unsigned long long)a.keys[blockIdx.x],
+                                     (unsigned long long)a.steps[blockIdx.x]);
+        const float coin = u * acc;
+        float run = 0.f;
+        int pick = cidx[kept - 1];
+        for (int i = 0; i < kept; i++) {
+            run += cval[i] / sum;
+            if (run > coin) { pick = cidx[i]; break; }
+        }
+        a.out[blockIdx.x] = pick;
+    }
+}
+
+// whole vocabulary, no top-k, no top-p: first index whose running probability exceeds u
+__global__ void __launch_bounds__(SB) sample_full_kernel(SampleArgs a) {
+    __shared__ float red[33];
+    __shared__ float scan_f[33];
+    __shared__ int s_owner;
+    const int t = threadIdx.x, V = a.V;
+    const float* x = a.logits + (size_t)blockIdx.x * a.ld;
+    const float temp = a.temperature;
+    float mx = -INFINITY;
+    for (int i = t; i < V; i += SB) mx = fmaxf(mx, x[i] / temp);
+    mx = warp_max(mx);
+    if ((t & 31) == 0) red[t >> 5] = mx;
+    __syncthreads();
+    if (t < 32) {
+        float m2 = red[t];
+        m2 = warp_max(m2);
+        if (t == 0) red[32] = m2;
+    }
+    __syncthreads();
+    mx = red[32];
+    const int chunk = (V + SB - 1) / SB;
+    const int lo = min(V, t * chunk), hi = min(V, lo + chunk);
+    float part = 0.f;
+    for (int i = lo; i < hi; i++) part += expf(x[i] / temp - mx);
+    float total;
+    const float off = block_exclusive_scan<float>(part, &total, scan_f);
+    const float u = uniform_from(a.seed, (unsigned long long)a.keys[blockIdx.x],
+                                 (unsigned long long)a.steps[blockIdx.x]);
+    const float target = u * total;
+    if (t == 0) s_owner = SB;
+    __syncthreads();
+    if (hi > lo && off + part > target) atomicMin(&s_owner, t);
+    __syncthreads();
+    int owner = s_owner;
+    if (owner == SB) {   // rounding left the target at the very end: last thread that has entries
+        owner = min(SB - 1, (V - 1) / chunk);
+    }
+    if (t == owner) {
+        float acc = off;
+        int pick = hi - 1;
+        for (int i = lo; i < hi; i++) {
+            acc += expf(x[i] / temp - mx);
+            if (acc > target) { pick = i; break; }
+        }
+        a.out[blockIdx.x] = pick;
+    }
+}
+}  // namespace
+
+extern "C" int ti_argmax(const float* logits, long long ld, int R, int V, int* out, cudaStream_t stream) {
+    if (R == 0) return 0;
+    TI_REQUIRE(R > 0 && V > 0 && ld >= V, "argmax: bad sizes R=%d V=%d ld=%lld", R, V, ld);
+    argmax_kernel<<<R, SB, 0, stream>>>(logits, ld, V, out);
+    TI_CHECK_LAUNCH("argmax");
+    return 0;
+}
+
+// keys[R] (int64) and steps[R] (int32) on the device name each row's sequence and how many
+// tokens it has drawn so far.
+extern "C" int ti_sample(const float* logits, long long ld, int R, int V, float temperature, int top_k,
+                         float top_p, unsigned long long seed, const long long* keys, const int* steps,
+                         int* out, cudaStream_t stream) {
+    if (R == 0) return 0;
+    TI_REQUIRE(R > 0 && V > 0 && ld >= V, "sample: bad sizes R=%d V=%d ld=%lld", R, V, ld);
+    TI_REQUIRE(temperature > 0.f, "sample: temperature %g must be positive (zero is the argmax rule)", temperature);
+    TI_REQUIRE(top_p > 0.f, "sample: top_p %g must be positive", top_p);
+    SampleArgs a;
+    a.logits = logits; a.ld = ld; a.V = V; a.temperature = temperature; a.top_k = top_k;
+    a.top_p = top_p; a.seed = seed; a.keys = keys; a.steps = steps; a.out = out;
+    const bool k_off = top_k <= 0 || top_k >= V;
+    if (k_off) {
+        TI_REQUIRE(top_p >= 1.0f, "sample: top_p %g without a top_k of at most %d is not implemented", top_p, MAXK);
+        sample_full_kernel<<<R, SB, 0, stream>>>(a);
+    } else {
+        TI_REQUIRE(top_k <= MAXK, "sample: top_k %d exceeds the %d candidates this kernel sorts", top_k, MAXK);
+        sample_topk_kernel<<<R, SB, 0, stream>>>(a);
+    }
+    TI_CHECK_LAUNCH("sample");
+    return 0;
+}
+
+extern "C" float ti_uniform_from(unsigned long long seed, unsigned long long key, unsigned long long step) {
+    return uniform_from(seed, key, step);
+}

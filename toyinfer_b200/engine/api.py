@@ -1,0 +1,104 @@
+"""The Python entry point: a model folder (or a configuration with random weights)
+in, generated token ids out.
+
+    llm = LLM("path/to/model", dtype="bfloat16", max_seq_len=8192)
+    results = llm.generate([[1, 2, 3], [4, 5]], SamplingParams(temperature=0.0), max_new_tokens=16)
+
+Prompts are token ids: the reference's tokenizer and chat template
+(src/tokenizer.cpp) are not part of this library.  Option names follow the
+reference's command line (src/options.cpp:7-45) where it has them.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..sampling import GREEDY, Sampler, SamplingParams
+from .engine import Engine, parse_dtype
+from .generate import GenerationLoop, GenerationResult, GenerationStats
+
+
+class _Stepper:
+    """What the generation loop drives: the engine's steps plus a sampler."""
+
+    def __init__(self, engine: Engine, sampler: Sampler):
+        self.engine, self.sampler = engine, sampler
+
+    def new_sequence(self) -> int:
+        return self.engine.new_sequence()
+
+    def end_sequence(self, slot: int) -> None:
+        self.engine.end_sequence(slot)
+
+    def step(self, entries, want):
+        return self.engine.step(entries, want)
+
+    def sample(self, logits, keys, steps) -> List[int]:
+        return self.sampler.sample(logits, keys, steps).tolist()   # device -> host, waits for the step
+
+
+def default_max_tokens(engine_kw: dict, model, max_batch: int, max_seq_len: int) -> int:
+    """Cache capacity when the caller gives none: what max_batch full sequences need,
+    limited to 60 % of the device memory that is free once the weights are loaded."""
+    want = max_batch * ((max_seq_len + 63) // 64 * 64)
+    per_token = 0
+    for req in model.memory_requests():
+        if req is not None and hasattr(req, "n_kv_heads"):
+            per_token += 2 * req.n_kv_heads * req.head_dim * (2 if model.dtype == torch.bfloat16 else 4)
+    if model.device.type == "cuda" and per_token:
+        free, _ = torch.cuda.mem_get_info(model.device)
+        want = min(want, max(64, int(free * 0.6) // per_token))
+    return max(64, want // 64 * 64)
+
+
+class LLM:
+    def __init__(self, model_dir: Optional[str] = None, *, config: Optional[dict] = None, seed: int = 0,
+                 dtype="bfloat16", max_seq_len: Optional[int] = None, max_batch: int = 64,
+                 max_tokens: Optional[int] = None, enable_cuda_graph: bool = True,
+                 use_dedicated_prefill: bool = True, device="cuda"):
+        if (model_dir is None) == (config is None):
+            raise ValueError("give either model_dir or config (random weights)")
+        from .. import models  # noqa: F401
+        from ..config.registry import architecture_of, load_config
+        from ..parts.model import DecoderModel
+        from ..weights import load_parameters, random_parameters
+        dt = parse_dtype(dtype)
+        if model_dir is not None:
+            arch, cfg = load_config(model_dir)
+        else:
+            arch = architecture_of(config)
+            cfg = arch.config_cls.from_dict(config)
+        model = DecoderModel(arch.describe(cfg), dt, device)
+        if model_dir is not None:
+            model.bind(load_parameters(model.param_specs(), model_dir, dt, model.device,
+                                       ignorable=model.ignorable_names()))
+        else:
+            model.bind(random_parameters(model.param_specs(), seed, dt, model.device))
+        limit = model.spec.max_positions
+        msl = int(min(max_seq_len or limit, limit))
+        if max_tokens is None:
+            max_tokens = default_max_tokens({}, model, max_batch, msl)
+        self.engine = Engine(model, max_tokens=max_tokens, max_batch=max_batch, max_seq_len=msl,
+                             use_cuda_graph=enable_cuda_graph)
+        self.config = cfg
+        self.use_dedicated_prefill = use_dedicated_prefill
+        self.last_stats: Optional[GenerationStats] = None
+
+    @property
+    def stop_token_ids(self):
+        return tuple(self.engine.spec.stop_token_ids)
+
+    def generate(self, prompts: Sequence[Sequence[int]], sampling: Optional[SamplingParams] = None,
+                 max_new_tokens: int = 16, stop_token_ids: Optional[Sequence[int]] = None,
+                 ignore_eos: bool = False) -> List[GenerationResult]:
+        sampling = sampling or SamplingParams()
+        stops = set(self.stop_token_ids)
+        stops.update(stop_token_ids or ())
+        e = self.engine
+        loop = GenerationLoop(_Stepper(e, Sampler(sampling, e.device)), stops, e.max_batch, e.max_seq_len,
+                              e.cache.max_tokens, ignore_eos=ignore_eos,
+                              dedicated_prefill=self.use_dedicated_prefill)
+        out = loop.run(prompts, max_new_tokens)
+        self.last_stats = loop.stats
+        return out

@@ -1,0 +1,240 @@
+"""The step function: runs exactly the tokens it is given, as one batch, from the cache.
+
+``Engine.step(entries, want)`` takes for each sequence its slot and its next tokens.
+Either every sequence of the step starts at position 0 (prompts of unequal lengths, all
+in one step) or every sequence goes on by one token.  It returns float32 logits
+[wanted, vocab] for the wanted places, in the order of the entries.  Finished sequences
+are simply absent from the next step; ``end_sequence`` gives their slot and pages back.
+
+The reference has two entry points for one sequence, ``prefill(ids, n)`` and
+``forward(id, pos)`` (include/transformer.h:110-111); its decode body is captured once
+into a CUDA graph and replayed (src/transformer.cpp:647-669).  Here a decode step is
+captured per batch-size bucket; the graph reads slots, lengths and token ids from device
+buffers refreshed before each replay.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache import CacheError, CacheManager, PAGE, pages_for
+from ..config.registry import load_config
+from ..parts.model import DecoderModel, ModelSpec
+from ..weights import load_parameters, random_parameters
+from .batch import BatchBuffers, StepBatch, fill_batch
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype {name} is not supported (bfloat16 or float32)")
+        return name
+    try:
+        return _DTYPES[str(name).lower()]
+    except KeyError:
+        raise ValueError(f"dtype {name!r} is not supported (bfloat16 or float32)") from None
+
+
+class StepError(ValueError):
+    """A step that cannot be run as asked; nothing was changed."""
+
+
+def _bucket(n: int, cap: int) -> int:
+    b = 1
+    while b < n:
+        b <<= 1
+    return min(b, cap) if cap >= n else n
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, max_tokens: int, max_batch: int = 64,
+                 max_seq_len: Optional[int] = None, n_slots: Optional[int] = None,
+                 use_cuda_graph: bool = True):
+        self.model = model
+        self.spec: ModelSpec = model.spec
+        self.device = model.device
+        self.dtype = model.dtype
+        self.max_batch = int(max_batch)
+        limit = self.spec.max_positions
+        self.max_seq_len = int(min(max_seq_len or limit, limit))
+        self.max_tokens = int(max_tokens)
+        if n_slots is None:
+            n_slots = max(self.max_batch, min(pages_for(self.max_tokens), 1024))
+        self.cache = CacheManager(model.memory_requests(), self.max_tokens, n_slots, self.max_seq_len,
+                                  self.dtype, self.device)
+        self.memories = self.cache.views(len(model.schedule))
+        self.use_cuda_graph = bool(use_cuda_graph) and self.device.type == "cuda"
+        self._eager_bufs: Dict[Tuple[int, int], BatchBuffers] = {}
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self.graph_replays = 0
+
+    # -- construction -----------------------------------------------------------
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype="bfloat16", device="cuda", **kw) -> "Engine":
+        """Model folder (config.json + safetensors) -> engine; the model class is the one
+        that config.json names."""
+        from .. import models  # noqa: F401  (registers the architectures)
+        arch, cfg = load_config(model_dir)
+        dt = parse_dtype(dtype)
+        model = DecoderModel(arch.describe(cfg), dt, device)
+        tensors = load_parameters(model.param_specs(), model_dir, dt, model.device,
+                                  ignorable=model.ignorable_names())
+        model.bind(tensors)
+        eng = cls(model, **kw)
+        eng.config = cfg
+        return eng
+
+    @classmethod
+    def from_config(cls, config: dict, seed: int = 0, dtype="bfloat16", device="cuda", **kw) -> "Engine":
+        """Random weights drawn on the device, without a file (for measurements)."""
+        from .. import models  # noqa: F401
+        from ..config.registry import architecture_of
+        arch = architecture_of(config)
+        cfg = arch.config_cls.from_dict(config)
+        dt = parse_dtype(dtype)
+        model = DecoderModel(arch.describe(cfg), dt, device)
+        model.bind(random_parameters(model.param_specs(), seed, dt, model.device))
+        eng = cls(model, **kw)
+        eng.config = cfg
+        return eng
+
+    # -- sequences ----------------------------------------------------------------
+    def new_sequence(self) -> int:
+        return self.cache.allocate_slot()
+
+    def end_sequence(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length[slot]
+
+    # -- one step -------------------------------------------------------------------
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
+        """entries: (slot, next tokens) per sequence.  want: per entry the places among its
+        tokens whose logits are asked for (None: the last place of each).  Returns float32
+        [wanted, vocab] on the device, or None when nothing is wanted.  The tensor may be
+        a buffer that the next step overwrites: use or copy it before stepping again."""
+        n = len(entries)
+        if n == 0:
+            return None
+        if n > self.max_batch:
+            raise StepError(f"a step of {n} sequences exceeds max_batch {self.max_batch}")
+        slots = [int(s) for s, _ in entries]
+        tokens = [list(t) for _, t in entries]
+        if len(set(slots)) != n:
+            raise StepError("a slot appears twice in one step")
+        for s in slots:
+            if s not in self.cache.length:
+                raise StepError(f"slot {s} is not in use")
+        for s, t in zip(slots, tokens):
+            if not t:
+                raise StepError(f"slot {s}: a step needs at least one token per sequence")
+            for tok in t:
+                if not (0 <= tok < self.spec.vocab_size):
+                    raise StepError(f"slot {s}: token id {tok} is outside the vocabulary of {self.spec.vocab_size}")
+        starts = [self.cache.length[s] for s in slots]
+        if all(st == 0 for st in starts):
+            mode = "start"
+        elif all(len(t) == 1 for t in tokens):
+            mode = "extend"
+        else:
+            raise StepError("the sequences of a step either all start at their first token or all "
+                            "go on by one token")
+        if want is None:
+            want = [[len(t) - 1] for t in tokens]
+        if len(want) != n:
+            raise StepError("want needs one list per entry")
+        for w, t in zip(want, tokens):
+            for p in w:
+                if not (0 <= p < len(t)):
+                    raise StepError(f"wanted place {p} is outside the entry's {len(t)} tokens")
+        for s, st, t in zip(slots, starts, tokens):
+            if st + len(t) > self.max_seq_len:
+                raise StepError(f"slot {s}: {st + len(t)} positions exceed the limit of {self.max_seq_len}")
+        for s, st, t in zip(slots, starts, tokens):
+            self.cache.reserve(s, st + len(t))      # CacheError when the cache is full
+        self.cache.flush()
+
+        if mode == "extend" and self.use_cuda_graph:
+            logits_all = self._decode_graph(slots, starts, tokens)
+            rows = [i for i, w in enumerate(want) if w]
+            if not rows:
+                logits = None
+            elif len(rows) == n:
+                logits = logits_all[:n]
+            else:
+                logits = logits_all[torch.tensor(rows, device=self.device)]
+        else:
+            batch = self._eager_batch(mode, slots, starts, tokens)
+            h, delta = self.model.forward_hidden(batch, self.memories)
+            rows, o = [], 0
+            for w, t in zip(want, tokens):
+                rows.extend(o + p for p in w)
+                o += len(t)
+            if rows:
+                rows_dev = torch.tensor(rows, dtype=torch.int32, device=self.device)
+                logits = self.model.logits(h, delta, rows_dev)
+            else:
+                logits = None
+        for s, st, t in zip(slots, starts, tokens):
+            self.cache.commit(s, st + len(t))
+        return logits
+
+    # -- helpers ----------------------------------------------------------------------
+    def _eager_batch(self, mode, slots, starts, tokens) -> StepBatch:
+        n_seq, n_tok = len(slots), sum(len(t) for t in tokens)
+        key = (_bucket(n_seq, 1 << 30), _bucket(n_tok, 1 << 30))
+        buf = self._eager_bufs.get(key)
+        if buf is None:
+            buf = self._eager_bufs[key] = BatchBuffers(key[0], key[1], self.device)
+        return fill_batch(buf, mode, slots, starts, tokens, self.cache.scratch_slot, self.max_seq_len)
+
+    def _decode_graph(self, slots, starts, tokens) -> torch.Tensor:
+        n = len(slots)
+        b = _bucket(n, self.max_batch)
+        g = self._graphs.get(b)
+        if g is None:
+            g = self._graphs[b] = _DecodeGraph(self, b)
+        return g.run(slots, starts, tokens)
+
+
+class _DecodeGraph:
+    """A decode step of ``bucket`` sequences captured into a CUDA graph."""
+
+    def __init__(self, engine: Engine, bucket: int):
+        self.engine = engine
+        self.bucket = bucket
+        self.buf = BatchBuffers(bucket, bucket, engine.device)
+        self.rows = torch.arange(bucket, dtype=torch.int32, device=engine.device)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+
+    def _body(self, batch: StepBatch) -> torch.Tensor:
+        e = self.engine
+        h, delta = e.model.forward_hidden(batch, e.memories)
+        return e.model.logits(h, delta, self.rows)
+
+    def run(self, slots, starts, tokens) -> torch.Tensor:
+        e = self.engine
+        pad = self.bucket - len(slots)
+        batch = fill_batch(self.buf, "extend", slots, starts, tokens, e.cache.scratch_slot,
+                           e.max_seq_len, pad_seqs=pad)
+        if self.graph is None:
+            # one eager run first: it is this step's result, and it lets every kernel do its
+            # one-time set-up outside the capture
+            out = self._body(batch)
+            torch.cuda.current_stream().synchronize()
+            g = torch.cuda.CUDAGraph()
+            # the capture only records; nothing runs until the first replay
+            with torch.cuda.graph(g):
+                self.logits = self._body(batch)
+            self.graph = g
+            return out
+        self.graph.replay()
+        e.graph_replays += 1
+        return self.logits

@@ -1,0 +1,265 @@
+"""Python face of the CUDA kernels: one function per operation.
+
+Each function checks shapes, dtypes and devices, allocates its output with torch and
+calls the C entry point of the shared library on the current CUDA stream.  There is no
+other implementation behind these names: a tensor that is not on a CUDA device, or a
+library that cannot be built and loaded, is an error.
+
+The parts of a model call these through the module (``K.linear(...)``), never through
+names imported from it, so that the functions can be looked up at call time.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .lib import KernelError, library  # noqa: F401
+
+_CODES = {torch.float32: 0, torch.bfloat16: 1}
+launch_count = 0   # kernels launched through this module since import (for measurements)
+
+
+def _code(t: torch.Tensor, what: str) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors, what: str) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError(f"{what}: tensors must be on a CUDA device (got {t.device}); there is no CPU path")
+
+
+def _call(fn, *args, launches: int = 1) -> None:
+    global launch_count
+    rc = fn(*args)
+    if rc != 0:
+        raise KernelError(library().ti_last_error().decode("utf-8", "replace"))
+    launch_count += launches
+
+
+def _i32(t: torch.Tensor, what: str) -> torch.Tensor:
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{what}: expected a contiguous int32 tensor, got {t.dtype}")
+    return t
+
+
+def _row_stride(t: torch.Tensor, what: str) -> int:
+    """Elements between consecutive tokens of a [M, heads, dim] or [M, N] view whose
+    trailing dimensions are dense."""
+    if t.dim() == 3:
+        if t.stride(2) != 1 or t.stride(1) != t.shape[2]:
+            raise KernelError(f"{what}: heads of a token must be dense")
+    elif t.dim() == 2:
+        if t.stride(1) != 1:
+            raise KernelError(f"{what}: rows must be dense")
+    else:
+        raise KernelError(f"{what}: expected 2 or 3 dimensions")
+    return t.stride(0)
+
+
+# ---------------------------------------------------------------------------
+def embed(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    _need_cuda(table, ids, what="embed")
+    _i32(ids, "embed ids")
+    V, H = table.shape
+    out = torch.empty((ids.numel(), H), dtype=table.dtype, device=table.device)
+    _call(library().ti_embed, _ptr(table), _ptr(ids), _ptr(out), ids.numel(), H, V, _code(table, "embed"), _stream())
+    return out
+
+
+def _wcode(x: torch.Tensor, w: torch.Tensor, what: str) -> int:
+    wc = _code(w, what + " weight")
+    if x.dtype == torch.float32 and wc != 0:
+        raise KernelError(f"{what}: float32 rows need a float32 weight")
+    return wc
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    _need_cuda(x, w, what="rmsnorm")
+    M, H = x.shape
+    if w.shape != (H,) or not w.is_contiguous():
+        raise KernelError(f"rmsnorm: weight {tuple(w.shape)} does not fit rows of {H}")
+    stride = _row_stride(x, "rmsnorm")
+    out = torch.empty((M, H), dtype=x.dtype, device=x.device)
+    _call(library().ti_rmsnorm, _ptr(x), _ptr(None), _ptr(w), _ptr(out), M, H, stride, float(eps),
+          _code(x, "rmsnorm"), _wcode(x, w, "rmsnorm"), _stream())
+    return out
+
+
+def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """h <- h + delta in place (rounded once); returns rmsnorm(h) * w."""
+    _need_cuda(h, delta, w, what="add_rmsnorm")
+    M, H = h.shape
+    if delta.shape != h.shape or delta.dtype != h.dtype or not h.is_contiguous() or not delta.is_contiguous():
+        raise KernelError("add_rmsnorm: h and delta must be dense tensors of one shape and dtype")
+    if w.shape != (H,) or not w.is_contiguous():
+        raise KernelError(f"add_rmsnorm: weight {tuple(w.shape)} does not fit rows of {H}")
+    out = torch.empty_like(h)
+    _call(library().ti_rmsnorm, _ptr(h), _ptr(delta), _ptr(w), _ptr(out), M, H, H, float(eps),
+          _code(h, "add_rmsnorm"), _wcode(h, w, "add_rmsnorm"), _stream())
+    return out
+
+
+def gather_add(h: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
+    """out[r] = h[rows[r]] + delta[rows[r]] (delta may be None)."""
+    _need_cuda(h, delta, rows, what="gather_add")
+    _i32(rows, "gather_add rows")
+    M, H = h.shape
+    if not h.is_contiguous() or (delta is not None and (delta.shape != h.shape or not delta.is_contiguous()
+                                                        or delta.dtype != h.dtype)):
+        raise KernelError("gather_add: h and delta must be dense tensors of one shape and dtype")
+    out = torch.empty((rows.numel(), H), dtype=h.dtype, device=h.device)
+    _call(library().ti_gather_add, _ptr(h), _ptr(delta), _ptr(rows), _ptr(out), rows.numel(), H, M,
+          _code(h, "gather_add"), _stream())
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x[M, K] times w[N, K] transposed -> [M, N]; 32-bit accumulation.  ``out_dtype`` may
+    ask for float32 results from bfloat16 operands (the head)."""
+    _need_cuda(x, w, what="linear")
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise KernelError(f"linear: shapes {tuple(x.shape)} and {tuple(w.shape)} do not contract")
+    if x.dtype != w.dtype:
+        raise KernelError(f"linear: activations are {x.dtype} but the weight is {w.dtype}")
+    M, K = x.shape
+    N = w.shape[0]
+    out_dtype = out_dtype or x.dtype
+    if out_dtype not in (x.dtype, torch.float32):
+        raise KernelError(f"linear: output dtype {out_dtype} is not supported for {x.dtype} operands")
+    ldx, ldw = _row_stride(x, "linear x"), _row_stride(w, "linear w")
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    from . import gemm
+    gemm.run(x, w, out, M, N, K, ldx, ldw)
+    return out
+
+
+def swiglu(gu: torch.Tensor) -> torch.Tensor:
+    _need_cuda(gu, what="swiglu")
+    M, two_i = gu.shape
+    if two_i % 2 or not gu.is_contiguous():
+        raise KernelError("swiglu: expected a dense [M, 2*I] tensor")
+    out = torch.empty((M, two_i // 2), dtype=gu.dtype, device=gu.device)
+    _call(library().ti_swiglu, _ptr(gu), _ptr(out), M, two_i // 2, _code(gu, "swiglu"), _stream())
+    return out
+
+
+def qk_norm_rope_store(q, k, v, q_w, k_w, eps, tables, batch, mem) -> None:
+    """In place on the views q[M, heads, d], k[M, kv_heads, d]: per-head RMS norm (when a
+    weight is given), rotation by the cos/sin ``tables`` (when given), and the store of k and
+    v[M, kv_heads, d] into ``mem``'s pages (when given).  Any of q, k, v may be None."""
+    ref = q if q is not None else k if k is not None else v
+    if ref is None:
+        return
+    _need_cuda(q, k, v, q_w, k_w, what="qk_norm_rope_store")
+    M, hd = ref.shape[0], ref.shape[2]
+    nh = q.shape[1] if q is not None else 0
+    nkv = k.shape[1] if k is not None else (v.shape[1] if v is not None else 0)
+    for t in (q, k, v):
+        if t is not None and (t.dtype != ref.dtype or t.shape[0] != M or t.shape[2] != hd):
+            raise KernelError("qk_norm_rope_store: q, k and v must agree in tokens, head size and dtype")
+    w_f32 = 0
+    for wt in (q_w, k_w):
+        if wt is not None:
+            if wt.shape != (hd,) or not wt.is_contiguous():
+                raise KernelError(f"qk_norm_rope_store: norm weight {tuple(wt.shape)} does not fit heads of {hd}")
+            w_f32 = 1 if wt.dtype == torch.float32 else 0
+            if wt.dtype not in (ref.dtype, torch.float32):
+                raise KernelError("qk_norm_rope_store: norm weight dtype must be the rows' or float32")
+    if q_w is not None and k_w is not None and q_w.dtype != k_w.dtype:
+        raise KernelError("qk_norm_rope_store: q and k norm weights differ in dtype")
+    cos = sin = None
+    rot, max_pos = 0, 0
+    if tables is not None:
+        cos, sin, rot = tables
+        max_pos = cos.shape[0]
+        if cos.dtype != torch.float32 or cos.shape != sin.shape or cos.shape[1] * 2 != rot:
+            raise KernelError("qk_norm_rope_store: rotary tables must be float32 [positions, dim/2]")
+        if batch.max_pos_after > max_pos:
+            raise KernelError(f"qk_norm_rope_store: position {batch.max_pos_after - 1} is beyond the rotary tables' {max_pos}")
+    kp = vp = pt = None
+    width = page = ring = n_pages = 0
+    if mem is not None:
+        kp, vp, pt = mem.k_pages, mem.v_pages, mem.page_table
+        if kp.dtype != ref.dtype or tuple(kp.shape[1:]) != (nkv, mem.page_size, hd) or not kp.is_contiguous():
+            raise KernelError("qk_norm_rope_store: the cache pages do not fit these keys")
+        width, page, ring, n_pages = pt.shape[1], mem.page_size, mem.ring_rows, kp.shape[0]
+    _call(library().ti_qk_norm_rope_store,
+          _ptr(q), _ptr(k), _ptr(v),
+          _row_stride(q, "q") if q is not None else 0, _row_stride(k, "k") if k is not None else 0,
+          _row_stride(v, "v") if v is not None else 0,
+          nh, nkv, hd, _ptr(q_w), _ptr(k_w), w_f32, float(eps),
+          _ptr(cos), _ptr(sin), rot, max_pos,
+          _ptr(batch.tok_pos), _ptr(batch.tok_seq), _ptr(batch.seq_slot), _ptr(batch.seq_len),
+          _ptr(kp), _ptr(vp), _ptr(pt), width, page, ring, n_pages, M, _code(ref, "qk_norm_rope_store"), _stream())
+
+
+def attention_prefill(q, k, v, scale: float, window: int, batch) -> torch.Tensor:
+    """Causal attention among the step's own tokens (every sequence starts at position 0).
+    q[M, heads, d], k and v[M, kv_heads, d] -> [M, heads, d]."""
+    _need_cuda(q, k, v, what="attention_prefill")
+    M, nh, hd = q.shape
+    nkv = k.shape[1]
+    if k.shape != v.shape or k.shape[0] != M or k.shape[2] != hd or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise KernelError("attention_prefill: q, k and v do not fit together")
+    out = torch.empty((M, nh, hd), dtype=q.dtype, device=q.device)
+    from . import attention
+    attention.prefill(q, k, v, out, float(scale), int(window), batch)
+    return out
+
+
+def attention_decode(q, mem, scale: float, window: int, batch) -> torch.Tensor:
+    """One query per sequence over the cache (the new token's key already stored).
+    q[B, heads, d] -> [B, heads, d]."""
+    _need_cuda(q, what="attention_decode")
+    B, nh, hd = q.shape
+    out = torch.empty((B, nh, hd), dtype=q.dtype, device=q.device)
+    from . import attention
+    attention.decode(q, mem, out, float(scale), int(window), batch)
+    return out
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    _need_cuda(logits, what="argmax")
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("argmax: expected float32 [rows, vocab] with dense rows")
+    R, V = logits.shape
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _call(library().ti_argmax, _ptr(logits), logits.stride(0), R, V, _ptr(out), _stream())
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int,
+           keys: torch.Tensor, steps: torch.Tensor) -> torch.Tensor:
+    """One draw per row from softmax(logits / temperature) restricted by top_k and top_p.
+    ``keys`` (int64) and ``steps`` (int32) make each row's uniform number."""
+    _need_cuda(logits, keys, steps, what="sample")
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: expected float32 [rows, vocab] with dense rows")
+    R, V = logits.shape
+    if keys.dtype != torch.int64 or steps.dtype != torch.int32 or keys.numel() != R or steps.numel() != R:
+        raise KernelError("sample: keys must be int64[rows] and steps int32[rows]")
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _call(library().ti_sample, _ptr(logits), logits.stride(0), R, V, float(temperature), int(top_k), float(top_p),
+          ctypes.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), _ptr(keys), _ptr(steps), _ptr(out), _stream())
+    return out
+
+
+def uniform_from(seed: int, key: int, step: int) -> float:
+    """The uniform number in [0, 1) that ``sample`` draws for (seed, key, step)."""
+    return float(library().ti_uniform_from(ctypes.c_uint64(seed & 0xFFFFFFFFFFFFFFFF),
+                                           ctypes.c_uint64(key & 0xFFFFFFFFFFFFFFFF),
+                                           ctypes.c_uint64(step & 0xFFFFFFFFFFFFFFFF)))

@@ -1,0 +1,136 @@
+"""A decoder described by data, and the object built from the description.
+
+``ModelSpec`` holds what an architecture's ``describe(config)`` returns: the
+embedding, the position encodings, one ``LayerSpec`` per layer (arrangement, norm,
+mixer, feed-forward, each with its parameters), the schedule in which layers run,
+the final norm and the head.  The schedule is a list of ``ScheduleEntry``: an entry
+names a layer (a layer may be named more than once: its weights are shared, each
+entry has memory of its own) and may borrow the memory of an earlier entry
+(``memory_of``), in which case its mixer reads what that entry stored.
+
+``DecoderModel`` runs: embedding gather (src/prefill.cu:6-22), the scheduled blocks,
+and for the rows whose logits are wanted the final norm and the head in 32-bit
+output (src/transformer.cpp:460-470, src/decode.cu:251-286).  The head is the
+embedding table when the model ties them (the reference always ties,
+src/qwen.cpp:482-483) and a matrix of its own otherwise.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import kernels as K
+from .base import BuildContext, ParamSpec, Part, PartSpec, build_part
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    prefix: str                      # checkpoint prefix of the layer, e.g. "model.layers.3."
+    block: PartSpec                  # arrangement; its params carry norm/mixer/feed_forward PartSpecs
+
+
+@dataclass(frozen=True)
+class ScheduleEntry:
+    layer: int                       # index into ModelSpec.layers
+    memory_of: Optional[int] = None  # index of an earlier entry whose memory this one reads
+
+
+@dataclass
+class ModelSpec:
+    vocab_size: int
+    hidden_size: int
+    max_positions: int
+    layers: List[LayerSpec]
+    final_norm: PartSpec
+    schedule: Optional[List[ScheduleEntry]] = None      # default: every layer once, in order
+    positions: Dict[str, PartSpec] = field(default_factory=dict)
+    tie_head: bool = False
+    embed_name: str = "model.embed_tokens.weight"
+    head_name: str = "lm_head.weight"
+    final_norm_prefix: str = "model.norm."
+    stop_token_ids: Tuple[int, ...] = ()
+    ignorable: Tuple[str, ...] = ()                     # tensors a checkpoint may hold that are not used
+
+    def run_order(self) -> List[ScheduleEntry]:
+        if self.schedule is None:
+            return [ScheduleEntry(i) for i in range(len(self.layers))]
+        return list(self.schedule)
+
+
+class DecoderModel(Part):
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device):
+        self.spec = spec
+        self.dtype = dtype
+        self.device = torch.device(device)
+        ctx = BuildContext(dtype=dtype, device=self.device, hidden_size=spec.hidden_size)
+        for name, pspec in spec.positions.items():
+            ctx.positions[name] = build_part("position", pspec, ctx, "")
+        self.ctx = ctx
+        self.blocks = [build_part("block", ls.block, ctx, ls.prefix) for ls in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm, ctx, spec.final_norm_prefix)
+        self.schedule = spec.run_order()
+        for i, e in enumerate(self.schedule):
+            if not (0 <= e.layer < len(self.blocks)):
+                raise ValueError(f"schedule entry {i} names layer {e.layer}; there are {len(self.blocks)}")
+            if e.memory_of is not None:
+                if not (0 <= e.memory_of < i):
+                    raise ValueError(f"schedule entry {i} borrows memory of entry {e.memory_of}, which does not run before it")
+                if self.schedule[e.memory_of].memory_of is not None:
+                    raise ValueError(f"schedule entry {i} borrows from entry {e.memory_of}, which itself borrows")
+        self.embed: Optional[torch.Tensor] = None
+        self.head: Optional[torch.Tensor] = None
+
+    # -- parameters ---------------------------------------------------------
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        s = self.spec
+        out: Dict[str, ParamSpec] = {s.embed_name: ParamSpec((s.vocab_size, s.hidden_size))}
+        for b in self.blocks:
+            out.update(b.param_specs())
+        for p in self.ctx.positions.values():
+            out.update(p.param_specs())
+        out.update(self.final_norm.param_specs())
+        if not s.tie_head:
+            out[s.head_name] = ParamSpec((s.vocab_size, s.hidden_size))
+        return out
+
+    def ignorable_names(self) -> Tuple[str, ...]:
+        extra = (self.spec.head_name,) if self.spec.tie_head else ()
+        return tuple(self.spec.ignorable) + extra
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        self.embed = tensors.pop(s.embed_name)
+        self.head = self.embed if s.tie_head else tensors.pop(s.head_name)
+        for p in self.ctx.positions.values():
+            p.bind(tensors)
+        for b in self.blocks:
+            b.bind(tensors)
+        self.final_norm.bind(tensors)
+
+    # -- what the cache must hold ---------------------------------------------
+    def memory_requests(self) -> List[Any]:
+        """One request (or None) per schedule entry; a borrowing entry asks for nothing."""
+        out = []
+        for e in self.schedule:
+            out.append(None if e.memory_of is not None else self.blocks[e.layer].mixer.memory_request())
+        return out
+
+    # -- one step -------------------------------------------------------------
+    def forward_hidden(self, batch, memories: Sequence[Any]):
+        """Runs the given tokens through all scheduled blocks.  Returns (h, delta):
+        the hidden state is h + delta."""
+        h = K.embed(self.embed, batch.token_ids)
+        delta = None
+        shared: List[dict] = [dict() for _ in self.schedule]
+        for i, e in enumerate(self.schedule):
+            owner = i if e.memory_of is None else e.memory_of
+            h, delta = self.blocks[e.layer].forward(h, delta, batch, memories[owner], shared[owner])
+        return h, delta
+
+    def logits(self, h, delta, rows: torch.Tensor) -> torch.Tensor:
+        """float32 logits [len(rows), vocab] of the tokens at the given rows."""
+        x = K.gather_add(h, delta, rows)
+        x = self.final_norm.forward(x)
+        return K.linear(x, self.head, out_dtype=torch.float32)
