@@ -1,0 +1,369 @@
+"""Each CUDA kernel alone against the plain implementation's function for the same
+part, at sizes other than the tiny models': odd widths, several head sizes, rows that
+straddle block boundaries, padded buffers whose tails must stay untouched (the idiom of
+the reference's kernel tests, tests/rmsnorm_test_common.h:40-43)."""
+from __future__ import annotations
+
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    # elementwise results: one rounding of the storage type apart at most (plus float32 noise)
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-3)
+
+
+def rnd_mode(dtype):
+    return None if dtype == torch.float32 else torch.bfloat16
+
+
+def dev(x, dtype=None):
+    return x.to("cuda", dtype) if dtype is not None else x.to("cuda")
+
+
+def randn(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g) * scale
+
+
+@pytest.fixture(scope="module")
+def K():
+    import toyinfer_b200.kernels as K
+    K.library()
+    return K
+
+
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("H", [40, 258, 2560, 1030])
+def test_embed(K, dtype, H):
+    V, M = 77, 19
+    table = randn(V, H, seed=1).to(dtype)
+    ids = torch.randint(0, V, (M,), generator=torch.Generator().manual_seed(2), dtype=torch.int32)
+    out = K.embed(dev(table), dev(ids))
+    assert torch.equal(out.cpu(), table[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("M,H", [(1, 64), (5, 258), (33, 514), (7, 1030), (3, 2560), (2, 5120)])
+def test_rmsnorm_and_fused_sum(K, dtype, M, H):
+    x = randn(M, H, seed=3).to(dtype)
+    d = randn(M, H, seed=4).to(dtype)
+    w = (1 + randn(H, seed=5, scale=0.1)).to(dtype)
+    eps = 1e-5
+    want = plain.rms_norm(x.double(), w, eps, rnd_mode(dtype))
+    got = K.rmsnorm(dev(x), dev(w), eps)
+    torch.testing.assert_close(got.cpu().double(), want, **tol(dtype))
+    # fused: h <- h + d (rounded once), then the norm of the rounded sum
+    h = dev(x).clone()
+    got = K.add_rmsnorm(h, dev(d), dev(w), eps)
+    hs = plain.rnd(x.double() + d.double(), rnd_mode(dtype))
+    torch.testing.assert_close(h.cpu().double(), hs, **tol(dtype))
+    want = plain.rms_norm(h.cpu().double(), w, eps, rnd_mode(dtype))
+    torch.testing.assert_close(got.cpu().double(), want, **tol(dtype))
+
+
+def test_rmsnorm_float32_weight_with_bfloat16_rows(K):
+    x = randn(9, 96, seed=6).to(torch.bfloat16)
+    w = 1 + randn(96, seed=7, scale=0.1)
+    got = K.rmsnorm(dev(x), dev(w), 1e-6)
+    want = plain.rms_norm(x.double(), w, 1e-6, torch.bfloat16)
+    torch.testing.assert_close(got.cpu().double(), want, **tol(torch.bfloat16))
+
+
+def test_rmsnorm_strided_rows_and_tail(K):
+    buf = torch.full((6, 300), 7.0, dtype=torch.float32, device="cuda")
+    x = randn(6, 130, seed=8)
+    buf[:, :130] = dev(x)
+    w = dev(1 + randn(130, seed=9, scale=0.1))
+    got = K.rmsnorm(buf[:, :130], w, 1e-6)
+    want = plain.rms_norm(x.double(), w.cpu(), 1e-6)
+    torch.testing.assert_close(got.cpu().double(), want, **tol(torch.float32))
+    assert torch.all(buf[:, 130:] == 7.0)
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_gather_add(K, dtype):
+    h, d = randn(11, 70, seed=10).to(dtype), randn(11, 70, seed=11).to(dtype)
+    rows = torch.tensor([10, 0, 3, 3], dtype=torch.int32)
+    got = K.gather_add(dev(h), dev(d), dev(rows))
+    want = plain.rnd(h.double()[rows.long()] + d.double()[rows.long()], rnd_mode(dtype))
+    torch.testing.assert_close(got.cpu().double(), want, **tol(dtype))
+    got = K.gather_add(dev(h), None, dev(rows))
+    assert torch.equal(got.cpu(), h[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("M,I", [(1, 128), (5, 200), (3, 9728), (2, 1001)])
+def test_swiglu(K, dtype, M, I):
+    gu = randn(M, 2 * I, seed=12, scale=2.0).to(dtype)
+    got = K.swiglu(dev(gu))
+    want = plain.swiglu(gu[:, :I].double(), gu[:, I:].double(), rnd_mode(dtype))
+    torch.testing.assert_close(got.cpu().double(), want, **tol(dtype))
+
+
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("M,N,K_", [(1, 64, 64), (3, 200, 96), (8, 384, 100), (13, 130, 258), (17, 300, 72),
+                                    (70, 130, 200), (128, 256, 512), (200, 1000, 264), (5, 2560, 4096)])
+def test_linear(K, dtype, M, N, K_):
+    x = randn(M, K_, seed=13).to(dtype)
+    w = randn(N, K_, seed=14, scale=0.05).to(dtype)
+    got = K.linear(dev(x), dev(w))
+    want = x.double() @ w.double().T
+    if dtype == torch.float32:
+        torch.testing.assert_close(got.cpu().double(), want, rtol=1e-4, atol=1e-5)
+    else:
+        torch.testing.assert_close(got.cpu().double(), plain.rnd(want, torch.bfloat16), rtol=1.6e-2, atol=2e-3)
+        got32 = K.linear(dev(x), dev(w), out_dtype=torch.float32)
+        torch.testing.assert_close(got32.cpu().double(), want, rtol=1e-3, atol=1e-4)
+
+
+def test_linear_strided_input_and_tail(K):
+    buf = torch.full((9, 500), 3.0, dtype=torch.float32, device="cuda")
+    x = randn(9, 120, seed=15)
+    buf[:, 100:220] = dev(x)
+    w = randn(50, 120, seed=16, scale=0.1)
+    got = K.linear(buf[:, 100:220], dev(w))
+    torch.testing.assert_close(got.cpu().double(), x.double() @ w.double().T, rtol=1e-4, atol=1e-5)
+
+
+# ---------------------------------------------------------------------------
+def make_mem(dtype, n_slots, nkv, hd, pages, window=0, dirty=0.0):
+    from toyinfer_b200.cache.manager import KVView, PAGE, pages_for
+    ring = pages_for(window) * PAGE if window else 0
+    k = torch.full((pages + 1, nkv, PAGE, hd), dirty, dtype=dtype, device="cuda")
+    v = torch.full((pages + 1, nkv, PAGE, hd), dirty, dtype=dtype, device="cuda")
+    table = torch.zeros((n_slots + 1, pages), dtype=torch.int32, device="cuda")
+    return KVView(k, v, table, nkv, hd, window, ring)
+
+
+def make_batch(mode, slots, starts, news, plan_len=4096):
+    from toyinfer_b200.engine.batch import BatchBuffers, fill_batch
+    buf = BatchBuffers(len(slots), sum(news), "cuda")
+    toks = [[0] * n for n in news]
+    return fill_batch(buf, mode, slots, starts, toks, scratch_slot=max(slots) + 1, plan_len=plan_len)
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 2, 32), (5, 1, 48), (8, 8, 64), (32, 8, 128), (2, 1, 256)])
+def test_qk_norm_rope_store(K, dtype, nh, nkv, hd):
+    from toyinfer_b200.parts.rope import rotary_tables
+    news = [5, 70, 1]
+    M = sum(news)
+    width = (nh + 2 * nkv) * hd
+    qkv = randn(M, width, seed=17).to(dtype)
+    qw = (1 + randn(hd, seed=18, scale=0.1)).to(dtype)
+    kw = (1 + randn(hd, seed=19, scale=0.1)).to(dtype)
+    cos, sin = rotary_tables(hd, 1e4, 128)
+    mem = make_mem(dtype, 4, nkv, hd, pages=6, dirty=9.0)
+    # slots 2, 0, 3 with pages chosen out of order
+    mem.page_table[2, 0] = 5
+    mem.page_table[0, 0] = 2
+    mem.page_table[0, 1] = 4
+    mem.page_table[3, 0] = 1
+    batch = make_batch("start", [2, 0, 3], [0, 0, 0], news)
+    g = dev(qkv).clone()
+    q = g[:, : nh * hd].view(M, nh, hd)
+    k = g[:, nh * hd: (nh + nkv) * hd].view(M, nkv, hd)
+    v = g[:, (nh + nkv) * hd:].view(M, nkv, hd)
+    K.qk_norm_rope_store(q, k, v, dev(qw), dev(kw), 1e-6, (dev(cos), dev(sin), hd), batch, mem)
+    pos = [p for n in news for p in range(n)]
+    r = rnd_mode(dtype)
+    ang = plain.rope_angles(hd, 1e4, pos)
+    q0 = qkv[:, : nh * hd].view(M, nh, hd).double()
+    k0 = qkv[:, nh * hd: (nh + nkv) * hd].view(M, nkv, hd).double()
+    v0 = qkv[:, (nh + nkv) * hd:].view(M, nkv, hd)
+    wq = plain.rope(plain.rms_norm(q0, qw, 1e-6, r), ang, r)
+    wk = plain.rope(plain.rms_norm(k0, kw, 1e-6, r), ang, r)
+    torch.testing.assert_close(q.cpu().double(), wq, **tol(dtype))
+    torch.testing.assert_close(k.cpu().double(), wk, **tol(dtype))
+    assert torch.equal(v.cpu(), v0)
+    # cache contents: sequence 1 (slot 0) spans pages 2 and 4
+    kp, vp = mem.k_pages.cpu(), mem.v_pages.cpu()
+    assert torch.equal(kp[5, :, :5], k.cpu()[0:5].transpose(0, 1))
+    assert torch.equal(kp[2, :, :64], k.cpu()[5:69].transpose(0, 1))
+    assert torch.equal(kp[4, :, :6], k.cpu()[69:75].transpose(0, 1))
+    assert torch.equal(vp[4, :, :6], v0[69:75].transpose(0, 1))
+    assert torch.equal(kp[1, :, :1], k.cpu()[75:76].transpose(0, 1))
+    # untouched lines keep the dirty value
+    assert torch.all(kp[5, :, 5:] == 9.0) and torch.all(kp[4, :, 6:] == 9.0) and torch.all(kp[3] == 9.0)
+    assert torch.all(kp[0] == 9.0)
+
+
+def test_store_into_ring_keeps_only_the_window(K):
+    dtype = torch.float32
+    nkv, hd, n = 1, 16, 150
+    mem = make_mem(dtype, 1, nkv, hd, pages=1, window=40, dirty=-1.0)   # ring of 64 rows = one page
+    mem.page_table[0, 0] = 1
+    batch = make_batch("start", [0], [0], [n])
+    k = torch.arange(n, dtype=dtype, device="cuda")[:, None, None].expand(n, nkv, hd).contiguous()
+    v = (k + 1000).contiguous()
+    K.qk_norm_rope_store(None, k, v, None, None, 0.0, None, batch, mem)
+    kp = mem.k_pages.cpu()[1, 0, :, 0]
+    # positions 86..149 live at row p mod 64
+    for p in range(n - 64, n):
+        assert kp[p % 64] == p
+    assert torch.all(mem.v_pages.cpu()[1, 0, :, 0] == kp + 1000)
+
+
+# ---------------------------------------------------------------------------
+def plain_attention_seq(q, k, v, scale, window, dtype):
+    return plain.attention(q.double(), k.double(), v.double(), scale, window, rnd_mode(dtype))
+
+
+ATT_TOL = {torch.float32: dict(rtol=1e-4, atol=1e-5), torch.bfloat16: dict(rtol=1.6e-2, atol=4e-3)}
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 32, 0), (5, 1, 48, 40), (8, 4, 64, 0),
+                                               (8, 2, 128, 0), (4, 4, 128, 33), (2, 1, 256, 0)])
+def test_attention_prefill(K, dtype, nh, nkv, hd, window):
+    news = [1, 100, 32, 33, 7]
+    M = sum(news)
+    q = randn(M, nh, hd, seed=20).to(dtype)
+    k = randn(M, nkv, hd, seed=21).to(dtype)
+    v = randn(M, nkv, hd, seed=22).to(dtype)
+    batch = make_batch("start", list(range(len(news))), [0] * len(news), news)
+    scale = 1.0 / math.sqrt(hd)
+    got = K.attention_prefill(dev(q), dev(k), dev(v), scale, window, batch).cpu().double()
+    o = 0
+    for n in news:
+        want = plain_attention_seq(q[o:o + n], k[o:o + n], v[o:o + n], scale, window, dtype)
+        torch.testing.assert_close(got[o:o + n], want, **ATT_TOL[dtype])
+        o += n
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_attention_prefill_far_key_and_window_edge(K, dtype):
+    """One key far back is made to dominate: without a window every later query must
+    return its value; with a window only the queries that still see it."""
+    nh, nkv, hd, n, far, W = 4, 2, 32, 300, 17, 64
+    q = randn(n, nh, hd, seed=23, scale=0.1)
+    k = randn(n, nkv, hd, seed=24, scale=0.1)
+    v = randn(n, nkv, hd, seed=25)
+    k[far] = 0
+    k[far, :, 0] = 40.0
+    q[:, :, 0] = 40.0            # score with the far key ~ 1600 * scale, others ~ 0
+    q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    batch = make_batch("start", [0], [0], [n])
+    scale = 1.0 / math.sqrt(hd)
+    for window in (0, W):
+        got = K.attention_prefill(dev(q), dev(k), dev(v), scale, window, batch).cpu().double()
+        want = plain_attention_seq(q, k, v, scale, window, dtype)
+        torch.testing.assert_close(got, want, **ATT_TOL[dtype])
+        sees = [i for i in range(n) if i >= far and (window == 0 or far > i - window)]
+        for i in (sees[0], sees[-1]):
+            torch.testing.assert_close(got[i, 0], v[far, 0].double(), rtol=1e-2, atol=1e-2)
+        if window:
+            first_blind = far + window      # the key at p - window is just outside
+            assert (got[first_blind, 0] - v[far, 0].double()).abs().max() > 0.1
+
+
+def fill_cache(mem, slot, pages, k, v):
+    """k, v [n, kv_heads, hd] into the given pages of a slot (ring-aware)."""
+    from toyinfer_b200.cache.manager import PAGE
+    n = k.shape[0]
+    for i, p in enumerate(pages):
+        mem.page_table[slot, i] = p
+    for pos in range(n):
+        row = pos % mem.ring_rows if mem.ring_rows else pos
+        if mem.ring_rows and pos < n - mem.ring_rows:
+            continue
+        page = pages[row // PAGE]
+        mem.k_pages[page, :, row % PAGE] = k[pos]
+        mem.v_pages[page, :, row % PAGE] = v[pos]
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 32, 0), (5, 1, 48, 40), (32, 8, 128, 0),
+                                               (8, 1, 128, 100), (2, 2, 256, 0), (16, 1, 64, 0)])
+def test_attention_decode(K, dtype, nh, nkv, hd, window):
+    lens = [1, 64, 65, 300, 129]
+    mem = make_mem(dtype, len(lens), nkv, hd, pages=24, window=window, dirty=float("nan"))
+    ks = [randn(n, nkv, hd, seed=30 + i).to(dtype) for i, n in enumerate(lens)]
+    vs = [randn(n, nkv, hd, seed=40 + i).to(dtype) for i, n in enumerate(lens)]
+    free = list(range(24, 0, -1))
+    for s, n in enumerate(lens):
+        need = (min(n, mem.ring_rows) if mem.ring_rows else n) + 63 >> 6
+        fill_cache(mem, s, [free.pop() for _ in range(need)], dev(ks[s]), dev(vs[s]))
+    q = randn(len(lens), nh, hd, seed=50).to(dtype)
+    scale = 1.0 / math.sqrt(hd)
+    for plan in (64, 4096, 40960):     # different split counts must agree
+        batch = make_batch("extend", list(range(len(lens))), [n - 1 for n in lens], [1] * len(lens), plan_len=plan)
+        got = K.attention_decode(dev(q), mem, scale, window, batch).cpu().double()
+        for s, n in enumerate(lens):
+            qq = torch.zeros(n, nh, hd, dtype=dtype)
+            qq[-1] = q[s]
+            want = plain_attention_seq(qq, ks[s], vs[s], scale, window, dtype)[-1]
+            torch.testing.assert_close(got[s], want, **ATT_TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_attention_decode_far_key(K, dtype):
+    nh, nkv, hd, n, far = 8, 2, 64, 700, 3
+    k = randn(n, nkv, hd, seed=60, scale=0.1)
+    v = randn(n, nkv, hd, seed=61)
+    k[far] = 0
+    k[far, :, 1] = 30.0
+    q = randn(1, nh, hd, seed=62, scale=0.1)
+    q[:, :, 1] = 30.0
+    k, v, q = k.to(dtype), v.to(dtype), q.to(dtype)
+    mem = make_mem(dtype, 1, nkv, hd, pages=12)
+    fill_cache(mem, 0, list(range(12, 0, -1))[:11], dev(k), dev(v))
+    batch = make_batch("extend", [0], [n - 1], [1])
+    got = K.attention_decode(dev(q), mem, 1.0 / math.sqrt(hd), 0, batch).cpu().double()
+    for h in range(nh):
+        torch.testing.assert_close(got[0, h], v[far, h // 4].double(), rtol=1e-2, atol=1e-2)
+
+
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("V", [256, 1000, 151936])
+def test_argmax(K, V):
+    x = randn(5, V, seed=70)
+    x[1, 17] = x[1, 900 % V] = 50.0          # a tie: the lower index wins
+    got = K.argmax(dev(x)).cpu().tolist()
+    assert got == [plain.argmax(r) for r in x]
+
+
+@pytest.mark.parametrize("V,top_k,top_p,temp", [(300, 0, 1.0, 0.8), (300, 20, 0.95, 0.6), (5000, 50, 0.5, 1.3),
+                                                (151936, 20, 0.95, 0.6), (1000, 1000, 1.0, 0.7),
+                                                (2000, 1024, 0.9, 1.0)])
+def test_sample_matches_plain(K, V, top_k, top_p, temp):
+    R = 6
+    x = randn(R, V, seed=71, scale=3.0)
+    x[2, 5] = x[2, 9] = x[2].max() + 1      # tied maxima
+    keys = torch.arange(100, 100 + R, dtype=torch.int64)
+    steps = torch.arange(R, dtype=torch.int32)
+    got = K.sample(dev(x), temp, top_k if top_k < V else 0, top_p, 1234, dev(keys), dev(steps)).cpu().tolist()
+    for r in range(R):
+        u = plain.uniform_from(1234, int(keys[r]), int(steps[r]))
+        assert abs(u - K.uniform_from(1234, int(keys[r]), int(steps[r]))) == 0.0
+        want = plain.sample(x[r], temp, top_k, top_p, u)
+        if got[r] != want:
+            # allowed only when the draw falls within float rounding of a boundary between
+            # the two tokens' cumulative intervals
+            alt = {plain.sample(x[r], temp, top_k, top_p, min(max(u + d, 0.0), 0.99999994)) for d in (-3e-6, 3e-6)}
+            assert got[r] in alt, (r, got[r], want, alt)
+
+
+def test_sample_distribution(K):
+    """Many draws from a small distribution land where softmax(logits / T) says."""
+    V, n = 8, 20000
+    logits = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, -2.0, 3.0, 0.2])
+    x = logits.repeat(n, 1)
+    keys = torch.arange(n, dtype=torch.int64)
+    steps = torch.zeros(n, dtype=torch.int32)
+    got = K.sample(dev(x), 0.7, 0, 1.0, 99, dev(keys), dev(steps)).cpu()
+    freq = torch.bincount(got.long(), minlength=V).double() / n
+    p = torch.softmax(logits.double() / 0.7, 0)
+    assert (freq - p).abs().max() < 0.015

@@ -1,0 +1,139 @@
+"""The engine on the GPU against the plain implementation, in float32 and bfloat16:
+each request alone and whole; with the last 32 tokens one by one; in batches of unequal
+lengths whose shorter requests end earlier, batch after batch so that slots are used
+again; long decoding; the first tokens of a sequence; graph replay against eager steps."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import TINY, prompts_for
+from helpers import assert_logits_close, plain_logits
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+NAMES = ["A", "B", "C"]
+
+
+def make_engine(folder, dtype, **kw):
+    from toyinfer_b200.engine import Engine
+    kw.setdefault("max_tokens", 4096)
+    kw.setdefault("max_batch", 8)
+    return Engine.from_folder(folder, dtype=dtype, device="cuda", **kw)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_each_request_alone_and_whole(model_folders, name, dtype):
+    eng = make_engine(model_folders[name], dtype)
+    lens = [1, 2, 17, 64, 65, 100] if name != "C" else [1, 40, 41, 130, 200]
+    for i, ids in enumerate(prompts_for(name, lens, seed=3)):
+        slot = eng.new_sequence()
+        got = eng.step([(slot, ids)], [list(range(len(ids)))])
+        assert_logits_close(got, plain_logits(model_folders[name], ids, dtype), dtype, f"{name} len {len(ids)}")
+        eng.end_sequence(slot)
+
+
+@pytest.mark.parametrize("graph", [True, False])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_last_32_tokens_one_by_one(model_folders, name, dtype, graph):
+    eng = make_engine(model_folders[name], dtype, use_cuda_graph=graph)
+    n = {"A": 100, "B": 77, "C": 190}[name]
+    ids = prompts_for(name, [n], seed=4)[0]
+    want = plain_logits(model_folders[name], ids, dtype)
+    slot = eng.new_sequence()
+    head = n - 32
+    got = [eng.step([(slot, ids[:head])], [[head - 1]]).clone()]
+    for t in range(head, n):
+        got.append(eng.step([(slot, [ids[t]])], [[0]]).clone())
+    assert_logits_close(torch.cat(got), want[head - 1:], dtype, f"{name} one by one")
+    if graph:
+        assert eng.graph_replays >= 30
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_first_tokens_token_by_token(model_folders, name, dtype):
+    """A sequence fed from its very first token through single-token steps."""
+    eng = make_engine(model_folders[name], dtype)
+    ids = prompts_for(name, [70], seed=5)[0]
+    want = plain_logits(model_folders[name], ids, dtype)
+    slot = eng.new_sequence()
+    got = [eng.step([(slot, [t])], [[0]]).clone() for t in ids]
+    assert_logits_close(torch.cat(got), want, dtype, f"{name} from the first token")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_batches_one_after_another(model_folders, name, dtype):
+    # a cache of 8 pages: three batches can only run if pages and slots come back
+    eng = make_engine(model_folders[name], dtype, max_tokens=64 * 8, max_batch=4)
+    plans = [([5, 9, 2], [8, 8, 8]), ([17, 1, 40, 8], [12, 3, 7, 1]), ([70, 3, 100], [4, 20, 9])]
+    for r, (lens, dec) in enumerate(plans):
+        seqs = prompts_for(name, [n + d for n, d in zip(lens, dec)], seed=20 + r)
+        want = [plain_logits(model_folders[name], s, dtype) for s in seqs]
+        slots = [eng.new_sequence() for _ in seqs]
+        logits = eng.step([(sl, s[:n]) for sl, s, n in zip(slots, seqs, lens)], None).clone()
+        for i, n in enumerate(lens):
+            assert_logits_close(logits[i], want[i][n - 1], dtype, f"{name} batch {r} prompt {i}")
+        live, t = list(range(len(seqs))), 0
+        while live:
+            logits = eng.step([(slots[i], [seqs[i][lens[i] + t]]) for i in live], None).clone()
+            for row, i in enumerate(live):
+                assert_logits_close(logits[row], want[i][lens[i] + t], dtype, f"{name} batch {r} seq {i} step {t}")
+            t += 1
+            for i in [i for i in live if t >= dec[i]]:
+                eng.end_sequence(slots[i])
+            live = [i for i in live if t < dec[i]]
+        assert eng.cache.slots.n_free == eng.cache.n_slots
+        assert all(g.pool.n_free == g.pool.n_pages for g in eng.cache.kv_groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(model_folders, dtype):
+    """More than 200 single-token steps after a short prompt (ring wrapped three times)."""
+    name = "C"
+    eng = make_engine(model_folders[name], dtype)
+    ids = prompts_for(name, [300], seed=6)[0]
+    want = plain_logits(model_folders[name], ids, dtype)
+    slot = eng.new_sequence()
+    got = [eng.step([(slot, ids[:9])], [[8]]).clone()]
+    for t in range(9, 300):
+        got.append(eng.step([(slot, [ids[t]])], [[0]]).clone())
+    assert_logits_close(torch.cat(got), want[8:], dtype, "long decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_padding_and_company_change_nothing(model_folders, dtype):
+    """A request's logits are the same alone, in a batch of 3 (padded to 4 by the graph's
+    bucket) and in a batch of 5 (padded to 8), beyond rounding."""
+    name = "B"
+    seqs = prompts_for(name, [30, 11, 50, 3, 19], seed=7)
+    outs = []
+    for group in ([0], [0, 1, 2], [0, 1, 2, 3, 4]):
+        eng = make_engine(model_folders[name], dtype)
+        slots = [eng.new_sequence() for _ in group]
+        a = eng.step([(s, seqs[i][:-4]) for s, i in zip(slots, group)], None)[0].clone()
+        rows = [a]
+        for t in range(4, 0, -1):
+            rows.append(eng.step([(s, [seqs[i][-t]]) for s, i in zip(slots, group)], None)[0].clone())
+        outs.append(torch.stack(rows))
+    want = plain_logits(model_folders[name], seqs[0], dtype)[-5:]
+    for o in outs:
+        assert_logits_close(o, want, dtype, "company")
+    if dtype == "float32":
+        torch.testing.assert_close(outs[0], outs[2], rtol=1e-5, atol=1e-6)
+
+
+def test_step_refuses_mixed_batches(model_folders):
+    from toyinfer_b200.engine import StepError
+    eng = make_engine(model_folders["A"], "float32")
+    a, b = eng.new_sequence(), eng.new_sequence()
+    eng.step([(a, [1, 2, 3])], None)
+    with pytest.raises(StepError):
+        eng.step([(a, [4]), (b, [1, 2])], None)     # one goes on, one starts
+    with pytest.raises(StepError):
+        eng.step([(a, [4, 5])], None)               # goes on by two
+    with pytest.raises(StepError):
+        eng.step([(b, [10 ** 6])], None)            # token outside the vocabulary
