@@ -93,7 +93,8 @@ def load_parameters(
             tgt, _ = _target_dtype(name, spec, f.entries[name].dtype, dtype)
             cpu = f.tensor(name)
             # one shard-sized staging copy at a time: .to() of a mapped view streams it
-            out[name] = cpu.to(device=device, dtype=tgt).contiguous()
+            # always a copy: the mapped file is closed when loading ends
+            out[name] = cpu.to(device=device, dtype=tgt, copy=True).contiguous()
         return out
     finally:
         for f in files:
