@@ -1,0 +1,266 @@
+#!/usr/bin/env python3
+"""Measures generation on one B200 and prints one JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run has the layer sizes of Qwen3-4B (BASELINE.json configs[2]) with random
+weights, a batch of 8 and a context of 8,192 positions.  A step is one decode step of
+the whole batch.  ``value`` is decoded tokens per second over K steps timed on the
+device with CUDA events (token ids chosen beforehand, no host round trip inside);
+``e2e`` is the same through the Python entry point ``LLM.generate`` (host token ids in,
+sampled token ids read back every step).  The line also carries a 2,048-token prefill,
+the decode step's share of the memory roofline, and decode rates at batch 1 and 64.
+Every decode step reads all weights (8 GB) and the live sequences' cache, far more than
+the 126 MB L2, so nothing is flushed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_4B = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 36, "hidden_size": 2560,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 9728,
+    "vocab_size": 151936, "rope_theta": 1e6, "rms_norm_eps": 1e-6, "max_position_embeddings": 40960,
+    "tie_word_embeddings": True,
+}
+FULL_LAYERS = 36
+CONTEXT = 8192
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = dict(FALLBACK_PEAKS, source="fallback")
+    try:
+        with open(path) as f:
+            m = json.load(f)
+        for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+            if k in m:
+                out[k] = float(m[k])
+        out["source"] = "measured"
+    except (OSError, ValueError):
+        pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        def pump():
+            for line in self.proc.stdout:
+                self.rows.append([c.strip() for c in line.split(",")])
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                mhz.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def flops_prefill(cfg, T):
+    H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    linear = 2.0 * T * L * (H * (q + 2 * kv) + q * H + 3 * H * I)
+    attn = L * 4.0 * q * T * (T + 1) / 2          # QK^T and PV over the causal half
+    return linear + attn + 2.0 * H * V            # one row of the head
+
+
+def bytes_decode(cfg, batch, context, elem=2):
+    H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    weights = L * (H * (q + 2 * kv) + q * H + 3 * H * I + 2 * H + 2 * cfg["head_dim"]) + H + V * H
+    if not cfg.get("tie_word_embeddings", False):
+        weights += 0  # the embedding table itself is only gathered from (batch rows)
+    cache = 2.0 * L * kv * context * batch
+    return (weights + cache) * elem
+
+
+def random_tokens(n, vocab, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def time_decode(engine, batch, context, steps, warmup, seed=0):
+    """Prefills ``batch`` prompts so that warm-up plus timed steps end at ``context``
+    positions, then times ``steps`` decode steps on the device.  Returns (ms per step,
+    kernels launched per step)."""
+    import torch
+    import toyinfer_b200.kernels as K
+    vocab = engine.spec.vocab_size
+    prompt_len = context - steps - warmup
+    slots = [engine.new_sequence() for _ in range(batch)]
+    try:
+        # prompts run in groups so that the step's activations stay small; all start together
+        engine.step([(s, random_tokens(prompt_len, vocab, seed + i)) for i, s in enumerate(slots)], [[] for _ in slots])
+        toks = [random_tokens(steps + warmup, vocab, seed + 1000 + i) for i in range(batch)]
+        for t in range(warmup):
+            engine.step([(s, [toks[i][t]]) for i, s in enumerate(slots)], None)
+        torch.cuda.synchronize()
+        per_step = engine.launches_per_step(batch)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for t in range(warmup, warmup + steps):
+            engine.step([(s, [toks[i][t]]) for i, s in enumerate(slots)], None)
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / steps, per_step
+    finally:
+        for s in slots:
+            engine.end_sequence(s)
+
+
+def time_prefill(engine, tokens, reps=3):
+    import torch
+    vocab = engine.spec.vocab_size
+    best = None
+    for r in range(reps + 1):
+        slot = engine.new_sequence()
+        ids = random_tokens(tokens, vocab, 77 + r)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step([(slot, ids)], None)
+        stop.record()
+        torch.cuda.synchronize()
+        engine.end_sequence(slot)
+        ms = start.elapsed_time(stop)
+        if r > 0:                      # the first run warms up
+            best = ms if best is None else min(best, ms)
+    return best
+
+
+def run_ours(args):
+    import torch
+    from toyinfer_b200 import LLM, SamplingParams
+    import toyinfer_b200.kernels as K
+
+    pk = peaks()
+    cfg = dict(QWEN3_4B)
+    cfg["num_hidden_layers"] = args.layers
+    batch, ctx = args.batch, args.context
+    K.library()
+    big = max(batch, 64 if not args.skip_points else batch)
+    max_tokens = max(batch * (ctx + 64), (64 * (PREFILL_TOKENS + 256)) if not args.skip_points else 0)
+    llm = LLM(config=cfg, seed=0, dtype="bfloat16", max_seq_len=ctx, max_batch=big, max_tokens=max_tokens)
+    engine = llm.engine
+
+    sampler = ClockSampler()
+    sampler.start()
+    ms_step, per_step = time_decode(engine, batch, ctx, args.steps, args.warmup)
+    clocks = sampler.stop()
+    value = batch * 1000.0 / ms_step
+    mean_ctx = ctx - args.steps / 2.0
+    gbs = bytes_decode(cfg, batch, mean_ctx) / (ms_step * 1e-3) / 1e9
+
+    # end to end through the entry point: host ids in, sampled ids back every step
+    prompts = [random_tokens(ctx - args.steps - 1, cfg["vocab_size"], 500 + i) for i in range(batch)]
+    llm.generate(prompts[:1], SamplingParams(temperature=0.0), max_new_tokens=2, ignore_eos=True)     # warm-up
+    torch.cuda.synchronize()
+    llm.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=args.steps + 1, ignore_eos=True)
+    st = llm.last_stats
+    e2e_value = batch * st.decode_steps / st.decode_seconds if st.decode_seconds > 0 else None
+    meta_bytes = engine.decode_metadata_bytes(batch)
+
+    out = {
+        "metric": "decode tokens/s", "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen3-4B shape", "layers": args.layers, "layers_of_named_config": FULL_LAYERS,
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "tied": True, "global_batch": batch, "seq_len": ctx, "context": ctx, "prefill_tokens": PREFILL_TOKENS,
+            "points_context": PREFILL_TOKENS, "parallelism": "single GPU", "l2": "inputs larger than L2, no flush",
+            "cuda_graph": True, "peaks": pk["source"],
+        },
+        "e2e": {"value": round(e2e_value, 2) if e2e_value else None, "unit": "tokens/s",
+                "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": batch * 4},
+        "gpu_launches": per_step * args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(gbs / pk["hbm_gbs"], 4)},
+    }
+
+    ms_pre = time_prefill(engine, PREFILL_TOKENS)
+    fl = flops_prefill(cfg, PREFILL_TOKENS)
+    out["prefill"] = {"value": round(PREFILL_TOKENS * 1000.0 / ms_pre, 1), "tokens": PREFILL_TOKENS,
+                      "ms": round(ms_pre, 3), "frac": round(fl / (ms_pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    if not args.skip_points:
+        pts = {}
+        for b in (1, 64):
+            ms_b, _ = time_decode(engine, b, PREFILL_TOKENS + args.steps + args.warmup, args.steps, args.warmup, seed=b)
+            pts[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 2)
+        out["points"] = pts
+    return out
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the named configuration (reported)")
+    ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "wiketool/ToyInfer has no setup.py or pyproject.toml (pip: 'not installable'); it is a "
+                                         "CMake program whose third_party sources are absent and that builds for sm_89 only"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    print(json.dumps(run_ours(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

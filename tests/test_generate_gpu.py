@@ -1,0 +1,105 @@
+"""Generation through the entry point and the command line on the GPU: greedy tokens
+equal the plain implementation's; sampled tokens follow the fixed seed whatever the
+batch; the BASELINE workloads of the two tiny configurations."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from conftest import ROOT, TINY, prompts_for
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+
+def _plain(folder):
+    return plain.read_weights(folder), plain.read_config(folder)
+
+
+@pytest.mark.parametrize("graph", [True, False])
+def test_greedy_matches_plain_tiny_a(model_folders, graph):
+    """Tiny A workload: prompts of 5, 9 and 2 tokens, 8 greedy tokens each, float32."""
+    from toyinfer_b200 import LLM, SamplingParams
+    f = model_folders["A"]
+    llm = LLM(f, dtype="float32", max_seq_len=128, max_batch=4, max_tokens=1024, enable_cuda_graph=graph)
+    prompts = prompts_for("A", [5, 9, 2], seed=50)
+    got = llm.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=8, ignore_eos=True)
+    w, cfg = _plain(f)
+    assert [r.tokens for r in got] == [plain.generate(w, cfg, p, 8) for p in prompts]
+    assert llm.engine.cache.slots.n_free == llm.engine.cache.n_slots
+
+
+def test_temperature_sampling_tiny_b(model_folders):
+    """Tiny B workload: prompts of 17, 1, 40 and 8 tokens, 12 tokens at temperature 0.8
+    with a fixed seed.  The same request draws the same tokens alone and in the batch, and
+    they are the plain sampler's (float32 engine, so logits agree to rounding)."""
+    from toyinfer_b200 import LLM, SamplingParams
+    f = model_folders["B"]
+    params = SamplingParams(temperature=0.8, top_k=0, top_p=1.0, seed=321)
+    prompts = prompts_for("B", [17, 1, 40, 8], seed=51)
+    llm = LLM(f, dtype="float32", max_seq_len=256, max_batch=4, max_tokens=2048)
+    together = [r.tokens for r in llm.generate(prompts, params, max_new_tokens=12, ignore_eos=True)]
+    w, cfg = _plain(f)
+    for i, p in enumerate(prompts):
+        want = plain.generate(w, cfg, p, 12, temperature=0.8, top_k=0, top_p=1.0, seed=321, key=i)
+        assert together[i] == want, (i, together[i], want)
+    llm2 = LLM(f, dtype="float32", max_seq_len=256, max_batch=1, max_tokens=2048)
+    one_by_one = [r.tokens for r in llm2.generate(prompts, params, max_new_tokens=12, ignore_eos=True)]
+    assert one_by_one == together
+
+
+def test_bfloat16_greedy_follows_its_own_logits(model_folders):
+    """In bfloat16 near-ties may resolve differently from the plain result, so each drawn
+    token is checked against the plain logits of the engine's own sequence: it must be the
+    maximum or within rounding of it."""
+    from toyinfer_b200 import LLM, SamplingParams
+    f = model_folders["C"]
+    llm = LLM(f, dtype="bfloat16", max_seq_len=320, max_batch=4, max_tokens=2048)
+    prompts = prompts_for("C", [70, 3, 130], seed=52)
+    got = llm.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=20, ignore_eos=True)
+    w, cfg = _plain(f)
+    for p, r in zip(prompts, got):
+        assert len(r.tokens) == 20
+        logits = plain.forward(w, cfg, p + r.tokens, torch.bfloat16)
+        for t, tok in enumerate(r.tokens):
+            row = logits[len(p) + t - 1]
+            assert row[tok] >= row.max() - 0.03 * row.abs().max()
+
+
+def test_stop_token_and_queue_of_batches(model_folders):
+    from toyinfer_b200 import LLM, SamplingParams
+    f = model_folders["A"]
+    w, cfg = _plain(f)
+    prompts = prompts_for("A", [5, 9, 2, 30, 4, 11, 7], seed=53)
+    free = [plain.generate(w, cfg, p, 10) for p in prompts]
+    stop = free[3][2]
+    llm = LLM(f, dtype="float32", max_seq_len=128, max_batch=3, max_tokens=64 * 4)
+    got = llm.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=10, stop_token_ids=[stop])
+    want = [plain.generate(w, cfg, p, 10, stop_ids=(stop, 7)) for p in prompts]
+    assert [r.tokens for r in got] == want
+    assert llm.last_stats.batches >= 3
+    assert llm.engine.cache.slots.n_free == llm.engine.cache.n_slots
+
+
+def test_command_line(model_folders):
+    f = model_folders["A"]
+    prompts = prompts_for("A", [6, 3], seed=54)
+    arg = ";".join(",".join(map(str, p)) for p in prompts)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "toyinfer"), "--model_dir", f, "--max_seq_len", "128",
+           "--dtype", "float32", "--temperature", "0", "--prompt_ids", arg, "--max_new_tokens", "6",
+           "--ignore_eos", "1", "--detail_time", "1", "--enable_cuda_graph", "1"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    w, cfg = _plain(f)
+    assert [l["tokens"] for l in lines] == [plain.generate(w, cfg, p, 6) for p in prompts]
+    assert "[perf]" in r.stderr and "[detail]" in r.stderr
+    # token-by-token prompts give the same tokens
+    r2 = subprocess.run(cmd + ["--use_dedicated_prefill", "0"], capture_output=True, text=True, timeout=300)
+    assert r2.returncode == 0, r2.stderr
+    assert [json.loads(l)["tokens"] for l in r2.stdout.splitlines() if l.startswith("{")] == [l["tokens"] for l in lines]

@@ -185,6 +185,17 @@ class Engine:
             self.cache.commit(s, st + len(t))
         return logits
 
+    # -- accounting for measurements ----------------------------------------------------
+    def launches_per_step(self, n_seq: int) -> int:
+        """Kernels that one captured decode step of ``n_seq`` sequences launches."""
+        g = self._graphs.get(_bucket(n_seq, self.max_batch))
+        return g.launches if g is not None else 0
+
+    def decode_metadata_bytes(self, n_seq: int) -> int:
+        """Bytes copied host to device before each decode step of ``n_seq`` sequences."""
+        g = self._graphs.get(_bucket(n_seq, self.max_batch))
+        return g.buf.total * 4 if g is not None else 0
+
     # -- helpers ----------------------------------------------------------------------
     def _eager_batch(self, mode, slots, starts, tokens) -> StepBatch:
         n_seq, n_tok = len(slots), sum(len(t) for t in tokens)
@@ -213,6 +224,7 @@ class _DecodeGraph:
         self.rows = torch.arange(bucket, dtype=torch.int32, device=engine.device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
+        self.launches = 0
 
     def _body(self, batch: StepBatch) -> torch.Tensor:
         e = self.engine
@@ -227,7 +239,10 @@ class _DecodeGraph:
         if self.graph is None:
             # one eager run first: it is this step's result, and it lets every kernel do its
             # one-time set-up outside the capture
+            from .. import kernels as K
+            before = K.launch_count
             out = self._body(batch)
+            self.launches = K.launch_count - before
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()
             # the capture only records; nothing runs until the first replay
