@@ -128,6 +128,32 @@ def test_linear(K, dtype, M, N, K_):
         torch.testing.assert_close(got32.cpu().double(), want, rtol=1e-3, atol=1e-4)
 
 
+@pytest.mark.parametrize("M,N,K_,f32", [
+    (2048, 6144, 2560, False),     # prefill, q/k/v rows of a 4B-shaped layer
+    (2048, 2560, 9728, False),     # prefill, down projection (long contraction)
+    (300, 2560, 4096, False),      # few tiles: the contraction is split
+    (8, 19456, 2560, False),       # decode at batch 8, gate and up rows
+    (64, 2560, 9728, False),       # decode at batch 64, split contraction
+    (1, 151936, 2560, True),       # head for one row, float32 logits
+    (33, 1000, 264, False), (16, 128, 64, False), (65, 136, 72, True), (129, 250, 200, False),
+])
+def test_linear_tensor_cores_at_model_sizes(K, M, N, K_, f32):
+    """The tcgen05 kernel against a float32 product of the same bfloat16 operands."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(M, K_, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K_, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
+    got = K.linear(x, w, out_dtype=torch.float32 if f32 else None)
+    K.check_status()
+    want = x.float() @ w.float().T
+    if f32:
+        torch.testing.assert_close(got, want, rtol=1e-3, atol=1e-3)
+    else:
+        torch.testing.assert_close(got.float(), want.to(torch.bfloat16).float(), rtol=1.6e-2, atol=4e-3)
+    # a second call reuses tickets and workspace
+    got2 = K.linear(x, w, out_dtype=torch.float32 if f32 else None)
+    assert torch.equal(got, got2)
+
+
 def test_linear_strided_input_and_tail(K):
     buf = torch.full((9, 500), 3.0, dtype=torch.float32, device="cuda")
     x = randn(9, 120, seed=15)
@@ -301,6 +327,7 @@ def test_attention_decode(K, dtype, nh, nkv, hd, window):
     for plan in (64, 4096, 40960):     # different split counts must agree
         batch = make_batch("extend", list(range(len(lens))), [n - 1 for n in lens], [1] * len(lens), plan_len=plan)
         got = K.attention_decode(dev(q), mem, scale, window, batch).cpu().double()
+        K.check_status()
         for s, n in enumerate(lens):
             qq = torch.zeros(n, nh, hd, dtype=dtype)
             qq[-1] = q[s]

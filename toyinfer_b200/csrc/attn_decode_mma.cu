@@ -1,0 +1,355 @@
+// Grouped-query attention of one new token per sequence over the paged cache, bfloat16,
+// tensor cores, keys and values brought in by TMA.  Same contract and formulas as
+// attn_decode_simt.cu (reference: src/decode.cu:401-432, :471-532, :598-628); this is the
+// kernel the bfloat16 engine decodes with for head sizes 64 and 128.
+//
+// Grid (sequences, kv heads x groups of 16 query heads, splits), 128 threads, up to two
+// blocks per SM.  The cache page of a tile (64 positions x head_dim of one kv head, 8 or
+// 16 KB, contiguous) arrives as 64x64 boxes through a tensor map with the 128-byte
+// swizzle, into a ring of STAGES buffers guarded by mbarriers; one thread issues the loads
+// STAGES-1 tiles ahead.  The step is bound by the read of the cache: every key and value
+// byte is read once for all query heads of its kv head.
+//
+// Each warp owns 16 of a tile's 64 positions and keeps an online softmax of its own:
+//   S = Q K^T   mma.m16n8k16, the query heads (padded to 16 rows) as the M dimension,
+//   P = exp(S * scale - max), O += P V with P rounded to bfloat16 for the second product.
+// The four warps' maxima, sums and outputs are merged through shared memory at the end,
+// then written as this split's partial result (or the final one when there is one split).
+#include "attn_decode.cuh"
+#include "tma.cuh"
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace {
+constexpr int TILE = 64, THREADS = 128, STAGES = 3;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of element (row, d) inside a tile stored as HD/64 boxes of [64 rows][128 bytes]
+// with the 128-byte swizzle (16-byte chunk c of row r sits at chunk c ^ (r % 8)).
+template <int HD>
+__device__ __forceinline__ uint32_t tile_offset(int row, int d) {
+    const int box = d >> 6, chunk = (d & 63) >> 3;
+    return (uint32_t)(box * (TILE * 128) + row * 128 + ((chunk ^ (row & 7)) << 4) + (d & 7) * 2);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 2)
+attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                       tiattn::DecodeArgs a, int* status) {
+    constexpr int TILE_BYTES = TILE * HD * 2;          // one of K or V
+    constexpr int KSTEPS = HD / 16, NT = HD / 8;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // 1024-byte alignment of the boxes is what the swizzle pattern is defined against
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t full[STAGES];
+    __shared__ int s_abort;
+
+    const int b = blockIdx.x, split = blockIdx.z;
+    const int g = a.n_heads / a.n_kv_heads;
+    const int groups = (g + 15) / 16;
+    const int kvh = blockIdx.y / groups, grp = blockIdx.y - kvh * groups;
+    const int h0 = kvh * g + grp * 16;                 // first query head of this block
+    const int rows = min(16, g - grp * 16);            // query heads of this block
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int L = a.seq_len[b];
+    const int slot = a.seq_slot[b];
+    const int lo = a.window > 0 ? max(0, L - a.window) : 0;
+    const int tile_lo = lo / TILE;
+    const int n_tiles = L > 0 ? (L - 1) / TILE - tile_lo + 1 : 0;
+    const int per = (n_tiles + a.n_splits - 1) / a.n_splits;
+    const int my_lo = tile_lo + split * per;
+    const int my_n = max(0, min(my_lo + per, tile_lo + n_tiles) - my_lo);
+
+    if (t == 0) {
+        for (int s = 0; s < STAGES; s++) mbar_init(&full[s], 1);
+        s_abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    auto issue = [&](int i) {      // tile my_lo + i into stage i % STAGES; one thread calls this
+        const int p0 = (my_lo + i) * TILE;
+        const int row0 = a.ring_rows > 0 ? p0 % a.ring_rows : p0;
+        const int pidx = row0 / TILE;
+        int page = pidx < a.table_width ? a.page_table[(size_t)slot * a.table_width + pidx] : 0;
+        if (page < 0 || page >= a.n_pages) page = 0;
+        const int y = (page * a.n_kv_heads + kvh) * TILE;
+        unsigned char* dst = smem + (size_t)(i % STAGES) * 2 * TILE_BYTES;
+        uint64_t* bar = &full[i % STAGES];
+        mbar_expect_tx(bar, 2 * TILE_BYTES);
+#pragma unroll
+        for (int bx = 0; bx < HD / 64; bx++) {
+            tma_load_2d(dst + bx * (TILE * 128), &k_map, bx * 64, y, bar);
+            tma_load_2d(dst + TILE_BYTES + bx * (TILE * 128), &v_map, bx * 64, y, bar);
+        }
+    };
+    if (t == 0)
+        for (int i = 0; i < STAGES - 1 && i < my_n; i++) issue(i);
+
+    // the queries as A fragments: row lane/4 (and +8) is a query head, zero beyond `rows`
+    uint32_t qf[KSTEPS][4];
+    {
+        const bf16* q = (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)h0 * HD;
+        const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            const int d = ks * 16 + c;
+            qf[ks][0] = r0 < rows ? *reinterpret_cast<const uint32_t*>(q + (size_t)r0 * HD + d) : 0u;
+            qf[ks][1] = r1 < rows ? *reinterpret_cast<const uint32_t*>(q + (size_t)r1 * HD + d) : 0u;
+            qf[ks][2] = r0 < rows ? *reinterpret_cast<const uint32_t*>(q + (size_t)r0 * HD + d + 8) : 0u;
+            qf[ks][3] = r1 < rows ? *reinterpret_cast<const uint32_t*>(q + (size_t)r1 * HD + d + 8) : 0u;
+        }
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // rows lane/4 and lane/4 + 8
+
+    for (int i = 0; i < my_n; i++) {
+        const int stage = i % STAGES;
+        if (t == 0 && i + STAGES - 1 < my_n) issue(i + STAGES - 1);   // its stage was drained in iteration i-1
+        if (!mbar_wait(&full[stage], (uint32_t)((i / STAGES) & 1))) {
+            ti_report(status, TI_STATUS_TMA_WAIT);
+            s_abort = 1;
+        }
+        __syncthreads();
+        if (s_abort) {            // uniform: every thread sees the flag after the barrier
+            // give the loads still in flight a bounded time to land before the block's shared
+            // memory is released, then leave without a result
+            if (t == 0)
+                for (int j = i; j < my_n && j < i + STAGES; j++) mbar_wait(&full[j % STAGES], (uint32_t)((j / STAGES) & 1));
+            return;
+        }
+        const uint32_t kbase = smem_u32(smem + (size_t)stage * 2 * TILE_BYTES);
+        const uint32_t vbase = kbase + TILE_BYTES;
+        const int p0 = (my_lo + i) * TILE;
+        const int key0 = warp * 16;                      // this warp's positions within the tile
+        const bool edge = p0 < lo || p0 + TILE > L;      // some positions of the tile are out of range
+
+        if (edge) {
+            // lines outside [lo, L) may hold anything: clear this warp's such value rows
+            for (int r = 0; r < 16; r++) {
+                const int p = p0 + key0 + r;
+                if (p < lo || p >= L)
+                    for (int d = lane * 8; d < HD; d += 256)
+                        *reinterpret_cast<uint4*>(smem + (size_t)stage * 2 * TILE_BYTES + TILE_BYTES + tile_offset<HD>(key0 + r, d)) = make_uint4(0, 0, 0, 0);
+            }
+            __syncwarp();
+        }
+
+        // S = Q K^T for 16 positions: two n-tiles of 8
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+            const int mid = lane >> 3, rr = lane & 7;
+            const int key = key0 + (mid >> 1) * 8 + rr;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks++) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3, kbase + tile_offset<HD>(key, ks * 16 + (mid & 1) * 8));
+                mma_bf16(s[0], qf[ks], b0, b1);
+                mma_bf16(s[1], qf[ks], b2, b3);
+            }
+        }
+        // scale, mask, online softmax (rows lane/4 and lane/4 + 8; columns are positions)
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int p = p0 + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                const bool ok = !edge || (p >= lo && p < L);
+                s[nt][e] = ok ? s[nt][e] * a.scale : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+            }
+        float alpha[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r]);
+            alpha[r] = m_new > -INFINITY ? expf(m_run[r] - m_new) : 1.f;
+            m_run[r] = m_new;
+        }
+        uint32_t pf[4];
+        {
+            float p[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    p[nt][e] = m_run[e >> 1] > -INFINITY ? expf(s[nt][e] - m_run[e >> 1]) : 0.f;
+            l_run[0] = l_run[0] * alpha[0] + p[0][0] + p[0][1] + p[1][0] + p[1][1];   // this thread's share of the row
+            l_run[1] = l_run[1] * alpha[1] + p[0][2] + p[0][3] + p[1][2] + p[1][3];
+            pf[0] = pack_bf16(p[0][0], p[0][1]);
+            pf[1] = pack_bf16(p[0][2], p[0][3]);
+            pf[2] = pack_bf16(p[1][0], p[1][1]);
+            pf[3] = pack_bf16(p[1][2], p[1][3]);
+        }
+        // O = O * alpha + P V
+        {
+            const int mid = lane >> 3, rr = lane & 7;
+            const int key = key0 + (mid & 1) * 8 + rr;
+#pragma unroll
+            for (int n2 = 0; n2 < NT / 2; n2++) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(b0, b1, b2, b3, vbase + tile_offset<HD>(key, n2 * 16 + (mid >> 1) * 8));
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    float(&acc)[4] = o[n2 * 2 + h];
+                    acc[0] *= alpha[0]; acc[1] *= alpha[0]; acc[2] *= alpha[1]; acc[3] *= alpha[1];
+                }
+                mma_bf16(o[n2 * 2], pf, b0, b1);
+                mma_bf16(o[n2 * 2 + 1], pf, b2, b3);
+            }
+        }
+        if (edge) fence_proxy_async();   // this stage was written by threads; a TMA load will overwrite it
+        __syncthreads();                 // the stage may be refilled
+    }
+
+    // ---- merge the four warps (each holds an online softmax over its own positions)
+    __syncthreads();
+    float* Om = reinterpret_cast<float*>(smem);            // [4 warps][16 rows][HD]
+    float* Mm = Om + 4 * 16 * HD;                          // [4][16]
+    float* Lm = Mm + 4 * 16;                               // [4][16]
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    {
+        const int r0 = lane >> 2, c = (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < NT; n++) {
+            float* w0 = Om + ((size_t)warp * 16 + r0) * HD + n * 8 + c;
+            float* w1 = Om + ((size_t)warp * 16 + r0 + 8) * HD + n * 8 + c;
+            w0[0] = o[n][0]; w0[1] = o[n][1];
+            w1[0] = o[n][2]; w1[1] = o[n][3];
+        }
+        if ((lane & 3) == 0) {
+            Mm[warp * 16 + r0] = m_run[0]; Mm[warp * 16 + r0 + 8] = m_run[1];
+            Lm[warp * 16 + r0] = l_run[0]; Lm[warp * 16 + r0 + 8] = l_run[1];
+        }
+    }
+    __syncthreads();
+    for (int idx = t; idx < rows * HD; idx += THREADS) {
+        const int r = idx / HD, d = idx - r * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) m = fmaxf(m, Mm[w * 16 + r]);
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float mw = Mm[w * 16 + r];
+            if (mw > -INFINITY) {
+                const float f = expf(mw - m);
+                l += Lm[w * 16 + r] * f;
+                acc += Om[((size_t)w * 16 + r) * HD + d] * f;
+            }
+        }
+        const int h = h0 + r;
+        if (a.n_splits == 1) {
+            ((bf16*)a.out)[(size_t)b * a.o_stride + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else {
+            const size_t base = ((size_t)b * a.n_heads + h) * a.n_splits + split;
+            a.part_o[base * HD + d] = acc;
+            if (d == 0) { a.part_ml[base * 2] = m; a.part_ml[base * 2 + 1] = l; }
+        }
+    }
+}
+
+struct MapKey {
+    const void* ptr; long long rows; int hd;
+    bool operator<(const MapKey& o) const { return std::tie(ptr, rows, hd) < std::tie(o.ptr, o.rows, o.hd); }
+};
+std::map<MapKey, CUtensorMap> g_maps;
+std::mutex g_maps_lock;
+
+int page_map(const void* pages, long long rows, int hd, CUtensorMap* out) {
+    std::lock_guard<std::mutex> guard(g_maps_lock);
+    MapKey key{pages, rows, hd};
+    auto it = g_maps.find(key);
+    if (it == g_maps.end()) {
+        CUtensorMap m;
+        if (int rc = ti_make_tensor_map_2d_bf16(&m, pages, (uint64_t)rows, (uint64_t)hd, (uint64_t)hd * 2, TILE, 64)) return rc;
+        if (g_maps.size() > 4096) g_maps.clear();
+        it = g_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+
+template <int HD>
+int launch(const tiattn::DecodeArgs& a, int n_seq, cudaStream_t stream) {
+    constexpr size_t stage_bytes = 2 * TILE * HD * 2;
+    constexpr size_t merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * sizeof(float);
+    constexpr size_t smem = (STAGES * stage_bytes > merge_bytes ? STAGES * stage_bytes : merge_bytes) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        TI_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    CUtensorMap km, vm;
+    const long long rows = (long long)a.n_pages * a.n_kv_heads * TILE;
+    if (int rc = page_map(a.k_pages, rows, HD, &km)) return rc;
+    if (int rc = page_map(a.v_pages, rows, HD, &vm)) return rc;
+    int* status = ti_status_ptr();
+    TI_REQUIRE(status != nullptr, "attention_decode: no status word");
+    const int g = a.n_heads / a.n_kv_heads;
+    dim3 grid(n_seq, a.n_kv_heads * ((g + 15) / 16), a.n_splits);
+    attn_decode_mma_kernel<HD><<<grid, THREADS, smem, stream>>>(km, vm, a, status);
+    TI_CHECK_LAUNCH("attention_decode (tensor cores)");
+    if (a.n_splits > 1) {
+        dim3 cgrid(n_seq, a.n_heads);
+        tiattn::attn_decode_combine_kernel<bf16><<<cgrid, HD < 128 ? 64 : 128, 0, stream>>>(
+            a.part_o, a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits);
+        TI_CHECK_LAUNCH("attention_decode (combine)");
+    }
+    return 0;
+}
+}  // namespace
+
+// bfloat16 only; head_dim 64 or 128; pages of 64 positions.  Same arguments as
+// ti_attn_decode_simt.
+extern "C" int ti_attn_decode_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                  const int* page_table, int table_width, int page_size, int ring_rows,
+                                  int n_pages, const int* seq_slot, const int* seq_len, int n_seq,
+                                  int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                  int n_splits, void* out, long long o_stride, float* part_o,
+                                  float* part_ml, int dtype, cudaStream_t stream) {
+    if (n_seq == 0) return 0;
+    TI_REQUIRE(dtype == TI_BF16, "attention_decode (tensor cores): bfloat16 only");
+    TI_REQUIRE(head_dim == 64 || head_dim == 128, "attention_decode (tensor cores): head size %d is not 64 or 128", head_dim);
+    TI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_decode: bad head counts");
+    TI_REQUIRE(page_size == TILE, "attention_decode: pages of %d positions, this kernel works on %d", page_size, TILE);
+    TI_REQUIRE(ring_rows % page_size == 0, "attention_decode: ring of %d rows is not whole pages", ring_rows);
+    TI_REQUIRE(window == 0 || ring_rows == 0 || ring_rows >= window, "attention_decode: ring smaller than the window");
+    TI_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention_decode: bad split count %d", n_splits);
+    TI_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_decode: split results need scratch memory");
+    TI_REQUIRE((reinterpret_cast<uintptr_t>(q) & 3) == 0 && q_stride % 2 == 0, "attention_decode: queries must be 4-byte aligned");
+    tiattn::DecodeArgs a;
+    a.q = q; a.q_stride = q_stride; a.k_pages = k_pages; a.v_pages = v_pages; a.page_table = page_table;
+    a.table_width = table_width; a.page_size = page_size; a.ring_rows = ring_rows; a.n_pages = n_pages;
+    a.seq_slot = seq_slot; a.seq_len = seq_len; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.hd = head_dim;
+    a.window = window; a.n_splits = n_splits; a.scale = scale; a.out = out; a.o_stride = o_stride;
+    a.part_o = part_o; a.part_ml = part_ml;
+    return head_dim == 64 ? launch<64>(a, n_seq, stream) : launch<128>(a, n_seq, stream);
+}

@@ -14,21 +14,12 @@
 // is one page of the cache.  Each split writes an unnormalised partial result with
 // its maximum and sum; `attn_decode_combine_kernel` merges them.  With one split the
 // result is written directly.
-#include "common.cuh"
+#include "attn_decode.cuh"
 
 namespace {
+using tiattn::DecodeArgs;
+using tiattn::attn_decode_combine_kernel;
 constexpr int TILE = 64, THREADS = 128, MAXACC = 32;
-
-struct DecodeArgs {
-    const void* q; long long q_stride;        // [B, heads, hd]
-    const void* k_pages; const void* v_pages; // [pages, kv_heads, page, hd]
-    const int* page_table; int table_width; int page_size; int ring_rows; int n_pages;
-    const int* seq_slot; const int* seq_len;
-    int n_heads, n_kv_heads, hd, window, n_splits;
-    float scale;
-    void* out; long long o_stride;            // [B, heads, hd]
-    float* part_o; float* part_ml;            // [B, heads, splits, hd], [B, heads, splits, 2]
-};
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS) attn_decode_kernel(DecodeArgs a) {
@@ -145,30 +136,6 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(DecodeArgs a) {
         float* ml = a.part_ml + (((size_t)b * a.n_heads + h0 + t) * a.n_splits + split) * 2;
         ml[0] = Mh[t];
         ml[1] = Lh[t];
-    }
-}
-
-// one block per (sequence, head); threads over the head's elements
-template <typename T>
-__global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                           T* __restrict__ out, long long o_stride, int n_heads, int hd,
-                                           int n_splits) {
-    const int b = blockIdx.x, h = blockIdx.y;
-    const size_t base = ((size_t)b * n_heads + h) * n_splits;
-    float m = -INFINITY;
-    for (int s = 0; s < n_splits; s++) m = fmaxf(m, part_ml[(base + s) * 2]);
-    float l = 0.f;
-    for (int s = 0; s < n_splits; s++) {
-        const float ms = part_ml[(base + s) * 2];
-        if (ms > -INFINITY) l += part_ml[(base + s) * 2 + 1] * expf(ms - m);
-    }
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float o = 0.f;
-        for (int s = 0; s < n_splits; s++) {
-            const float ms = part_ml[(base + s) * 2];
-            if (ms > -INFINITY) o = fmaf(part_o[(base + s) * hd + d], expf(ms - m), o);
-        }
-        out[(size_t)b * o_stride + (size_t)h * hd + d] = from_f32<T>(l > 0.f ? o / l : 0.f);
     }
 }
 

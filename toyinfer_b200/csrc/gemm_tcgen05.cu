@@ -1,0 +1,369 @@
+// out = X W^T in bfloat16 on the 5th-generation tensor cores: tcgen05.mma with the
+// accumulator in tensor memory, operands staged in shared memory by TMA.
+//
+// The kernel computes D[i, j] = sum_k A[i, k] B[j, k] for a tile of 128 rows of A and BN
+// rows of B, both operands K-contiguous ("K-major"), which is how activations [tokens, K]
+// and weights [out, K] already lie in memory.  Either may play A:
+//   * many tokens (prefill): A = activations, B = weights, D stored as out[i, j];
+//   * few tokens (decode):   A = weights, B = activations (BN = 16..64), D stored
+//     transposed as out[j, i].  The weight matrix is streamed once at full width of the
+//     128-row MMA whatever the batch; the step is bound by that read.
+// The contraction may be split over blockIdx.z; partial tiles go to a float32 workspace and
+// the last block to finish a tile (a ticket per tile) adds them in split order, so the
+// result does not depend on timing.
+//
+// Roles inside a block of 192 threads: warp 0 issues TMA loads into a ring of stages
+// (full/empty mbarriers), one lane of warp 1 issues the MMAs (four K = 16 steps per
+// 64-wide stage) and commits them to the stage's empty barrier, warps 2..5 read the
+// accumulator back with tcgen05.ld (each its own 32 TMEM lanes) and store.  Every wait is
+// bounded (see tma.cuh); a block always frees its tensor memory before it returns.
+//
+// Contraction and rounding are those of the reference's projections (src/decode.cu:202-236,
+// src/prefill.cu:124-161): bfloat16 operands, float32 accumulation, one rounding of the result.
+#include "tma.cuh"
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace {
+constexpr int BM = 128, BK = 64, THREADS = 192;
+
+struct GemmArgs {
+    int rows_a, rows_b, K;
+    void* out; long long ld_out; int out_f32; int transposed;
+    int splits; float* workspace; int* tickets;
+};
+
+// ---- tcgen05 wrappers ------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot_in_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns: thread = lane, r[c] = column c
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&r)[16]) {
+    uint32_t u[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+          "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) r[i] = __uint_as_float(u[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16)
+// under the 128-byte swizzle: 8-row groups 1024 bytes apart, descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);   // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                        // leading byte offset (unused with a swizzle), 16-byte units
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset: next group of 8 rows
+    d |= (uint64_t)1 << 46;                        // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                        // layout: 128-byte swizzle
+    return d;
+}
+
+// kind::f16 instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M = 128
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t instr_desc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int BN> constexpr int stages_for() {
+    constexpr int per = BM * BK * 2 + BN * BK * 2;
+    constexpr int n = (200 * 1024) / per;
+    return n > 8 ? 8 : n;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
+               GemmArgs g, int* status) {
+    constexpr int STAGES = stages_for<BN>();
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t full[STAGES], empty[STAGES], acc_ready;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int s_last;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a0 = blockIdx.x * BM, b0 = blockIdx.y * BN, split = blockIdx.z;
+    const int nkb = (g.K + BK - 1) / BK;
+    const int per = (nkb + g.splits - 1) / g.splits;
+    const int kb0 = split * per, kb1 = min(nkb, kb0 + per);
+    const int n_iter = max(0, kb1 - kb0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(&acc_ready, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tmem_alloc(&tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer
+        if (lane == 0) {
+            for (int it = 0; it < n_iter; it++) {
+                const int s = it % STAGES;
+                if (!mbar_wait(&empty[s], (uint32_t)(((it / STAGES) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); break; }
+                unsigned char* sa = smem + (size_t)s * (A_BYTES + B_BYTES);
+                mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                tma_load_2d(sa, &a_map, (kb0 + it) * BK, a0, &full[s]);
+                tma_load_2d(sa + A_BYTES, &b_map, (kb0 + it) * BK, b0, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc<BN>();
+            bool ok = true;
+            for (int it = 0; it < n_iter && ok; it++) {
+                const int s = it % STAGES;
+                if (!mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1))) { ti_report(status, TI_STATUS_TMA_WAIT); ok = false; break; }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + (size_t)s * (A_BYTES + B_BYTES));
+                const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++)   // 16 elements = 32 bytes = 2 descriptor units along K
+                    tc_mma_bf16(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (it > 0 || k > 0) ? 1u : 0u);
+                tc_commit(&empty[s]);               // the stage is free once these MMAs have read it
+            }
+            if (ok) tc_commit(&acc_ready);          // the accumulator is complete once all MMAs are done
+        }
+    } else {
+        // ---- epilogue: warps 2..5, each reads the 32 TMEM lanes it may access
+        const int q = warp & 3;                     // lanes q*32 .. q*32+31
+        const int i = a0 + q * 32 + lane;           // row of A this thread holds
+        bool ok = true;
+        if (n_iter > 0) {
+            if (!mbar_wait(&acc_ready, 0)) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);   // the reads below are warp-wide instructions
+            tc_fence_after();
+        }
+        const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
+        if (g.splits > 1) {
+            // partial tile to the workspace, element (i, j) at [j * 128 + i_local]
+            float* ws = g.workspace + (((size_t)split * gridDim.x + blockIdx.x) * gridDim.y + blockIdx.y) * (size_t)(BM * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float r[16];
+                if (ok && n_iter > 0) tmem_ld16(taddr + c, r);
+                else {
+#pragma unroll
+                    for (int e = 0; e < 16; e++) r[e] = 0.f;
+                }
+#pragma unroll
+                for (int e = 0; e < 16; e++) ws[(size_t)(c + e) * BM + q * 32 + lane] = r[e];
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) {
+                const int tile = blockIdx.x * gridDim.y + blockIdx.y;
+                const int prev = atomicAdd(&g.tickets[tile], 1);
+                s_last = prev == g.splits - 1;
+                if (s_last) g.tickets[tile] = 0;    // ready for the next launch
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!s_last) ok = false;                // another block finishes this tile
+            else __threadfence();
+        }
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float r[16];
+                if (g.splits > 1) {
+#pragma unroll
+                    for (int e = 0; e < 16; e++) r[e] = 0.f;
+                    for (int sp = 0; sp < g.splits; sp++) {
+                        const float* ws = g.workspace + (((size_t)sp * gridDim.x + blockIdx.x) * gridDim.y + blockIdx.y) * (size_t)(BM * BN);
+#pragma unroll
+                        for (int e = 0; e < 16; e++) r[e] += __ldcg(&ws[(size_t)(c + e) * BM + q * 32 + lane]);
+                    }
+                } else if (n_iter > 0) {
+                    tmem_ld16(taddr + c, r);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; e++) r[e] = 0.f;
+                }
+                if (i < g.rows_a) {
+                    if (g.transposed) {
+                        // out[j, i]: the warp's lanes are consecutive i, so each j is one coalesced store
+#pragma unroll
+                        for (int e = 0; e < 16; e++) {
+                            const int j = b0 + c + e;
+                            if (j < g.rows_b) {
+                                if (g.out_f32) ((float*)g.out)[(size_t)j * g.ld_out + i] = r[e];
+                                else ((bf16*)g.out)[(size_t)j * g.ld_out + i] = __float2bfloat16_rn(r[e]);
+                            }
+                        }
+                    } else {
+                        const int j0 = b0 + c;
+                        if (g.out_f32) {
+                            float* o = (float*)g.out + (size_t)i * g.ld_out + j0;
+                            if (j0 + 16 <= g.rows_b && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                                for (int e = 0; e < 16; e += 4) *reinterpret_cast<float4*>(o + e) = make_float4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 16; e++) if (j0 + e < g.rows_b) o[e] = r[e];
+                            }
+                        } else {
+                            bf16* o = (bf16*)g.out + (size_t)i * g.ld_out + j0;
+                            if (j0 + 16 <= g.rows_b && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+                                uint32_t pk[8];
+#pragma unroll
+                                for (int e = 0; e < 8; e++) {
+                                    __nv_bfloat162 v = __floats2bfloat162_rn(r[2 * e], r[2 * e + 1]);
+                                    pk[e] = *reinterpret_cast<uint32_t*>(&v);
+                                }
+                                *reinterpret_cast<uint4*>(o) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                                *reinterpret_cast<uint4*>(o + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 16; e++) if (j0 + e < g.rows_b) o[e] = __float2bfloat16_rn(r[e]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// ---- host ------------------------------------------------------------------
+struct MapKey {
+    const void* ptr; long long rows, cols, stride; int box_rows;
+    bool operator<(const MapKey& o) const {
+        return std::tie(ptr, rows, cols, stride, box_rows) < std::tie(o.ptr, o.rows, o.cols, o.stride, o.box_rows);
+    }
+};
+std::map<MapKey, CUtensorMap> g_maps;
+std::mutex g_lock;
+
+int operand_map(const void* ptr, long long rows, long long cols, long long stride_elems, int box_rows, CUtensorMap* out) {
+    std::lock_guard<std::mutex> guard(g_lock);
+    MapKey key{ptr, rows, cols, stride_elems, box_rows};
+    auto it = g_maps.find(key);
+    if (it == g_maps.end()) {
+        CUtensorMap m;
+        if (int rc = ti_make_tensor_map_2d_bf16(&m, ptr, (uint64_t)rows, (uint64_t)cols, (uint64_t)stride_elems * 2,
+                                                (uint32_t)box_rows, BK))
+            return rc;
+        if (g_maps.size() > 8192) g_maps.clear();
+        it = g_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+
+template <int BN>
+int launch(const CUtensorMap& am, const CUtensorMap& bm, const GemmArgs& g, cudaStream_t stream) {
+    constexpr int STAGES = stages_for<BN>();
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        TI_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    int* status = ti_status_ptr();
+    TI_REQUIRE(status != nullptr, "linear: no status word");
+    dim3 grid((g.rows_a + BM - 1) / BM, (g.rows_b + BN - 1) / BN, g.splits);
+    TI_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "linear: grid of %u x %u x %u is too large", grid.x, grid.y, grid.z);
+    gemm_tc_kernel<BN><<<grid, THREADS, smem, stream>>>(am, bm, g, status);
+    TI_CHECK_LAUNCH("linear (tcgen05)");
+    return 0;
+}
+}  // namespace
+
+// Bytes of float32 workspace ti_linear_tc needs for this shape (0: no split), and how it
+// splits.  `sms` blocks fill the device once.
+extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* bn, int* splits, long long* ws_floats,
+                                 int* n_tiles) {
+    const bool sw = M <= 64;
+    const int rows_a = sw ? N : M, rows_b = sw ? M : N;
+    int b;
+    if (sw) b = rows_b <= 16 ? 16 : rows_b <= 32 ? 32 : 64;
+    else b = rows_b >= 256 ? 256 : rows_b > 64 ? 128 : rows_b > 32 ? 64 : rows_b > 16 ? 32 : 16;
+    const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + b - 1) / b);
+    const int nkb = (K + BK - 1) / BK;
+    int sp = 1;
+    if (tiles < sms) {
+        sp = (sms + tiles - 1) / tiles;
+        const int max_sp = nkb / 4 > 0 ? nkb / 4 : 1;       // at least four 64-wide blocks per split
+        if (sp > max_sp) sp = max_sp;
+        if (sp > 32) sp = 32;
+        // drop splits that would get no work
+        const int per = (nkb + sp - 1) / sp;
+        sp = (nkb + per - 1) / per;
+    }
+    *swap = sw; *bn = b; *splits = sp; *n_tiles = tiles;
+    *ws_floats = sp > 1 ? (long long)sp * tiles * BM * b : 0;
+    return 0;
+}
+
+// x[M, K] (row stride ldx), w[N, K] (row stride ldw), both bfloat16; out[M, N] bfloat16 or
+// float32 with row stride ldo.  `workspace` (float32) and `tickets` (int32, zero before the
+// first use, left zero) as planned by ti_linear_tc_plan; tickets needs n_tiles entries.
+extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
+                            long long ldw, long long ldo, int out_f32, int sms, float* workspace, int* tickets,
+                            cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    TI_REQUIRE(M > 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
+    TI_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "linear (tcgen05): K and the row strides must be multiples of 8 elements");
+    TI_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+               "linear (tcgen05): operands must be 16-byte aligned");
+    int swap, bn, splits, tiles;
+    long long ws;
+    ti_linear_tc_plan(M, N, K, sms, &swap, &bn, &splits, &ws, &tiles);
+    TI_REQUIRE(splits == 1 || (workspace && tickets), "linear (tcgen05): a split contraction needs workspace and tickets");
+    GemmArgs g;
+    g.rows_a = swap ? N : M; g.rows_b = swap ? M : N; g.K = K;
+    g.out = out; g.ld_out = ldo; g.out_f32 = out_f32; g.transposed = swap;
+    g.splits = splits; g.workspace = workspace; g.tickets = tickets;
+    CUtensorMap am, bm;
+    if (int rc = operand_map(swap ? w : x, g.rows_a, K, swap ? ldw : ldx, BM, &am)) return rc;
+    if (int rc = operand_map(swap ? x : w, g.rows_b, K, swap ? ldx : ldw, bn, &bm)) return rc;
+    switch (bn) {
+        case 16: return launch<16>(am, bm, g, stream);
+        case 32: return launch<32>(am, bm, g, stream);
+        case 64: return launch<64>(am, bm, g, stream);
+        case 128: return launch<128>(am, bm, g, stream);
+        default: return launch<256>(am, bm, g, stream);
+    }
+}

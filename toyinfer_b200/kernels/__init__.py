@@ -263,3 +263,17 @@ def uniform_from(seed: int, key: int, step: int) -> float:
     return float(library().ti_uniform_from(ctypes.c_uint64(seed & 0xFFFFFFFFFFFFFFFF),
                                            ctypes.c_uint64(key & 0xFFFFFFFFFFFFFFFF),
                                            ctypes.c_uint64(step & 0xFFFFFFFFFFFFFFFF)))
+
+
+_STATUS = {1: "a wait for a TMA load ran out", 2: "a wait for tensor-core work ran out",
+           3: "a wait for a pipeline slot ran out"}
+
+
+def check_status() -> None:
+    """Waits for the device and raises if a kernel gave up on one of its bounded waits
+    since the last check (its results are then not to be trusted)."""
+    v = ctypes.c_int(0)
+    if library().ti_read_status(ctypes.byref(v)) != 0:
+        raise KernelError(library().ti_last_error().decode("utf-8", "replace"))
+    if v.value:
+        raise KernelError(f"a kernel reported status {v.value}: {_STATUS.get(v.value, 'unknown')}")

@@ -20,11 +20,11 @@ def prefill(q, k, v, out, scale, window, batch) -> None:
 
 def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int) -> int:
     """Splits along the keys so that the grid has about two blocks per SM, but no split
-    shorter than four pages.  Depends only on the batch's padded size and the longest
+    shorter than two pages.  Depends only on the batch's padded size and the longest
     length the step was planned for, so that a captured launch stays valid."""
     tiles = max(1, (max_len + page - 1) // page)
     want = max(1, (2 * SM_COUNT) // max(1, n_seq * n_kv_heads))
-    return max(1, min(want, (tiles + 3) // 4, 64))
+    return max(1, min(want, (tiles + 1) // 2, 64))
 
 
 def decode(q, mem, out, scale, window, batch) -> None:
@@ -37,7 +37,9 @@ def decode(q, mem, out, scale, window, batch) -> None:
         part_o = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((B, nh, splits, 2), dtype=torch.float32, device=q.device)
     pt = mem.page_table
-    _call(library().ti_attn_decode_simt, _ptr(q), _row_stride(q, "q"), _ptr(mem.k_pages), _ptr(mem.v_pages),
+    lib = library()
+    fn = lib.ti_attn_decode_mma if (q.dtype == torch.bfloat16 and hd in (64, 128)) else lib.ti_attn_decode_simt
+    _call(fn, _ptr(q), _row_stride(q, "q"), _ptr(mem.k_pages), _ptr(mem.v_pages),
           _ptr(pt), pt.shape[1], mem.page_size, mem.ring_rows, mem.k_pages.shape[0],
           _ptr(batch.seq_slot), _ptr(batch.seq_len), B, nh, nkv, hd, scale, window, splits,
           _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _code(q, "attention_decode"), _stream(),

@@ -1,13 +1,50 @@
-"""Which matrix-product kernel runs a given shape."""
+"""Which matrix-product kernel runs a given shape.
+
+bfloat16 operands whose rows are 16-byte aligned go to the tcgen05 kernel (the weights play
+the 128-row operand when there are at most 64 tokens); everything else, and the whole
+32-bit engine, runs on the CUDA-core kernels.
+"""
 from __future__ import annotations
+
+import ctypes
 
 import torch
 
 from . import _call, _code, _ptr, _stream
 from .lib import library
 
+SM_COUNT = 148
+_tickets = {}
+
+
+def _tickets_for(device) -> torch.Tensor:
+    t = _tickets.get(device)
+    if t is None:
+        t = _tickets[device] = torch.zeros(4096, dtype=torch.int32, device=device)
+    return t
+
+
+def tc_eligible(x, w, K, ldx, ldw) -> bool:
+    return (x.dtype == torch.bfloat16 and K % 8 == 0 and ldx % 8 == 0 and ldw % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
 
 def run(x, w, out, M, N, K, ldx, ldw) -> None:
+    lib = library()
     out_f32 = 1 if (out.dtype == torch.float32 and x.dtype != torch.float32) else 0
-    _call(library().ti_linear_simt, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0),
+    if tc_eligible(x, w, K, ldx, ldw):
+        swap, bn, splits, n_tiles = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        ws = ctypes.c_longlong()
+        lib.ti_linear_tc_plan(M, N, K, SM_COUNT, ctypes.byref(swap), ctypes.byref(bn), ctypes.byref(splits),
+                              ctypes.byref(ws), ctypes.byref(n_tiles))
+        workspace = tickets = None
+        if splits.value > 1:
+            workspace = torch.empty(ws.value, dtype=torch.float32, device=x.device)
+            tickets = _tickets_for(x.device)
+            if n_tiles.value > tickets.numel():
+                raise RuntimeError("linear: more split tiles than tickets")
+        _call(lib.ti_linear_tc, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, SM_COUNT,
+              _ptr(workspace), _ptr(tickets), _stream())
+        return
+    _call(lib.ti_linear_simt, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0),
           _code(x, "linear"), out_f32, _stream())

@@ -28,6 +28,10 @@ def _declare(lib) -> None:
                                   P, P, P, I, I, I, I, I, I, P],
         "ti_attn_prefill_simt": [P, P, P, P, L, L, L, L, P, I, I, I, I, I, F, I, I, P],
         "ti_attn_decode_simt": [P, L, P, P, P, I, I, I, I, P, P, I, I, I, I, F, I, I, P, L, P, P, I, P],
+        "ti_attn_decode_mma": [P, L, P, P, P, I, I, I, I, P, P, I, I, I, I, F, I, I, P, L, P, P, I, P],
+        "ti_linear_tc": [P, P, P, I, I, I, L, L, L, I, I, P, P, P],
+        "ti_linear_tc_plan": [I, I, I, I, P, P, P, P, P],
+        "ti_read_status": [P],
         "ti_argmax": [P, L, I, I, P, P],
         "ti_sample": [P, L, I, I, F, I, F, c_uint64, P, P, P, P],
     }
