@@ -269,11 +269,35 @@ def test_attention_prefill(K, dtype, nh, nkv, hd, window):
         o += n
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, 0), (4, 4, 64, 0), (6, 2, 128, 100), (2, 1, 64, 64), (32, 8, 128, 0)])
+def test_attention_prefill_on_views_of_one_buffer(K, nh, nkv, hd, window):
+    """q, k and v as strided views of one projection output, the way the mixer calls it
+    (this is the shape of call that the tensor-core kernel takes)."""
+    dtype = torch.bfloat16
+    news = [200, 1, 64, 65, 333]
+    M = sum(news)
+    width = (nh + 2 * nkv) * hd
+    qkv = randn(M, width, seed=26).to(dtype)
+    g = dev(qkv)
+    q = g[:, : nh * hd].view(M, nh, hd)
+    k = g[:, nh * hd: (nh + nkv) * hd].view(M, nkv, hd)
+    v = g[:, (nh + nkv) * hd:].view(M, nkv, hd)
+    batch = make_batch("start", list(range(len(news))), [0] * len(news), news)
+    scale = 1.0 / math.sqrt(hd)
+    got = K.attention_prefill(q, k, v, scale, window, batch).cpu().double()
+    K.check_status()
+    o = 0
+    for n in news:
+        want = plain_attention_seq(q[o:o + n].cpu(), k[o:o + n].cpu(), v[o:o + n].cpu(), scale, window, dtype)
+        torch.testing.assert_close(got[o:o + n], want, **ATT_TOL[dtype])
+        o += n
+
+
 @pytest.mark.parametrize("dtype", DT)
 def test_attention_prefill_far_key_and_window_edge(K, dtype):
     """One key far back is made to dominate: without a window every later query must
     return its value; with a window only the queries that still see it."""
-    nh, nkv, hd, n, far, W = 4, 2, 32, 300, 17, 64
+    nh, nkv, hd, n, far, W = 4, 2, 64, 300, 17, 64
     q = randn(n, nh, hd, seed=23, scale=0.1)
     k = randn(n, nkv, hd, seed=24, scale=0.1)
     v = randn(n, nkv, hd, seed=25)

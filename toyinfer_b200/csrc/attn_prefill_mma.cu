@@ -1,0 +1,277 @@
+// Causal grouped-query attention over the tokens of one step (sequences that start at
+// position 0), bfloat16, tensor cores, tiles brought in by TMA.  Same contract and formulas
+// as attn_prefill_simt.cu (reference: src/prefill.cu:224-379); this is the kernel the
+// bfloat16 engine runs prompts with for head sizes 64 and 128.
+//
+// Grid (query tiles of 64 taken from the last to the first, heads, sequences), 128 threads,
+// two blocks per SM.  q, k and v are strided views of the projection's output
+// [tokens, heads * head_dim]; tensor maps with the 128-byte swizzle cut 64 x 64 boxes out of
+// them.  The query tile is loaded once; key/value tiles of 64 positions run through a ring
+// of stages guarded by mbarriers, one thread issuing loads ahead.  Key tiles that the causal
+// mask or the window excludes entirely are never loaded.
+//
+// Each warp owns 16 queries: S = Q K^T (mma.m16n8k16), scale, mask, online softmax with the
+// running maximum subtracted before every exp, O += P V with P rounded to bfloat16, and
+// O / sum at the end.
+#include "mma_utils.cuh"
+#include "tma.cuh"
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace {
+constexpr int BQ = 64, BKV = 64, THREADS = 128, STAGES = 2;
+
+struct PrefillArgs {
+    const int* cu_new; int n_heads, n_kv_heads; float scale; int window;
+    void* out; long long o_stride;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 2)
+attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                        const __grid_constant__ CUtensorMap v_map, PrefillArgs a, int* status) {
+    constexpr int TILE_BYTES = BKV * HD * 2;
+    constexpr int KSTEPS = HD / 16, NT = HD / 8;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* q_s = smem;                         // [64][HD] swizzled
+    unsigned char* kv_s = smem + TILE_BYTES;           // STAGES x (K tile, V tile)
+    __shared__ uint64_t full[STAGES], q_full;
+    __shared__ int s_abort;
+
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int tok0 = a.cu_new[b];
+    const int n = a.cu_new[b + 1] - tok0;
+    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BQ;     // long rows of the triangle first
+    if (q0 >= n) return;
+    const int kvh = h / (a.n_heads / a.n_kv_heads);
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+
+    const int last_q = min(q0 + BQ, n) - 1;
+    const int kt_lo = a.window > 0 ? max(0, q0 - a.window + 1) / BKV : 0;
+    const int kt_hi = last_q / BKV;
+    const int n_tiles = kt_hi - kt_lo + 1;
+
+    if (t == 0) {
+        for (int s = 0; s < STAGES; s++) mbar_init(&full[s], 1);
+        mbar_init(&q_full, 1);
+        s_abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    auto issue = [&](int i) {
+        const int y = tok0 + (kt_lo + i) * BKV;
+        unsigned char* dst = kv_s + (size_t)(i % STAGES) * 2 * TILE_BYTES;
+        uint64_t* bar = &full[i % STAGES];
+        mbar_expect_tx(bar, 2 * TILE_BYTES);
+#pragma unroll
+        for (int bx = 0; bx < HD / 64; bx++) {
+            tma_load_2d(dst + bx * (BKV * 128), &k_map, kvh * HD + bx * 64, y, bar);
+            tma_load_2d(dst + TILE_BYTES + bx * (BKV * 128), &v_map, kvh * HD + bx * 64, y, bar);
+        }
+    };
+    if (t == 0) {
+        mbar_expect_tx(&q_full, TILE_BYTES);
+#pragma unroll
+        for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(q_s + bx * (BQ * 128), &q_map, h * HD + bx * 64, tok0 + q0, &q_full);
+        for (int i = 0; i < STAGES - 1 && i < n_tiles; i++) issue(i);
+    }
+
+    // the warp's 16 queries as A fragments
+    uint32_t qf[KSTEPS][4];
+    {
+        const bool ok = mbar_wait(&q_full, 0);
+        if (!ok) { ti_report(status, TI_STATUS_TMA_WAIT); s_abort = 1; }
+        __syncthreads();
+        if (s_abort) {
+            if (t == 0)
+                for (int j = 0; j < n_tiles && j < STAGES - 1; j++) mbar_wait(&full[j % STAGES], 0);
+            return;
+        }
+        const int mid = lane >> 3, rr = lane & 7;
+        const int row = warp * 16 + (mid & 1) * 8 + rr;
+        const uint32_t qb = smem_u32(q_s);
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++)
+            ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], qb + swizzled_offset<BQ>(row, ks * 16 + (mid >> 1) * 8));
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int qi0 = q0 + warp * 16 + (lane >> 2);       // this thread's rows: qi0 and qi0 + 8
+
+    for (int i = 0; i < n_tiles; i++) {
+        const int stage = i % STAGES;
+        if (t == 0 && i + STAGES - 1 < n_tiles) issue(i + STAGES - 1);
+        if (!mbar_wait(&full[stage], (uint32_t)((i / STAGES) & 1))) { ti_report(status, TI_STATUS_TMA_WAIT); s_abort = 1; }
+        __syncthreads();
+        if (s_abort) {
+            if (t == 0)
+                for (int j = i; j < n_tiles && j < i + STAGES; j++) mbar_wait(&full[j % STAGES], (uint32_t)((j / STAGES) & 1));
+            return;
+        }
+        const uint32_t kb = smem_u32(kv_s + (size_t)stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
+        const int k0 = (kt_lo + i) * BKV;
+
+        float s[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        {
+            const int mid = lane >> 3, rr = lane & 7;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks++)
+#pragma unroll
+                for (int np = 0; np < 4; np++) {        // two n-tiles (16 keys) per ldmatrix
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4(b0, b1, b2, b3, kb + swizzled_offset<BKV>(np * 16 + (mid >> 1) * 8 + rr, ks * 16 + (mid & 1) * 8));
+                    mma_bf16(s[np * 2], qf[ks], b0, b1);
+                    mma_bf16(s[np * 2 + 1], qf[ks], b2, b3);
+                }
+        }
+        // scale and mask
+        const bool edge = a.window > 0 || k0 + BKV - 1 > q0 + warp * 16 || k0 + BKV > n;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                float v = s[nt][e] * a.scale;
+                if (edge) {
+                    const int kj = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const int qi = qi0 + (e >> 1) * 8;
+                    const bool ok = kj <= qi && kj < n && (a.window <= 0 || kj > qi - a.window);
+                    v = ok ? v : -INFINITY;
+                }
+                s[nt][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        float alpha[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r]);
+            alpha[r] = m_new > -INFINITY ? expf(m_run[r] - m_new) : 1.f;
+            m_run[r] = m_new;
+        }
+        float ls[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float p = m_run[e >> 1] > -INFINITY ? expf(s[nt][e] - m_run[e >> 1]) : 0.f;
+                s[nt][e] = p;
+                ls[e >> 1] += p;
+            }
+        l_run[0] = l_run[0] * alpha[0] + ls[0];
+        l_run[1] = l_run[1] * alpha[1] + ls[1];
+#pragma unroll
+        for (int i2 = 0; i2 < NT; i2++) { o[i2][0] *= alpha[0]; o[i2][1] *= alpha[0]; o[i2][2] *= alpha[1]; o[i2][3] *= alpha[1]; }
+        // O += P V, 16 keys at a time
+        {
+            const int mid = lane >> 3, rr = lane & 7;
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++) {
+                uint32_t pf[4];
+                pf[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                pf[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                pf[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pf[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int n2 = 0; n2 < NT / 2; n2++) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(b0, b1, b2, b3, vb + swizzled_offset<BKV>(kk * 16 + (mid & 1) * 8 + rr, n2 * 16 + (mid >> 1) * 8));
+                    mma_bf16(o[n2 * 2], pf, b0, b1);
+                    mma_bf16(o[n2 * 2 + 1], pf, b2, b3);
+                }
+            }
+        }
+        __syncthreads();    // the stage may be refilled
+    }
+
+    // normalise and store
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    const float inv0 = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+    bf16* out = (bf16*)a.out;
+    const int c = (lane & 3) * 2;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        if (qi0 < n)
+            *reinterpret_cast<uint32_t*>(out + (size_t)(tok0 + qi0) * a.o_stride + (size_t)h * HD + nt * 8 + c) =
+                pack_bf16(o[nt][0] * inv0, o[nt][1] * inv0);
+        if (qi0 + 8 < n)
+            *reinterpret_cast<uint32_t*>(out + (size_t)(tok0 + qi0 + 8) * a.o_stride + (size_t)h * HD + nt * 8 + c) =
+                pack_bf16(o[nt][2] * inv1, o[nt][3] * inv1);
+    }
+}
+
+struct MapKey {
+    const void* ptr; long long rows, cols, stride;
+    bool operator<(const MapKey& o) const { return std::tie(ptr, rows, cols, stride) < std::tie(o.ptr, o.rows, o.cols, o.stride); }
+};
+std::map<MapKey, CUtensorMap> g_maps;
+std::mutex g_lock;
+
+int view_map(const void* ptr, long long rows, long long cols, long long stride, CUtensorMap* out) {
+    std::lock_guard<std::mutex> guard(g_lock);
+    MapKey key{ptr, rows, cols, stride};
+    auto it = g_maps.find(key);
+    if (it == g_maps.end()) {
+        CUtensorMap m;
+        if (int rc = ti_make_tensor_map_2d_bf16(&m, ptr, (uint64_t)rows, (uint64_t)cols, (uint64_t)stride * 2, 64, 64)) return rc;
+        if (g_maps.size() > 8192) g_maps.clear();
+        it = g_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+
+template <int HD>
+int launch(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillArgs& a, int n_seq, int max_new,
+           cudaStream_t stream) {
+    constexpr size_t smem = (size_t)BKV * HD * 2 * (1 + 2 * STAGES) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        TI_CUDA(cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    int* status = ti_status_ptr();
+    TI_REQUIRE(status != nullptr, "attention_prefill: no status word");
+    dim3 grid((max_new + BQ - 1) / BQ, a.n_heads, n_seq);
+    attn_prefill_mma_kernel<HD><<<grid, THREADS, smem, stream>>>(qm, km, vm, a, status);
+    TI_CHECK_LAUNCH("attention_prefill (tensor cores)");
+    return 0;
+}
+}  // namespace
+
+// bfloat16 only; head_dim 64 or 128.  n_tokens is the number of rows of q, k and v.
+extern "C" int ti_attn_prefill_mma(const void* q, const void* k, const void* v, void* out,
+                                   long long q_stride, long long k_stride, long long v_stride, long long o_stride,
+                                   const int* cu_new, int n_seq, int max_new, int n_tokens, int n_heads, int n_kv_heads,
+                                   int head_dim, float scale, int window, cudaStream_t stream) {
+    if (n_seq == 0 || max_new == 0) return 0;
+    TI_REQUIRE(head_dim == 64 || head_dim == 128, "attention_prefill (tensor cores): head size %d is not 64 or 128", head_dim);
+    TI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_prefill: bad head counts");
+    TI_REQUIRE(n_seq <= 65535 && n_heads <= 65535, "attention_prefill: too many sequences or heads for one launch");
+    TI_REQUIRE(q_stride % 8 == 0 && k_stride % 8 == 0 && v_stride % 8 == 0 && o_stride % 2 == 0,
+               "attention_prefill (tensor cores): token strides must be multiples of 8 elements");
+    TI_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0 &&
+               (reinterpret_cast<uintptr_t>(out) & 3) == 0, "attention_prefill (tensor cores): misaligned operands");
+    CUtensorMap qm, km, vm;
+    if (int rc = view_map(q, n_tokens, (long long)n_heads * head_dim, q_stride, &qm)) return rc;
+    if (int rc = view_map(k, n_tokens, (long long)n_kv_heads * head_dim, k_stride, &km)) return rc;
+    if (int rc = view_map(v, n_tokens, (long long)n_kv_heads * head_dim, v_stride, &vm)) return rc;
+    PrefillArgs a;
+    a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = window;
+    a.out = out; a.o_stride = o_stride;
+    return head_dim == 64 ? launch<64>(qm, km, vm, a, n_seq, max_new, stream)
+                          : launch<128>(qm, km, vm, a, n_seq, max_new, stream);
+}
