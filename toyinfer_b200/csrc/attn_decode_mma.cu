@@ -41,6 +41,14 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
     __shared__ uint64_t full[STAGES];
     __shared__ int s_abort;
 
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) mbar_init(&full[s], 1);
+        s_abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    ti_pdl_sync();      // everything above touched only this block's shared memory
+
     const int b = blockIdx.x, split = blockIdx.z;
     const int g = a.n_heads / a.n_kv_heads;
     const int groups = (g + 15) / 16;
@@ -56,13 +64,6 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
     const int per = (n_tiles + a.n_splits - 1) / a.n_splits;
     const int my_lo = tile_lo + split * per;
     const int my_n = max(0, min(my_lo + per, tile_lo + n_tiles) - my_lo);
-
-    if (t == 0) {
-        for (int s = 0; s < STAGES; s++) mbar_init(&full[s], 1);
-        s_abort = 0;
-        mbar_fence_init();
-    }
-    __syncthreads();
 
     auto issue = [&](int i) {      // tile my_lo + i into stage i % STAGES; one thread calls this
         const int p0 = (my_lo + i) * TILE;
@@ -293,12 +294,11 @@ int launch(const tiattn::DecodeArgs& a, int n_seq, cudaStream_t stream) {
     TI_REQUIRE(status != nullptr, "attention_decode: no status word");
     const int g = a.n_heads / a.n_kv_heads;
     dim3 grid(n_seq, a.n_kv_heads * ((g + 15) / 16), a.n_splits);
-    attn_decode_mma_kernel<HD><<<grid, THREADS, smem, stream>>>(km, vm, a, status);
+    TI_CUDA(ti_launch(attn_decode_mma_kernel<HD>, grid, dim3(THREADS), smem, stream, km, vm, a, status));
     TI_CHECK_LAUNCH("attention_decode (tensor cores)");
     if (a.n_splits > 1) {
         dim3 cgrid(n_seq, a.n_heads);
-        tiattn::attn_decode_combine_kernel<bf16><<<cgrid, HD < 128 ? 64 : 128, 0, stream>>>(
-            a.part_o, a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits);
+        TI_CUDA(ti_launch(tiattn::attn_decode_combine_kernel<bf16>, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits));
         TI_CHECK_LAUNCH("attention_decode (combine)");
     }
     return 0;

@@ -24,6 +24,7 @@ constexpr int TILE = 64, THREADS = 128, MAXACC = 32;
 template <typename T>
 __global__ void __launch_bounds__(THREADS) attn_decode_kernel(DecodeArgs a) {
     extern __shared__ float sm[];
+    ti_pdl_sync();
     const int hd = a.hd, ld = hd + 1;
     const int g = a.n_heads / a.n_kv_heads;
     float* Qs = sm;                    // [g][hd]
@@ -151,12 +152,11 @@ int launch(const DecodeArgs& a, int n_seq, cudaStream_t stream) {
         configured = smem;
     }
     dim3 grid(n_seq, a.n_kv_heads, a.n_splits);
-    attn_decode_kernel<T><<<grid, THREADS, smem, stream>>>(a);
+    TI_CUDA(ti_launch(attn_decode_kernel<T>, grid, dim3(THREADS), smem, stream, a));
     TI_CHECK_LAUNCH("attention_decode");
     if (a.n_splits > 1) {
         dim3 cgrid(n_seq, a.n_heads);
-        attn_decode_combine_kernel<T><<<cgrid, hd < 128 ? 64 : 128, 0, stream>>>(a.part_o, a.part_ml, (T*)a.out, a.o_stride,
-                                                                               a.n_heads, hd, a.n_splits);
+        TI_CUDA(ti_launch(attn_decode_combine_kernel<T>, cgrid, dim3(hd < 128 ? 64 : 128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (T*)a.out, a.o_stride, a.n_heads, hd, a.n_splits));
         TI_CHECK_LAUNCH("attention_decode (combine)");
     }
     return 0;

@@ -41,6 +41,15 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
     __shared__ uint64_t full[STAGES], q_full;
     __shared__ int s_abort;
 
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) mbar_init(&full[s], 1);
+        mbar_init(&q_full, 1);
+        s_abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    ti_pdl_sync();      // everything above touched only this block's shared memory
+
     const int b = blockIdx.z, h = blockIdx.y;
     const int tok0 = a.cu_new[b];
     const int n = a.cu_new[b + 1] - tok0;
@@ -53,14 +62,6 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
     const int kt_lo = a.window > 0 ? max(0, q0 - a.window + 1) / BKV : 0;
     const int kt_hi = last_q / BKV;
     const int n_tiles = kt_hi - kt_lo + 1;
-
-    if (t == 0) {
-        for (int s = 0; s < STAGES; s++) mbar_init(&full[s], 1);
-        mbar_init(&q_full, 1);
-        s_abort = 0;
-        mbar_fence_init();
-    }
-    __syncthreads();
 
     auto issue = [&](int i) {
         const int y = tok0 + (kt_lo + i) * BKV;
@@ -246,7 +247,7 @@ int launch(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, 
     int* status = ti_status_ptr();
     TI_REQUIRE(status != nullptr, "attention_prefill: no status word");
     dim3 grid((max_new + BQ - 1) / BQ, a.n_heads, n_seq);
-    attn_prefill_mma_kernel<HD><<<grid, THREADS, smem, stream>>>(qm, km, vm, a, status);
+    TI_CUDA(ti_launch(attn_prefill_mma_kernel<HD>, grid, dim3(THREADS), smem, stream, qm, km, vm, a, status));
     TI_CHECK_LAUNCH("attention_prefill (tensor cores)");
     return 0;
 }

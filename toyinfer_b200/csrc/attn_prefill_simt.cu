@@ -25,6 +25,7 @@ attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* _
                     long long o_stride, const int* __restrict__ cu_new, int n_heads, int n_kv_heads,
                     int hd, float scale, int window) {
     extern __shared__ float sm[];
+    ti_pdl_sync();
     const int ld = hd + 1;
     float* Qs = sm;
     float* Ks = Qs + BQ * ld;
@@ -133,8 +134,8 @@ int launch(const void* q, const void* k, const void* v, void* out, long long qs,
         configured = smem;
     }
     dim3 grid((max_new + BQ - 1) / BQ, nh, n_seq);
-    attn_prefill_kernel<T, MAXC><<<grid, THREADS, smem, stream>>>((const T*)q, (const T*)k, (const T*)v, (T*)out,
-                                                                  qs, ks, vs, os, cu_new, nh, nkv, hd, scale, window);
+    TI_CUDA(ti_launch(attn_prefill_kernel<T, MAXC>, grid, dim3(THREADS), smem, stream, (const T*)q, (const T*)k,
+                      (const T*)v, (T*)out, qs, ks, vs, os, cu_new, nh, nkv, hd, scale, window));
     TI_CHECK_LAUNCH("attention_prefill");
     return 0;
 }

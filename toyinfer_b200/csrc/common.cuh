@@ -86,6 +86,35 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return red[32];
 }
 
+// Programmatic dependent launch: a kernel may be scheduled while the kernel before it in the
+// stream still runs, so that its launch latency and set-up overlap that kernel's tail.  It
+// must not touch global memory before `ti_pdl_sync()`, which waits until the earlier kernels
+// have finished and their writes are visible, and then allows the next kernel to be scheduled.
+// Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void ti_pdl_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+int ti_pdl_enabled();
+
+// Launches `kernel` with the programmatic-serialization attribute (see ti_pdl_sync).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ti_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ti_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename F>
 static inline int ti_dispatch_dtype(int dtype, F&& f) {
     // f is called with a value of the element type

@@ -65,6 +65,7 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 template <typename T, int V>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              T* __restrict__ out, int H, int vocab) {
+    ti_pdl_sync();
     const int m = blockIdx.x;
     const int id = ids[m];
     const bool ok = id >= 0 && id < vocab;
@@ -90,9 +91,9 @@ extern "C" int ti_embed(const void* table, const int* ids, void* out, int M, int
         constexpr int V = vec_width<T>();
         const int threads = 128;
         if (H % V == 0 && aligned16(table) && aligned16(out))
-            embed_kernel<T, V><<<M, threads, 0, stream>>>((const T*)table, ids, (T*)out, H, vocab);
+            TI_CUDA(ti_launch(embed_kernel<T, V>, dim3(M), dim3(threads), 0, stream, (const T*)table, ids, (T*)out, H, vocab));
         else
-            embed_kernel<T, 1><<<M, threads, 0, stream>>>((const T*)table, ids, (T*)out, H, vocab);
+            TI_CUDA(ti_launch(embed_kernel<T, 1>, dim3(M), dim3(threads), 0, stream, (const T*)table, ids, (T*)out, H, vocab));
         TI_CHECK_LAUNCH("embed");
         return 0;
     });
@@ -108,6 +109,7 @@ __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
                                const W* __restrict__ w, T* __restrict__ out, int H,
                                long long x_stride, float eps) {
     __shared__ float red[33];
+    ti_pdl_sync();
     const size_t row = blockIdx.x;
     T* xr = x + row * x_stride;
     const T* dr = ADD ? delta + row * (size_t)H : nullptr;
@@ -148,11 +150,11 @@ static int launch_rmsnorm(void* x, const void* delta, const void* w, void* out, 
     if (H <= 256) threads = 64;
     else if (H <= 1024) threads = 128;
     if (vec)
-        rmsnorm_kernel<T, W, V, ADD><<<M, threads, 0, stream>>>((T*)x, (const T*)delta, (const W*)w,
-                                                                (T*)out, H, x_stride, eps);
+        TI_CUDA(ti_launch(rmsnorm_kernel<T, W, V, ADD>, dim3(M), dim3(threads), 0, stream, (T*)x, (const T*)delta,
+                          (const W*)w, (T*)out, H, x_stride, eps));
     else
-        rmsnorm_kernel<T, W, 1, ADD><<<M, threads, 0, stream>>>((T*)x, (const T*)delta, (const W*)w,
-                                                                (T*)out, H, x_stride, eps);
+        TI_CUDA(ti_launch(rmsnorm_kernel<T, W, 1, ADD>, dim3(M), dim3(threads), 0, stream, (T*)x, (const T*)delta,
+                          (const W*)w, (T*)out, H, x_stride, eps));
     TI_CHECK_LAUNCH("rmsnorm");
     return 0;
 }
@@ -183,6 +185,7 @@ extern "C" int ti_rmsnorm(void* x, const void* delta, const void* w, void* out, 
 template <typename T>
 __global__ void gather_add_kernel(const T* __restrict__ h, const T* __restrict__ delta,
                                   const int* __restrict__ rows, T* __restrict__ out, int H, int M) {
+    ti_pdl_sync();
     const int r = blockIdx.x;
     const int src = rows[r];
     const bool ok = src >= 0 && src < M;
@@ -202,7 +205,7 @@ extern "C" int ti_gather_add(const void* h, const void* delta, const int* rows, 
     TI_REQUIRE(R > 0 && H > 0 && M > 0, "gather_add: bad sizes R=%d H=%d M=%d", R, H, M);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
-        gather_add_kernel<T><<<R, 256, 0, stream>>>((const T*)h, (const T*)delta, rows, (T*)out, H, M);
+        TI_CUDA(ti_launch(gather_add_kernel<T>, dim3(R), dim3(256), 0, stream, (const T*)h, (const T*)delta, rows, (T*)out, H, M));
         TI_CHECK_LAUNCH("gather_add");
         return 0;
     });
@@ -213,6 +216,7 @@ extern "C" int ti_gather_add(const void* h, const void* delta, const int* rows, 
 // ---------------------------------------------------------------------------
 template <typename T, int V>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, long long total_vecs) {
+    ti_pdl_sync();
     const int per_row = I / V;
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_vecs;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -237,11 +241,11 @@ extern "C" int ti_swiglu(const void* gu, void* out, int M, int I, int dtype, cud
         if (I % V == 0 && aligned16(gu) && aligned16(out)) {
             const long long n = (long long)M * (I / V);
             const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
-            swiglu_kernel<T, V><<<blocks, threads, 0, stream>>>((const T*)gu, (T*)out, I, n);
+            TI_CUDA(ti_launch(swiglu_kernel<T, V>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu, (T*)out, I, n));
         } else {
             const long long n = (long long)M * I;
             const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
-            swiglu_kernel<T, 1><<<blocks, threads, 0, stream>>>((const T*)gu, (T*)out, I, n);
+            TI_CUDA(ti_launch(swiglu_kernel<T, 1>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu, (T*)out, I, n));
         }
         TI_CHECK_LAUNCH("swiglu");
         return 0;

@@ -24,6 +24,7 @@ gemm_tile_kernel(const T* __restrict__ X, const T* __restrict__ W, OT* __restric
                  int M, int N, int K, long long ldx, long long ldw, long long ldo) {
     __shared__ float As[BK][BM + PAD];
     __shared__ float Bs[BK][BN + PAD];
+    ti_pdl_sync();
     const int t = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int ty = t / 16, tx = t % 16;
@@ -86,6 +87,7 @@ template <typename T, typename OT, int V>
 __global__ void __launch_bounds__(GV_THREADS)
 gemv_rows_kernel(const T* __restrict__ X, const T* __restrict__ W, OT* __restrict__ out,
                  int M, int N, int K, long long ldx, long long ldw, long long ldo) {
+    ti_pdl_sync();
     const int lane = threadIdx.x & 31;
     const int warp = (blockIdx.x * GV_THREADS + threadIdx.x) >> 5;
     const int n_warps = (gridDim.x * GV_THREADS) >> 5;
@@ -141,15 +143,15 @@ int launch_simt(const void* x, const void* w, void* out, int M, int N, int K, lo
         if (blocks > cap) blocks = cap;
         dim3 grid(blocks, (M + GV_ROWS - 1) / GV_ROWS);
         if (vec)
-            gemv_rows_kernel<T, OT, V><<<grid, GV_THREADS, 0, stream>>>((const T*)x, (const T*)w, (OT*)out, M, N, K, ldx, ldw, ldo);
+            TI_CUDA(ti_launch(gemv_rows_kernel<T, OT, V>, grid, dim3(GV_THREADS), 0, stream, (const T*)x, (const T*)w, (OT*)out, M, N, K, ldx, ldw, ldo));
         else
-            gemv_rows_kernel<T, OT, 1><<<grid, GV_THREADS, 0, stream>>>((const T*)x, (const T*)w, (OT*)out, M, N, K, ldx, ldw, ldo);
+            TI_CUDA(ti_launch(gemv_rows_kernel<T, OT, 1>, grid, dim3(GV_THREADS), 0, stream, (const T*)x, (const T*)w, (OT*)out, M, N, K, ldx, ldw, ldo));
         TI_CHECK_LAUNCH("linear (few rows)");
         return 0;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     TI_REQUIRE(grid.y <= 65535, "linear: %d rows exceed the tiled kernel's grid", M);
-    gemm_tile_kernel<T, OT><<<grid, TILE_THREADS, 0, stream>>>((const T*)x, (const T*)w, (OT*)out, M, N, K, ldx, ldw, ldo);
+    TI_CUDA(ti_launch(gemm_tile_kernel<T, OT>, grid, dim3(TILE_THREADS), 0, stream, (const T*)x, (const T*)w, (OT*)out, M, N, K, ldx, ldw, ldo));
     TI_CHECK_LAUNCH("linear (tiled)");
     return 0;
 }

@@ -88,14 +88,18 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
+// Narrow tiles (few tokens, the weights stream) keep four stages so that three blocks share
+// an SM: what matters there is how many bytes the whole device has in flight, and blocks
+// that are resident together even out the grid's last wave.  Wide tiles take the SM alone.
 template <int BN> constexpr int stages_for() {
     constexpr int per = BM * BK * 2 + BN * BK * 2;
     constexpr int n = (200 * 1024) / per;
-    return n > 8 ? 8 : n;
+    return BN <= 64 ? 4 : (n > 8 ? 8 : n);
 }
+template <int BN> constexpr int blocks_per_sm() { return BN <= 64 ? 3 : 1; }
 
 template <int BN>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, blocks_per_sm<BN>())
 gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                GemmArgs g, int* status) {
     constexpr int STAGES = stages_for<BN>();
@@ -128,6 +132,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
+    ti_pdl_sync();      // barriers and tensor memory are set up; from here on global memory is touched
 
     if (warp == 0) {
         // ---- TMA producer
@@ -305,7 +310,7 @@ int launch(const CUtensorMap& am, const CUtensorMap& bm, const GemmArgs& g, cuda
     TI_REQUIRE(status != nullptr, "linear: no status word");
     dim3 grid((g.rows_a + BM - 1) / BM, (g.rows_b + BN - 1) / BN, g.splits);
     TI_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "linear: grid of %u x %u x %u is too large", grid.x, grid.y, grid.z);
-    gemm_tc_kernel<BN><<<grid, THREADS, smem, stream>>>(am, bm, g, status);
+    TI_CUDA(ti_launch(gemm_tc_kernel<BN>, grid, dim3(THREADS), smem, stream, am, bm, g, status));
     TI_CHECK_LAUNCH("linear (tcgen05)");
     return 0;
 }
@@ -323,8 +328,10 @@ extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* b
     const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + b - 1) / b);
     const int nkb = (K + BK - 1) / BK;
     int sp = 1;
-    if (tiles < sms) {
-        sp = (sms + tiles - 1) / tiles;
+    const int want = sw ? 2 * sms : sms;      // narrow tiles run three to an SM, two rounds balance well
+    if (tiles < want) {
+        sp = (want + tiles / 2) / tiles;
+        if (sp < 1) sp = 1;
         const int max_sp = nkb / 4 > 0 ? nkb / 4 : 1;       // at least four 64-wide blocks per split
         if (sp > max_sp) sp = max_sp;
         if (sp > 32) sp = 32;

@@ -29,6 +29,7 @@ struct RopeStoreArgs {
 
 template <typename T>
 __global__ void rope_store_kernel(RopeStoreArgs a) {
+    ti_pdl_sync();
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const int heads_q = a.q ? a.n_heads : 0;
@@ -149,7 +150,7 @@ extern "C" int ti_qk_norm_rope_store(
     TI_REQUIRE(blocks < 2147483647LL, "qk_norm_rope_store: too many heads x tokens (%lld)", items);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
-        rope_store_kernel<T><<<(unsigned)blocks, warps * 32, 0, stream>>>(a);
+        TI_CUDA(ti_launch(rope_store_kernel<T>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, a));
         TI_CHECK_LAUNCH("qk_norm_rope_store");
         return 0;
     });

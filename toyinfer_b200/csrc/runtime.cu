@@ -27,6 +27,12 @@ int load_encode() {
 }
 }  // namespace
 
+static int g_pdl = 1;
+int ti_pdl_enabled() { return g_pdl; }
+// 0 switches programmatic dependent launch off (every kernel then starts after the one before
+// it has ended), 1 switches it on again.
+extern "C" int ti_set_pdl(int on) { g_pdl = on ? 1 : 0; return 0; }
+
 int* ti_status_ptr() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;

@@ -70,6 +70,7 @@ __global__ void __launch_bounds__(SB) argmax_kernel(const float* __restrict__ lo
                                                     int* __restrict__ out) {
     __shared__ float bv[32];
     __shared__ int bi[32];
+    ti_pdl_sync();
     const float* x = logits + (size_t)blockIdx.x * ld;
     float best = -INFINITY;
     int idx = INT_MAX;
@@ -116,6 +117,7 @@ __global__ void __launch_bounds__(SB) sample_topk_kernel(SampleArgs a) {
     __shared__ int scan_i[33];
     __shared__ unsigned s_prefix;
     __shared__ int s_rem, s_count;
+    ti_pdl_sync();
     const int t = threadIdx.x, V = a.V, k = a.top_k;
     const float* x = a.logits + (size_t)blockIdx.x * a.ld;
     const float temp = a.temperature;
@@ -231,6 +233,7 @@ __global__ void __launch_bounds__(SB) sample_full_kernel(SampleArgs a) {
     __shared__ float red[33];
     __shared__ float scan_f[33];
     __shared__ int s_owner;
+    ti_pdl_sync();
     const int t = threadIdx.x, V = a.V;
     const float* x = a.logits + (size_t)blockIdx.x * a.ld;
     const float temp = a.temperature;
@@ -278,7 +281,7 @@ __global__ void __launch_bounds__(SB) sample_full_kernel(SampleArgs a) {
 extern "C" int ti_argmax(const float* logits, long long ld, int R, int V, int* out, cudaStream_t stream) {
     if (R == 0) return 0;
     TI_REQUIRE(R > 0 && V > 0 && ld >= V, "argmax: bad sizes R=%d V=%d ld=%lld", R, V, ld);
-    argmax_kernel<<<R, SB, 0, stream>>>(logits, ld, V, out);
+    TI_CUDA(ti_launch(argmax_kernel, dim3(R), dim3(SB), 0, stream, logits, ld, V, out));
     TI_CHECK_LAUNCH("argmax");
     return 0;
 }
@@ -298,10 +301,10 @@ extern "C" int ti_sample(const float* logits, long long ld, int R, int V, float 
     const bool k_off = top_k <= 0 || top_k >= V;
     if (k_off) {
         TI_REQUIRE(top_p >= 1.0f, "sample: top_p %g without a top_k of at most %d is not implemented", top_p, MAXK);
-        sample_full_kernel<<<R, SB, 0, stream>>>(a);
+        TI_CUDA(ti_launch(sample_full_kernel, dim3(R), dim3(SB), 0, stream, a));
     } else {
         TI_REQUIRE(top_k <= MAXK, "sample: top_k %d exceeds the %d candidates this kernel sorts", top_k, MAXK);
-        sample_topk_kernel<<<R, SB, 0, stream>>>(a);
+        TI_CUDA(ti_launch(sample_topk_kernel, dim3(R), dim3(SB), 0, stream, a));
     }
     TI_CHECK_LAUNCH("sample");
     return 0;
