@@ -1,0 +1,421 @@
+"""Each part of a model alone against the plain implementation, and the generality of
+the assembly: a toy mixer with a state of its own, a toy feed-forward with routing and
+another position encoding are defined here, registered, built and stepped without a
+change to the library's files; a schedule that names a layer twice and lets a layer read
+another layer's cache runs and matches a plain composition of the same parts."""
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def lib():
+    import toyinfer_b200.kernels as K
+    from toyinfer_b200 import parts
+    from toyinfer_b200.cache import CacheManager
+    from toyinfer_b200.engine import Engine
+    from toyinfer_b200.engine.batch import BatchBuffers, fill_batch
+    from toyinfer_b200.parts.model import DecoderModel, LayerSpec, ModelSpec, ScheduleEntry
+    from toyinfer_b200.weights import random_parameters
+    return dict(K=K, parts=parts, CacheManager=CacheManager, Engine=Engine, BatchBuffers=BatchBuffers,
+                fill_batch=fill_batch, DecoderModel=DecoderModel, LayerSpec=LayerSpec, ModelSpec=ModelSpec,
+                ScheduleEntry=ScheduleEntry, random_parameters=random_parameters)
+
+
+def bind_random(part, seed, dtype):
+    """Draws the part's tensors on the CPU (float32), binds device copies, returns the CPU ones."""
+    from toyinfer_b200.weights import random_parameters
+    cpu = random_parameters(part.param_specs(), seed, torch.float32, "cpu")
+    if dtype == torch.bfloat16:
+        cpu = {k: v.to(torch.bfloat16).float() for k, v in cpu.items()}
+    part.bind({k: v.to(DEV, dtype) for k, v in cpu.items()})
+    return cpu
+
+
+def ctx_for(dtype, hidden, positions=None):
+    from toyinfer_b200.parts import BuildContext
+    c = BuildContext(dtype=dtype, device=torch.device(DEV), hidden_size=hidden)
+    c.positions.update(positions or {})
+    return c
+
+
+def batch_for(mode, slots, starts, news, scratch):
+    L = lib()
+    buf = L["BatchBuffers"](len(slots), sum(news), DEV)
+    return L["fill_batch"](buf, mode, slots, starts, [[0] * n for n in news], scratch, 4096)
+
+
+def rmode(dtype):
+    return None if dtype == torch.float32 else torch.bfloat16
+
+
+def tol(dtype):
+    return dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=6e-3)
+
+
+DT = [torch.float32, torch.bfloat16]
+
+
+# ---------------------------------------------------------------------------
+# the shipped parts, one at a time
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DT)
+def test_norm_part(dtype):
+    from toyinfer_b200.parts import PartSpec, build_part
+    n = build_part("norm", PartSpec("rmsnorm", {"size": 72, "eps": 1e-5}), ctx_for(dtype, 72), "x.")
+    w = bind_random(n, 1, dtype)["x.weight"]
+    g = torch.Generator().manual_seed(0)
+    h = torch.randn(5, 72, generator=g).to(dtype)
+    d = torch.randn(5, 72, generator=g).to(dtype)
+    torch.testing.assert_close(n.forward(h.to(DEV)).cpu().double(), plain.rms_norm(h.double(), w, 1e-5, rmode(dtype)), **tol(dtype))
+    hd = h.to(DEV).clone()
+    y = n.add_forward(hd, d.to(DEV))
+    hs = plain.rnd(h.double() + d.double(), rmode(dtype))
+    torch.testing.assert_close(hd.cpu().double(), hs, **tol(dtype))
+    torch.testing.assert_close(y.cpu().double(), plain.rms_norm(hs, w, 1e-5, rmode(dtype)), **tol(dtype))
+
+
+def test_position_part_tables():
+    from toyinfer_b200.parts import PartSpec, build_part
+    p = build_part("position", PartSpec("rotary_half", {"dim": 48, "theta": 5e5, "max_positions": 300}),
+                   ctx_for(torch.float32, 8), "")
+    cos, sin, dim = p.rotary_tables()
+    ang = plain.rope_angles(48, 5e5, range(300))
+    assert dim == 48 and cos.shape == (300, 24)
+    torch.testing.assert_close(cos.cpu().double(), torch.cos(ang), rtol=0, atol=1e-7)
+    torch.testing.assert_close(sin.cpu().double(), torch.sin(ang), rtol=0, atol=1e-7)
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_feed_forward_part(dtype):
+    from toyinfer_b200.parts import PartSpec, build_part
+    f = build_part("feed_forward", PartSpec("swiglu", {"intermediate_size": 200}), ctx_for(dtype, 96), "m.")
+    w = bind_random(f, 2, dtype)
+    x = torch.randn(7, 96, generator=torch.Generator().manual_seed(3)).to(dtype)
+    got = f.forward(x.to(DEV), None).cpu().double()
+    r = rmode(dtype)
+    gate, up = plain.linear(x.double(), w["m.gate_proj.weight"], r), plain.linear(x.double(), w["m.up_proj.weight"], r)
+    want = plain.linear(plain.swiglu(gate, up, r), w["m.down_proj.weight"], r)
+    torch.testing.assert_close(got, want, **tol(dtype))
+
+
+def plain_attention_layer(x, w, p, nh, nkv, hd, eps, theta, window, r, positions=None, rope_fn=None):
+    T = x.shape[0]
+    q = plain.linear(x, w[p + "q_proj.weight"], r).view(T, nh, hd)
+    k = plain.linear(x, w[p + "k_proj.weight"], r).view(T, nkv, hd)
+    v = plain.linear(x, w[p + "v_proj.weight"], r).view(T, nkv, hd)
+    q, k = plain.rms_norm(q, w[p + "q_norm.weight"], eps, r), plain.rms_norm(k, w[p + "k_norm.weight"], eps, r)
+    if rope_fn is None:
+        ang = plain.rope_angles(hd, theta, range(T))
+        q, k = plain.rope(q, ang, r), plain.rope(k, ang, r)
+    else:
+        q, k = rope_fn(q), rope_fn(k)
+    a = plain.attention(q, k, v, 1 / math.sqrt(hd), window, r)
+    return plain.linear(a.reshape(T, nh * hd), w[p + "o_proj.weight"], r), (k, v)
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (5, 1, 48, 40), (4, 2, 64, 0)])
+def test_attention_mixer_alone(dtype, nh, nkv, hd, window):
+    """The mixer with memory from a cache manager: a whole prompt, then tokens one by one."""
+    from toyinfer_b200.cache import CacheManager
+    from toyinfer_b200.parts import PartSpec, build_part
+    H, eps, theta, n, extra = 80, 1e-6, 1e4, 70, 6
+    ctx = ctx_for(dtype, H)
+    ctx.positions["rope"] = build_part("position", PartSpec("rotary_half", {"dim": hd, "theta": theta, "max_positions": 256}), ctx, "")
+    m = build_part("mixer", PartSpec("gqa_attention", {"n_heads": nh, "n_kv_heads": nkv, "head_dim": hd,
+                                                        "qk_norm_eps": eps, "position": "rope", "window": window}), ctx, "a.")
+    w = bind_random(m, 4, dtype)
+    cache = CacheManager([m.memory_request()], 64 * 8, 3, 256, dtype, DEV)
+    x = torch.randn(n + extra, H, generator=torch.Generator().manual_seed(5)).to(dtype)
+    want, _ = plain_attention_layer(x.double(), w, "a.", nh, nkv, hd, eps, theta, window, rmode(dtype))
+    cache.allocate_slot()                     # slot 0 stays empty; the sequence lives in slot 1
+    s = cache.allocate_slot()
+    cache.reserve(s, n)
+    cache.flush()
+    got = m.forward(x[:n].to(DEV), batch_for("start", [s], [0], [n], cache.scratch_slot), cache.view(0), {})
+    torch.testing.assert_close(got.cpu().double(), want[:n], **tol(dtype))
+    cache.commit(s, n)
+    for t in range(n, n + extra):
+        cache.reserve(s, t + 1)
+        cache.flush()
+        got = m.forward(x[t:t + 1].to(DEV), batch_for("extend", [s], [t], [1], cache.scratch_slot), cache.view(0), {})
+        torch.testing.assert_close(got.cpu().double(), want[t:t + 1], **tol(dtype))
+        cache.commit(s, t + 1)
+
+
+# ---------------------------------------------------------------------------
+# toy parts defined here, not in the library
+# ---------------------------------------------------------------------------
+def make_toy_parts():
+    import toyinfer_b200.kernels as K
+    from toyinfer_b200.parts import FeedForward, Mixer, ParamSpec, PositionEncoding, StateRequest, register_part
+
+    class DecayMixer(Mixer):
+        """state <- decay * state + W x;  y = state.  A state of its own per sequence."""
+
+        def __init__(self, ctx, prefix, decay):
+            self.h, self.decay, self.name = ctx.hidden_size, float(decay), prefix + "w.weight"
+            self.dtype = ctx.dtype
+
+        def param_specs(self):
+            return {self.name: ParamSpec((self.h, self.h), std=0.1)}
+
+        def bind(self, tensors):
+            self.w = tensors.pop(self.name)
+
+        def memory_request(self):
+            return StateRequest((self.h,), torch.float32)
+
+        def forward(self, x, batch, mem, shared):
+            u = K.linear(x, self.w).float()
+            if batch.mode == "extend":                      # device only: works inside a captured graph
+                idx = batch.seq_slot.long()
+                st = mem.state.index_select(0, idx) * self.decay + u
+                mem.state.index_copy_(0, idx, st)
+                return st.to(self.dtype)
+            out = torch.empty_like(u)
+            o = 0
+            for slot, n in zip(batch.host_slots, batch.host_new):
+                st = mem.state[slot].clone()
+                for t in range(n):
+                    st = st * self.decay + u[o + t]
+                    out[o + t] = st
+                mem.state[slot] = st
+                o += n
+            return out.to(self.dtype)
+
+    class RoutedFF(FeedForward):
+        """Two experts; a router picks one per token (32-bit logits, lower index on ties)."""
+
+        def __init__(self, ctx, prefix, inner):
+            self.h, self.inner, self.p = ctx.hidden_size, inner, prefix
+
+        def param_specs(self):
+            s = {self.p + "router.weight": ParamSpec((2, self.h), std=0.5)}
+            for e in range(2):
+                s[f"{self.p}e{e}.up.weight"] = ParamSpec((self.inner, self.h), std=0.1)
+                s[f"{self.p}e{e}.down.weight"] = ParamSpec((self.h, self.inner), std=0.1)
+            return s
+
+        def bind(self, tensors):
+            self.t = {k: tensors.pop(k) for k in list(self.param_specs())}
+
+        def forward(self, x, batch):
+            logits = K.linear(x, self.t[self.p + "router.weight"], out_dtype=torch.float32)
+            pick = (logits[:, 1] > logits[:, 0])
+            ys = []
+            for e in range(2):
+                hmid = torch.relu(K.linear(x, self.t[f"{self.p}e{e}.up.weight"]).float()).to(x.dtype)
+                ys.append(K.linear(hmid, self.t[f"{self.p}e{e}.down.weight"]))
+            return torch.where(pick[:, None], ys[1], ys[0])
+
+    class PairRotary(PositionEncoding):
+        """Rotates neighbouring pairs (2i, 2i+1) instead of halves; no tables for the fused kernel."""
+
+        def __init__(self, ctx, prefix, dim, theta):
+            i = torch.arange(dim // 2, dtype=torch.float64)
+            self.inv_freq = torch.pow(torch.tensor(theta, dtype=torch.float64), -2 * i / dim).to(ctx.device)
+
+        def apply(self, q, k, tok_pos):
+            ang = tok_pos.double()[:, None] * self.inv_freq[None, :]
+            c, s = torch.cos(ang).float()[:, None, :], torch.sin(ang).float()[:, None, :]
+            for t in (q, k):
+                a, b = t[..., 0::2].float(), t[..., 1::2].float()
+                t[..., 0::2] = (a * c - b * s).to(t.dtype)
+                t[..., 1::2] = (b * c + a * s).to(t.dtype)
+
+    for fam, kind, cls in (("mixer", "toy_decay", DecayMixer), ("feed_forward", "toy_routed", RoutedFF),
+                           ("position", "toy_pair_rotary", PairRotary)):
+        register_part(fam, kind, cls, replace=True)
+
+
+def pair_rope_plain(x, theta):
+    T, _, d = x.shape
+    i = torch.arange(d // 2, dtype=torch.float64)
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * torch.pow(torch.tensor(theta, dtype=torch.float64), -2 * i / d)
+    c, s = torch.cos(ang).float().double()[:, None, :], torch.sin(ang).float().double()[:, None, :]
+    out = x.clone()
+    a, b = x[..., 0::2], x[..., 1::2]
+    out[..., 0::2] = a * c - b * s
+    out[..., 1::2] = b * c + a * s
+    return out
+
+
+def toy_spec(H=48, V=90):
+    """Three layers: a decay mixer with a routed feed-forward, attention with the toy pair
+    rotation, attention with the shipped rotation and a dense feed-forward."""
+    from toyinfer_b200.parts import PartSpec
+    from toyinfer_b200.parts.model import LayerSpec, ModelSpec
+    norm = PartSpec("rmsnorm", {"size": H, "eps": 1e-5})
+    att = lambda pos: PartSpec("gqa_attention", {"n_heads": 3, "n_kv_heads": 1, "head_dim": 16, "qk_norm_eps": 1e-5, "position": pos})
+    blocks = [
+        PartSpec("prenorm", {"norm": norm, "mixer": PartSpec("toy_decay", {"decay": 0.9}), "feed_forward": PartSpec("toy_routed", {"inner": 40})}),
+        PartSpec("prenorm", {"norm": norm, "mixer": att("pairs"), "feed_forward": PartSpec("swiglu", {"intermediate_size": 56})}),
+        PartSpec("prenorm", {"norm": norm, "mixer": att("halves"), "feed_forward": PartSpec("toy_routed", {"inner": 24})}),
+    ]
+    return ModelSpec(vocab_size=V, hidden_size=H, max_positions=256,
+                     layers=[LayerSpec(f"model.layers.{i}.", b) for i, b in enumerate(blocks)], final_norm=norm,
+                     positions={"pairs": PartSpec("toy_pair_rotary", {"dim": 16, "theta": 1e4}),
+                                "halves": PartSpec("rotary_half", {"dim": 16, "theta": 1e4, "max_positions": 256})},
+                     tie_head=True)
+
+
+def toy_plain_forward(w, ids, H=48):
+    """The same three layers from plain parts, float64, whole sequence."""
+    eps = 1e-5
+    h = plain.embedding(w["model.embed_tokens.weight"], ids)
+    T = len(ids)
+
+    def routed(x, p, inner):
+        logits = (x @ w[p + "router.weight"].double().T).float()
+        pick = logits[:, 1] > logits[:, 0]
+        ys = [torch.relu(x @ w[f"{p}e{e}.up.weight"].double().T) @ w[f"{p}e{e}.down.weight"].double().T for e in range(2)]
+        return torch.where(pick[:, None], ys[1], ys[0])
+
+    # layer 0
+    p = "model.layers.0."
+    x = plain.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+    u = x @ w[p + "self_attn.w.weight"].double().T
+    st, rows = torch.zeros(H, dtype=torch.float64), []
+    for t in range(T):
+        st = st * 0.9 + u[t]
+        rows.append(st)
+    h = h + torch.stack(rows)
+    h = h + routed(plain.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps), p + "mlp.", 40)
+    # layers 1 and 2
+    for layer, rope_fn in ((1, lambda t: pair_rope_plain(t, 1e4)), (2, None)):
+        p = f"model.layers.{layer}."
+        x = plain.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+        a, _ = plain_attention_layer(x, w, p + "self_attn.", 3, 1, 16, eps, 1e4, 0, None, rope_fn=rope_fn)
+        h = h + a
+        x = plain.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
+        if layer == 1:
+            m = plain.linear(plain.swiglu(plain.linear(x, w[p + "mlp.gate_proj.weight"]), plain.linear(x, w[p + "mlp.up_proj.weight"])),
+                             w[p + "mlp.down_proj.weight"])
+        else:
+            m = routed(x, p + "mlp.", 24)
+        h = h + m
+    return plain.linear(plain.rms_norm(h, w["model.norm.weight"], eps), w["model.embed_tokens.weight"])
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_toy_parts_register_build_and_step(graph):
+    """A mixer with a state, a routed feed-forward and another position encoding, all defined
+    in this file: whole prompts, token by token, unequal batches, slots used again."""
+    from toyinfer_b200.engine import Engine
+    from toyinfer_b200.parts.model import DecoderModel
+    make_toy_parts()
+    model = DecoderModel(toy_spec(), torch.float32, DEV)
+    w = bind_random(model, 7, torch.float32)
+    reqs = model.memory_requests()
+    assert type(reqs[0]).__name__ == "StateRequest" and type(reqs[1]).__name__ == "KVRequest"
+    eng = Engine(model, max_tokens=64 * 6, max_batch=4, max_seq_len=256, use_cuda_graph=graph)
+    g = torch.Generator().manual_seed(8)
+    for round_ in range(3):
+        lens, dec = [9, 30, 2], [5, 2, 7]
+        seqs = [torch.randint(0, 90, (n + d,), generator=g).tolist() for n, d in zip(lens, dec)]
+        want = [toy_plain_forward(w, s) for s in seqs]
+        slots = [eng.new_sequence() for _ in seqs]
+        logits = eng.step([(sl, s[:n]) for sl, s, n in zip(slots, seqs, lens)], None).clone()
+        for i, n in enumerate(lens):
+            torch.testing.assert_close(logits[i].cpu().double(), want[i][n - 1], rtol=1e-4, atol=1e-5)
+        live, t = [0, 1, 2], 0
+        while live:
+            logits = eng.step([(slots[i], [seqs[i][lens[i] + t]]) for i in live], None).clone()
+            for row, i in enumerate(live):
+                torch.testing.assert_close(logits[row].cpu().double(), want[i][lens[i] + t], rtol=1e-4, atol=1e-5)
+            t += 1
+            for i in [i for i in live if t >= dec[i]]:
+                eng.end_sequence(slots[i])          # its state must not leak into the slot's next user
+            live = [i for i in live if t < dec[i]]
+    if graph:
+        assert eng.graph_replays > 0
+
+
+# ---------------------------------------------------------------------------
+# the order of layers is data
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DT)
+def test_schedule_names_a_layer_twice_and_borrows_a_cache(dtype):
+    """Layers A, B and C (C has no keys and values of its own).  Schedule: A, B, B again
+    (same weights, a cache of its own), C reading the cache of the first B."""
+    from toyinfer_b200.engine import Engine
+    from toyinfer_b200.parts import PartSpec
+    from toyinfer_b200.parts.model import DecoderModel, LayerSpec, ModelSpec, ScheduleEntry
+    H, nh, nkv, hd, eps, theta, V = 64, 4, 2, 16, 1e-6, 1e4, 100
+    norm = PartSpec("rmsnorm", {"size": H, "eps": eps})
+    ffn = PartSpec("swiglu", {"intermediate_size": 72})
+    att = lambda own: PartSpec("gqa_attention", {"n_heads": nh, "n_kv_heads": nkv, "head_dim": hd, "qk_norm_eps": eps,
+                                                 "position": "rope", "own_kv": own})
+    layers = [LayerSpec(f"model.layers.{i}.", PartSpec("prenorm", {"norm": norm, "mixer": att(i < 2), "feed_forward": ffn}))
+              for i in range(3)]
+    schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1), ScheduleEntry(2, memory_of=1)]
+    spec = ModelSpec(vocab_size=V, hidden_size=H, max_positions=128, layers=layers, final_norm=norm, schedule=schedule,
+                     positions={"rope": PartSpec("rotary_half", {"dim": hd, "theta": theta, "max_positions": 128})},
+                     tie_head=False)
+    model = DecoderModel(spec, dtype, DEV)
+    w = bind_random(model, 9, dtype)
+    assert "model.layers.2.self_attn.k_proj.weight" not in w
+    eng = Engine(model, max_tokens=64 * 4, max_batch=2, max_seq_len=128)
+    assert len(eng.cache.kv_groups) == 1 and eng.cache.kv_groups[0].entries == [0, 1, 2]
+    r = rmode(dtype)
+
+    def plain_forward(ids):
+        h = plain.rnd(plain.embedding(w["model.embed_tokens.weight"], ids), r)
+        kept = {}
+        for e, ent in enumerate(schedule):
+            p = f"model.layers.{ent.layer}."
+            x = plain.rms_norm(h, w[p + "input_layernorm.weight"], eps, r)
+            if ent.memory_of is None:
+                a, kept[e] = plain_attention_layer(x, w, p + "self_attn.", nh, nkv, hd, eps, theta, 0, r)
+            else:
+                T = x.shape[0]
+                q = plain.linear(x, w[p + "self_attn.q_proj.weight"], r).view(T, nh, hd)
+                q = plain.rope(plain.rms_norm(q, w[p + "self_attn.q_norm.weight"], eps, r), plain.rope_angles(hd, theta, range(T)), r)
+                k, v = kept[ent.memory_of]
+                a = plain.linear(plain.attention(q, k, v, 1 / math.sqrt(hd), 0, r).reshape(T, nh * hd), w[p + "self_attn.o_proj.weight"], r)
+            h = plain.rnd(h + a, r)
+            x = plain.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps, r)
+            m = plain.linear(plain.swiglu(plain.linear(x, w[p + "mlp.gate_proj.weight"], r), plain.linear(x, w[p + "mlp.up_proj.weight"], r), r),
+                             w[p + "mlp.down_proj.weight"], r)
+            h = plain.rnd(h + m, r)
+        return plain.linear(plain.rms_norm(h, w["model.norm.weight"], eps, r), w["lm_head.weight"])
+
+    from helpers import assert_logits_close
+    name = "float32" if dtype == torch.float32 else "bfloat16"
+    g = torch.Generator().manual_seed(10)
+    seqs = [torch.randint(0, V, (n,), generator=g).tolist() for n in (40, 75)]
+    want = [plain_forward(s) for s in seqs]
+    slots = [eng.new_sequence() for _ in seqs]
+    heads = [30, 70]
+    logits = eng.step([(sl, s[:n]) for sl, s, n in zip(slots, seqs, heads)], [list(range(n)) for n in heads])
+    assert_logits_close(logits, torch.cat([want[0][:30], want[1][:70]]), name, "schedule, whole")
+    for t in range(5):
+        logits = eng.step([(slots[i], [seqs[i][heads[i] + t]]) for i in range(2)], None).clone()
+        assert_logits_close(logits, torch.stack([want[i][heads[i] + t] for i in range(2)]), name, f"schedule, step {t}")
+
+
+def test_unknown_part_and_bad_schedule_are_refused():
+    from toyinfer_b200.parts import PartSpec
+    from toyinfer_b200.parts.model import DecoderModel, LayerSpec, ModelSpec, ScheduleEntry
+    norm = PartSpec("rmsnorm", {"size": 32, "eps": 1e-5})
+    blk = PartSpec("prenorm", {"norm": norm, "mixer": PartSpec("no_such_mixer", {}), "feed_forward": PartSpec("swiglu", {"intermediate_size": 8})})
+    with pytest.raises(ValueError) as e:
+        DecoderModel(ModelSpec(10, 32, 64, [LayerSpec("l.", blk)], norm), torch.float32, DEV)
+    assert "no_such_mixer" in str(e.value) and "gqa_attention" in str(e.value)
+    ok = PartSpec("prenorm", {"norm": norm, "mixer": PartSpec("gqa_attention", {"n_heads": 2, "n_kv_heads": 1, "head_dim": 16}),
+                              "feed_forward": PartSpec("swiglu", {"intermediate_size": 8})})
+    with pytest.raises(ValueError):
+        DecoderModel(ModelSpec(10, 32, 64, [LayerSpec("l.", ok)], norm, schedule=[ScheduleEntry(0, memory_of=0)]), torch.float32, DEV)
+    with pytest.raises(ValueError):
+        DecoderModel(ModelSpec(10, 32, 64, [LayerSpec("l.", ok)], norm, schedule=[ScheduleEntry(3)]), torch.float32, DEV)
+EOF
+echo done
