@@ -417,5 +417,3 @@ def test_unknown_part_and_bad_schedule_are_refused():
         DecoderModel(ModelSpec(10, 32, 64, [LayerSpec("l.", ok)], norm, schedule=[ScheduleEntry(0, memory_of=0)]), torch.float32, DEV)
     with pytest.raises(ValueError):
         DecoderModel(ModelSpec(10, 32, 64, [LayerSpec("l.", ok)], norm, schedule=[ScheduleEntry(3)]), torch.float32, DEV)
-EOF
-echo done
