@@ -228,7 +228,7 @@ def make_toy_parts():
             ang = tok_pos.double()[:, None] * self.inv_freq[None, :]
             c, s = torch.cos(ang).float()[:, None, :], torch.sin(ang).float()[:, None, :]
             for t in (q, k):
-                a, b = t[..., 0::2].float(), t[..., 1::2].float()
+                a, b = t[..., 0::2].float().clone(), t[..., 1::2].float().clone()
                 t[..., 0::2] = (a * c - b * s).to(t.dtype)
                 t[..., 1::2] = (b * c + a * s).to(t.dtype)
 
