@@ -41,10 +41,14 @@ def linear(x, w, out_dtype=None):
     return (x.float() @ w.float().T).to(out_dtype or x.dtype)
 
 
-def swiglu(gu):
+def swiglu(gu, pairs=False):
     i = gu.shape[1] // 2
-    g, u = gu[:, :i].float(), gu[:, i:].float()
+    g, u = (gu[:, 0::2].float(), gu[:, 1::2].float()) if pairs else (gu[:, :i].float(), gu[:, i:].float())
     return (u * (g / (1.0 + torch.exp(-g)))).to(gu.dtype)
+
+
+def linear_swiglu(x, w_pairs):
+    return swiglu(linear(x, w_pairs), pairs=True)
 
 
 def _norm_heads(x, w, eps):
@@ -133,6 +137,6 @@ def argmax(logits):
 
 
 def install(monkeypatch) -> None:
-    for name in ("embed", "rmsnorm", "add_rmsnorm", "gather_add", "linear", "swiglu", "qk_norm_rope_store",
+    for name in ("embed", "rmsnorm", "add_rmsnorm", "gather_add", "linear", "swiglu", "linear_swiglu", "qk_norm_rope_store",
                  "attention_prefill", "attention_decode", "argmax"):
         monkeypatch.setattr(K, name, globals()[name])

@@ -111,6 +111,29 @@ def test_swiglu(K, dtype, M, I):
     torch.testing.assert_close(got.cpu().double(), want, **tol(dtype))
 
 
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("M,I,K_", [(1, 128, 64), (8, 9728, 2560), (5, 200, 96), (70, 144, 80), (300, 1000, 264), (3, 50, 100)])
+def test_linear_swiglu(K, dtype, M, I, K_):
+    """Gate and up rows side by side in one matrix; the activation in the product's epilogue
+    (tensor-core shapes) or in a kernel after it (the rest)."""
+    x = randn(M, K_, seed=27).to(dtype)
+    wg = randn(I, K_, seed=28, scale=0.08).to(dtype)
+    wu = randn(I, K_, seed=29, scale=0.08).to(dtype)
+    w = torch.stack([wg, wu], dim=1).reshape(2 * I, K_).contiguous()
+    got = K.linear_swiglu(dev(x), dev(w)).cpu().double()
+    K.check_status()
+    r = rnd_mode(dtype)
+    want = plain.swiglu(plain.linear(x.double(), wg, r), plain.linear(x.double(), wu, r), r)
+    if dtype == torch.float32:
+        torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
+    else:
+        torch.testing.assert_close(got, want, rtol=3e-2, atol=4e-3)
+    pairs = dev(torch.stack([wg @ x.T, wu @ x.T], dim=1).permute(2, 0, 1).reshape(M, 2 * I).contiguous().to(dtype))
+    got2 = K.swiglu(pairs, pairs=True).cpu().double()
+    want2 = plain.swiglu(pairs.cpu().double()[:, 0::2], pairs.cpu().double()[:, 1::2], r)
+    torch.testing.assert_close(got2, want2, **tol(dtype))
+
+
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("M,N,K_", [(1, 64, 64), (3, 200, 96), (8, 384, 100), (13, 130, 258), (17, 300, 72),

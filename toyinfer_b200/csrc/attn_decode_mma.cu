@@ -47,8 +47,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
         mbar_fence_init();
     }
     __syncthreads();
-    ti_pdl_sync();      // everything above touched only this block's shared memory
 
+    // What is read before ti_pdl_sync() below does not depend on the kernel just before this
+    // one: the step's lengths, slots and page table were uploaded before the step's first
+    // kernel, and cache lines of positions before the newest were written in earlier steps.
     const int b = blockIdx.x, split = blockIdx.z;
     const int g = a.n_heads / a.n_kv_heads;
     const int groups = (g + 15) / 16;
@@ -81,8 +83,17 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
             tma_load_2d(dst + TILE_BYTES + bx * (TILE * 128), &v_map, bx * 64, y, bar);
         }
     };
+    // The tile that holds the newest position is being written by the kernel before this one;
+    // every other tile may be requested right away, while that kernel still runs.
+    const int newest_tile = (L - 1) / TILE;
+    unsigned early = 0;
     if (t == 0)
-        for (int i = 0; i < STAGES - 1 && i < my_n; i++) issue(i);
+        for (int i = 0; i < STAGES - 1 && i < my_n; i++)
+            if (my_lo + i != newest_tile) { issue(i); early |= 1u << i; }
+    ti_pdl_sync();
+    if (t == 0)
+        for (int i = 0; i < STAGES - 1 && i < my_n; i++)
+            if (!((early >> i) & 1u)) issue(i);
 
     // the queries as A fragments: row lane/4 (and +8) is a query head, zero beyond `rows`
     uint32_t qf[KSTEPS][4];

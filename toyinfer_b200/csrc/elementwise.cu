@@ -214,6 +214,17 @@ extern "C" int ti_gather_add(const void* h, const void* delta, const int* rows, 
 // ---------------------------------------------------------------------------
 // SwiGLU: gu[m, 0:I] = gate, gu[m, I:2I] = up; out[m, i] = up * gate / (1 + exp(-gate))
 // ---------------------------------------------------------------------------
+// gu[m, 2i] = gate_i, gu[m, 2i + 1] = up_i
+template <typename T>
+__global__ void swiglu_pairs_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, long long total) {
+    ti_pdl_sync();
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const float g = to_f32(gu[2 * idx]), u = to_f32(gu[2 * idx + 1]);
+        out[idx] = from_f32<T>(u * (g / (1.0f + expf(-g))));
+    }
+}
+
 template <typename T, int V>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, long long total_vecs) {
     ti_pdl_sync();
@@ -231,13 +242,20 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
 }
 
-extern "C" int ti_swiglu(const void* gu, void* out, int M, int I, int dtype, cudaStream_t stream) {
+extern "C" int ti_swiglu(const void* gu, void* out, int M, int I, int pairs, int dtype, cudaStream_t stream) {
     if (M == 0) return 0;
     TI_REQUIRE(M > 0 && I > 0, "swiglu: bad sizes M=%d I=%d", M, I);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         constexpr int V = vec_width<T>();
         const int threads = 256;
+        if (pairs) {
+            const long long n = (long long)M * I;
+            const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+            TI_CUDA(ti_launch(swiglu_pairs_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu, (T*)out, I, n));
+            TI_CHECK_LAUNCH("swiglu");
+            return 0;
+        }
         if (I % V == 0 && aligned16(gu) && aligned16(out)) {
             const long long n = (long long)M * (I / V);
             const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);

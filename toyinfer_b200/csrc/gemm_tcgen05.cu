@@ -33,6 +33,7 @@ struct GemmArgs {
     int rows_a, rows_b, K;
     void* out; long long ld_out; int out_f32; int transposed;
     int splits; float* workspace; int* tickets;
+    int gated;      // rows of the weight operand come in (gate, up) pairs: store up * silu(gate), half as many columns
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------
@@ -132,12 +133,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    ti_pdl_sync();      // barriers and tensor memory are set up; from here on global memory is touched
+    // The weights are constant, so their tiles for the first stages are requested now, while
+    // the kernel before this one may still be running; only the activations have to wait.
+    const int n_pre = min(STAGES, n_iter);
+    const bool weights_are_a = g.transposed != 0;
+    if (warp == 0 && lane == 0) {
+        for (int it = 0; it < n_pre; it++) {
+            unsigned char* sa = smem + (size_t)it * (A_BYTES + B_BYTES);
+            mbar_expect_tx(&full[it], A_BYTES + B_BYTES);
+            if (weights_are_a) tma_load_2d(sa, &a_map, (kb0 + it) * BK, a0, &full[it]);
+            else tma_load_2d(sa + A_BYTES, &b_map, (kb0 + it) * BK, b0, &full[it]);
+        }
+    }
+    ti_pdl_sync();      // from here on memory written by earlier kernels may be read
 
     if (warp == 0) {
         // ---- TMA producer
         if (lane == 0) {
-            for (int it = 0; it < n_iter; it++) {
+            for (int it = 0; it < n_pre; it++) {
+                unsigned char* sa = smem + (size_t)it * (A_BYTES + B_BYTES);
+                if (weights_are_a) tma_load_2d(sa + A_BYTES, &b_map, (kb0 + it) * BK, b0, &full[it]);
+                else tma_load_2d(sa, &a_map, (kb0 + it) * BK, a0, &full[it]);
+            }
+            for (int it = n_pre; it < n_iter; it++) {
                 const int s = it % STAGES;
                 if (!mbar_wait(&empty[s], (uint32_t)(((it / STAGES) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); break; }
                 unsigned char* sa = smem + (size_t)s * (A_BYTES + B_BYTES);
@@ -219,7 +237,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
 #pragma unroll
                     for (int e = 0; e < 16; e++) r[e] = 0.f;
                 }
-                if (i < g.rows_a) {
+                if (g.gated) {
+                    // gate and up are neighbours along the weight operand's rows; both are rounded to
+                    // the storage type first, as if the product had been stored (src/decode.cu:756-762)
+                    if (g.transposed) {
+                        // neighbours are lanes 2n and 2n+1: the even lane stores column i / 2
+#pragma unroll
+                        for (int e = 0; e < 16; e++) {
+                            const float mine = __bfloat162float(__float2bfloat16_rn(r[e]));
+                            const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+                            const int j = b0 + c + e;
+                            if ((lane & 1) == 0 && i < g.rows_a && j < g.rows_b)
+                                ((bf16*)g.out)[(size_t)j * g.ld_out + (i >> 1)] =
+                                    __float2bfloat16_rn(other * (mine / (1.0f + expf(-mine))));
+                        }
+                    } else if (i < g.rows_a) {
+                        const int j0 = b0 + c;
+                        bf16* o = (bf16*)g.out + (size_t)i * g.ld_out + (j0 >> 1);
+                        uint32_t pk[4];
+                        float z[8];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) {
+                            const float gate = __bfloat162float(__float2bfloat16_rn(r[2 * e]));
+                            const float up = __bfloat162float(__float2bfloat16_rn(r[2 * e + 1]));
+                            z[e] = up * (gate / (1.0f + expf(-gate)));
+                        }
+                        if (j0 + 16 <= g.rows_b && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                __nv_bfloat162 v = __floats2bfloat162_rn(z[2 * e], z[2 * e + 1]);
+                                pk[e] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                            *reinterpret_cast<uint4*>(o) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; e++) if (j0 + 2 * e + 1 < g.rows_b) o[e] = __float2bfloat16_rn(z[e]);
+                        }
+                    }
+                } else if (i < g.rows_a) {
                     if (g.transposed) {
                         // out[j, i]: the warp's lanes are consecutive i, so each j is one coalesced store
 #pragma unroll
@@ -345,10 +400,11 @@ extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* b
 }
 
 // x[M, K] (row stride ldx), w[N, K] (row stride ldw), both bfloat16; out[M, N] bfloat16 or
-// float32 with row stride ldo.  `workspace` (float32) and `tickets` (int32, zero before the
+// float32 with row stride ldo.  With `gated`, w's rows are (gate_0, up_0, gate_1, up_1, ...) and
+// out is [M, N / 2] = up * gate / (1 + exp(-gate)).  `workspace` (float32) and `tickets` (int32, zero before the
 // first use, left zero) as planned by ti_linear_tc_plan; tickets needs n_tiles entries.
 extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
-                            long long ldw, long long ldo, int out_f32, int sms, float* workspace, int* tickets,
+                            long long ldw, long long ldo, int out_f32, int gated, int sms, float* workspace, int* tickets,
                             cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     TI_REQUIRE(M > 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
@@ -363,6 +419,8 @@ extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int 
     g.rows_a = swap ? N : M; g.rows_b = swap ? M : N; g.K = K;
     g.out = out; g.ld_out = ldo; g.out_f32 = out_f32; g.transposed = swap;
     g.splits = splits; g.workspace = workspace; g.tickets = tickets;
+    g.gated = gated;
+    TI_REQUIRE(!gated || (N % 2 == 0 && !out_f32), "linear (tcgen05): a gated product needs an even number of weight rows and a bfloat16 result");
     CUtensorMap am, bm;
     if (int rc = operand_map(swap ? w : x, g.rows_a, K, swap ? ldw : ldx, BM, &am)) return rc;
     if (int rc = operand_map(swap ? x : w, g.rows_b, K, swap ? ldx : ldw, bn, &bm)) return rc;

@@ -147,14 +147,36 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     return out
 
 
-def swiglu(gu: torch.Tensor) -> torch.Tensor:
+def swiglu(gu: torch.Tensor, pairs: bool = False) -> torch.Tensor:
+    """up * gate / (1 + exp(-gate)).  gu[M, 2*I] holds gate in its first I columns and up in
+    the rest, or with ``pairs`` gate_i and up_i side by side."""
     _need_cuda(gu, what="swiglu")
     M, two_i = gu.shape
     if two_i % 2 or not gu.is_contiguous():
         raise KernelError("swiglu: expected a dense [M, 2*I] tensor")
     out = torch.empty((M, two_i // 2), dtype=gu.dtype, device=gu.device)
-    _call(library().ti_swiglu, _ptr(gu), _ptr(out), M, two_i // 2, _code(gu, "swiglu"), _stream())
+    _call(library().ti_swiglu, _ptr(gu), _ptr(out), M, two_i // 2, 1 if pairs else 0, _code(gu, "swiglu"), _stream())
     return out
+
+
+def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor) -> torch.Tensor:
+    """x[M, K] times w_pairs[2*I, K] (rows gate_0, up_0, gate_1, up_1, ...) followed by the
+    gated activation -> [M, I].  The activation runs in the product's epilogue where the
+    tensor-core kernel takes the shape, else as a kernel of its own."""
+    _need_cuda(x, w_pairs, what="linear_swiglu")
+    if x.dim() != 2 or w_pairs.dim() != 2 or x.shape[1] != w_pairs.shape[1] or w_pairs.shape[0] % 2:
+        raise KernelError(f"linear_swiglu: shapes {tuple(x.shape)} and {tuple(w_pairs.shape)} do not fit")
+    if x.dtype != w_pairs.dtype:
+        raise KernelError(f"linear_swiglu: activations are {x.dtype} but the weight is {w_pairs.dtype}")
+    from . import gemm
+    M, K = x.shape
+    N = w_pairs.shape[0]
+    ldx, ldw = _row_stride(x, "linear x"), _row_stride(w_pairs, "linear w")
+    if gemm.tc_eligible(x, w_pairs, K, ldx, ldw):
+        out = torch.empty((M, N // 2), dtype=x.dtype, device=x.device)
+        gemm.run(x, w_pairs, out, M, N, K, ldx, ldw, gated=True)
+        return out
+    return swiglu(linear(x, w_pairs), pairs=True)
 
 
 def qk_norm_rope_store(q, k, v, q_w, k_w, eps, tables, batch, mem) -> None:

@@ -29,7 +29,8 @@ def tc_eligible(x, w, K, ldx, ldw) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def run(x, w, out, M, N, K, ldx, ldw) -> None:
+def run(x, w, out, M, N, K, ldx, ldw, gated: bool = False) -> None:
+    """``gated``: only for shapes the tensor-core kernel takes (see tc_eligible)."""
     lib = library()
     out_f32 = 1 if (out.dtype == torch.float32 and x.dtype != torch.float32) else 0
     if tc_eligible(x, w, K, ldx, ldw):
@@ -43,8 +44,10 @@ def run(x, w, out, M, N, K, ldx, ldw) -> None:
             tickets = _tickets_for(x.device)
             if n_tiles.value > tickets.numel():
                 raise RuntimeError("linear: more split tiles than tickets")
-        _call(lib.ti_linear_tc, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, SM_COUNT,
+        _call(lib.ti_linear_tc, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, 1 if gated else 0, SM_COUNT,
               _ptr(workspace), _ptr(tickets), _stream())
         return
+    if gated:
+        raise RuntimeError("linear: the gated epilogue exists in the tensor-core kernel only")
     _call(lib.ti_linear_simt, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0),
           _code(x, "linear"), out_f32, _stream())

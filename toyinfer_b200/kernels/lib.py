@@ -22,7 +22,7 @@ def _declare(lib) -> None:
         "ti_embed": [P, P, P, I, I, I, I, P],
         "ti_rmsnorm": [P, P, P, P, I, I, L, F, I, I, P],
         "ti_gather_add": [P, P, P, P, I, I, I, I, P],
-        "ti_swiglu": [P, P, I, I, I, P],
+        "ti_swiglu": [P, P, I, I, I, I, P],
         "ti_linear_simt": [P, P, P, I, I, I, L, L, L, I, I, P],
         "ti_qk_norm_rope_store": [P, P, P, L, L, L, I, I, I, P, P, I, F, P, P, I, I, P, P, P, P,
                                   P, P, P, I, I, I, I, I, I, P],
@@ -30,7 +30,7 @@ def _declare(lib) -> None:
         "ti_attn_decode_simt": [P, L, P, P, P, I, I, I, I, P, P, I, I, I, I, F, I, I, P, L, P, P, I, P],
         "ti_attn_decode_mma": [P, L, P, P, P, I, I, I, I, P, P, I, I, I, I, F, I, I, P, L, P, P, I, P],
         "ti_attn_prefill_mma": [P, P, P, P, L, L, L, L, P, I, I, I, I, I, I, F, I, P],
-        "ti_linear_tc": [P, P, P, I, I, I, L, L, L, I, I, P, P, P],
+        "ti_linear_tc": [P, P, P, I, I, I, L, L, L, I, I, I, P, P, P],
         "ti_linear_tc_plan": [I, I, I, I, P, P, P, P, P],
         "ti_read_status": [P],
         "ti_argmax": [P, L, I, I, P, P],

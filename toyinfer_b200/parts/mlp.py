@@ -3,7 +3,8 @@
 gate = Wg x, up = Wu x, z = up * gate / (1 + exp(-gate)) with the activation and the
 product in 32-bit and one rounding, y = Wd z; no bias.  Reference:
 src/transformer.cpp:597-617 (order), src/decode.cu:746-764 (activation).  Gate and
-up rows are kept in one matrix so that one product makes both.
+up rows are kept in one matrix, row 2i the gate's and row 2i+1 the up's i-th, so that one
+product makes both and the activation can run in that product's epilogue.
 """
 from __future__ import annotations
 
@@ -36,13 +37,12 @@ class SwiGLU(FeedForward):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         g = tensors.pop(self.names["gate"])
         u = tensors.pop(self.names["up"])
-        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        self.w_gate_up = torch.stack([g, u], dim=1).reshape(2 * self.inter, self.hidden).contiguous()
         del g, u
         self.w_down = tensors.pop(self.names["down"]).contiguous()
 
     def forward(self, x, batch) -> torch.Tensor:
-        gu = K.linear(x, self.w_gate_up)          # [M, 2*inter]: gate | up
-        z = K.swiglu(gu)                          # [M, inter]
+        z = K.linear_swiglu(x, self.w_gate_up)    # [M, inter]
         return K.linear(z, self.w_down)
 
 
