@@ -190,3 +190,51 @@ extern "C" int ti_attn_decode_simt(const void* q, long long q_stride, const void
     a.part_o = part_o; a.part_ml = part_ml;
     return ti_dispatch_dtype(dtype, [&](auto t) -> int { return launch<decltype(t)>(a, n_seq, stream); });
 }
+
+// ---------------------------------------------------------------------------
+// The same kernels with their scratch inside the library (see attn_decode_noalloc.h).
+// ---------------------------------------------------------------------------
+#include "attn_decode_noalloc.h"
+
+// Partial outputs first, then the (maximum, sum) pairs.  In host code this name is only a
+// handle for the runtime; the address kernels can use comes from cudaGetSymbolAddress.
+static __device__ __align__(256) float g_noalloc_scratch[TI_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+float* g_noalloc_ptr[64] = {nullptr};   // per device, looked up at the first call on it
+
+int noalloc_scratch(float** out) {
+    int dev = 0;
+    TI_CUDA(cudaGetDevice(&dev));
+    TI_REQUIRE(dev >= 0 && dev < 64, "attention_decode (no allocation): device %d out of range", dev);
+    if (!g_noalloc_ptr[dev]) {
+        float* p = nullptr;
+        TI_CUDA(cudaGetSymbolAddress((void**)&p, g_noalloc_scratch));
+        TI_REQUIRE(p != nullptr, "attention_decode (no allocation): the scratch array has no device address");
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return 0;
+}
+}  // namespace
+
+extern "C" int ti_attn_decode_noalloc(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                      const int* page_table, int table_width, int page_size, int ring_rows,
+                                      int n_pages, const int* seq_slot, const int* seq_len, int n_seq,
+                                      int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                      int n_splits, void* out, long long o_stride, int dtype, cudaStream_t stream) {
+    if (n_seq == 0) return 0;
+    TI_REQUIRE(n_seq > 0 && n_heads > 0 && head_dim > 0 && n_splits >= 1, "attention_decode (no allocation): bad sizes");
+    const long long need = (long long)n_seq * n_heads * n_splits * (head_dim + 2);
+    TI_REQUIRE(need <= (long long)TI_NOALLOC_SCRATCH_FLOATS,
+               "attention_decode (no allocation): %d sequences x %d heads x %d splits x head size %d need %lld floats of "
+               "scratch, the library holds %d; use fewer splits or sequences per call, or the entry point that takes scratch",
+               n_seq, n_heads, n_splits, head_dim, need, TI_NOALLOC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    if (int rc = noalloc_scratch(&scratch)) return rc;
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)n_seq * n_heads * n_splits * head_dim;
+    return ti_attn_decode_simt(q, q_stride, k_pages, v_pages, page_table, table_width, page_size, ring_rows, n_pages,
+                               seq_slot, seq_len, n_seq, n_heads, n_kv_heads, head_dim, scale, window, n_splits, out,
+                               o_stride, part_o, part_ml, dtype, stream);
+}
