@@ -241,8 +241,10 @@ def run_ours(args):
 # one kernel at a time, at the sizes of one layer of the benchmark model
 # ---------------------------------------------------------------------------
 def run_kernel(name: str, reps: int):
-    """Times one kernel on a small case (a few launches, CUDA events, L2 flushed in between by
-    writing 256 MB) and reports its rate against the roofline.  Small enough to sit under ncu."""
+    """Times one kernel on a small case and reports its rate against the roofline.  Launches run
+    back to back over several sets of operands that together exceed the L2 (126 MB), so every
+    launch reads from memory; the time is the CUDA-event total divided by the launches.  Small
+    enough to sit under ncu."""
     import math
     import torch
     import toyinfer_b200.kernels as K
@@ -252,64 +254,57 @@ def run_kernel(name: str, reps: int):
     pk = peaks()
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(0)
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    H, I, QKV = 2560, 9728, 6144
+    H, I = 2560, 9728
 
     def rnd(*shape, scale=1.0):
         return (torch.randn(*shape, generator=g, device=dev) * scale).to(torch.bfloat16)
 
-    if name in ("gemm_decode", "gemm_decode_b64", "gemm_prefill", "gemm_head"):
-        M = {"gemm_decode": 8, "gemm_decode_b64": 64, "gemm_prefill": 2048, "gemm_head": 8}[name]
-        N = 151936 if name == "gemm_head" else 2 * I
-        x, w = rnd(M, H), rnd(N, H, scale=0.02)
-        fn = lambda: K.linear(x, w)
-        nbytes, flops = (N * H + M * H + M * N) * 2, 2.0 * M * N * H
-    elif name == "gemm_down":
-        x, w = rnd(8, I), rnd(H, I, scale=0.02)
-        fn = lambda: K.linear(x, w)
-        nbytes, flops = (H * I + 8 * I + 8 * H) * 2, 2.0 * 8 * H * I
-    elif name in ("attn_decode", "attn_decode_b64"):
-        B, ctx = (8, 8192) if name == "attn_decode" else (64, 2048)
-        nh, nkv, hd = 32, 8, 128
-        pages = B * ctx // 64
-        mem = KVView(rnd(pages + 1, nkv, 64, hd), rnd(pages + 1, nkv, 64, hd),
-                     (torch.arange(B * (ctx // 64), dtype=torch.int32, device=dev).view(B, ctx // 64) + 1).contiguous(),
-                     nkv, hd, 0, 0)
-        mem.page_table = torch.cat([mem.page_table, torch.zeros(1, ctx // 64, dtype=torch.int32, device=dev)])
-        buf = BatchBuffers(B, B, dev)
-        batch = fill_batch(buf, "extend", list(range(B)), [ctx - 1] * B, [[0]] * B, B, ctx)
-        q = rnd(B, nh, hd)
-        fn = lambda: K.attention_decode(q, mem, 1 / math.sqrt(hd), 0, batch)
-        nbytes, flops = 2 * B * ctx * nkv * hd * 2, 4.0 * B * ctx * nh * hd
-    elif name == "attn_prefill":
-        T, nh, nkv, hd = PREFILL_TOKENS, 32, 8, 128
-        qkv = rnd(T, (nh + 2 * nkv) * hd)
-        q = qkv[:, :nh * hd].view(T, nh, hd)
-        k = qkv[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
-        v = qkv[:, (nh + nkv) * hd:].view(T, nkv, hd)
-        buf = BatchBuffers(1, T, dev)
-        batch = fill_batch(buf, "start", [0], [0], [[0] * T], 1, T)
-        fn = lambda: K.attention_prefill(q, k, v, 1 / math.sqrt(hd), 0, batch)
-        nbytes, flops = qkv.numel() * 2 + T * nh * hd * 2, 4.0 * nh * hd * T * (T + 1) / 2
-    else:
+    def make():
+        if name in ("gemm_decode", "gemm_decode_b64", "gemm_prefill", "gemm_head", "gemm_down", "gemm_qkv", "gemm_o"):
+            M = {"gemm_decode_b64": 64, "gemm_prefill": 2048}.get(name, 8)
+            N, Kd = {"gemm_head": (151936, H), "gemm_down": (H, I), "gemm_qkv": (6144, H), "gemm_o": (H, 4096)}.get(name, (2 * I, H))
+            x, w = rnd(M, Kd), rnd(N, Kd, scale=0.02)
+            return (lambda: K.linear(x, w)), (N * Kd + M * Kd + M * N) * 2, 2.0 * M * N * Kd
+        if name in ("attn_decode", "attn_decode_b64", "attn_decode_b1"):
+            B, ctx = {"attn_decode": (8, 8192), "attn_decode_b64": (64, 2048), "attn_decode_b1": (1, 2048)}[name]
+            nh, nkv, hd = 32, 8, 128
+            pages = B * ctx // 64
+            table = (torch.arange(pages, dtype=torch.int32, device=dev).view(B, ctx // 64) + 1)
+            table = torch.cat([table, torch.zeros(1, ctx // 64, dtype=torch.int32, device=dev)]).contiguous()
+            mem = KVView(rnd(pages + 1, nkv, 64, hd), rnd(pages + 1, nkv, 64, hd), table, nkv, hd, 0, 0)
+            batch = fill_batch(BatchBuffers(B, B, dev), "extend", list(range(B)), [ctx - 1] * B, [[0]] * B, B, ctx)
+            q = rnd(B, nh, hd)
+            return (lambda: K.attention_decode(q, mem, 1 / math.sqrt(hd), 0, batch)), 2 * B * ctx * nkv * hd * 2, 4.0 * B * ctx * nh * hd
+        if name == "attn_prefill":
+            T, nh, nkv, hd = PREFILL_TOKENS, 32, 8, 128
+            qkv = rnd(T, (nh + 2 * nkv) * hd)
+            q = qkv[:, :nh * hd].view(T, nh, hd)
+            k = qkv[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
+            v = qkv[:, (nh + nkv) * hd:].view(T, nkv, hd)
+            batch = fill_batch(BatchBuffers(1, T, dev), "start", [0], [0], [[0] * T], 1, T)
+            return (lambda: K.attention_prefill(q, k, v, 1 / math.sqrt(hd), 0, batch)), qkv.numel() * 2 + T * nh * hd * 2, \
+                4.0 * nh * hd * T * (T + 1) / 2
         raise SystemExit(f"unknown kernel case {name!r}")
-    for _ in range(2):
-        fn()
-    times = []
+
+    fn, nbytes, flops = make()
+    sets = [fn]
+    while len(sets) * nbytes < 400e6 and len(sets) < 16:
+        sets.append(make()[0])
+    for f in sets:
+        f()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
     for _ in range(reps):
-        flush.fill_(1)
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn()
-        b.record()
-        torch.cuda.synchronize()
-        times.append(a.elapsed_time(b))
+        for f in sets:
+            f()
+    b.record()
+    torch.cuda.synchronize()
     K.check_status()
-    ms = statistics.median(times)
+    ms = a.elapsed_time(b) / (reps * len(sets))
     return {"kernel": name, "ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1), "tflops": round(flops / ms / 1e9, 1),
             "hbm_frac": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4), "tensor_frac": round(flops / ms / 1e9 / pk["bf16_tflops"], 4),
-            "peaks": pk["source"], "reps": reps, "l2": "flushed between launches"}
+            "peaks": pk["source"], "launches": reps * len(sets), "operand_sets": len(sets)}
 
 
 def main() -> int:
@@ -323,8 +318,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the named configuration (reported)")
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
-                    "gemm_head, gemm_prefill, attn_decode, attn_decode_b64, attn_prefill")
-    ap.add_argument("--reps", type=int, default=5)
+                    "gemm_qkv, gemm_o, gemm_head, gemm_prefill, attn_decode, attn_decode_b64, attn_decode_b1, attn_prefill")
+    ap.add_argument("--reps", type=int, default=20)
     args = ap.parse_args()
     if args.kernel:
         print(json.dumps(run_kernel(args.kernel, args.reps)))
