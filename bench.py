@@ -242,9 +242,9 @@ def run_ours(args):
 # ---------------------------------------------------------------------------
 def run_kernel(name: str, reps: int):
     """Times one kernel on a small case and reports its rate against the roofline.  Launches run
-    back to back over several sets of operands that together exceed the L2 (126 MB), so every
-    launch reads from memory; the time is the CUDA-event total divided by the launches.  Small
-    enough to sit under ncu."""
+    back to back (replayed from a CUDA graph) over several sets of operands that together exceed
+    the L2 (126 MB), so every launch reads from memory; the time is the CUDA-event total divided
+    by the launches.  Small enough to sit under ncu."""
     import math
     import torch
     import toyinfer_b200.kernels as K
@@ -293,11 +293,18 @@ def run_kernel(name: str, reps: int):
     for f in sets:
         f()
     torch.cuda.synchronize()
+    # one pass over the sets captured into a CUDA graph, as decode steps are in serving: the
+    # host's launch rate (tens of microseconds per call from Python) stays out of the number
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for f in sets:
+            f()
+    graph.replay()
+    torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(reps):
-        for f in sets:
-            f()
+        graph.replay()
     b.record()
     torch.cuda.synchronize()
     K.check_status()
