@@ -240,7 +240,7 @@ def run_ours(args):
 # ---------------------------------------------------------------------------
 # one kernel at a time, at the sizes of one layer of the benchmark model
 # ---------------------------------------------------------------------------
-def run_kernel(name: str, reps: int):
+def run_kernel(name: str, reps: int, eager: bool = False):
     """Times one kernel on a small case and reports its rate against the roofline.  Launches run
     back to back (replayed from a CUDA graph) over several sets of operands that together exceed
     the L2 (126 MB), so every launch reads from memory; the time is the CUDA-event total divided
@@ -295,10 +295,17 @@ def run_kernel(name: str, reps: int):
     torch.cuda.synchronize()
     # one pass over the sets captured into a CUDA graph, as decode steps are in serving: the
     # host's launch rate (tens of microseconds per call from Python) stays out of the number
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        for f in sets:
-            f()
+    if eager:                      # plain launches (for a profiler that wants to see each one)
+        class _Eager:
+            def replay(self):
+                for f in sets:
+                    f()
+        graph = _Eager()
+    else:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for f in sets:
+                f()
     graph.replay()
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -327,9 +334,10 @@ def main() -> int:
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
                     "gemm_qkv, gemm_o, gemm_head, gemm_prefill, attn_decode, attn_decode_b64, attn_decode_b1, attn_prefill")
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--eager", action="store_true", help="with --kernel: plain launches instead of a graph replay")
     args = ap.parse_args()
     if args.kernel:
-        print(json.dumps(run_kernel(args.kernel, args.reps)))
+        print(json.dumps(run_kernel(args.kernel, args.reps, args.eager)))
         return 0
     if args.impl == "reference":
         print(json.dumps({"impl": "reference",

@@ -23,6 +23,7 @@ template <typename T>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            T* __restrict__ out, long long o_stride, int n_heads, int hd,
                                            int n_splits) {
+    ti_pdl_trigger();
     ti_pdl_sync();
     const int b = blockIdx.x, h = blockIdx.y;
     const size_t base = ((size_t)b * n_heads + h) * n_splits;

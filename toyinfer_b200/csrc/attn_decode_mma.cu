@@ -33,6 +33,7 @@ template <int HD>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                        tiattn::DecodeArgs a, int* status) {
+    ti_pdl_trigger();
     constexpr int TILE_BYTES = TILE * HD * 2;          // one of K or V
     constexpr int KSTEPS = HD / 16, NT = HD / 8;
     extern __shared__ __align__(1024) unsigned char smem_raw[];

@@ -23,6 +23,7 @@ constexpr int TILE = 64, THREADS = 128, MAXACC = 32;
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS) attn_decode_kernel(DecodeArgs a) {
+    ti_pdl_trigger();
     extern __shared__ float sm[];
     ti_pdl_sync();
     const int hd = a.hd, ld = hd + 1;

@@ -32,6 +32,7 @@ template <int HD>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                         const __grid_constant__ CUtensorMap v_map, PrefillArgs a, int* status) {
+    ti_pdl_trigger();
     constexpr int TILE_BYTES = BKV * HD * 2;
     constexpr int KSTEPS = HD / 16, NT = HD / 8;
     extern __shared__ __align__(1024) unsigned char smem_raw[];

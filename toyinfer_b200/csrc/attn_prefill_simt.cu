@@ -24,6 +24,7 @@ attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* _
                     T* __restrict__ out, long long q_stride, long long k_stride, long long v_stride,
                     long long o_stride, const int* __restrict__ cu_new, int n_heads, int n_kv_heads,
                     int hd, float scale, int window) {
+    ti_pdl_trigger();
     extern __shared__ float sm[];
     ti_pdl_sync();
     const int ld = hd + 1;

@@ -89,10 +89,16 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // Programmatic dependent launch: a kernel may be scheduled while the kernel before it in the
 // stream still runs, so that its launch latency and set-up overlap that kernel's tail.  It
 // must not touch global memory before `ti_pdl_sync()`, which waits until the earlier kernels
-// have finished and their writes are visible, and then allows the next kernel to be scheduled.
+// have finished and their writes are visible.
 // Without the launch attribute both instructions do nothing.
 __device__ __forceinline__ void ti_pdl_sync() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Called first thing in every kernel: the next kernel in the stream may be scheduled as soon as
+// all blocks of this one have started.  It still waits (ti_pdl_sync) for this kernel to finish
+// before it reads anything this kernel or an earlier one wrote, so several kernels can sit on the
+// SMs at once, each with its set-up done and its constant operands on the way.
+__device__ __forceinline__ void ti_pdl_trigger() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 

@@ -65,6 +65,7 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 template <typename T, int V>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              T* __restrict__ out, int H, int vocab) {
+    ti_pdl_trigger();
     ti_pdl_sync();
     const int m = blockIdx.x;
     const int id = ids[m];
@@ -108,6 +109,7 @@ template <typename T, typename W, int V, bool ADD>
 __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
                                const W* __restrict__ w, T* __restrict__ out, int H,
                                long long x_stride, float eps) {
+    ti_pdl_trigger();
     __shared__ float red[33];
     ti_pdl_sync();
     const size_t row = blockIdx.x;
@@ -185,6 +187,7 @@ extern "C" int ti_rmsnorm(void* x, const void* delta, const void* w, void* out, 
 template <typename T>
 __global__ void gather_add_kernel(const T* __restrict__ h, const T* __restrict__ delta,
                                   const int* __restrict__ rows, T* __restrict__ out, int H, int M) {
+    ti_pdl_trigger();
     ti_pdl_sync();
     const int r = blockIdx.x;
     const int src = rows[r];
@@ -217,6 +220,7 @@ extern "C" int ti_gather_add(const void* h, const void* delta, const int* rows, 
 // gu[m, 2i] = gate_i, gu[m, 2i + 1] = up_i
 template <typename T>
 __global__ void swiglu_pairs_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, long long total) {
+    ti_pdl_trigger();
     ti_pdl_sync();
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -227,6 +231,7 @@ __global__ void swiglu_pairs_kernel(const T* __restrict__ gu, T* __restrict__ ou
 
 template <typename T, int V>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, long long total_vecs) {
+    ti_pdl_trigger();
     ti_pdl_sync();
     const int per_row = I / V;
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_vecs;

@@ -22,6 +22,7 @@ template <typename T, typename OT>
 __global__ void __launch_bounds__(TILE_THREADS)
 gemm_tile_kernel(const T* __restrict__ X, const T* __restrict__ W, OT* __restrict__ out,
                  int M, int N, int K, long long ldx, long long ldw, long long ldo) {
+    ti_pdl_trigger();
     __shared__ float As[BK][BM + PAD];
     __shared__ float Bs[BK][BN + PAD];
     ti_pdl_sync();
@@ -87,6 +88,7 @@ template <typename T, typename OT, int V>
 __global__ void __launch_bounds__(GV_THREADS)
 gemv_rows_kernel(const T* __restrict__ X, const T* __restrict__ W, OT* __restrict__ out,
                  int M, int N, int K, long long ldx, long long ldw, long long ldo) {
+    ti_pdl_trigger();
     ti_pdl_sync();
     const int lane = threadIdx.x & 31;
     const int warp = (blockIdx.x * GV_THREADS + threadIdx.x) >> 5;

@@ -89,20 +89,21 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
-// Narrow tiles (few tokens, the weights stream) keep four stages so that three blocks share
-// an SM: what matters there is how many bytes the whole device has in flight, and blocks
-// that are resident together even out the grid's last wave.  Wide tiles take the SM alone.
+// Narrow tiles (few tokens, the weights stream) keep five stages so that two blocks share an
+// SM: a grid of about one block per SM then leaves room for the next kernel's blocks, which
+// request their weights while this kernel is still running.  Wide tiles take the SM alone.
 template <int BN> constexpr int stages_for() {
     constexpr int per = BM * BK * 2 + BN * BK * 2;
     constexpr int n = (200 * 1024) / per;
-    return BN <= 64 ? 4 : (n > 8 ? 8 : n);
+    return BN <= 64 ? 5 : (n > 8 ? 8 : n);
 }
-template <int BN> constexpr int blocks_per_sm() { return BN <= 64 ? 3 : 1; }
+template <int BN> constexpr int blocks_per_sm() { return BN <= 64 ? 2 : 1; }
 
 template <int BN>
 __global__ void __launch_bounds__(THREADS, blocks_per_sm<BN>())
 gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                GemmArgs g, int* status) {
+    ti_pdl_trigger();
     constexpr int STAGES = stages_for<BN>();
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
@@ -383,7 +384,7 @@ extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* b
     const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + b - 1) / b);
     const int nkb = (K + BK - 1) / BK;
     int sp = 1;
-    const int want = sw ? 2 * sms : sms;      // narrow tiles run three to an SM, two rounds balance well
+    const int want = sms;
     if (tiles < want) {
         sp = (want + tiles / 2) / tiles;
         if (sp < 1) sp = 1;

@@ -29,6 +29,7 @@ struct RopeStoreArgs {
 
 template <typename T>
 __global__ void rope_store_kernel(RopeStoreArgs a) {
+    ti_pdl_trigger();
     ti_pdl_sync();
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;

@@ -68,6 +68,7 @@ __device__ V block_exclusive_scan(V v, V* total, V* sm /* 33 entries */) {
 
 __global__ void __launch_bounds__(SB) argmax_kernel(const float* __restrict__ logits, long long ld, int V,
                                                     int* __restrict__ out) {
+    ti_pdl_trigger();
     __shared__ float bv[32];
     __shared__ int bi[32];
     ti_pdl_sync();
@@ -111,6 +112,7 @@ struct SampleArgs {
 // top_k in [1, MAXK], top_k < V.  Keeps exactly top_k entries (ties at the k-th value
 // go to the lowest indices), then applies top_p on the sorted list.
 __global__ void __launch_bounds__(SB) sample_topk_kernel(SampleArgs a) {
+    ti_pdl_trigger();
     __shared__ int hist[256];
     __shared__ float cval[MAXK];
     __shared__ int cidx[MAXK];
@@ -230,6 +232,7 @@ __global__ void __launch_bounds__(SB) sample_topk_kernel(SampleArgs a) {
 
 // whole vocabulary, no top-k, no top-p: first index whose running probability exceeds u
 __global__ void __launch_bounds__(SB) sample_full_kernel(SampleArgs a) {
+    ti_pdl_trigger();
     __shared__ float red[33];
     __shared__ float scan_f[33];
     __shared__ int s_owner;
