@@ -29,6 +29,12 @@ constexpr int TILE = 64, THREADS = 128, STAGES = 3;
 template <int HD>
 __device__ __forceinline__ uint32_t tile_offset(int row, int d) { return swizzled_offset<TILE>(row, d); }
 
+__device__ __forceinline__ float ex2(float x) {      // 2^x, the hardware's approximation (2 ulp)
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
@@ -115,20 +121,18 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
     for (int n = 0; n < NT; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // rows lane/4 and lane/4 + 8
 
+    // Scores are kept in base-2 units: exp(x * scale - m) = 2^(x * scale * log2(e) - m2), one
+    // multiply-add and one ex2 per element.
+    const float scale2 = a.scale * 1.4426950408889634f;
+    const bool upper = rows > 8;        // rows lane/4 + 8 are real query heads, not padding
     for (int i = 0; i < my_n; i++) {
         const int stage = i % STAGES;
         if (t == 0 && i + STAGES - 1 < my_n) issue(i + STAGES - 1);   // its stage was drained in iteration i-1
         if (!mbar_wait(&full[stage], (uint32_t)((i / STAGES) & 1))) {
+            // the data never came: note it, work on whatever the buffer holds (shared memory only)
+            // and leave at the barrier below, where every thread sees the flag
             ti_report(status, TI_STATUS_TMA_WAIT);
             s_abort = 1;
-        }
-        __syncthreads();
-        if (s_abort) {            // uniform: every thread sees the flag after the barrier
-            // give the loads still in flight a bounded time to land before the block's shared
-            // memory is released, then leave without a result
-            if (t == 0)
-                for (int j = i; j < my_n && j < i + STAGES; j++) mbar_wait(&full[j % STAGES], (uint32_t)((j / STAGES) & 1));
-            return;
         }
         const uint32_t kbase = smem_u32(smem + (size_t)stage * 2 * TILE_BYTES);
         const uint32_t vbase = kbase + TILE_BYTES;
@@ -147,18 +151,27 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
             __syncwarp();
         }
 
-        // S = Q K^T for 16 positions: two n-tiles of 8
+        // S = Q K^T for 16 positions: two n-tiles of 8, even and odd K steps summed separately
+        // so that four chains of dependent MMAs run instead of two
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         {
+            float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
             const int mid = lane >> 3, rr = lane & 7;
             const int key = key0 + (mid >> 1) * 8 + rr;
 #pragma unroll
-            for (int ks = 0; ks < KSTEPS; ks++) {
-                uint32_t b0, b1, b2, b3;
+            for (int ks = 0; ks < KSTEPS; ks += 2) {
+                uint32_t b0, b1, b2, b3, c0, c1, c2, c3;
                 ldmatrix_x4(b0, b1, b2, b3, kbase + tile_offset<HD>(key, ks * 16 + (mid & 1) * 8));
+                ldmatrix_x4(c0, c1, c2, c3, kbase + tile_offset<HD>(key, (ks + 1) * 16 + (mid & 1) * 8));
                 mma_bf16(s[0], qf[ks], b0, b1);
                 mma_bf16(s[1], qf[ks], b2, b3);
+                mma_bf16(s2[0], qf[ks + 1], c0, c1);
+                mma_bf16(s2[1], qf[ks + 1], c2, c3);
             }
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) s[nt][e] += s2[nt][e];
         }
         // scale, mask, online softmax (rows lane/4 and lane/4 + 8; columns are positions)
         float mx[2] = {-INFINITY, -INFINITY};
@@ -168,7 +181,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
             for (int e = 0; e < 4; e++) {
                 const int p = p0 + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                 const bool ok = !edge || (p >= lo && p < L);
-                s[nt][e] = ok ? s[nt][e] * a.scale : -INFINITY;
+                s[nt][e] = ok ? s[nt][e] * scale2 : -INFINITY;
                 mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
             }
         float alpha[2];
@@ -177,17 +190,19 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
             const float m_new = fmaxf(m_run[r], mx[r]);
-            alpha[r] = m_new > -INFINITY ? expf(m_run[r] - m_new) : 1.f;
+            alpha[r] = (m_new > -INFINITY && m_new != m_run[r]) ? ex2(m_run[r] - m_new) : 1.f;
             m_run[r] = m_new;
         }
         uint32_t pf[4];
         {
             float p[2][4];
 #pragma unroll
-            for (int nt = 0; nt < 2; nt++)
-#pragma unroll
-                for (int e = 0; e < 4; e++)
-                    p[nt][e] = m_run[e >> 1] > -INFINITY ? expf(s[nt][e] - m_run[e >> 1]) : 0.f;
+            for (int nt = 0; nt < 2; nt++) {
+                p[nt][0] = m_run[0] > -INFINITY ? ex2(s[nt][0] - m_run[0]) : 0.f;
+                p[nt][1] = m_run[0] > -INFINITY ? ex2(s[nt][1] - m_run[0]) : 0.f;
+                p[nt][2] = (upper && m_run[1] > -INFINITY) ? ex2(s[nt][2] - m_run[1]) : 0.f;
+                p[nt][3] = (upper && m_run[1] > -INFINITY) ? ex2(s[nt][3] - m_run[1]) : 0.f;
+            }
             l_run[0] = l_run[0] * alpha[0] + p[0][0] + p[0][1] + p[1][0] + p[1][1];   // this thread's share of the row
             l_run[1] = l_run[1] * alpha[1] + p[0][2] + p[0][3] + p[1][2] + p[1][3];
             pf[0] = pack_bf16(p[0][0], p[0][1]);
@@ -195,18 +210,21 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
             pf[2] = pack_bf16(p[1][0], p[1][1]);
             pf[3] = pack_bf16(p[1][2], p[1][3]);
         }
-        // O = O * alpha + P V
+        // O = O * alpha + P V; the rescaling is skipped while no row's maximum moved
         {
+            const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
             const int mid = lane >> 3, rr = lane & 7;
             const int key = key0 + (mid & 1) * 8 + rr;
 #pragma unroll
             for (int n2 = 0; n2 < NT / 2; n2++) {
                 uint32_t b0, b1, b2, b3;
                 ldmatrix_x4_trans(b0, b1, b2, b3, vbase + tile_offset<HD>(key, n2 * 16 + (mid >> 1) * 8));
+                if (rescale) {
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    float(&acc)[4] = o[n2 * 2 + h];
-                    acc[0] *= alpha[0]; acc[1] *= alpha[0]; acc[2] *= alpha[1]; acc[3] *= alpha[1];
+                    for (int h = 0; h < 2; h++) {
+                        float(&acc)[4] = o[n2 * 2 + h];
+                        acc[0] *= alpha[0]; acc[1] *= alpha[0]; acc[2] *= alpha[1]; acc[3] *= alpha[1];
+                    }
                 }
                 mma_bf16(o[n2 * 2], pf, b0, b1);
                 mma_bf16(o[n2 * 2 + 1], pf, b2, b3);
@@ -214,7 +232,17 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
         }
         if (edge) fence_proxy_async();   // this stage was written by threads; a TMA load will overwrite it
         __syncthreads();                 // the stage may be refilled
+        if (s_abort) {
+            // give the loads still in flight a bounded time to land before the block's shared
+            // memory is released, then leave without a result
+            if (t == 0)
+                for (int j = i + 1; j < my_n && j < i + STAGES; j++) mbar_wait(&full[j % STAGES], (uint32_t)((j / STAGES) & 1));
+            return;
+        }
     }
+    // back to natural-log units for the merge
+#pragma unroll
+    for (int r = 0; r < 2; r++) m_run[r] *= 0.6931471805599453f;
 
     // ---- merge the four warps (each holds an online softmax over its own positions)
     __syncthreads();
