@@ -23,6 +23,12 @@
 namespace {
 constexpr int BQ = 64, BKV = 64, THREADS = 128, STAGES = 2;
 
+__device__ __forceinline__ float ex2(float x) {      // 2^x, the hardware's approximation (2 ulp)
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 struct PrefillArgs {
     const int* cu_new; int n_heads, n_kv_heads; float scale; int window;
     void* out; long long o_stride;
@@ -105,16 +111,17 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
     for (int i = 0; i < NT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int qi0 = q0 + warp * 16 + (lane >> 2);       // this thread's rows: qi0 and qi0 + 8
+    // scores in base-2 units: exp(x * scale - m) = 2^(x * scale * log2(e) - m2)
+    const float scale2 = a.scale * 1.4426950408889634f;
 
     for (int i = 0; i < n_tiles; i++) {
         const int stage = i % STAGES;
         if (t == 0 && i + STAGES - 1 < n_tiles) issue(i + STAGES - 1);
-        if (!mbar_wait(&full[stage], (uint32_t)((i / STAGES) & 1))) { ti_report(status, TI_STATUS_TMA_WAIT); s_abort = 1; }
-        __syncthreads();
-        if (s_abort) {
-            if (t == 0)
-                for (int j = i; j < n_tiles && j < i + STAGES; j++) mbar_wait(&full[j % STAGES], (uint32_t)((j / STAGES) & 1));
-            return;
+        if (!mbar_wait(&full[stage], (uint32_t)((i / STAGES) & 1))) {
+            // the data never came: note it, work on whatever the buffer holds (shared memory only)
+            // and leave at the barrier below, where every thread sees the flag
+            ti_report(status, TI_STATUS_TMA_WAIT);
+            s_abort = 1;
         }
         const uint32_t kb = smem_u32(kv_s + (size_t)stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
         const int k0 = (kt_lo + i) * BKV;
@@ -141,7 +148,7 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
         for (int nt = 0; nt < 8; nt++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                float v = s[nt][e] * a.scale;
+                float v = s[nt][e] * scale2;
                 if (edge) {
                     const int kj = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int qi = qi0 + (e >> 1) * 8;
@@ -157,7 +164,7 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
             const float m_new = fmaxf(m_run[r], mx[r]);
-            alpha[r] = m_new > -INFINITY ? expf(m_run[r] - m_new) : 1.f;
+            alpha[r] = (m_new > -INFINITY && m_new != m_run[r]) ? ex2(m_run[r] - m_new) : 1.f;
             m_run[r] = m_new;
         }
         float ls[2] = {0.f, 0.f};
@@ -165,14 +172,16 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
         for (int nt = 0; nt < 8; nt++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const float p = m_run[e >> 1] > -INFINITY ? expf(s[nt][e] - m_run[e >> 1]) : 0.f;
+                const float p = m_run[e >> 1] > -INFINITY ? ex2(s[nt][e] - m_run[e >> 1]) : 0.f;
                 s[nt][e] = p;
                 ls[e >> 1] += p;
             }
         l_run[0] = l_run[0] * alpha[0] + ls[0];
         l_run[1] = l_run[1] * alpha[1] + ls[1];
+        if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {     // some row's maximum moved
 #pragma unroll
-        for (int i2 = 0; i2 < NT; i2++) { o[i2][0] *= alpha[0]; o[i2][1] *= alpha[0]; o[i2][2] *= alpha[1]; o[i2][3] *= alpha[1]; }
+            for (int i2 = 0; i2 < NT; i2++) { o[i2][0] *= alpha[0]; o[i2][1] *= alpha[0]; o[i2][2] *= alpha[1]; o[i2][3] *= alpha[1]; }
+        }
         // O += P V, 16 keys at a time
         {
             const int mid = lane >> 3, rr = lane & 7;
@@ -193,6 +202,11 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
             }
         }
         __syncthreads();    // the stage may be refilled
+        if (s_abort) {
+            if (t == 0)
+                for (int j = i + 1; j < n_tiles && j < i + STAGES; j++) mbar_wait(&full[j % STAGES], (uint32_t)((j / STAGES) & 1));
+            return;
+        }
     }
 
     // normalise and store
