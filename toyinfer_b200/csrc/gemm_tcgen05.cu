@@ -95,9 +95,92 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
 template <int BN> constexpr int stages_for() {
     constexpr int per = BM * BK * 2 + BN * BK * 2;
     constexpr int n = (200 * 1024) / per;
-    return BN <= 64 ? 5 : (n > 8 ? 8 : n);
+    return BN <= 32 ? 5 : BN == 64 ? 4 : (n > 8 ? 8 : n);
 }
 template <int BN> constexpr int blocks_per_sm() { return BN <= 64 ? 2 : 1; }
+
+// Stores 16 consecutive columns (c .. c+15 of the tile that starts at column b0) of row i of D.
+// All lanes of a warp must call it together (the gated, transposed form exchanges values
+// between neighbouring lanes).
+__device__ __forceinline__ void store_chunk(const GemmArgs& g, int i, int b0, int c, float (&r)[16], int lane) {
+    if (g.gated) {
+        // gate and up are neighbours along the weight operand's rows; both are rounded to
+        // the storage type first, as if the product had been stored (src/decode.cu:756-762)
+        if (g.transposed) {
+            // neighbours are lanes 2n and 2n+1: the even lane stores column i / 2
+#pragma unroll
+            for (int e = 0; e < 16; e++) {
+                const float mine = __bfloat162float(__float2bfloat16_rn(r[e]));
+                const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+                const int j = b0 + c + e;
+                if ((lane & 1) == 0 && i < g.rows_a && j < g.rows_b)
+                    ((bf16*)g.out)[(size_t)j * g.ld_out + (i >> 1)] =
+                        __float2bfloat16_rn(other * (mine / (1.0f + expf(-mine))));
+            }
+        } else if (i < g.rows_a) {
+            const int j0 = b0 + c;
+            bf16* o = (bf16*)g.out + (size_t)i * g.ld_out + (j0 >> 1);
+            uint32_t pk[4];
+            float z[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const float gate = __bfloat162float(__float2bfloat16_rn(r[2 * e]));
+                const float up = __bfloat162float(__float2bfloat16_rn(r[2 * e + 1]));
+                z[e] = up * (gate / (1.0f + expf(-gate)));
+            }
+            if (j0 + 16 <= g.rows_b && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(z[2 * e], z[2 * e + 1]);
+                    pk[e] = *reinterpret_cast<uint32_t*>(&v);
+                }
+                *reinterpret_cast<uint4*>(o) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; e++) if (j0 + 2 * e + 1 < g.rows_b) o[e] = __float2bfloat16_rn(z[e]);
+            }
+        }
+    } else if (i < g.rows_a) {
+        if (g.transposed) {
+            // out[j, i]: the warp's lanes are consecutive i, so each j is one coalesced store
+#pragma unroll
+            for (int e = 0; e < 16; e++) {
+                const int j = b0 + c + e;
+                if (j < g.rows_b) {
+                    if (g.out_f32) ((float*)g.out)[(size_t)j * g.ld_out + i] = r[e];
+                    else ((bf16*)g.out)[(size_t)j * g.ld_out + i] = __float2bfloat16_rn(r[e]);
+                }
+            }
+        } else {
+            const int j0 = b0 + c;
+            if (g.out_f32) {
+                float* o = (float*)g.out + (size_t)i * g.ld_out + j0;
+                if (j0 + 16 <= g.rows_b && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                    for (int e = 0; e < 16; e += 4) *reinterpret_cast<float4*>(o + e) = make_float4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; e++) if (j0 + e < g.rows_b) o[e] = r[e];
+                }
+            } else {
+                bf16* o = (bf16*)g.out + (size_t)i * g.ld_out + j0;
+                if (j0 + 16 <= g.rows_b && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+                    uint32_t pk[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        __nv_bfloat162 v = __floats2bfloat162_rn(r[2 * e], r[2 * e + 1]);
+                        pk[e] = *reinterpret_cast<uint32_t*>(&v);
+                    }
+                    *reinterpret_cast<uint4*>(o) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    *reinterpret_cast<uint4*>(o + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; e++) if (j0 + e < g.rows_b) o[e] = __float2bfloat16_rn(r[e]);
+                }
+            }
+        }
+    }
+}
 
 template <int BN>
 __global__ void __launch_bounds__(THREADS, blocks_per_sm<BN>())
@@ -106,7 +189,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
     ti_pdl_trigger();
     constexpr int STAGES = stages_for<BN>();
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t TMEM_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full[STAGES], empty[STAGES], acc_ready;
@@ -238,84 +321,130 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
 #pragma unroll
                     for (int e = 0; e < 16; e++) r[e] = 0.f;
                 }
-                if (g.gated) {
-                    // gate and up are neighbours along the weight operand's rows; both are rounded to
-                    // the storage type first, as if the product had been stored (src/decode.cu:756-762)
-                    if (g.transposed) {
-                        // neighbours are lanes 2n and 2n+1: the even lane stores column i / 2
-#pragma unroll
-                        for (int e = 0; e < 16; e++) {
-                            const float mine = __bfloat162float(__float2bfloat16_rn(r[e]));
-                            const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-                            const int j = b0 + c + e;
-                            if ((lane & 1) == 0 && i < g.rows_a && j < g.rows_b)
-                                ((bf16*)g.out)[(size_t)j * g.ld_out + (i >> 1)] =
-                                    __float2bfloat16_rn(other * (mine / (1.0f + expf(-mine))));
-                        }
-                    } else if (i < g.rows_a) {
-                        const int j0 = b0 + c;
-                        bf16* o = (bf16*)g.out + (size_t)i * g.ld_out + (j0 >> 1);
-                        uint32_t pk[4];
-                        float z[8];
-#pragma unroll
-                        for (int e = 0; e < 8; e++) {
-                            const float gate = __bfloat162float(__float2bfloat16_rn(r[2 * e]));
-                            const float up = __bfloat162float(__float2bfloat16_rn(r[2 * e + 1]));
-                            z[e] = up * (gate / (1.0f + expf(-gate)));
-                        }
-                        if (j0 + 16 <= g.rows_b && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                __nv_bfloat162 v = __floats2bfloat162_rn(z[2 * e], z[2 * e + 1]);
-                                pk[e] = *reinterpret_cast<uint32_t*>(&v);
-                            }
-                            *reinterpret_cast<uint4*>(o) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 8; e++) if (j0 + 2 * e + 1 < g.rows_b) o[e] = __float2bfloat16_rn(z[e]);
-                        }
-                    }
-                } else if (i < g.rows_a) {
-                    if (g.transposed) {
-                        // out[j, i]: the warp's lanes are consecutive i, so each j is one coalesced store
-#pragma unroll
-                        for (int e = 0; e < 16; e++) {
-                            const int j = b0 + c + e;
-                            if (j < g.rows_b) {
-                                if (g.out_f32) ((float*)g.out)[(size_t)j * g.ld_out + i] = r[e];
-                                else ((bf16*)g.out)[(size_t)j * g.ld_out + i] = __float2bfloat16_rn(r[e]);
-                            }
-                        }
-                    } else {
-                        const int j0 = b0 + c;
-                        if (g.out_f32) {
-                            float* o = (float*)g.out + (size_t)i * g.ld_out + j0;
-                            if (j0 + 16 <= g.rows_b && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-                                for (int e = 0; e < 16; e += 4) *reinterpret_cast<float4*>(o + e) = make_float4(r[e], r[e + 1], r[e + 2], r[e + 3]);
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 16; e++) if (j0 + e < g.rows_b) o[e] = r[e];
-                            }
-                        } else {
-                            bf16* o = (bf16*)g.out + (size_t)i * g.ld_out + j0;
-                            if (j0 + 16 <= g.rows_b && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-                                uint32_t pk[8];
-#pragma unroll
-                                for (int e = 0; e < 8; e++) {
-                                    __nv_bfloat162 v = __floats2bfloat162_rn(r[2 * e], r[2 * e + 1]);
-                                    pk[e] = *reinterpret_cast<uint32_t*>(&v);
-                                }
-                                *reinterpret_cast<uint4*>(o) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                                *reinterpret_cast<uint4*>(o + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 16; e++) if (j0 + e < g.rows_b) o[e] = __float2bfloat16_rn(r[e]);
-                            }
-                        }
-                    }
+                store_chunk(g, i, b0, c, r, lane);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Many tokens: one block per SM walks over the output tiles (activations as the 128-row
+// operand, BN weight rows per tile).  Two accumulators in tensor memory: while the epilogue
+// warps read one back and store it, the MMA warp already fills the other, so the tensor
+// cores do not idle during a tile's epilogue.  The TMA ring runs on across tile borders.
+// ---------------------------------------------------------------------------
+template <int BN> constexpr int persistent_stages() {
+    constexpr int per = BM * BK * 2 + BN * BK * 2;
+    constexpr int n = (196 * 1024) / per;
+    return n > 8 ? 8 : n;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
+                          GemmArgs g, int* status) {
+    ti_pdl_trigger();
+    constexpr int STAGES = persistent_stages<BN>();
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr uint32_t ACC_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;   // columns of one accumulator
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_a = (g.rows_a + BM - 1) / BM, tiles_b = (g.rows_b + BN - 1) / BN;
+    const int n_tiles = tiles_a * tiles_b;
+    const int nkb = (g.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tmem_alloc(&tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    ti_pdl_sync();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int a0 = (tile % tiles_a) * BM, b0 = (tile / tiles_a) * BN;   // neighbours share the weight tile
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&empty[s], (uint32_t)(((it / STAGES) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); ok = false; break; }
+                    unsigned char* sa = smem + (size_t)s * (A_BYTES + B_BYTES);
+                    mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                    tma_load_2d(sa, &a_map, kb * BK, a0, &full[s]);
+                    tma_load_2d(sa + A_BYTES, &b_map, kb * BK, b0, &full[s]);
                 }
             }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc<BN>();
+            int it = 0, n = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, n++) {
+                const int buf = n & 1;
+                // the epilogue must have drained this accumulator (its use before last)
+                if (!mbar_wait(&acc_empty[buf], (uint32_t)(((n >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); ok = false; break; }
+                tc_fence_after();
+                const uint32_t acc = tmem + buf * ACC_COLS;
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1))) { ti_report(status, TI_STATUS_TMA_WAIT); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)s * (A_BYTES + B_BYTES));
+                    const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++)
+                        tc_mma_bf16(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(&empty[s]);
+                }
+                if (ok) tc_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        int n = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, n++) {
+            const int buf = n & 1;
+            const int a0 = (tile % tiles_a) * BM, b0 = (tile / tiles_a) * BN;
+            const int i = a0 + q * 32 + lane;
+            if (!mbar_wait(&acc_full[buf], (uint32_t)((n >> 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem + buf * ACC_COLS + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float r[16];
+                tmem_ld16(taddr + c, r);
+                store_chunk(g, i, b0, c, r, lane);
+            }
+            // this warp has read its lanes of the accumulator: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     }
     tc_fence_before();
@@ -370,6 +499,40 @@ int launch(const CUtensorMap& am, const CUtensorMap& bm, const GemmArgs& g, cuda
     TI_CHECK_LAUNCH("linear (tcgen05)");
     return 0;
 }
+template <int BN>
+int launch_persistent(const CUtensorMap& am, const CUtensorMap& bm, const GemmArgs& g, int sms, cudaStream_t stream) {
+    constexpr int STAGES = persistent_stages<BN>();
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        TI_CUDA(cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    int* status = ti_status_ptr();
+    TI_REQUIRE(status != nullptr, "linear: no status word");
+    const int tiles = ((g.rows_a + BM - 1) / BM) * ((g.rows_b + BN - 1) / BN);
+    dim3 grid(tiles < sms ? tiles : sms);
+    TI_CUDA(ti_launch(gemm_tc_persistent_kernel<BN>, grid, dim3(THREADS), smem, stream, am, bm, g, status));
+    TI_CHECK_LAUNCH("linear (tcgen05, persistent)");
+    return 0;
+}
+
+// Weight rows per tile for many tokens: the width whose tiles fill whole rounds of `sms`
+// blocks best, wider tiles being a little more efficient per flop.
+int wide_tile(int rows_a, int rows_b, int sms) {
+    const int cand[4] = {256, 192, 160, 128};
+    const double mma_eff[4] = {1.0, 0.97, 0.95, 0.92};
+    int best = 256;
+    double best_score = -1.0;
+    for (int c = 0; c < 4; c++) {
+        const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + cand[c] - 1) / cand[c]);
+        const int rounds = (tiles + sms - 1) / sms;
+        const double useful = (double)rows_b / (((rows_b + cand[c] - 1) / cand[c]) * (double)cand[c]);
+        const double score = mma_eff[c] * useful * tiles / ((double)rounds * sms);
+        if (score > best_score + 1e-9) { best_score = score; best = cand[c]; }
+    }
+    return best;
+}
 }  // namespace
 
 // Bytes of float32 workspace ti_linear_tc needs for this shape (0: no split), and how it
@@ -380,7 +543,7 @@ extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* b
     const int rows_a = sw ? N : M, rows_b = sw ? M : N;
     int b;
     if (sw) b = rows_b <= 16 ? 16 : rows_b <= 32 ? 32 : 64;
-    else b = rows_b >= 256 ? 256 : rows_b > 64 ? 128 : rows_b > 32 ? 64 : rows_b > 16 ? 32 : 16;
+    else b = rows_b >= 256 ? wide_tile(rows_a, rows_b, sms) : rows_b > 64 ? 128 : rows_b > 32 ? 64 : rows_b > 16 ? 32 : 16;
     const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + b - 1) / b);
     const int nkb = (K + BK - 1) / BK;
     int sp = 1;
@@ -425,11 +588,21 @@ extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int 
     CUtensorMap am, bm;
     if (int rc = operand_map(swap ? w : x, g.rows_a, K, swap ? ldw : ldx, BM, &am)) return rc;
     if (int rc = operand_map(swap ? x : w, g.rows_b, K, swap ? ldx : ldw, bn, &bm)) return rc;
+    if (!swap && splits == 1 && bn >= 128) {
+        switch (bn) {
+            case 128: return launch_persistent<128>(am, bm, g, sms, stream);
+            case 160: return launch_persistent<160>(am, bm, g, sms, stream);
+            case 192: return launch_persistent<192>(am, bm, g, sms, stream);
+            default: return launch_persistent<256>(am, bm, g, sms, stream);
+        }
+    }
     switch (bn) {
         case 16: return launch<16>(am, bm, g, stream);
         case 32: return launch<32>(am, bm, g, stream);
         case 64: return launch<64>(am, bm, g, stream);
         case 128: return launch<128>(am, bm, g, stream);
+        case 160: return launch<160>(am, bm, g, stream);
+        case 192: return launch<192>(am, bm, g, stream);
         default: return launch<256>(am, bm, g, stream);
     }
 }
