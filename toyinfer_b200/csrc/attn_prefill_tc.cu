@@ -1,0 +1,325 @@
+// Causal grouped-query attention over the tokens of one step on the 5th-generation tensor
+// cores: both products of a tile, S = Q K^T and O += P V, are tcgen05 MMAs with their
+// accumulators in tensor memory.  Same contract and formulas as attn_prefill_simt.cu
+// (reference: src/prefill.cu:224-379); head_dim 128, bfloat16.
+//
+// A block owns 128 queries of one head (grid: query tiles from the last to the first, heads,
+// sequences) and walks over key/value tiles of 128 positions; tiles that the causal mask or the
+// window excludes entirely are never loaded.  Roles, 192 threads:
+//   warp 0     TMA: the query tile once, then K and V tiles into a ring of two stages;
+//   warp 1     one lane issues the MMAs: S_{j+1} = Q K_{j+1}^T goes out before O += P_j V_j, into
+//              the other of two score buffers in tensor memory, so the tensor cores work on the
+//              next tile's scores while the softmax warps are busy with this tile's;
+//   warps 2-5  softmax: thread = query row = TMEM lane.  It reads its row of S (a first pass for
+//              the maximum, a second for 2^(s - m)), writes P as bfloat16 into shared memory in
+//              the swizzled K-major layout the second MMA reads, and keeps the running sum.
+// The output accumulator stays in tensor memory for the whole row of tiles.  It is rescaled
+// only when a row's maximum has grown by more than 2^8 since the scale was last fixed (P then
+// holds values up to 256 instead of 1, which float32 sums and bfloat16 products carry without
+// loss); the final division by the running sum makes the result the same.
+// V is stored [position][d]: for the second product that is the "MN-major" form of the B
+// operand, described as such to the MMA instead of being transposed.
+#include "tcgen05.cuh"
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace {
+constexpr int BQ = 128, BKV = 128, THREADS = 192;
+
+struct Args {
+    const int* cu_new; int n_heads, n_kv_heads; float scale; int window;
+    void* out; long long o_stride;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                       const __grid_constant__ CUtensorMap v_map, Args a, int* status) {
+    ti_pdl_trigger();
+    constexpr int Q_BYTES = BQ * HD * 2, KV_BYTES = BKV * HD * 2, P_BYTES = BQ * BKV * 2;
+    constexpr int BOX = 128 * 128;                     // bytes of one [128 rows][64 columns] box
+    constexpr uint32_t S_COLS = BKV, O_COL = 2 * BKV;  // tensor memory: S0 | S1 | O
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* q_s = smem;
+    unsigned char* kv_s = q_s + Q_BYTES;               // stage s: K at kv_s + s * 2 * KV_BYTES, V after it
+    unsigned char* p_s = kv_s + 4 * KV_BYTES;
+    __shared__ uint64_t q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, p_empty;
+    __shared__ uint32_t tmem_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        mbar_init(&q_full, 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1);
+            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
+        }
+        mbar_init(&p_full, 4);
+        mbar_init(&p_empty, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tmem_alloc(&tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    ti_pdl_sync();
+
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int tok0 = a.cu_new[b];
+    const int n = a.cu_new[b + 1] - tok0;
+    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BQ;
+    const bool active = q0 < n;
+    const int kvh = h / (a.n_heads / a.n_kv_heads);
+    const int last_q = min(q0 + BQ, n) - 1;
+    const int kt_lo = a.window > 0 ? max(0, q0 - a.window + 1) / BKV : 0;
+    const int n_tiles = active ? last_q / BKV - kt_lo + 1 : 0;
+
+    if (active && warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&q_full, Q_BYTES);
+#pragma unroll
+            for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(q_s + bx * BOX, &q_map, h * HD + bx * 64, tok0 + q0, &q_full);
+            for (int j = 0; j < n_tiles; j++) {
+                const int s = j & 1;
+                if (!mbar_wait(&kv_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); break; }
+                const int y = tok0 + (kt_lo + j) * BKV;
+                unsigned char* ks = kv_s + (size_t)s * 2 * KV_BYTES;
+                mbar_expect_tx(&k_full[s], KV_BYTES);
+#pragma unroll
+                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + bx * BOX, &k_map, kvh * HD + bx * 64, y, &k_full[s]);
+                mbar_expect_tx(&v_full[s], KV_BYTES);
+#pragma unroll
+                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + KV_BYTES + bx * BOX, &v_map, kvh * HD + bx * 64, y, &v_full[s]);
+            }
+        }
+    } else if (active && warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc_bf16(BKV, false);    // S: N = positions, K tile K-major
+            constexpr uint32_t idesc_o = instr_desc_bf16(HD, true);      // O: N = head elements, V tile MN-major
+            const uint32_t qa = smem_u32(q_s), pa = smem_u32(p_s);
+            auto issue_s = [&](int j) {       // S_j = Q K_j^T into score buffer j & 1
+                const uint32_t ka = smem_u32(kv_s + (size_t)(j & 1) * 2 * KV_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; kk++) {
+                    const uint32_t off = (kk >> 2) * BOX + (kk & 3) * 32;     // 64 columns per box, 32 bytes per step
+                    tc_mma_bf16(tmem + (j & 1) * S_COLS, smem_desc_sw128(qa + off), smem_desc_sw128(ka + off), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(&s_full[j & 1]);
+            };
+            bool ok = mbar_wait(&q_full, 0) && mbar_wait(&k_full[0], 0);
+            if (!ok) ti_report(status, TI_STATUS_TMA_WAIT);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0);
+            }
+            for (int j = 0; j < n_tiles && ok; j++) {
+                if (j + 1 < n_tiles) {
+                    const int sb = (j + 1) & 1, u = (j + 1) >> 1;
+                    if (!mbar_wait(&k_full[sb], (uint32_t)(u & 1)) || !mbar_wait(&s_empty[sb], (uint32_t)((u & 1) ^ 1))) {
+                        ti_report(status, TI_STATUS_TMA_WAIT); ok = false; break;
+                    }
+                    tc_fence_after();
+                    issue_s(j + 1);
+                }
+                if (!mbar_wait(&p_full, (uint32_t)(j & 1)) || !mbar_wait(&v_full[j & 1], (uint32_t)((j >> 1) & 1))) {
+                    ti_report(status, TI_STATUS_PIPE_WAIT); ok = false; break;
+                }
+                tc_fence_after();
+                const uint32_t va = smem_u32(kv_s + (size_t)(j & 1) * 2 * KV_BYTES + KV_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BKV / 16; kk++) {      // 16 positions per step
+                    const uint64_t da = smem_desc_sw128(pa + (kk >> 2) * BOX + (kk & 3) * 32);
+                    const uint64_t db = smem_desc_mn_sw128(va + kk * 16 * 128, BOX);
+                    tc_mma_bf16(tmem + O_COL, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                tc_commit(&kv_empty[j & 1]);     // the stage's K and V have been read
+                tc_commit(&p_empty);             // so has P, and O holds this tile's contribution
+            }
+        }
+    } else if (active) {
+        // ---- softmax: one thread per query row
+        const int qd = warp & 3;
+        const int r = qd * 32 + lane;
+        const int qi = q0 + r;
+        const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
+        const float scale2 = a.scale * 1.4426950408889634f;
+        float m_used = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; j++) {
+            const int sb = j & 1;
+            if (!mbar_wait(&s_full[sb], (uint32_t)((j >> 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int k0 = (kt_lo + j) * BKV;
+            const bool edge = a.window > 0 || k0 + BKV - 1 > q0 + qd * 32 || k0 + BKV > n;
+            const uint32_t s_addr = tmem + sb * S_COLS + lane_base;
+            auto visible = [&](int kj) { return kj <= qi && kj < n && (a.window <= 0 || kj > qi - a.window); };
+            // pass 1: the row's maximum
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; c++) {
+                float v[32];
+                tmem_ld32(s_addr + c * 32, v);
+#pragma unroll
+                for (int e = 0; e < 32; e++) {
+                    const float x = (!edge || visible(k0 + c * 32 + e)) ? v[e] * scale2 : -INFINITY;
+                    mx = fmaxf(mx, x);
+                }
+            }
+            float alpha = 1.f, m_new = m_used;
+            if (mx > m_used + 8.f || (m_used == -INFINITY && mx > -INFINITY)) {
+                m_new = mx;
+                alpha = ex2(m_used - m_new);        // 0 when nothing was visible before
+            }
+            // P's buffer and O are free once the previous tile's second product has finished
+            if (j > 0 && !mbar_wait(&p_empty, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; c++) {
+                    float o[32];
+                    tmem_ld32(tmem + O_COL + lane_base + c * 32, o);
+#pragma unroll
+                    for (int e = 0; e < 32; e++) o[e] *= alpha;
+                    tmem_st32(tmem + O_COL + lane_base + c * 32, o);
+                }
+            }
+            // pass 2: P = 2^(s - m) as bfloat16 into shared memory, row r, 16-byte chunk cc at cc ^ (r % 8)
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; c++) {
+                float v[32];
+                tmem_ld32(s_addr + c * 32, v);
+                uint32_t pk[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const bool ok0 = m_new > -INFINITY && (!edge || visible(k0 + c * 32 + e));
+                    const bool ok1 = m_new > -INFINITY && (!edge || visible(k0 + c * 32 + e + 1));
+                    const float p0 = ok0 ? ex2(v[e] * scale2 - m_new) : 0.f;
+                    const float p1 = ok1 ? ex2(v[e + 1] * scale2 - m_new) : 0.f;
+                    sum += p0 + p1;
+                    __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+                    pk[e >> 1] = *reinterpret_cast<uint32_t*>(&t);
+                }
+#pragma unroll
+                for (int t4 = 0; t4 < 4; t4++) {
+                    const int cc = c * 4 + t4;               // chunk of 8 positions within the tile
+                    unsigned char* dst = p_s + (cc >> 3) * BOX + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(pk[t4 * 4], pk[t4 * 4 + 1], pk[t4 * 4 + 2], pk[t4 * 4 + 3]);
+                }
+            }
+            l_run = l_run * alpha + sum;
+            m_used = m_new;
+            // the score buffer may be overwritten, and P (with O rescaled) is ready for the second product
+            tc_fence_before();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&s_empty[sb]); mbar_arrive(&p_full); }
+        }
+        if (ok && n_tiles > 0) {
+            if (!mbar_wait(&p_empty, (uint32_t)((n_tiles - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            bf16* orow = (bf16*)a.out + (size_t)(tok0 + qi) * a.o_stride + (size_t)h * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; c++) {
+                float o[32];
+                tmem_ld32(tmem + O_COL + lane_base + c * 32, o);
+                if (qi < n) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        __nv_bfloat162 t = __floats2bfloat162_rn(o[e] * inv, o[e + 1] * inv);
+                        pk[e >> 1] = *reinterpret_cast<uint32_t*>(&t);
+                    }
+#pragma unroll
+                    for (int t4 = 0; t4 < 4; t4++)
+                        *reinterpret_cast<uint4*>(orow + c * 32 + t4 * 8) = make_uint4(pk[t4 * 4], pk[t4 * 4 + 1], pk[t4 * 4 + 2], pk[t4 * 4 + 3]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+struct MapKey {
+    const void* ptr; long long rows, cols, stride;
+    bool operator<(const MapKey& o) const { return std::tie(ptr, rows, cols, stride) < std::tie(o.ptr, o.rows, o.cols, o.stride); }
+};
+std::map<MapKey, CUtensorMap> g_maps;
+std::mutex g_lock;
+
+int view_map(const void* ptr, long long rows, long long cols, long long stride, CUtensorMap* out) {
+    std::lock_guard<std::mutex> guard(g_lock);
+    MapKey key{ptr, rows, cols, stride};
+    auto it = g_maps.find(key);
+    if (it == g_maps.end()) {
+        CUtensorMap m;
+        if (int rc = ti_make_tensor_map_2d_bf16(&m, ptr, (uint64_t)rows, (uint64_t)cols, (uint64_t)stride * 2, 128, 64)) return rc;
+        if (g_maps.size() > 8192) g_maps.clear();
+        it = g_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+}  // namespace
+
+// bfloat16, head_dim 128.  Same arguments as ti_attn_prefill_mma.
+extern "C" int ti_attn_prefill_tc(const void* q, const void* k, const void* v, void* out,
+                                  long long q_stride, long long k_stride, long long v_stride, long long o_stride,
+                                  const int* cu_new, int n_seq, int max_new, int n_tokens, int n_heads, int n_kv_heads,
+                                  int head_dim, float scale, int window, cudaStream_t stream) {
+    if (n_seq == 0 || max_new == 0) return 0;
+    TI_REQUIRE(head_dim == 128, "attention_prefill (tcgen05): head size %d is not 128", head_dim);
+    TI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_prefill: bad head counts");
+    TI_REQUIRE(n_seq <= 65535 && n_heads <= 65535, "attention_prefill: too many sequences or heads for one launch");
+    TI_REQUIRE(q_stride % 8 == 0 && k_stride % 8 == 0 && v_stride % 8 == 0 && o_stride % 8 == 0,
+               "attention_prefill (tcgen05): token strides must be multiples of 8 elements");
+    TI_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                 reinterpret_cast<uintptr_t>(out)) & 15) == 0, "attention_prefill (tcgen05): misaligned operands");
+    CUtensorMap qm, km, vm;
+    if (int rc = view_map(q, n_tokens, (long long)n_heads * head_dim, q_stride, &qm)) return rc;
+    if (int rc = view_map(k, n_tokens, (long long)n_kv_heads * head_dim, k_stride, &km)) return rc;
+    if (int rc = view_map(v, n_tokens, (long long)n_kv_heads * head_dim, v_stride, &vm)) return rc;
+    Args a;
+    a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = window;
+    a.out = out; a.o_stride = o_stride;
+    constexpr int HD = 128;
+    constexpr size_t smem = (size_t)BQ * HD * 2 + 4 * (size_t)BKV * HD * 2 + (size_t)BQ * BKV * 2 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        TI_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    int* status = ti_status_ptr();
+    TI_REQUIRE(status != nullptr, "attention_prefill: no status word");
+    dim3 grid((max_new + BQ - 1) / BQ, n_heads, n_seq);
+    TI_CUDA(ti_launch(attn_prefill_tc_kernel<HD>, grid, dim3(THREADS), smem, stream, qm, km, vm, a, status));
+    TI_CHECK_LAUNCH("attention_prefill (tcgen05)");
+    return 0;
+}

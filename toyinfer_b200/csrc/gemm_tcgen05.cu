@@ -20,7 +20,7 @@
 //
 // Contraction and rounding are those of the reference's projections (src/decode.cu:202-236,
 // src/prefill.cu:124-161): bfloat16 operands, float32 accumulation, one rounding of the result.
-#include "tma.cuh"
+#include "tcgen05.cuh"
 
 #include <map>
 #include <mutex>
@@ -35,53 +35,6 @@ struct GemmArgs {
     int splits; float* workspace; int* tickets;
     int gated;      // rows of the weight operand come in (gate, up) pairs: store up * silu(gate), half as many columns
 };
-
-// ---- tcgen05 wrappers ------------------------------------------------------
-__device__ __forceinline__ void tmem_alloc(uint32_t* slot_in_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// 32 lanes x 16 consecutive 32-bit columns: thread = lane, r[c] = column c
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&r)[16]) {
-    uint32_t u[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
-          "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; i++) r[i] = __uint_as_float(u[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16)
-// under the 128-byte swizzle: 8-row groups 1024 bytes apart, descriptor version 1.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);   // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                        // leading byte offset (unused with a swizzle), 16-byte units
-    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset: next group of 8 rows
-    d |= (uint64_t)1 << 46;                        // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;                        // layout: 128-byte swizzle
-    return d;
-}
 
 // kind::f16 instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M = 128
 template <int BN>

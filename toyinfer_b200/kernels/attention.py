@@ -15,7 +15,8 @@ def prefill(q, k, v, out, scale, window, batch) -> None:
     qs, ks, vs = _row_stride(q, "q"), _row_stride(k, "k"), _row_stride(v, "v")
     if (q.dtype == torch.bfloat16 and hd in (64, 128) and qs % 8 == 0 and ks % 8 == 0 and vs % 8 == 0
             and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0):
-        _call(library().ti_attn_prefill_mma, _ptr(q), _ptr(k), _ptr(v), _ptr(out), qs, ks, vs, out.stride(0),
+        fn = library().ti_attn_prefill_tc if (hd == 128 and out.stride(0) % 8 == 0) else library().ti_attn_prefill_mma
+        _call(fn, _ptr(q), _ptr(k), _ptr(v), _ptr(out), qs, ks, vs, out.stride(0),
               _ptr(batch.cu_new), batch.n_seq, batch.max_new, M, nh, k.shape[1], hd, scale, window, _stream())
         return
     _call(library().ti_attn_prefill_simt, _ptr(q), _ptr(k), _ptr(v), _ptr(out),
