@@ -26,7 +26,7 @@
 #include <tuple>
 
 namespace {
-constexpr int BQ = 128, BKV = 128, THREADS = 192;
+constexpr int BQ = 128, BKV = 64, THREADS = 192;
 
 struct Args {
     const int* cu_new; int n_heads, n_kv_heads; float scale; int window;
@@ -39,42 +39,63 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Shared memory of a block (all dynamic, so that two blocks fit an SM): the query tile, two
+// stages of (K tile, V tile), the P tile, then the mbarriers.
+template <int HD> struct Smem {
+    static constexpr int Q_BYTES = BQ * HD * 2, KV_BYTES = BKV * HD * 2, P_BYTES = BQ * BKV * 2;
+    static constexpr int Q_OFF = 0, KV_OFF = Q_BYTES, P_OFF = KV_OFF + 4 * KV_BYTES, BAR_OFF = P_OFF + P_BYTES;
+    static constexpr int TOTAL = BAR_OFF + 256;
+};
+
 template <int HD>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, Args a, int* status) {
     ti_pdl_trigger();
-    constexpr int Q_BYTES = BQ * HD * 2, KV_BYTES = BKV * HD * 2, P_BYTES = BQ * BKV * 2;
-    constexpr int BOX = 128 * 128;                     // bytes of one [128 rows][64 columns] box
-    constexpr uint32_t S_COLS = BKV, O_COL = 2 * BKV;  // tensor memory: S0 | S1 | O
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* q_s = smem;
-    unsigned char* kv_s = q_s + Q_BYTES;               // stage s: K at kv_s + s * 2 * KV_BYTES, V after it
-    unsigned char* p_s = kv_s + 4 * KV_BYTES;
-    __shared__ uint64_t q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, p_empty;
-    __shared__ uint32_t tmem_slot;
+    using L = Smem<HD>;
+    constexpr int Q_BYTES = L::Q_BYTES, KV_BYTES = L::KV_BYTES;
+    constexpr int QBOX = 128 * 128, KBOX = BKV * 128;      // bytes of one 64-column box of 128 / BKV rows
+    constexpr uint32_t S_COLS = BKV, O_COL = 2 * BKV;      // tensor memory: S0 | S1 | O
+    constexpr uint32_t TMEM_COLS = 256;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    unsigned char* q_s = smem + L::Q_OFF;
+    unsigned char* kv_s = smem + L::KV_OFF;                // stage s: K at kv_s + s * 2 * KV_BYTES, V after it
+    unsigned char* p_s = smem + L::P_OFF;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+    uint64_t* q_full = bars;
+    uint64_t* k_full = bars + 1;      // [2]
+    uint64_t* v_full = bars + 3;      // [2]
+    uint64_t* kv_empty = bars + 5;    // [2]
+    uint64_t* s_full = bars + 7;      // [2]
+    uint64_t* s_empty = bars + 9;     // [2]
+    uint64_t* p_full = bars + 11;
+    uint64_t* p_empty = bars + 12;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (smem_u32(smem) & 1023u) {       // the swizzled tiles need a 1024-byte aligned base
+        if (threadIdx.x == 0) ti_report(status, TI_STATUS_PIPE_WAIT);
+        return;
+    }
     if (threadIdx.x == 0) {
-        mbar_init(&q_full, 1);
+        mbar_init(q_full, 1);
         for (int s = 0; s < 2; s++) {
             mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1);
             mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
         }
-        mbar_init(&p_full, 4);
-        mbar_init(&p_empty, 1);
+        mbar_init(p_full, 4);
+        mbar_init(p_empty, 1);
         mbar_fence_init();
     }
     if (warp == 1) {
         __syncwarp();
-        tmem_alloc(&tmem_slot, 512);
+        tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = tmem_slot;
+    const uint32_t tmem = *tmem_slot;
     ti_pdl_sync();
 
     const int b = blockIdx.z, h = blockIdx.y;
@@ -89,9 +110,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 
     if (active && warp == 0) {
         if (lane == 0) {
-            mbar_expect_tx(&q_full, Q_BYTES);
+            mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
-            for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(q_s + bx * BOX, &q_map, h * HD + bx * 64, tok0 + q0, &q_full);
+            for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(q_s + bx * QBOX, &q_map, h * HD + bx * 64, tok0 + q0, q_full);
             for (int j = 0; j < n_tiles; j++) {
                 const int s = j & 1;
                 if (!mbar_wait(&kv_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); break; }
@@ -99,10 +120,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 unsigned char* ks = kv_s + (size_t)s * 2 * KV_BYTES;
                 mbar_expect_tx(&k_full[s], KV_BYTES);
 #pragma unroll
-                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + bx * BOX, &k_map, kvh * HD + bx * 64, y, &k_full[s]);
+                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + bx * KBOX, &k_map, kvh * HD + bx * 64, y, &k_full[s]);
                 mbar_expect_tx(&v_full[s], KV_BYTES);
 #pragma unroll
-                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + KV_BYTES + bx * BOX, &v_map, kvh * HD + bx * 64, y, &v_full[s]);
+                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + KV_BYTES + bx * KBOX, &v_map, kvh * HD + bx * 64, y, &v_full[s]);
             }
         }
     } else if (active && warp == 1) {
@@ -113,13 +134,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             auto issue_s = [&](int j) {       // S_j = Q K_j^T into score buffer j & 1
                 const uint32_t ka = smem_u32(kv_s + (size_t)(j & 1) * 2 * KV_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < HD / 16; kk++) {
-                    const uint32_t off = (kk >> 2) * BOX + (kk & 3) * 32;     // 64 columns per box, 32 bytes per step
-                    tc_mma_bf16(tmem + (j & 1) * S_COLS, smem_desc_sw128(qa + off), smem_desc_sw128(ka + off), idesc_s, kk > 0 ? 1u : 0u);
-                }
+                for (int kk = 0; kk < HD / 16; kk++)      // 64 columns per box, 32 bytes per step of 16
+                    tc_mma_bf16(tmem + (j & 1) * S_COLS, smem_desc_sw128(qa + (kk >> 2) * QBOX + (kk & 3) * 32),
+                                smem_desc_sw128(ka + (kk >> 2) * KBOX + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
                 tc_commit(&s_full[j & 1]);
             };
-            bool ok = mbar_wait(&q_full, 0) && mbar_wait(&k_full[0], 0);
+            bool ok = mbar_wait(q_full, 0) && mbar_wait(&k_full[0], 0);
             if (!ok) ti_report(status, TI_STATUS_TMA_WAIT);
             if (ok) {
                 tc_fence_after();
@@ -134,19 +154,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     tc_fence_after();
                     issue_s(j + 1);
                 }
-                if (!mbar_wait(&p_full, (uint32_t)(j & 1)) || !mbar_wait(&v_full[j & 1], (uint32_t)((j >> 1) & 1))) {
+                if (!mbar_wait(p_full, (uint32_t)(j & 1)) || !mbar_wait(&v_full[j & 1], (uint32_t)((j >> 1) & 1))) {
                     ti_report(status, TI_STATUS_PIPE_WAIT); ok = false; break;
                 }
                 tc_fence_after();
                 const uint32_t va = smem_u32(kv_s + (size_t)(j & 1) * 2 * KV_BYTES + KV_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < BKV / 16; kk++) {      // 16 positions per step
-                    const uint64_t da = smem_desc_sw128(pa + (kk >> 2) * BOX + (kk & 3) * 32);
-                    const uint64_t db = smem_desc_mn_sw128(va + kk * 16 * 128, BOX);
-                    tc_mma_bf16(tmem + O_COL, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-                }
+                for (int kk = 0; kk < BKV / 16; kk++)        // 16 positions per step
+                    tc_mma_bf16(tmem + O_COL, smem_desc_sw128(pa + kk * 32), smem_desc_mn_sw128(va + kk * 16 * 128, KBOX),
+                                idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                 tc_commit(&kv_empty[j & 1]);     // the stage's K and V have been read
-                tc_commit(&p_empty);             // so has P, and O holds this tile's contribution
+                tc_commit(p_empty);              // so has P, and O holds this tile's contribution
             }
         }
     } else if (active) {
@@ -167,26 +185,53 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const int k0 = (kt_lo + j) * BKV;
             const bool edge = a.window > 0 || k0 + BKV - 1 > q0 + qd * 32 || k0 + BKV > n;
             const uint32_t s_addr = tmem + sb * S_COLS + lane_base;
-            auto visible = [&](int kj) { return kj <= qi && kj < n && (a.window <= 0 || kj > qi - a.window); };
-            // pass 1: the row's maximum
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < BKV / 32; c++) {
-                float v[32];
-                tmem_ld32(s_addr + c * 32, v);
+            // the row's 64 scores, in base-2 units
+            float v[BKV];
+            {
+                float lo[32], hi[32];
+                tmem_ld32(s_addr, lo);
+                tmem_ld32(s_addr + 32, hi);
 #pragma unroll
-                for (int e = 0; e < 32; e++) {
-                    const float x = (!edge || visible(k0 + c * 32 + e)) ? v[e] * scale2 : -INFINITY;
-                    mx = fmaxf(mx, x);
+                for (int e = 0; e < 32; e++) { v[e] = lo[e] * scale2; v[32 + e] = hi[e] * scale2; }
+            }
+            // the score buffer may be overwritten by the tile after next
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[sb]);
+            if (edge) {
+#pragma unroll
+                for (int e = 0; e < BKV; e++) {
+                    const int kj = k0 + e;
+                    const bool vis = kj <= qi && kj < n && (a.window <= 0 || kj > qi - a.window);
+                    v[e] = vis ? v[e] : -INFINITY;
                 }
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int e = 0; e < BKV; e += 4) {
+                mx4[0] = fmaxf(mx4[0], v[e]); mx4[1] = fmaxf(mx4[1], v[e + 1]);
+                mx4[2] = fmaxf(mx4[2], v[e + 2]); mx4[3] = fmaxf(mx4[3], v[e + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             float alpha = 1.f, m_new = m_used;
             if (mx > m_used + 8.f || (m_used == -INFINITY && mx > -INFINITY)) {
                 m_new = mx;
                 alpha = ex2(m_used - m_new);        // 0 when nothing was visible before
             }
+            const float m_sub = m_new > -INFINITY ? m_new : 0.f;      // masked scores stay -inf, 2^-inf = 0
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pk[BKV / 2];
+#pragma unroll
+            for (int e = 0; e < BKV; e += 4) {
+                const float p0 = ex2(v[e] - m_sub), p1 = ex2(v[e + 1] - m_sub);
+                const float p2 = ex2(v[e + 2] - m_sub), p3 = ex2(v[e + 3] - m_sub);
+                sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
+                __nv_bfloat162 t0 = __floats2bfloat162_rn(p0, p1), t1 = __floats2bfloat162_rn(p2, p3);
+                pk[e >> 1] = *reinterpret_cast<uint32_t*>(&t0);
+                pk[(e >> 1) + 1] = *reinterpret_cast<uint32_t*>(&t1);
+            }
             // P's buffer and O are free once the previous tile's second product has finished
-            if (j > 0 && !mbar_wait(&p_empty, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            if (j > 0 && !mbar_wait(p_empty, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -200,40 +245,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     tmem_st32(tmem + O_COL + lane_base + c * 32, o);
                 }
             }
-            // pass 2: P = 2^(s - m) as bfloat16 into shared memory, row r, 16-byte chunk cc at cc ^ (r % 8)
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < BKV / 32; c++) {
-                float v[32];
-                tmem_ld32(s_addr + c * 32, v);
-                uint32_t pk[16];
+            // P as bfloat16 into shared memory: row r, 16-byte chunk cc (8 positions) at cc ^ (r % 8)
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const bool ok0 = m_new > -INFINITY && (!edge || visible(k0 + c * 32 + e));
-                    const bool ok1 = m_new > -INFINITY && (!edge || visible(k0 + c * 32 + e + 1));
-                    const float p0 = ok0 ? ex2(v[e] * scale2 - m_new) : 0.f;
-                    const float p1 = ok1 ? ex2(v[e + 1] * scale2 - m_new) : 0.f;
-                    sum += p0 + p1;
-                    __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
-                    pk[e >> 1] = *reinterpret_cast<uint32_t*>(&t);
-                }
-#pragma unroll
-                for (int t4 = 0; t4 < 4; t4++) {
-                    const int cc = c * 4 + t4;               // chunk of 8 positions within the tile
-                    unsigned char* dst = p_s + (cc >> 3) * BOX + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
-                    *reinterpret_cast<uint4*>(dst) = make_uint4(pk[t4 * 4], pk[t4 * 4 + 1], pk[t4 * 4 + 2], pk[t4 * 4 + 3]);
-                }
-            }
-            l_run = l_run * alpha + sum;
+            for (int cc = 0; cc < BKV / 8; cc++)
+                *reinterpret_cast<uint4*>(p_s + r * 128 + ((cc ^ (r & 7)) << 4)) =
+                    make_uint4(pk[cc * 4], pk[cc * 4 + 1], pk[cc * 4 + 2], pk[cc * 4 + 3]);
+            l_run = l_run * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             m_used = m_new;
-            // the score buffer may be overwritten, and P (with O rescaled) is ready for the second product
             tc_fence_before();
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&s_empty[sb]); mbar_arrive(&p_full); }
+            if (lane == 0) mbar_arrive(p_full);
         }
         if (ok && n_tiles > 0) {
-            if (!mbar_wait(&p_empty, (uint32_t)((n_tiles - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            if (!mbar_wait(p_empty, (uint32_t)((n_tiles - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
@@ -245,15 +270,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 float o[32];
                 tmem_ld32(tmem + O_COL + lane_base + c * 32, o);
                 if (qi < n) {
-                    uint32_t pk[16];
+                    uint32_t ok4[16];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
                         __nv_bfloat162 t = __floats2bfloat162_rn(o[e] * inv, o[e + 1] * inv);
-                        pk[e >> 1] = *reinterpret_cast<uint32_t*>(&t);
+                        ok4[e >> 1] = *reinterpret_cast<uint32_t*>(&t);
                     }
 #pragma unroll
                     for (int t4 = 0; t4 < 4; t4++)
-                        *reinterpret_cast<uint4*>(orow + c * 32 + t4 * 8) = make_uint4(pk[t4 * 4], pk[t4 * 4 + 1], pk[t4 * 4 + 2], pk[t4 * 4 + 3]);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + t4 * 8) = make_uint4(ok4[t4 * 4], ok4[t4 * 4 + 1], ok4[t4 * 4 + 2], ok4[t4 * 4 + 3]);
                 }
             }
         }
@@ -263,24 +288,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc(tmem, 512);
+        tmem_dealloc(tmem, TMEM_COLS);
     }
 }
 
 struct MapKey {
-    const void* ptr; long long rows, cols, stride;
-    bool operator<(const MapKey& o) const { return std::tie(ptr, rows, cols, stride) < std::tie(o.ptr, o.rows, o.cols, o.stride); }
+    const void* ptr; long long rows, cols, stride; int box_rows;
+    bool operator<(const MapKey& o) const {
+        return std::tie(ptr, rows, cols, stride, box_rows) < std::tie(o.ptr, o.rows, o.cols, o.stride, o.box_rows);
+    }
 };
 std::map<MapKey, CUtensorMap> g_maps;
 std::mutex g_lock;
 
-int view_map(const void* ptr, long long rows, long long cols, long long stride, CUtensorMap* out) {
+int view_map(const void* ptr, long long rows, long long cols, long long stride, int box_rows, CUtensorMap* out) {
     std::lock_guard<std::mutex> guard(g_lock);
-    MapKey key{ptr, rows, cols, stride};
+    MapKey key{ptr, rows, cols, stride, box_rows};
     auto it = g_maps.find(key);
     if (it == g_maps.end()) {
         CUtensorMap m;
-        if (int rc = ti_make_tensor_map_2d_bf16(&m, ptr, (uint64_t)rows, (uint64_t)cols, (uint64_t)stride * 2, 128, 64)) return rc;
+        if (int rc = ti_make_tensor_map_2d_bf16(&m, ptr, (uint64_t)rows, (uint64_t)cols, (uint64_t)stride * 2, (uint32_t)box_rows, 64)) return rc;
         if (g_maps.size() > 8192) g_maps.clear();
         it = g_maps.emplace(key, m).first;
     }
@@ -303,14 +330,14 @@ extern "C" int ti_attn_prefill_tc(const void* q, const void* k, const void* v, v
     TI_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
                  reinterpret_cast<uintptr_t>(out)) & 15) == 0, "attention_prefill (tcgen05): misaligned operands");
     CUtensorMap qm, km, vm;
-    if (int rc = view_map(q, n_tokens, (long long)n_heads * head_dim, q_stride, &qm)) return rc;
-    if (int rc = view_map(k, n_tokens, (long long)n_kv_heads * head_dim, k_stride, &km)) return rc;
-    if (int rc = view_map(v, n_tokens, (long long)n_kv_heads * head_dim, v_stride, &vm)) return rc;
+    if (int rc = view_map(q, n_tokens, (long long)n_heads * head_dim, q_stride, BQ, &qm)) return rc;
+    if (int rc = view_map(k, n_tokens, (long long)n_kv_heads * head_dim, k_stride, BKV, &km)) return rc;
+    if (int rc = view_map(v, n_tokens, (long long)n_kv_heads * head_dim, v_stride, BKV, &vm)) return rc;
     Args a;
     a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = window;
     a.out = out; a.o_stride = o_stride;
     constexpr int HD = 128;
-    constexpr size_t smem = (size_t)BQ * HD * 2 + 4 * (size_t)BKV * HD * 2 + (size_t)BQ * BKV * 2 + 1024;
+    constexpr size_t smem = Smem<HD>::TOTAL;
     static bool configured = false;
     if (!configured) {
         TI_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
