@@ -15,7 +15,6 @@ struct DecodeArgs {
     float scale;
     void* out; long long o_stride;            // [B, heads, hd]
     float* part_o; float* part_ml;            // [B, heads, splits, hd], [B, heads, splits, 2]
-    int* tickets = nullptr;                   // one per (sequence, block row), zero between launches: merge in the kernel
 };
 
 // One block per (sequence, head); threads over the head's elements.  A split that saw no

@@ -46,7 +46,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
     // 1024-byte alignment of the boxes is what the swizzle pattern is defined against
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full[STAGES];
-    __shared__ int s_abort, s_last;
+    __shared__ int s_abort;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) mbar_init(&full[s], 1);
@@ -293,38 +293,6 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
             if (d == 0) { a.part_ml[base * 2] = m; a.part_ml[base * 2 + 1] = l; }
         }
     }
-    if (a.n_splits > 1 && a.tickets) {
-        // The last block to finish among the splits of this (sequence, head group) merges them,
-        // in split order, so that the result does not depend on which block that is.
-        __threadfence();
-        __syncthreads();
-        if (t == 0) {
-            int* ticket = a.tickets + (size_t)b * gridDim.y + blockIdx.y;
-            const int prev = atomicAdd(ticket, 1);
-            s_last = prev == a.n_splits - 1;
-            if (s_last) *ticket = 0;            // ready for the next launch
-        }
-        __syncthreads();
-        if (!s_last) return;
-        __threadfence();
-        for (int idx = t; idx < rows * HD; idx += THREADS) {
-            const int r = idx / HD, d = idx - r * HD;
-            const int h = h0 + r;
-            const size_t base = ((size_t)b * a.n_heads + h) * a.n_splits;
-            float m = -INFINITY;
-            for (int s = 0; s < a.n_splits; s++) m = fmaxf(m, __ldcg(&a.part_ml[(base + s) * 2]));
-            float l = 0.f, acc = 0.f;
-            for (int s = 0; s < a.n_splits; s++) {
-                const float ms = __ldcg(&a.part_ml[(base + s) * 2]);
-                if (ms > -INFINITY) {
-                    const float f = expf(ms - m);
-                    l += __ldcg(&a.part_ml[(base + s) * 2 + 1]) * f;
-                    acc = fmaf(__ldcg(&a.part_o[(base + s) * HD + d]), f, acc);
-                }
-            }
-            ((bf16*)a.out)[(size_t)b * a.o_stride + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-        }
-    }
 }
 
 struct MapKey {
@@ -368,7 +336,7 @@ int launch(const tiattn::DecodeArgs& a, int n_seq, cudaStream_t stream) {
     dim3 grid(n_seq, a.n_kv_heads * ((g + 15) / 16), a.n_splits);
     TI_CUDA(ti_launch(attn_decode_mma_kernel<HD>, grid, dim3(THREADS), smem, stream, km, vm, a, status));
     TI_CHECK_LAUNCH("attention_decode (tensor cores)");
-    if (a.n_splits > 1 && !a.tickets) {
+    if (a.n_splits > 1) {
         dim3 cgrid(n_seq, a.n_heads);
         TI_CUDA(ti_launch(tiattn::attn_decode_combine_kernel<bf16>, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits));
         TI_CHECK_LAUNCH("attention_decode (combine)");
@@ -378,15 +346,13 @@ int launch(const tiattn::DecodeArgs& a, int n_seq, cudaStream_t stream) {
 }  // namespace
 
 // bfloat16 only; head_dim 64 or 128; pages of 64 positions.  Same arguments as
-// ti_attn_decode_simt plus `tickets`: n_seq * kv_heads * ceil(group / 16) ints that are zero
-// between launches; with them the splits are merged inside the kernel, without them (null) by a
-// second kernel.
+// ti_attn_decode_simt.
 extern "C" int ti_attn_decode_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                   const int* page_table, int table_width, int page_size, int ring_rows,
                                   int n_pages, const int* seq_slot, const int* seq_len, int n_seq,
                                   int n_heads, int n_kv_heads, int head_dim, float scale, int window,
                                   int n_splits, void* out, long long o_stride, float* part_o,
-                                  float* part_ml, int* tickets, int dtype, cudaStream_t stream) {
+                                  float* part_ml, int dtype, cudaStream_t stream) {
     if (n_seq == 0) return 0;
     TI_REQUIRE(dtype == TI_BF16, "attention_decode (tensor cores): bfloat16 only");
     TI_REQUIRE(head_dim == 64 || head_dim == 128, "attention_decode (tensor cores): head size %d is not 64 or 128", head_dim);
@@ -402,6 +368,6 @@ extern "C" int ti_attn_decode_mma(const void* q, long long q_stride, const void*
     a.table_width = table_width; a.page_size = page_size; a.ring_rows = ring_rows; a.n_pages = n_pages;
     a.seq_slot = seq_slot; a.seq_len = seq_len; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.hd = head_dim;
     a.window = window; a.n_splits = n_splits; a.scale = scale; a.out = out; a.o_stride = o_stride;
-    a.part_o = part_o; a.part_ml = part_ml; a.tickets = tickets;
+    a.part_o = part_o; a.part_ml = part_ml;
     return head_dim == 64 ? launch<64>(a, n_seq, stream) : launch<128>(a, n_seq, stream);
 }

@@ -298,8 +298,4 @@ def check_status() -> None:
     if library().ti_read_status(ctypes.byref(v)) != 0:
         raise KernelError(library().ti_last_error().decode("utf-8", "replace"))
     if v.value:
-        # a kernel that gave up may have left a ticket half counted: start them from zero again
-        from . import attention, gemm
-        for t in list(attention._tickets.values()) + list(gemm._tickets.values()):
-            t.zero_()
         raise KernelError(f"a kernel reported status {v.value}: {_STATUS.get(v.value, 'unknown')}")

@@ -8,7 +8,6 @@ from . import KernelError, _call, _code, _ptr, _row_stride, _stream
 from .lib import library
 
 SM_COUNT = 148
-_tickets = {}
 
 
 def prefill(q, k, v, out, scale, window, batch) -> None:
@@ -46,19 +45,7 @@ def decode(q, mem, out, scale, window, batch) -> None:
         part_ml = torch.empty((B, nh, splits, 2), dtype=torch.float32, device=q.device)
     pt = mem.page_table
     lib = library()
-    if q.dtype == torch.bfloat16 and hd in (64, 128):
-        tickets = None
-        if splits > 1:
-            tickets = _tickets.get(q.device)
-            need = B * nkv * ((nh // nkv + 15) // 16)
-            if tickets is None or tickets.numel() < need:
-                tickets = _tickets[q.device] = torch.zeros(max(need, 65536), dtype=torch.int32, device=q.device)
-        _call(lib.ti_attn_decode_mma, _ptr(q), _row_stride(q, "q"), _ptr(mem.k_pages), _ptr(mem.v_pages),
-              _ptr(pt), pt.shape[1], mem.page_size, mem.ring_rows, mem.k_pages.shape[0],
-              _ptr(batch.seq_slot), _ptr(batch.seq_len), B, nh, nkv, hd, scale, window, splits,
-              _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _code(q, "attention_decode"), _stream())
-        return
-    fn = lib.ti_attn_decode_simt
+    fn = lib.ti_attn_decode_mma if (q.dtype == torch.bfloat16 and hd in (64, 128)) else lib.ti_attn_decode_simt
     _call(fn, _ptr(q), _row_stride(q, "q"), _ptr(mem.k_pages), _ptr(mem.v_pages),
           _ptr(pt), pt.shape[1], mem.page_size, mem.ring_rows, mem.k_pages.shape[0],
           _ptr(batch.seq_slot), _ptr(batch.seq_len), B, nh, nkv, hd, scale, window, splits,
