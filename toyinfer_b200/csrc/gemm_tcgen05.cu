@@ -244,6 +244,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
 #pragma unroll
                 for (int e = 0; e < 16; e++) ws[(size_t)(c + e) * BM + q * 32 + lane] = r[e];
             }
+            if (!g.tickets) ok = false;             // a second kernel adds the partial tiles
+            else {
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (threadIdx.x == 64) {
@@ -255,6 +257,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (!s_last) ok = false;                // another block finishes this tile
             else __threadfence();
+            }
         }
         if (ok) {
 #pragma unroll 1
@@ -409,6 +412,33 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
     }
 }
 
+// Adds the partial tiles of a split contraction (workspace layout as written above) in split order
+// and stores the result; one thread per (row of A, 16 columns).
+template <int BN>
+__global__ void splitk_reduce_kernel(GemmArgs g, int tiles_a, int tiles_b) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    const int lane = threadIdx.x & 31;
+    const int chunks = BN / 16;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);     // (tile, 32-row group, chunk)
+    const long long n_items = (long long)tiles_a * tiles_b * 4 * chunks;
+    if (item >= n_items) return;
+    const int c = (int)(item % chunks) * 16;
+    const int q = (int)((item / chunks) % 4);
+    const int tile = (int)(item / (chunks * 4));
+    const int ta = tile / tiles_b, tb = tile % tiles_b;
+    const int i = ta * BM + q * 32 + lane;
+    float r[16];
+#pragma unroll
+    for (int e = 0; e < 16; e++) r[e] = 0.f;
+    for (int sp = 0; sp < g.splits; sp++) {
+        const float* ws = g.workspace + (((size_t)sp * tiles_a + ta) * tiles_b + tb) * (size_t)(BM * BN);
+#pragma unroll
+        for (int e = 0; e < 16; e++) r[e] += ws[(size_t)(c + e) * BM + q * 32 + lane];
+    }
+    store_chunk(g, i, tb * BN, c, r, lane);
+}
+
 // ---- host ------------------------------------------------------------------
 struct MapKey {
     const void* ptr; long long rows, cols, stride; int box_rows;
@@ -450,6 +480,13 @@ int launch(const CUtensorMap& am, const CUtensorMap& bm, const GemmArgs& g, cuda
     TI_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "linear: grid of %u x %u x %u is too large", grid.x, grid.y, grid.z);
     TI_CUDA(ti_launch(gemm_tc_kernel<BN>, grid, dim3(THREADS), smem, stream, am, bm, g, status));
     TI_CHECK_LAUNCH("linear (tcgen05)");
+    if (g.splits > 1 && !g.tickets) {
+        const long long items = (long long)grid.x * grid.y * 4 * (BN / 16);
+        const int warps = 4;
+        TI_CUDA(ti_launch(splitk_reduce_kernel<BN>, dim3((unsigned)((items + warps - 1) / warps)), dim3(warps * 32), 0, stream, g,
+                          (int)grid.x, (int)grid.y));
+        TI_CHECK_LAUNCH("linear (tcgen05, split reduction)");
+    }
     return 0;
 }
 template <int BN>
@@ -519,7 +556,8 @@ extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* b
 // x[M, K] (row stride ldx), w[N, K] (row stride ldw), both bfloat16; out[M, N] bfloat16 or
 // float32 with row stride ldo.  With `gated`, w's rows are (gate_0, up_0, gate_1, up_1, ...) and
 // out is [M, N / 2] = up * gate / (1 + exp(-gate)).  `workspace` (float32) and `tickets` (int32, zero before the
-// first use, left zero) as planned by ti_linear_tc_plan; tickets needs n_tiles entries.
+// first use, left zero) as planned by ti_linear_tc_plan; tickets needs n_tiles entries and may be
+// null, in which case a second kernel adds the partial tiles.
 extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                             long long ldw, long long ldo, int out_f32, int gated, int sms, float* workspace, int* tickets,
                             cudaStream_t stream) {
@@ -531,7 +569,7 @@ extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int 
     int swap, bn, splits, tiles;
     long long ws;
     ti_linear_tc_plan(M, N, K, sms, &swap, &bn, &splits, &ws, &tiles);
-    TI_REQUIRE(splits == 1 || (workspace && tickets), "linear (tcgen05): a split contraction needs workspace and tickets");
+    TI_REQUIRE(splits == 1 || workspace, "linear (tcgen05): a split contraction needs a workspace");
     GemmArgs g;
     g.rows_a = swap ? N : M; g.rows_b = swap ? M : N; g.K = K;
     g.out = out; g.ld_out = ldo; g.out_f32 = out_f32; g.transposed = swap;

@@ -41,9 +41,11 @@ def run(x, w, out, M, N, K, ldx, ldw, gated: bool = False) -> None:
         workspace = tickets = None
         if splits.value > 1:
             workspace = torch.empty(ws.value, dtype=torch.float32, device=x.device)
+            # tickets let the last block of a tile add the partial tiles itself; measured faster
+            # than the separate reduction kernel the library falls back to without them
             tickets = _tickets_for(x.device)
             if n_tiles.value > tickets.numel():
-                raise RuntimeError("linear: more split tiles than tickets")
+                tickets = None
         _call(lib.ti_linear_tc, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, 1 if gated else 0, SM_COUNT,
               _ptr(workspace), _ptr(tickets), _stream())
         return
