@@ -260,6 +260,10 @@ def run_kernel(name: str, reps: int, eager: bool = False):
         return (torch.randn(*shape, generator=g, device=dev) * scale).to(torch.bfloat16)
 
     def make():
+        if name.startswith("gemm:"):                     # gemm:M,N,K
+            M, N, Kd = (int(v) for v in name[5:].split(","))
+            x, w = rnd(M, Kd), rnd(N, Kd, scale=0.02)
+            return (lambda: K.linear(x, w)), (N * Kd + M * Kd + M * N) * 2, 2.0 * M * N * Kd
         if name in ("gemm_decode", "gemm_decode_b64", "gemm_prefill", "gemm_head", "gemm_down", "gemm_qkv", "gemm_o"):
             M = {"gemm_decode_b64": 64, "gemm_prefill": 2048}.get(name, 8)
             N, Kd = {"gemm_head": (151936, H), "gemm_down": (H, I), "gemm_qkv": (6144, H), "gemm_o": (H, 4096)}.get(name, (2 * I, H))
@@ -332,7 +336,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the named configuration (reported)")
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
-                    "gemm_qkv, gemm_o, gemm_head, gemm_prefill, attn_decode, attn_decode_b64, attn_decode_b1, attn_prefill")
+                    "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K, attn_decode, attn_decode_b64, attn_decode_b1, attn_prefill")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--eager", action="store_true", help="with --kernel: plain launches instead of a graph replay")
     args = ap.parse_args()
