@@ -264,12 +264,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
             for (int c = 0; c < BN; c += 16) {
                 float r[16];
                 if (g.splits > 1) {
+                    // partial tiles are added in split order; four splits' loads are in flight together
 #pragma unroll
                     for (int e = 0; e < 16; e++) r[e] = 0.f;
-                    for (int sp = 0; sp < g.splits; sp++) {
-                        const float* ws = g.workspace + (((size_t)sp * gridDim.x + blockIdx.x) * gridDim.y + blockIdx.y) * (size_t)(BM * BN);
+                    const size_t tile_off = ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * (size_t)(BM * BN) + (size_t)c * BM + q * 32 + lane;
+                    const size_t split_stride = (size_t)gridDim.x * gridDim.y * (size_t)(BM * BN);
+                    for (int sp0 = 0; sp0 < g.splits; sp0 += 4) {
+                        float t4[4][16];
 #pragma unroll
-                        for (int e = 0; e < 16; e++) r[e] += __ldcg(&ws[(size_t)(c + e) * BM + q * 32 + lane]);
+                        for (int u = 0; u < 4; u++) {
+                            const bool live = sp0 + u < g.splits;
+                            const float* ws = g.workspace + (size_t)(live ? sp0 + u : sp0) * split_stride + tile_off;
+#pragma unroll
+                            for (int e = 0; e < 16; e++) t4[u][e] = live ? __ldcg(&ws[(size_t)e * BM]) : 0.f;
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; u++)
+#pragma unroll
+                            for (int e = 0; e < 16; e++) r[e] += t4[u][e];
                     }
                 } else if (n_iter > 0) {
                     tmem_ld16(taddr + c, r);
