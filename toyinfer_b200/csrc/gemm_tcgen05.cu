@@ -522,11 +522,11 @@ int launch_persistent(const CUtensorMap& am, const CUtensorMap& bm, const GemmAr
 // Weight rows per tile for many tokens: the width whose tiles fill whole rounds of `sms`
 // blocks best, wider tiles being a little more efficient per flop.
 int wide_tile(int rows_a, int rows_b, int sms) {
-    const int cand[4] = {256, 192, 160, 128};
-    const double mma_eff[4] = {1.0, 0.97, 0.95, 0.92};
+    const int cand[9] = {256, 240, 224, 208, 192, 176, 160, 144, 128};
+    const double mma_eff[9] = {1.0, 0.99, 0.98, 0.97, 0.96, 0.95, 0.94, 0.92, 0.90};
     int best = 256;
     double best_score = -1.0;
-    for (int c = 0; c < 4; c++) {
+    for (int c = 0; c < 9; c++) {
         const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + cand[c] - 1) / cand[c]);
         const int rounds = (tiles + sms - 1) / sms;
         const double useful = (double)rows_b / (((rows_b + cand[c] - 1) / cand[c]) * (double)cand[c]);
@@ -594,8 +594,13 @@ extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int 
     if (!swap && splits == 1 && bn >= 128) {
         switch (bn) {
             case 128: return launch_persistent<128>(am, bm, g, sms, stream);
+            case 144: return launch_persistent<144>(am, bm, g, sms, stream);
             case 160: return launch_persistent<160>(am, bm, g, sms, stream);
+            case 176: return launch_persistent<176>(am, bm, g, sms, stream);
             case 192: return launch_persistent<192>(am, bm, g, sms, stream);
+            case 208: return launch_persistent<208>(am, bm, g, sms, stream);
+            case 224: return launch_persistent<224>(am, bm, g, sms, stream);
+            case 240: return launch_persistent<240>(am, bm, g, sms, stream);
             default: return launch_persistent<256>(am, bm, g, sms, stream);
         }
     }
@@ -604,8 +609,13 @@ extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int 
         case 32: return launch<32>(am, bm, g, stream);
         case 64: return launch<64>(am, bm, g, stream);
         case 128: return launch<128>(am, bm, g, stream);
+        case 144: return launch<144>(am, bm, g, stream);
         case 160: return launch<160>(am, bm, g, stream);
+        case 176: return launch<176>(am, bm, g, stream);
         case 192: return launch<192>(am, bm, g, stream);
+        case 208: return launch<208>(am, bm, g, stream);
+        case 224: return launch<224>(am, bm, g, stream);
+        case 240: return launch<240>(am, bm, g, stream);
         default: return launch<256>(am, bm, g, stream);
     }
 }

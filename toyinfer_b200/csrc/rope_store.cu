@@ -125,33 +125,25 @@ template <typename T> __device__ __forceinline__ typename Pair<T>::type pair_fro
 template <> __device__ __forceinline__ float2 pair_from_f32<float>(float a, float b) { return make_float2(a, b); }
 template <> __device__ __forceinline__ __nv_bfloat162 pair_from_f32<bf16>(float a, float b) { return __floats2bfloat162_rn(a, b); }
 
+// One block per token: the token's position, slot and page are looked up once, then the
+// block's warps share the token's heads between them.
 template <typename T>
 __global__ void rope_store_pairs_kernel(RopeStoreArgs a) {
     ti_pdl_trigger();
     ti_pdl_sync();
     using P = typename Pair<T>::type;
-    const int warps_per_block = blockDim.x >> 5;
-    const int lane = threadIdx.x & 31;
+    const int n_warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_q = a.q ? a.n_heads : 0;
     const int heads_k = a.k ? a.n_kv_heads : 0;
     const int heads_v = a.v ? a.n_kv_heads : 0;
     const int per_tok = heads_q + heads_k + heads_v;
-    const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-    if (item >= (long long)a.M * per_tok) return;
-    const int m = (int)(item / per_tok);
-    int h = (int)(item - (long long)m * per_tok);
-    int kind;  // 0 q, 1 k, 2 v
-    if (h < heads_q) kind = 0;
-    else if (h < heads_q + heads_k) { kind = 1; h -= heads_q; }
-    else { kind = 2; h -= heads_q + heads_k; }
-
+    const int m = blockIdx.x;
     const int hd = a.head_dim, half = hd >> 1;
-    T* x = kind == 0 ? (T*)a.q + (size_t)m * a.q_stride + (size_t)h * hd
-         : kind == 1 ? (T*)a.k + (size_t)m * a.k_stride + (size_t)h * hd
-                     : (T*)a.v + (size_t)m * a.v_stride + (size_t)h * hd;
     int pos = a.tok_pos[m];
-    T* dst = nullptr;
-    if (kind != 0 && a.k_pages) {
+
+    // where the cache keeps this token (head 0 of keys; other heads and values follow from it)
+    long long dst_off = -1;
+    if (a.k_pages) {
         const int seq = a.tok_seq[m];
         const int slot = a.seq_slot[seq];
         int row = pos;
@@ -163,58 +155,69 @@ __global__ void rope_store_pairs_kernel(RopeStoreArgs a) {
         const int pidx = row / a.page_size;
         if (keep && pidx < a.table_width) {
             const int page = a.page_table[(size_t)slot * a.table_width + pidx];
-            if (page >= 0 && page < a.n_pages) {
-                T* base = (T*)(kind == 1 ? a.k_pages : a.v_pages);
-                dst = base + (((size_t)page * a.n_kv_heads + h) * a.page_size + (row % a.page_size)) * hd;
-            }
+            if (page >= 0 && page < a.n_pages)
+                dst_off = ((long long)page * a.n_kv_heads * a.page_size + (row % a.page_size)) * hd;
         }
-    }
-    if (kind == 2) {
-        if (dst)
-            for (int i = lane * 2; i < hd; i += 64) *reinterpret_cast<P*>(dst + i) = *reinterpret_cast<const P*>(x + i);
-        return;
-    }
-    const void* wv = kind == 0 ? a.q_w : a.k_w;
-    float r = 1.f;
-    if (wv) {
-        float ss = 0.f;
-        for (int i = lane * 2; i < hd; i += 64) {
-            const float2 t = pair_to_f32(*reinterpret_cast<const P*>(x + i));
-            ss = fmaf(t.x, t.x, ss);
-            ss = fmaf(t.y, t.y, ss);
-        }
-        ss = warp_sum(ss);
-        r = rsqrtf(fmaf(ss, 1.0f / (float)hd, a.eps));
     }
     if (pos < 0) pos = 0;
     if (pos >= a.max_pos) pos = a.max_pos - 1;
     const float* cs = a.cos_t ? a.cos_t + (size_t)pos * half : nullptr;
     const float* sn = a.sin_t ? a.sin_t + (size_t)pos * half : nullptr;
-    for (int i = lane * 2; i < half; i += 64) {
-        float2 lo = pair_to_f32(*reinterpret_cast<const P*>(x + i));
-        float2 hi = pair_to_f32(*reinterpret_cast<const P*>(x + i + half));
+
+    for (int item = warp; item < per_tok; item += n_warps) {
+        int h = item, kind;  // 0 q, 1 k, 2 v
+        if (h < heads_q) kind = 0;
+        else if (h < heads_q + heads_k) { kind = 1; h -= heads_q; }
+        else { kind = 2; h -= heads_q + heads_k; }
+        T* x = kind == 0 ? (T*)a.q + (size_t)m * a.q_stride + (size_t)h * hd
+             : kind == 1 ? (T*)a.k + (size_t)m * a.k_stride + (size_t)h * hd
+                         : (T*)a.v + (size_t)m * a.v_stride + (size_t)h * hd;
+        T* dst = nullptr;
+        if (kind != 0 && dst_off >= 0)
+            dst = (T*)(kind == 1 ? a.k_pages : a.v_pages) + dst_off + (size_t)h * a.page_size * hd;
+        if (kind == 2) {
+            if (dst)
+                for (int i = lane * 2; i < hd; i += 64) *reinterpret_cast<P*>(dst + i) = *reinterpret_cast<const P*>(x + i);
+            continue;
+        }
+        const void* wv = kind == 0 ? a.q_w : a.k_w;
+        float r = 1.f;
         if (wv) {
-            float2 wl, wh;
-            if (a.w_is_f32) {
-                wl = *reinterpret_cast<const float2*>((const float*)wv + i);
-                wh = *reinterpret_cast<const float2*>((const float*)wv + i + half);
-            } else {
-                wl = pair_to_f32(*reinterpret_cast<const P*>((const T*)wv + i));
-                wh = pair_to_f32(*reinterpret_cast<const P*>((const T*)wv + i + half));
+            float ss = 0.f;
+            for (int i = lane * 2; i < hd; i += 64) {
+                const float2 t = pair_to_f32(*reinterpret_cast<const P*>(x + i));
+                ss = fmaf(t.x, t.x, ss);
+                ss = fmaf(t.y, t.y, ss);
             }
-            lo.x = to_f32(from_f32<T>(lo.x * r * wl.x)); lo.y = to_f32(from_f32<T>(lo.y * r * wl.y));
-            hi.x = to_f32(from_f32<T>(hi.x * r * wh.x)); hi.y = to_f32(from_f32<T>(hi.y * r * wh.y));
+            ss = warp_sum(ss);
+            r = rsqrtf(fmaf(ss, 1.0f / (float)hd, a.eps));
         }
-        if (cs) {
-            const float2 c = *reinterpret_cast<const float2*>(cs + i), sv = *reinterpret_cast<const float2*>(sn + i);
-            const float2 nlo = make_float2(lo.x * c.x - hi.x * sv.x, lo.y * c.y - hi.y * sv.y);
-            const float2 nhi = make_float2(hi.x * c.x + lo.x * sv.x, hi.y * c.y + lo.y * sv.y);
-            lo = nlo; hi = nhi;
+        for (int i = lane * 2; i < half; i += 64) {
+            float2 lo = pair_to_f32(*reinterpret_cast<const P*>(x + i));
+            float2 hi = pair_to_f32(*reinterpret_cast<const P*>(x + i + half));
+            if (wv) {
+                float2 wl, wh;
+                if (a.w_is_f32) {
+                    wl = *reinterpret_cast<const float2*>((const float*)wv + i);
+                    wh = *reinterpret_cast<const float2*>((const float*)wv + i + half);
+                } else {
+                    wl = pair_to_f32(*reinterpret_cast<const P*>((const T*)wv + i));
+                    wh = pair_to_f32(*reinterpret_cast<const P*>((const T*)wv + i + half));
+                }
+                lo.x = to_f32(from_f32<T>(lo.x * r * wl.x)); lo.y = to_f32(from_f32<T>(lo.y * r * wl.y));
+                hi.x = to_f32(from_f32<T>(hi.x * r * wh.x)); hi.y = to_f32(from_f32<T>(hi.y * r * wh.y));
+            }
+            if (cs) {
+                const float2 c = *reinterpret_cast<const float2*>(cs + i), sv = *reinterpret_cast<const float2*>(sn + i);
+                const float2 nlo = make_float2(lo.x * c.x - hi.x * sv.x, lo.y * c.y - hi.y * sv.y);
+                const float2 nhi = make_float2(hi.x * c.x + lo.x * sv.x, hi.y * c.y + lo.y * sv.y);
+                lo = nlo; hi = nhi;
+            }
+            const P plo = pair_from_f32<T>(lo.x, lo.y), phi = pair_from_f32<T>(hi.x, hi.y);
+            *reinterpret_cast<P*>(x + i) = plo;
+            *reinterpret_cast<P*>(x + i + half) = phi;
+            if (dst) { *reinterpret_cast<P*>(dst + i) = plo; *reinterpret_cast<P*>(dst + i + half) = phi; }
         }
-        const P plo = pair_from_f32<T>(lo.x, lo.y), phi = pair_from_f32<T>(hi.x, hi.y);
-        *reinterpret_cast<P*>(x + i) = plo;
-        *reinterpret_cast<P*>(x + i + half) = phi;
-        if (dst) { *reinterpret_cast<P*>(dst + i) = plo; *reinterpret_cast<P*>(dst + i + half) = phi; }
     }
 }
 
@@ -260,8 +263,12 @@ extern "C" int ti_qk_norm_rope_store(
         const bool pairs = head_dim % 4 == 0 && even(q, q_stride) && even(k, k_stride) && even(v, v_stride) &&
                            even(q_w, 0) && even(k_w, 0) && even(k_pages, 0) && even(v_pages, 0) &&
                            (reinterpret_cast<uintptr_t>(cos_t) % 8 == 0) && (reinterpret_cast<uintptr_t>(sin_t) % 8 == 0);
-        if (pairs)
-            TI_CUDA(ti_launch(rope_store_pairs_kernel<T>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, a));
+        if (pairs) {
+            // few tokens: many warps per token so that a token's heads go side by side
+            int w = M >= 1024 ? 4 : 16;
+            if (w > per_tok) w = per_tok;
+            TI_CUDA(ti_launch(rope_store_pairs_kernel<T>, dim3((unsigned)M), dim3(w * 32), 0, stream, a));
+        }
         else
             TI_CUDA(ti_launch(rope_store_kernel<T>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, a));
         TI_CHECK_LAUNCH("qk_norm_rope_store");
