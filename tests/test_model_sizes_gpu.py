@@ -19,15 +19,23 @@ CFG = {
 }
 
 
-@pytest.fixture(scope="module")
-def engines():
+# one layer of the 32B shape: 64 heads over 8 kv heads (8 query heads per kv head), untied head
+CFG_32B = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 1, "hidden_size": 5120,
+    "num_attention_heads": 64, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 25600,
+    "vocab_size": 32000, "rope_theta": 1e6, "rms_norm_eps": 1e-6, "max_position_embeddings": 40960,
+    "tie_word_embeddings": False,
+}
+
+
+def _engines(cfg):
     from toyinfer_b200 import models  # noqa: F401
     from toyinfer_b200.config import Qwen3Config, resolve_architecture
     from toyinfer_b200.engine import Engine
     from toyinfer_b200.parts.model import DecoderModel
     from toyinfer_b200.weights import random_parameters
     arch = resolve_architecture("Qwen3ForCausalLM")
-    spec = arch.describe(Qwen3Config.from_dict(dict(CFG)))
+    spec = arch.describe(Qwen3Config.from_dict(dict(cfg)))
     out = {}
     ref = None
     for dt in (torch.bfloat16, torch.float32):
@@ -52,11 +60,13 @@ def _close(bf, fp, what):
         assert fp[i, picked[i]] >= fp[i, top[i]] - 0.03 * scale[i, 0], what
 
 
-def test_prompts_then_decoding_agree_between_the_engines(engines):
+@pytest.mark.parametrize("cfg", [CFG, CFG_32B], ids=["4B-shape", "32B-shape"])
+def test_prompts_then_decoding_agree_between_the_engines(cfg):
     import toyinfer_b200.kernels as K
+    engines = _engines(cfg)
     g = torch.Generator().manual_seed(5)
     lens, dec = [700, 129, 1], 6
-    seqs = [torch.randint(0, CFG["vocab_size"], (n + dec,), generator=g).tolist() for n in lens]
+    seqs = [torch.randint(0, cfg["vocab_size"], (n + dec,), generator=g).tolist() for n in lens]
     results = {}
     for dt, eng in engines.items():
         slots = [eng.new_sequence() for _ in seqs]
@@ -67,5 +77,5 @@ def test_prompts_then_decoding_agree_between_the_engines(engines):
             eng.end_sequence(s)
         K.check_status()
         results[dt] = torch.cat(rows)
-    _close(results[torch.bfloat16], results[torch.float32], "4B-shaped layers")
+    _close(results[torch.bfloat16], results[torch.float32], "real layer sizes")
     assert engines[torch.bfloat16].graph_replays > 0

@@ -4,15 +4,15 @@
 // (reference: src/prefill.cu:224-379); head_dim 128, bfloat16.
 //
 // A block owns 128 queries of one head (grid: query tiles from the last to the first, heads,
-// sequences) and walks over key/value tiles of 128 positions; tiles that the causal mask or the
+// sequences) and walks over key/value tiles of 64 positions; tiles that the causal mask or the
 // window excludes entirely are never loaded.  Roles, 192 threads:
 //   warp 0     TMA: the query tile once, then K and V tiles into a ring of two stages;
 //   warp 1     one lane issues the MMAs: S_{j+1} = Q K_{j+1}^T goes out before O += P_j V_j, into
 //              the other of two score buffers in tensor memory, so the tensor cores work on the
 //              next tile's scores while the softmax warps are busy with this tile's;
-//   warps 2-5  softmax: thread = query row = TMEM lane.  It reads its row of S (a first pass for
-//              the maximum, a second for 2^(s - m)), writes P as bfloat16 into shared memory in
-//              the swizzled K-major layout the second MMA reads, and keeps the running sum.
+//   warps 2-5  softmax: thread = query row = TMEM lane.  It reads its row of S once, takes the
+//              maximum, writes P = 2^(s - m) as bfloat16 back into tensor memory over the scores it
+//              has just read (the second MMA takes its A operand from there), and keeps the sum.
 // The output accumulator stays in tensor memory for the whole row of tiles.  It is rescaled
 // only when a row's maximum has grown by more than 2^8 since the scale was last fixed (P then
 // holds values up to 256 instead of 1, which float32 sums and bfloat16 products carry without
@@ -40,10 +40,10 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 // Shared memory of a block (all dynamic, so that two blocks fit an SM): the query tile, two
-// stages of (K tile, V tile), the P tile, then the mbarriers.
+// stages of (K tile, V tile), then the mbarriers.
 template <int HD> struct Smem {
-    static constexpr int Q_BYTES = BQ * HD * 2, KV_BYTES = BKV * HD * 2, P_BYTES = BQ * BKV * 2;
-    static constexpr int Q_OFF = 0, KV_OFF = Q_BYTES, P_OFF = KV_OFF + 4 * KV_BYTES, BAR_OFF = P_OFF + P_BYTES;
+    static constexpr int Q_BYTES = BQ * HD * 2, KV_BYTES = BKV * HD * 2;
+    static constexpr int Q_OFF = 0, KV_OFF = Q_BYTES, BAR_OFF = KV_OFF + 4 * KV_BYTES;
     static constexpr int TOTAL = BAR_OFF + 256;
 };
 
@@ -60,16 +60,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char* q_s = smem + L::Q_OFF;
     unsigned char* kv_s = smem + L::KV_OFF;                // stage s: K at kv_s + s * 2 * KV_BYTES, V after it
-    unsigned char* p_s = smem + L::P_OFF;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;      // [2]
     uint64_t* v_full = bars + 3;      // [2]
     uint64_t* kv_empty = bars + 5;    // [2]
-    uint64_t* s_full = bars + 7;      // [2]
-    uint64_t* s_empty = bars + 9;     // [2]
-    uint64_t* p_full = bars + 11;
-    uint64_t* p_empty = bars + 12;
+    uint64_t* s_full = bars + 7;      // [2] scores of a tile are in tensor memory
+    uint64_t* p_full = bars + 9;      // [2] the softmax warps have replaced them by P
+    uint64_t* pv_done = bars + 11;    //     a tile's second product has finished (one phase per tile)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -81,10 +79,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; s++) {
             mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1);
-            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
+            mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 4);
         }
-        mbar_init(p_full, 4);
-        mbar_init(p_empty, 1);
+        mbar_init(pv_done, 1);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -130,7 +127,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         if (lane == 0) {
             constexpr uint32_t idesc_s = instr_desc_bf16(BKV, false);    // S: N = positions, K tile K-major
             constexpr uint32_t idesc_o = instr_desc_bf16(HD, true);      // O: N = head elements, V tile MN-major
-            const uint32_t qa = smem_u32(q_s), pa = smem_u32(p_s);
+            const uint32_t qa = smem_u32(q_s);
             auto issue_s = [&](int j) {       // S_j = Q K_j^T into score buffer j & 1
                 const uint32_t ka = smem_u32(kv_s + (size_t)(j & 1) * 2 * KV_BYTES);
 #pragma unroll
@@ -147,24 +144,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             }
             for (int j = 0; j < n_tiles && ok; j++) {
                 if (j + 1 < n_tiles) {
+                    // its score buffer held P of tile j-1; the second product of that tile was issued
+                    // before this one and MMAs run in the order of issue
                     const int sb = (j + 1) & 1, u = (j + 1) >> 1;
-                    if (!mbar_wait(&k_full[sb], (uint32_t)(u & 1)) || !mbar_wait(&s_empty[sb], (uint32_t)((u & 1) ^ 1))) {
-                        ti_report(status, TI_STATUS_TMA_WAIT); ok = false; break;
-                    }
+                    if (!mbar_wait(&k_full[sb], (uint32_t)(u & 1))) { ti_report(status, TI_STATUS_TMA_WAIT); ok = false; break; }
                     tc_fence_after();
                     issue_s(j + 1);
                 }
-                if (!mbar_wait(p_full, (uint32_t)(j & 1)) || !mbar_wait(&v_full[j & 1], (uint32_t)((j >> 1) & 1))) {
+                if (!mbar_wait(&p_full[j & 1], (uint32_t)((j >> 1) & 1)) || !mbar_wait(&v_full[j & 1], (uint32_t)((j >> 1) & 1))) {
                     ti_report(status, TI_STATUS_PIPE_WAIT); ok = false; break;
                 }
                 tc_fence_after();
                 const uint32_t va = smem_u32(kv_s + (size_t)(j & 1) * 2 * KV_BYTES + KV_BYTES);
+                const uint32_t p_tmem = tmem + (j & 1) * S_COLS;       // P: two bfloat16 per column, 8 columns per step
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; kk++)        // 16 positions per step
-                    tc_mma_bf16(tmem + O_COL, smem_desc_sw128(pa + kk * 32), smem_desc_mn_sw128(va + kk * 16 * 128, KBOX),
-                                idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                    tc_mma_bf16_ts(tmem + O_COL, p_tmem + kk * 8, smem_desc_mn_sw128(va + kk * 16 * 128, KBOX),
+                                   idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                 tc_commit(&kv_empty[j & 1]);     // the stage's K and V have been read
-                tc_commit(p_empty);              // so has P, and O holds this tile's contribution
+                tc_commit(pv_done);              // and O holds this tile's contribution
             }
         }
     } else if (active) {
@@ -194,10 +192,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #pragma unroll
                 for (int e = 0; e < 32; e++) { v[e] = lo[e] * scale2; v[32 + e] = hi[e] * scale2; }
             }
-            // the score buffer may be overwritten by the tile after next
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[sb]);
             if (edge) {
 #pragma unroll
                 for (int e = 0; e < BKV; e++) {
@@ -230,12 +224,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 pk[e >> 1] = *reinterpret_cast<uint32_t*>(&t0);
                 pk[(e >> 1) + 1] = *reinterpret_cast<uint32_t*>(&t1);
             }
-            // P's buffer and O are free once the previous tile's second product has finished
-            if (j > 0 && !mbar_wait(p_empty, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                // O may be touched once the previous tile's second product has finished
+                if (!mbar_wait(pv_done, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; c++) {
                     float o[32];
@@ -245,20 +239,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     tmem_st32(tmem + O_COL + lane_base + c * 32, o);
                 }
             }
-            // P as bfloat16 into shared memory: row r, 16-byte chunk cc (8 positions) at cc ^ (r % 8)
-#pragma unroll
-            for (int cc = 0; cc < BKV / 8; cc++)
-                *reinterpret_cast<uint4*>(p_s + r * 128 + ((cc ^ (r & 7)) << 4)) =
-                    make_uint4(pk[cc * 4], pk[cc * 4 + 1], pk[cc * 4 + 2], pk[cc * 4 + 3]);
+            // P over the scores just read: this row's 64 values as 32 columns of bfloat16 pairs
+            tmem_st32_bits(s_addr, pk);
             l_run = l_run * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             m_used = m_new;
             tc_fence_before();
-            fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(&p_full[sb]);
         }
         if (ok && n_tiles > 0) {
-            if (!mbar_wait(p_empty, (uint32_t)((n_tiles - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            if (!mbar_wait(pv_done, (uint32_t)((n_tiles - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
