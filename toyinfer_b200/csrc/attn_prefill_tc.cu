@@ -144,10 +144,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             }
             for (int j = 0; j < n_tiles && ok; j++) {
                 if (j + 1 < n_tiles) {
-                    // its score buffer held P of tile j-1; the second product of that tile was issued
-                    // before this one and MMAs run in the order of issue
+                    // its score buffer holds P of tile j-1: that tile's second product must have read it
                     const int sb = (j + 1) & 1, u = (j + 1) >> 1;
-                    if (!mbar_wait(&k_full[sb], (uint32_t)(u & 1))) { ti_report(status, TI_STATUS_TMA_WAIT); ok = false; break; }
+                    if (!mbar_wait(&k_full[sb], (uint32_t)(u & 1)) || (j > 0 && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1)))) {
+                        ti_report(status, TI_STATUS_TMA_WAIT); ok = false; break;
+                    }
                     tc_fence_after();
                     issue_s(j + 1);
                 }
@@ -224,11 +225,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 pk[e >> 1] = *reinterpret_cast<uint32_t*>(&t0);
                 pk[(e >> 1) + 1] = *reinterpret_cast<uint32_t*>(&t1);
             }
+            // Every tile's completion is waited for, in order (a parity wait can only tell one phase
+            // from the next); by now the previous tile's second product has long been issued.
+            if (j > 0 && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                // O may be touched once the previous tile's second product has finished
-                if (!mbar_wait(pv_done, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+                // O may be touched: the previous tile's second product has finished
                 tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; c++) {
