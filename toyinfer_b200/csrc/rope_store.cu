@@ -125,8 +125,9 @@ template <typename T> __device__ __forceinline__ typename Pair<T>::type pair_fro
 template <> __device__ __forceinline__ float2 pair_from_f32<float>(float a, float b) { return make_float2(a, b); }
 template <> __device__ __forceinline__ __nv_bfloat162 pair_from_f32<bf16>(float a, float b) { return __floats2bfloat162_rn(a, b); }
 
-// One block per token: the token's position, slot and page are looked up once, then the
-// block's warps share the token's heads between them.
+// Blocks (token, group): the token's position, slot and page are looked up once per block, then
+// the block's warps share the heads of its group.  One group per token when there are many tokens
+// (the look-up is amortised over all heads), one head per warp when there are few (short chains).
 template <typename T>
 __global__ void rope_store_pairs_kernel(RopeStoreArgs a) {
     ti_pdl_trigger();
@@ -164,7 +165,7 @@ __global__ void rope_store_pairs_kernel(RopeStoreArgs a) {
     const float* cs = a.cos_t ? a.cos_t + (size_t)pos * half : nullptr;
     const float* sn = a.sin_t ? a.sin_t + (size_t)pos * half : nullptr;
 
-    for (int item = warp; item < per_tok; item += n_warps) {
+    for (int item = blockIdx.y * n_warps + warp; item < per_tok; item += n_warps * gridDim.y) {
         int h = item, kind;  // 0 q, 1 k, 2 v
         if (h < heads_q) kind = 0;
         else if (h < heads_q + heads_k) { kind = 1; h -= heads_q; }
@@ -264,10 +265,9 @@ extern "C" int ti_qk_norm_rope_store(
                            even(q_w, 0) && even(k_w, 0) && even(k_pages, 0) && even(v_pages, 0) &&
                            (reinterpret_cast<uintptr_t>(cos_t) % 8 == 0) && (reinterpret_cast<uintptr_t>(sin_t) % 8 == 0);
         if (pairs) {
-            // few tokens: many warps per token so that a token's heads go side by side
-            int w = M >= 1024 ? 4 : 16;
-            if (w > per_tok) w = per_tok;
-            TI_CUDA(ti_launch(rope_store_pairs_kernel<T>, dim3((unsigned)M), dim3(w * 32), 0, stream, a));
+            const int w = 4;
+            const int groups = M >= 1024 ? 1 : (per_tok + w - 1) / w;
+            TI_CUDA(ti_launch(rope_store_pairs_kernel<T>, dim3((unsigned)M, (unsigned)groups), dim3(w * 32), 0, stream, a));
         }
         else
             TI_CUDA(ti_launch(rope_store_kernel<T>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, a));
