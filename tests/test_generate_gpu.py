@@ -86,6 +86,37 @@ def test_stop_token_and_queue_of_batches(model_folders):
     assert llm.engine.cache.slots.n_free == llm.engine.cache.n_slots
 
 
+def test_starting_the_next_step_ahead_changes_no_token(model_folders):
+    """The loop starts each decode step from the drawn tokens on the device before it has read
+    them.  The same requests through a stepper without that ability (every token read first)
+    give the same tokens, with sequences that stop in the middle of a batch."""
+    from toyinfer_b200 import LLM, SamplingParams
+    from toyinfer_b200.engine.generate import GenerationLoop
+    from toyinfer_b200.sampling import Sampler
+
+    class OneByOne:
+        def __init__(self, inner):
+            self.new_sequence, self.end_sequence = inner.new_sequence, inner.end_sequence
+            self.step, self.sample = inner.step, inner.sample
+
+    for name, dtype, params in (("A", "float32", SamplingParams(temperature=0.0)),
+                                ("C", "bfloat16", SamplingParams(temperature=0.9, top_k=12, top_p=0.9, seed=5))):
+        llm = LLM(model_folders[name], dtype=dtype, max_seq_len=128, max_batch=4, max_tokens=64 * 16)
+        prompts = prompts_for(name, [5, 9, 2, 30, 4, 11], seed=56)
+        free = llm.generate(prompts, params, max_new_tokens=12, ignore_eos=True)
+        stops = [free[1].tokens[3], free[4].tokens[7]]
+        ahead = llm.generate(prompts, params, max_new_tokens=12, stop_token_ids=stops)
+        assert any(r.finish_reason == "stop" for r in ahead) and any(r.finish_reason == "length" for r in ahead)
+        e = llm.engine
+        llm._stepper.sampler = Sampler(params, e.device)
+        loop = GenerationLoop(OneByOne(llm._stepper), set(llm.stop_token_ids) | set(stops), e.max_batch, e.max_seq_len,
+                              e.cache.max_tokens)
+        plain_order = loop.run(prompts, 12)
+        assert [(r.tokens, r.finish_reason) for r in ahead] == [(r.tokens, r.finish_reason) for r in plain_order]
+        assert loop.stats.decode_steps <= llm.last_stats.decode_steps
+        assert e.cache.slots.n_free == e.cache.n_slots
+
+
 def test_command_line(model_folders):
     f = model_folders["A"]
     prompts = prompts_for("A", [6, 3], seed=54)

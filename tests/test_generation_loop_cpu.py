@@ -109,6 +109,58 @@ def test_slots_come_back_after_an_error():
     assert not st.live
 
 
+class AheadStepper(ScriptedStepper):
+    """The scripted stepper with the calls that let the loop start a step from tokens it
+    has not read yet.  ``step_from`` gets the handle of the draw and works the tokens out
+    itself, as a device would; it records which steps were started that way."""
+
+    def __init__(self):
+        super().__init__()
+        self.from_handle = []
+
+    def draw(self, logits, keys, steps):
+        return list(self.sample(logits, keys, steps))
+
+    def step_from(self, slots, handle):
+        assert len(slots) == len(handle)
+        self.from_handle.append(len(self.steps))
+        return self.step([(s, [t]) for s, t in zip(slots, handle)], [[0] for _ in slots])
+
+    def read(self, handle):
+        return list(handle)
+
+    def rows(self, logits, indices):
+        return [logits[r] for r in indices]
+
+
+@pytest.mark.parametrize("prompts, kw, max_new", [
+    ([[10], [50, 51], [20, 0, 0], [30]], dict(stop_ids=[13, 55], max_batch=3, max_seq_len=64), 6),
+    ([[10], [1, 2, 3, 4, 5, 6], [9] * 8], dict(stop_ids=[12], max_batch=4, max_seq_len=8, ignore_eos=True), 5),
+    ([[10, 20, 30], [40]], dict(stop_ids=[], max_batch=4, max_seq_len=64, dedicated_prefill=False), 3),
+    ([[10], [11], [12]], dict(stop_ids=[14], max_batch=3, max_seq_len=64), 9),      # three stops in three steps running
+    ([[7]], dict(stop_ids=[], max_batch=1, max_seq_len=64), 1),
+])
+def test_starting_ahead_changes_no_result(prompts, kw, max_new):
+    plain_st, ahead_st = ScriptedStepper(), AheadStepper()
+    a = GenerationLoop(plain_st, capacity_tokens=10 ** 6, **kw).run(prompts, max_new_tokens=max_new)
+    b = GenerationLoop(ahead_st, capacity_tokens=10 ** 6, **kw).run(prompts, max_new_tokens=max_new)
+    assert [(r.tokens, r.finish_reason) for r in a] == [(r.tokens, r.finish_reason) for r in b]
+    assert not ahead_st.live and sorted(ahead_st.ended) == sorted(plain_st.ended)
+
+
+def test_starting_ahead_is_used_and_bounded():
+    st = AheadStepper()
+    loop = GenerationLoop(st, stop_ids=[13], max_batch=2, max_seq_len=64, capacity_tokens=10 ** 6)
+    res = loop.run([[10], [20]], max_new_tokens=5)
+    assert res[0].tokens == [11, 12] and res[1].tokens == [21, 22, 23, 24, 25]
+    # steps: prompts; then steps started ahead, the third of them still with the sequence that
+    # had drawn its stop token; none is started when a sequence is about to reach its length
+    assert [len(s) for s in st.steps] == [2, 2, 2, 2, 1]
+    assert st.from_handle == [1, 2, 3, 4]
+    assert st.steps[3] == [(0, [13]), (1, [23])]            # one step too many for slot 0, dropped
+    assert len(st.steps) == 5                               # no step after the last token
+
+
 def test_generation_through_the_engine_matches_plain(monkeypatch, model_folders):
     """The real loop over the real engine (CPU stand-in kernels): greedy tokens equal the
     plain implementation's, for a batch of unequal prompts with a stop token in play."""

@@ -411,6 +411,32 @@ def test_argmax(K, V):
     assert got == [plain.argmax(r) for r in x]
 
 
+def test_argmax_ties_across_blocks_and_odd_rows(K):
+    """A row is scanned by several blocks: equal maxima far apart, zeros of both signs, NaNs,
+    a row of -inf, rows that start off a 16-byte boundary, many rows (one block each), and
+    the same call again (the kernel leaves its scratch as it found it)."""
+    V = 151936
+    x = randn(6, V, seed=71) - 100.0
+    x[0, 140000] = x[0, 3] = 7.0                       # tie: first and last block
+    x[1, :] = -1.0
+    x[1, 99999], x[1, 12345] = 0.0, -0.0               # -0 at the lower index equals +0: it wins
+    x[2, 5] = float("nan")
+    x[2, 77777] = 3.0
+    x[3, :] = float("-inf")                            # first index of the maximum: 0
+    x[4, V - 1] = 9.0
+    x[5, :] = float("nan")
+    want = [3, 12345, 77777, 0, V - 1, 0]
+    xd = dev(x)
+    for _ in range(3):
+        assert K.argmax(xd).cpu().tolist() == want
+    odd = torch.zeros(6, V + 3, device="cuda")
+    odd[:, 1:V + 1] = xd
+    assert K.argmax(odd[:, 1:V + 1]).cpu().tolist() == want
+    many = randn(700, 333, seed=72)
+    assert K.argmax(dev(many)).cpu().tolist() == [plain.argmax(r) for r in many]
+    assert K.argmax(xd[:1]).cpu().tolist() == want[:1]
+
+
 @pytest.mark.parametrize("V,top_k,top_p,temp", [(300, 0, 1.0, 0.8), (300, 20, 0.95, 0.6), (5000, 50, 0.5, 1.3),
                                                 (151936, 20, 0.95, 0.6), (1000, 1000, 1.0, 0.7),
                                                 (2000, 1024, 0.9, 1.0)])

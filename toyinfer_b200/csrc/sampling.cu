@@ -66,18 +66,41 @@ __device__ V block_exclusive_scan(V v, V* total, V* sm /* 33 entries */) {
     return sm[warp] + inc - v;
 }
 
-__global__ void __launch_bounds__(SB) argmax_kernel(const float* __restrict__ logits, long long ld, int V,
-                                                    int* __restrict__ out) {
+// The maximum of a row with its index as one 64-bit word that atomicMax can order: the
+// value's order-preserving key above, the index counted down below, so that among equal
+// values the lower index is the larger word.  -0 counts as +0, as in a float comparison.
+__device__ __forceinline__ unsigned long long pack_best(float v, int i) {
+    if (v == 0.f) v = 0.f;
+    return ((unsigned long long)order_key(v) << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)i);
+}
+
+// Grid (rows, chunks), 256 threads.  Each block finds the first maximum of its chunk and
+// folds it into the row's word; the block that arrives last (a ticket per row) writes the
+// index and leaves word and ticket zero for the next call.  NaNs are never chosen; a row of
+// nothing but NaNs gives index 0.
+constexpr int AB = 256;
+__global__ void __launch_bounds__(AB) argmax_kernel(const float* __restrict__ logits, long long ld, int V, int per,
+                                                    unsigned long long* __restrict__ best_word,
+                                                    int* __restrict__ tickets, int* __restrict__ out) {
     ti_pdl_trigger();
-    __shared__ float bv[32];
-    __shared__ int bi[32];
+    __shared__ float bv[AB / 32];
+    __shared__ int bi[AB / 32];
     ti_pdl_sync();
-    const float* x = logits + (size_t)blockIdx.x * ld;
+    const int row = blockIdx.x;
+    const float* x = logits + (size_t)row * ld;
+    const int lo = blockIdx.y * per, hi = min(V, lo + per);
     float best = -INFINITY;
     int idx = INT_MAX;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = x[i];
-        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    auto take = [&](float v, int i) { if (v > best || (v == best && i < idx)) { best = v; idx = i; } };
+    if ((ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0 && (per & 3) == 0) {
+        const int hi4 = lo + ((hi - lo) & ~3);
+        for (int i = lo + threadIdx.x * 4; i < hi4; i += AB * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(x + i);
+            take(v.x, i); take(v.y, i + 1); take(v.z, i + 2); take(v.w, i + 3);
+        }
+        for (int i = hi4 + threadIdx.x; i < hi; i += AB) take(x[i], i);
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += AB) take(x[i], i);
     }
     auto better = [](float v, int i, float w, int j) { return v > w || (v == w && i < j); };
 #pragma unroll
@@ -90,15 +113,28 @@ __global__ void __launch_bounds__(SB) argmax_kernel(const float* __restrict__ lo
     if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
     __syncthreads();
     if (warp == 0) {
-        best = lane < (blockDim.x >> 5) ? bv[lane] : -INFINITY;
-        idx = lane < (blockDim.x >> 5) ? bi[lane] : INT_MAX;
+        best = lane < AB / 32 ? bv[lane] : -INFINITY;
+        idx = lane < AB / 32 ? bi[lane] : INT_MAX;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float w = __shfl_xor_sync(0xffffffffu, best, o);
             const int j = __shfl_xor_sync(0xffffffffu, idx, o);
             if (better(w, j, best, idx)) { best = w; idx = j; }
         }
-        if (lane == 0) out[blockIdx.x] = idx == INT_MAX ? 0 : idx;
+        if (lane == 0) {
+            if (gridDim.y == 1) {
+                out[row] = idx == INT_MAX ? 0 : idx;
+                return;
+            }
+            if (idx != INT_MAX) atomicMax(best_word + row, pack_best(best, idx));
+            __threadfence();
+            if (atomicAdd(tickets + row, 1) == (int)gridDim.y - 1) {
+                __threadfence();
+                const unsigned long long w = atomicExch(best_word + row, 0ull);
+                out[row] = w ? (int)(0xFFFFFFFFu - (unsigned)(w & 0xFFFFFFFFull)) : 0;
+                tickets[row] = 0;
+            }
+        }
     }
 }
 
@@ -281,10 +317,25 @@ __global__ void __launch_bounds__(SB) sample_full_kernel(SampleArgs a) {
 }
 }  // namespace
 
-extern "C" int ti_argmax(const float* logits, long long ld, int R, int V, int* out, cudaStream_t stream) {
+// best_word[R] (64-bit) and tickets[R] are scratch that is zero before the first call and
+// left zero; calls that share them must be on one stream.  They may be null: one block per
+// row then.
+extern "C" int ti_argmax(const float* logits, long long ld, int R, int V, int sms, unsigned long long* best_word,
+                         int* tickets, int* out, cudaStream_t stream) {
     if (R == 0) return 0;
     TI_REQUIRE(R > 0 && V > 0 && ld >= V, "argmax: bad sizes R=%d V=%d ld=%lld", R, V, ld);
-    TI_CUDA(ti_launch(argmax_kernel, dim3(R), dim3(SB), 0, stream, logits, ld, V, out));
+    int chunks = 1;
+    if (best_word && tickets) {
+        chunks = (2 * (sms > 0 ? sms : 1)) / R;                      // about two blocks per SM
+        const int most = (V + 4 * AB - 1) / (4 * AB);                // at least one vector per thread
+        if (chunks > most) chunks = most;
+        if (chunks > 64) chunks = 64;
+        if (chunks < 1) chunks = 1;
+    }
+    int per = ((V + chunks - 1) / chunks + 3) & ~3;
+    chunks = (V + per - 1) / per;
+    TI_REQUIRE(chunks <= 65535, "argmax: too many chunks");
+    TI_CUDA(ti_launch(argmax_kernel, dim3(R, chunks), dim3(AB), 0, stream, logits, ld, V, per, best_word, tickets, out));
     TI_CHECK_LAUNCH("argmax");
     return 0;
 }

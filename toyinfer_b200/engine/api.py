@@ -24,6 +24,8 @@ class _Stepper:
 
     def __init__(self, engine: Engine, sampler: Sampler):
         self.engine, self.sampler = engine, sampler
+        self._side = None
+        self._host = None
 
     def new_sequence(self) -> int:
         return self.engine.new_sequence()
@@ -36,6 +38,37 @@ class _Stepper:
 
     def sample(self, logits, keys, steps) -> List[int]:
         return self.sampler.sample(logits, keys, steps).tolist()   # device -> host, waits for the step
+
+    # -- the next step started from tokens that are still on the device ---------------------
+    def draw(self, logits, keys, steps):
+        """Draws on the device; the handle is read later, beside whatever was started since."""
+        ids = self.sampler.sample(logits, keys, steps)
+        if ids.device.type != "cuda":
+            return ids, None
+        drawn = torch.cuda.Event()
+        drawn.record()
+        return ids, drawn
+
+    def step_from(self, slots, handle):
+        return self.engine.step([(s, None) for s in slots], [[0] for _ in slots], token_source=handle[0])
+
+    def read(self, handle) -> List[int]:
+        ids, drawn = handle
+        if drawn is None:
+            return ids.tolist()
+        # on a stream of its own, after the draw only: the step started meanwhile is not waited for
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=ids.device)
+            self._host = torch.empty(self.engine.max_batch, dtype=torch.int32, pin_memory=True)
+        n = ids.shape[0]
+        with torch.cuda.stream(self._side):
+            self._side.wait_event(drawn)
+            self._host[:n].copy_(ids, non_blocking=True)
+        self._side.synchronize()
+        return self._host[:n].tolist()
+
+    def rows(self, logits, indices):
+        return logits[torch.tensor(indices, dtype=torch.long, device=logits.device)]
 
 
 def default_max_tokens(engine_kw: dict, model, max_batch: int, max_seq_len: int) -> int:
@@ -82,6 +115,7 @@ class LLM:
         self.engine = Engine(model, max_tokens=max_tokens, max_batch=max_batch, max_seq_len=msl,
                              use_cuda_graph=enable_cuda_graph)
         self.config = cfg
+        self._stepper = _Stepper(self.engine, None)
         self.use_dedicated_prefill = use_dedicated_prefill
         self.last_stats: Optional[GenerationStats] = None
 
@@ -96,7 +130,8 @@ class LLM:
         stops = set(self.stop_token_ids)
         stops.update(stop_token_ids or ())
         e = self.engine
-        loop = GenerationLoop(_Stepper(e, Sampler(sampling, e.device)), stops, e.max_batch, e.max_seq_len,
+        self._stepper.sampler = Sampler(sampling, e.device)
+        loop = GenerationLoop(self._stepper, stops, e.max_batch, e.max_seq_len,
                               e.cache.max_tokens, ignore_eos=ignore_eos,
                               dedicated_prefill=self.use_dedicated_prefill)
         out = loop.run(prompts, max_new_tokens)

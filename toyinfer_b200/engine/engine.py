@@ -113,19 +113,35 @@ class Engine:
         return self.cache.length[slot]
 
     # -- one step -------------------------------------------------------------------
-    def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
-             want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[Tuple[int, Optional[Sequence[int]]]],
+             want: Optional[Sequence[Sequence[int]]] = None,
+             token_source: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """entries: (slot, next tokens) per sequence.  want: per entry the places among its
         tokens whose logits are asked for (None: the last place of each).  Returns float32
         [wanted, vocab] on the device, or None when nothing is wanted.  The tensor may be
-        a buffer that the next step overwrites: use or copy it before stepping again."""
+        a buffer that the next step overwrites: use or copy it before stepping again.
+
+        With ``token_source`` (int32 on the device, one id per entry, in the entries' order)
+        every entry's tokens are None and each sequence goes on by the id found there when
+        the step runs: tokens that an earlier kernel drew need not pass through the host.
+        Their range is the caller's duty."""
         n = len(entries)
         if n == 0:
             return None
         if n > self.max_batch:
             raise StepError(f"a step of {n} sequences exceeds max_batch {self.max_batch}")
         slots = [int(s) for s, _ in entries]
-        tokens = [list(t) for _, t in entries]
+        if token_source is not None:
+            if any(t is not None for _, t in entries):
+                raise StepError("with token_source every entry's tokens are None")
+            if token_source.dtype != torch.int32 or token_source.dim() != 1 or token_source.shape[0] != n \
+                    or token_source.device.type != self.device.type:
+                raise StepError(f"token_source must be int32 [{n}] on {self.device}")
+            tokens = [[0] for _ in entries]
+        else:
+            if any(t is None for _, t in entries):
+                raise StepError("an entry without tokens needs token_source")
+            tokens = [list(t) for _, t in entries]
         if len(set(slots)) != n:
             raise StepError("a slot appears twice in one step")
         for s in slots:
@@ -138,7 +154,7 @@ class Engine:
                 if not (0 <= tok < self.spec.vocab_size):
                     raise StepError(f"slot {s}: token id {tok} is outside the vocabulary of {self.spec.vocab_size}")
         starts = [self.cache.length[s] for s in slots]
-        if all(st == 0 for st in starts):
+        if all(st == 0 for st in starts) and token_source is None:
             mode = "start"
         elif all(len(t) == 1 for t in tokens):
             mode = "extend"
@@ -161,7 +177,7 @@ class Engine:
         self.cache.flush()
 
         if mode == "extend" and self.use_cuda_graph:
-            logits_all = self._decode_graph(slots, starts, tokens)
+            logits_all = self._decode_graph(slots, starts, tokens, token_source)
             rows = [i for i, w in enumerate(want) if w]
             if not rows:
                 logits = None
@@ -171,6 +187,8 @@ class Engine:
                 logits = logits_all[torch.tensor(rows, device=self.device)]
         else:
             batch = self._eager_batch(mode, slots, starts, tokens)
+            if token_source is not None:
+                batch.token_ids[:n].copy_(token_source)
             h, delta = self.model.forward_hidden(batch, self.memories)
             rows, o = [], 0
             for w, t in zip(want, tokens):
@@ -205,13 +223,13 @@ class Engine:
             buf = self._eager_bufs[key] = BatchBuffers(key[0], key[1], self.device)
         return fill_batch(buf, mode, slots, starts, tokens, self.cache.scratch_slot, self.max_seq_len)
 
-    def _decode_graph(self, slots, starts, tokens) -> torch.Tensor:
+    def _decode_graph(self, slots, starts, tokens, token_source=None) -> torch.Tensor:
         n = len(slots)
         b = _bucket(n, self.max_batch)
         g = self._graphs.get(b)
         if g is None:
             g = self._graphs[b] = _DecodeGraph(self, b)
-        return g.run(slots, starts, tokens)
+        return g.run(slots, starts, tokens, token_source)
 
 
 class _DecodeGraph:
@@ -231,11 +249,13 @@ class _DecodeGraph:
         h, delta = e.model.forward_hidden(batch, e.memories)
         return e.model.logits(h, delta, self.rows)
 
-    def run(self, slots, starts, tokens) -> torch.Tensor:
+    def run(self, slots, starts, tokens, token_source=None) -> torch.Tensor:
         e = self.engine
         pad = self.bucket - len(slots)
         batch = fill_batch(self.buf, "extend", slots, starts, tokens, e.cache.scratch_slot,
                            e.max_seq_len, pad_seqs=pad)
+        if token_source is not None:
+            batch.token_ids[:len(slots)].copy_(token_source)      # after the upload, before the replay
         if self.graph is None:
             # one eager run first: it is this step's result, and it lets every kernel do its
             # one-time set-up outside the capture

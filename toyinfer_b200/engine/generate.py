@@ -12,6 +12,14 @@ The loop only decides; it runs steps and draws tokens through a ``stepper`` with
 ``new_sequence()``, ``end_sequence(slot)``, ``step(entries, want) -> logits`` and
 ``sample(logits, keys, steps) -> list of ints``, so its decisions can be tested
 without a device.
+
+A stepper may also offer ``draw(logits, keys, steps) -> handle``, ``step_from(slots,
+handle) -> logits``, ``read(handle) -> list of ints`` and ``rows(logits, indices)``.
+Then, while every live sequence is decoding and none is about to reach a length limit,
+the loop starts the next step from the drawn tokens where they lie (on the device)
+before it reads them: the device goes on while the host decides.  A sequence that turns
+out to have drawn a stop token has then run one step too many; its row of that step is
+dropped and its slot is released as usual, and no other sequence's result depends on it.
 """
 from __future__ import annotations
 
@@ -109,8 +117,14 @@ class GenerationLoop:
             self._run_batch(batch, prompts, keys, max_new_tokens, results)
         return results
 
+    def _at_limit_after_next(self, res: GenerationResult, prompt_len: int, max_new: int) -> bool:
+        """True when the sequence ends by a length limit with the token it draws now."""
+        n = len(res.tokens) + 1
+        return n >= max_new or prompt_len + n >= self.max_seq_len
+
     def _run_batch(self, batch, prompts, keys, max_new, results) -> None:
         st = self.stepper
+        can_look_ahead = all(hasattr(st, name) for name in ("draw", "step_from", "read", "rows"))
         self.stats.batches += 1
         live: List[Tuple[int, int]] = []          # (request index, slot)
         for i in batch:
@@ -120,25 +134,47 @@ class GenerationLoop:
             live.append((i, st.new_sequence()))
         fed = {i: 0 for i, _ in live}             # prompt tokens already run
         last: Dict[int, int] = {}                 # the token each sequence drew last
+        ahead = None                              # (logits, sequences) of a step already started
         try:
             while live:
                 t0 = time.perf_counter()
-                entries, want, in_prompt = [], [], False
-                for i, slot in live:
-                    p = prompts[i]
-                    if fed[i] < len(p):
-                        in_prompt = True
-                        toks = list(p) if (self.dedicated_prefill and fed[i] == 0) else [p[fed[i]]]
-                        fed[i] += len(toks)
-                        want.append([len(toks) - 1] if fed[i] == len(p) else [])
-                    else:
-                        toks = [last[i]]
-                        want.append([0])
-                    entries.append((slot, toks))
-                logits = st.step(entries, want)
+                in_prompt = False
+                if ahead is not None:
+                    logits, started = ahead
+                    ahead = None
+                    if len(started) != len(live):         # some of them ended meanwhile
+                        alive = {i for i, _ in live}
+                        logits = st.rows(logits, [r for r, (i, _) in enumerate(started) if i in alive])
+                    want = [[0] for _ in live]
+                    n_run = len(started)
+                else:
+                    entries, want = [], []
+                    for i, slot in live:
+                        p = prompts[i]
+                        if fed[i] < len(p):
+                            in_prompt = True
+                            toks = list(p) if (self.dedicated_prefill and fed[i] == 0) else [p[fed[i]]]
+                            fed[i] += len(toks)
+                            want.append([len(toks) - 1] if fed[i] == len(p) else [])
+                        else:
+                            toks = [last[i]]
+                            want.append([0])
+                        entries.append((slot, toks))
+                    logits = st.step(entries, want)
+                    n_run = sum(len(t) for _, t in entries)
                 drawing = [(i, slot) for (i, slot), w in zip(live, want) if w]
-                drawn = st.sample(logits, [keys[i] for i, _ in drawing],
-                                  [len(results[i].tokens) for i, _ in drawing]) if drawing else []
+                draw_keys = [keys[i] for i, _ in drawing]
+                draw_steps = [len(results[i].tokens) for i, _ in drawing]
+                if not drawing:
+                    drawn = []
+                elif can_look_ahead:
+                    handle = st.draw(logits, draw_keys, draw_steps)
+                    if len(drawing) == len(live) and not any(
+                            self._at_limit_after_next(results[i], len(prompts[i]), max_new) for i, _ in live):
+                        ahead = (st.step_from([slot for _, slot in live], handle), list(live))
+                    drawn = st.read(handle)
+                else:
+                    drawn = st.sample(logits, draw_keys, draw_steps)
                 verdict = {}
                 for (i, slot), tok in zip(drawing, drawn):
                     verdict[i] = self._accept(results[i], len(prompts[i]), int(tok), max_new)
@@ -153,7 +189,7 @@ class GenerationLoop:
                 dt = time.perf_counter() - t0
                 if in_prompt:
                     self.stats.prefill_seconds += dt
-                    self.stats.prompt_tokens += sum(len(t) for _, t in entries)
+                    self.stats.prompt_tokens += n_run
                 else:
                     self.stats.decode_seconds += dt
                     self.stats.decode_steps += 1

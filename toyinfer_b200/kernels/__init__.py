@@ -254,13 +254,24 @@ def attention_decode(q, mem, scale: float, window: int, batch) -> torch.Tensor:
     return out
 
 
+_argmax_scratch = {}
+
+
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     _need_cuda(logits, what="argmax")
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise KernelError("argmax: expected float32 [rows, vocab] with dense rows")
     R, V = logits.shape
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    _call(library().ti_argmax, _ptr(logits), logits.stride(0), R, V, _ptr(out), _stream())
+    # scratch that the kernel leaves zero: a word and a ticket per row, for rows scanned by several blocks
+    scratch = _argmax_scratch.get(logits.device)
+    if scratch is None or scratch[1].numel() < R:
+        n = max(1024, 2 * R)
+        scratch = _argmax_scratch[logits.device] = (torch.zeros(n, dtype=torch.int64, device=logits.device),
+                                                    torch.zeros(n, dtype=torch.int32, device=logits.device))
+    from .gemm import sm_count
+    _call(library().ti_argmax, _ptr(logits), logits.stride(0), R, V, sm_count(logits.device), _ptr(scratch[0]),
+          _ptr(scratch[1]), _ptr(out), _stream())
     return out
 
 

@@ -5,9 +5,8 @@ from __future__ import annotations
 import torch
 
 from . import KernelError, _call, _code, _ptr, _row_stride, _stream
+from .gemm import sm_count
 from .lib import library
-
-SM_COUNT = 148
 
 
 def prefill(q, k, v, out, scale, window, batch) -> None:
@@ -25,12 +24,12 @@ def prefill(q, k, v, out, scale, window, batch) -> None:
           _code(q, "attention_prefill"), _stream())
 
 
-def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int) -> int:
+def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int) -> int:
     """Splits along the keys so that the grid has about two blocks per SM, but no split
     shorter than two pages.  Depends only on the batch's padded size and the longest
     length the step was planned for, so that a captured launch stays valid."""
     tiles = max(1, (max_len + page - 1) // page)
-    want = max(1, (2 * SM_COUNT) // max(1, n_seq * n_kv_heads))
+    want = max(1, (2 * sms) // max(1, n_seq * n_kv_heads))
     return max(1, min(want, (tiles + 1) // 2, 64))
 
 
@@ -38,7 +37,7 @@ def decode(q, mem, out, scale, window, batch) -> None:
     B, nh, hd = q.shape
     nkv = mem.n_kv_heads
     span = batch.plan_len if window <= 0 else min(batch.plan_len, window + mem.page_size)
-    splits = decode_splits(B, nkv, span, mem.page_size)
+    splits = decode_splits(B, nkv, span, mem.page_size, sm_count(q.device))
     part_o = part_ml = None
     if splits > 1:
         part_o = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device)

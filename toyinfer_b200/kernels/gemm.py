@@ -13,8 +13,16 @@ import torch
 from . import _call, _code, _ptr, _stream
 from .lib import library
 
-SM_COUNT = 148
 _tickets = {}
+_sm_counts = {}
+
+
+def sm_count(device) -> int:
+    """Streaming multiprocessors of the device; launch shapes are planned to fill them once."""
+    n = _sm_counts.get(device)
+    if n is None:
+        n = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
 
 
 def _tickets_for(device) -> torch.Tensor:
@@ -36,7 +44,8 @@ def run(x, w, out, M, N, K, ldx, ldw, gated: bool = False) -> None:
     if tc_eligible(x, w, K, ldx, ldw):
         swap, bn, splits, n_tiles = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
         ws = ctypes.c_longlong()
-        lib.ti_linear_tc_plan(M, N, K, SM_COUNT, ctypes.byref(swap), ctypes.byref(bn), ctypes.byref(splits),
+        sms = sm_count(x.device)
+        lib.ti_linear_tc_plan(M, N, K, sms, ctypes.byref(swap), ctypes.byref(bn), ctypes.byref(splits),
                               ctypes.byref(ws), ctypes.byref(n_tiles))
         workspace = tickets = None
         if splits.value > 1:
@@ -46,7 +55,7 @@ def run(x, w, out, M, N, K, ldx, ldw, gated: bool = False) -> None:
             tickets = _tickets_for(x.device)
             if n_tiles.value > tickets.numel():
                 tickets = None
-        _call(lib.ti_linear_tc, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, 1 if gated else 0, SM_COUNT,
+        _call(lib.ti_linear_tc, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, 1 if gated else 0, sms,
               _ptr(workspace), _ptr(tickets), _stream())
         return
     if gated:

@@ -34,7 +34,7 @@ def _declare(lib) -> None:
         "ti_linear_tc": [P, P, P, I, I, I, L, L, L, I, I, I, P, P, P],
         "ti_linear_tc_plan": [I, I, I, I, P, P, P, P, P],
         "ti_read_status": [P],
-        "ti_argmax": [P, L, I, I, P, P],
+        "ti_argmax": [P, L, I, I, I, P, P, P, P],
         "ti_sample": [P, L, I, I, F, I, F, c_uint64, P, P, P, P],
     }
     for name, args in sig.items():
