@@ -89,7 +89,9 @@ def test_stop_token_and_queue_of_batches(model_folders):
 def test_starting_the_next_step_ahead_changes_no_token(model_folders):
     """The loop starts each decode step from the drawn tokens on the device before it has read
     them.  The same requests through a stepper without that ability (every token read first)
-    give the same tokens, with sequences that stop in the middle of a batch."""
+    give the same tokens, with sequences that stop in the middle of a batch.  (In 32-bit: the
+    two orders run some steps with different batch sizes, hence through different kernels, and
+    in bfloat16 a near-tie may then fall the other way.)"""
     from toyinfer_b200 import LLM, SamplingParams
     from toyinfer_b200.engine.generate import GenerationLoop
     from toyinfer_b200.sampling import Sampler
@@ -100,7 +102,7 @@ def test_starting_the_next_step_ahead_changes_no_token(model_folders):
             self.step, self.sample = inner.step, inner.sample
 
     for name, dtype, params in (("A", "float32", SamplingParams(temperature=0.0)),
-                                ("C", "bfloat16", SamplingParams(temperature=0.9, top_k=12, top_p=0.9, seed=5))):
+                                ("C", "float32", SamplingParams(temperature=0.9, top_k=12, top_p=0.9, seed=5))):
         llm = LLM(model_folders[name], dtype=dtype, max_seq_len=128, max_batch=4, max_tokens=64 * 16)
         prompts = prompts_for(name, [5, 9, 2, 30, 4, 11], seed=56)
         free = llm.generate(prompts, params, max_new_tokens=12, ignore_eos=True)

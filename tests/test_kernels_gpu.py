@@ -179,6 +179,35 @@ def test_linear_tensor_cores_at_model_sizes(K, M, N, K_, f32):
     assert torch.equal(got, got2)
 
 
+@pytest.mark.parametrize("M", [1, 2])
+@pytest.mark.parametrize("N,K_", [(6144, 2560), (2560, 9728), (2560, 4096), (19456, 2560), (7, 8), (333, 200), (2, 4104),
+                                  (151936, 64), (100, 1024), (30, 20000)])
+def test_linear_few_tokens(K, monkeypatch, M, N, K_):
+    """The weight-streaming kernel for one or two tokens against a float32 product: bfloat16
+    and float32 results, the gated form, odd row counts, contractions shorter than a warp's
+    stride, rows shared by several warps (few rows, long contraction), and operands inside
+    wider buffers."""
+    import toyinfer_b200.kernels.gemm as gemm
+    monkeypatch.setattr(gemm, "GEMV_MAX_TOKENS", 2)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    xb = torch.randn(M, K_ + 16, generator=g, device="cuda").to(torch.bfloat16)
+    wb = (torch.randn(N, K_ + 8, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
+    x, w = xb[:, 8:8 + K_], wb[:, :K_]
+    before = K.launch_count
+    got = K.linear(x, w)
+    got32 = K.linear(x, w, out_dtype=torch.float32)
+    assert K.launch_count == before + 2
+    want = x.float() @ w.float().T
+    torch.testing.assert_close(got32, want, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(got.float(), want.to(torch.bfloat16).float(), rtol=1.6e-2, atol=4e-3)
+    if N % 2 == 0:
+        gated = K.linear_swiglu(x, w)
+        gate, up = want[:, 0::2], want[:, 1::2]
+        torch.testing.assert_close(gated.float(), (up * gate / (1 + torch.exp(-gate))).to(torch.bfloat16).float(),
+                                   rtol=3e-2, atol=4e-3)
+        assert gated.shape == (M, N // 2)
+
+
 def test_linear_strided_input_and_tail(K):
     buf = torch.full((9, 500), 3.0, dtype=torch.float32, device="cuda")
     x = randn(9, 120, seed=15)

@@ -26,6 +26,7 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
                                            int n_splits) {
     ti_pdl_trigger();
     ti_pdl_sync();
+    part_o = ti_dependent(part_o); part_ml = ti_dependent(part_ml);
     __shared__ float w_s[128];       // weight of each split (up to 128 at a time)
     const int b = blockIdx.x, h = blockIdx.y;
     const size_t base = ((size_t)b * n_heads + h) * n_splits;

@@ -27,6 +27,7 @@ attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* _
     ti_pdl_trigger();
     extern __shared__ float sm[];
     ti_pdl_sync();
+    q = ti_dependent(q); k = ti_dependent(k); v = ti_dependent(v);
     const int ld = hd + 1;
     float* Qs = sm;
     float* Ks = Qs + BQ * ld;

@@ -94,6 +94,17 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __device__ __forceinline__ void ti_pdl_sync() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
+// A pointer to what the kernel before this one wrote, to be used for loads after ti_pdl_sync().
+// A load through a pointer that the compiler knows to be read-only for the whole kernel (a
+// const __restrict__ parameter, __ldg) may be moved above any barrier, the wait included, and
+// then reads what the earlier kernel has not written yet.  The pointer that comes out of this
+// is the result of an asm statement that stays behind the wait, so loads through it do too.
+template <typename T>
+__device__ __forceinline__ T* ti_dependent(T* p) {
+    asm volatile("" : "+l"(p) :: "memory");
+    return p;
+}
+
 // Called first thing in every kernel: the next kernel in the stream may be scheduled as soon as
 // all blocks of this one have started.  It still waits (ti_pdl_sync) for this kernel to finish
 // before it reads anything this kernel or an earlier one wrote, so several kernels can sit on the

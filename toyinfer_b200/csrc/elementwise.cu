@@ -67,6 +67,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
                              T* __restrict__ out, int H, int vocab) {
     ti_pdl_trigger();
     ti_pdl_sync();
+    ids = ti_dependent(ids);
     const int m = blockIdx.x;
     const int id = ids[m];
     const bool ok = id >= 0 && id < vocab;
@@ -112,6 +113,7 @@ __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
     ti_pdl_trigger();
     __shared__ float red[33];
     ti_pdl_sync();
+    x = ti_dependent(x); delta = ti_dependent(delta);
     const size_t row = blockIdx.x;
     T* xr = x + row * x_stride;
     const T* dr = ADD ? delta + row * (size_t)H : nullptr;
@@ -189,6 +191,7 @@ __global__ void gather_add_kernel(const T* __restrict__ h, const T* __restrict__
                                   const int* __restrict__ rows, T* __restrict__ out, int H, int M) {
     ti_pdl_trigger();
     ti_pdl_sync();
+    h = ti_dependent(h); delta = ti_dependent(delta);
     const int r = blockIdx.x;
     const int src = rows[r];
     const bool ok = src >= 0 && src < M;
@@ -222,6 +225,7 @@ template <typename T>
 __global__ void swiglu_pairs_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, long long total) {
     ti_pdl_trigger();
     ti_pdl_sync();
+    gu = ti_dependent(gu);
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const float g = to_f32(gu[2 * idx]), u = to_f32(gu[2 * idx + 1]);
@@ -233,6 +237,7 @@ template <typename T, int V>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, long long total_vecs) {
     ti_pdl_trigger();
     ti_pdl_sync();
+    gu = ti_dependent(gu);
     const int per_row = I / V;
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_vecs;
          idx += (long long)gridDim.x * blockDim.x) {

@@ -26,6 +26,7 @@ gemm_tile_kernel(const T* __restrict__ X, const T* __restrict__ W, OT* __restric
     __shared__ float As[BK][BM + PAD];
     __shared__ float Bs[BK][BN + PAD];
     ti_pdl_sync();
+    X = ti_dependent(X);
     const int t = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int ty = t / 16, tx = t % 16;
@@ -90,6 +91,7 @@ gemv_rows_kernel(const T* __restrict__ X, const T* __restrict__ W, OT* __restric
                  int M, int N, int K, long long ldx, long long ldw, long long ldo) {
     ti_pdl_trigger();
     ti_pdl_sync();
+    X = ti_dependent(X);
     const int lane = threadIdx.x & 31;
     const int warp = (blockIdx.x * GV_THREADS + threadIdx.x) >> 5;
     const int n_warps = (gridDim.x * GV_THREADS) >> 5;

@@ -1,0 +1,197 @@
+// out[M, N] = x[M, K] w[N, K]^T for one or two tokens, bfloat16 operands, 32-bit sums.
+//
+// With so few rows the product is a read of the weights and nothing else: every weight is
+// used M times, the tensor cores have nothing to do, and what decides the time is how many
+// loads are in flight.  So there is no shared memory, no barrier and no split contraction to
+// add up afterwards: a warp owns R rows of w, its lanes stride over K in pieces of 8
+// elements (16 bytes), U pieces ahead, and a shuffle tree adds the lanes at the end.  Where
+// the matrix has too few rows to give every SM its warps, 2, 4 or 8 warps of a block share
+// the rows and each takes a part of K; their sums meet in shared memory.  The
+// pieces of x are the same for every warp and come from L1.  The first weights are requested
+// before the wait for the kernel before this one, which produces x.
+//
+// The reference decodes one token through products of this kind, one block per output row
+// and two elements per load (src/decode.cu:201-298: gemv_bf16_kernel and its float-output
+// twin for the logits); the gated form applies its SwiGLU (src/decode.cu:746-764) to
+// (gate, up) row pairs as they are finished.
+#include "common.cuh"
+
+namespace {
+constexpr int WARPS = 8;
+
+__device__ __forceinline__ uint4 load_stream(const bf16* p) {     // read once: no L1 allocation
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// two bfloat16 in a word -> two floats (a bfloat16 is the upper half of a float)
+__device__ __forceinline__ float lo_f32(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float hi_f32(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }
+
+template <int M>
+__device__ __forceinline__ void fma_piece(float (&acc)[M], const uint4& wv, const uint4 (&xv)[M]) {
+    const float w0 = lo_f32(wv.x), w1 = hi_f32(wv.x), w2 = lo_f32(wv.y), w3 = hi_f32(wv.y);
+    const float w4 = lo_f32(wv.z), w5 = hi_f32(wv.z), w6 = lo_f32(wv.w), w7 = hi_f32(wv.w);
+#pragma unroll
+    for (int m = 0; m < M; m++) {
+        float a = acc[m];
+        a = fmaf(w0, lo_f32(xv[m].x), a); a = fmaf(w1, hi_f32(xv[m].x), a);
+        a = fmaf(w2, lo_f32(xv[m].y), a); a = fmaf(w3, hi_f32(xv[m].y), a);
+        a = fmaf(w4, lo_f32(xv[m].z), a); a = fmaf(w5, hi_f32(xv[m].z), a);
+        a = fmaf(w6, lo_f32(xv[m].w), a); a = fmaf(w7, hi_f32(xv[m].w), a);
+        acc[m] = a;
+    }
+}
+
+template <int M, int R, int U, int WPR, bool GATED, typename OutT>
+__global__ void __launch_bounds__(WARPS * 32)
+gemv_kernel(const bf16* x, const bf16* __restrict__ w, OutT* __restrict__ out, int N, int K,
+            long long ldx, long long ldw, long long ldo) {
+    ti_pdl_trigger();
+    __shared__ float part_sum[WPR > 1 ? WARPS * R * M : 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int group = warp / WPR, part = warp % WPR;          // WPR warps share a group of R rows, each a part of K
+    const long long row0 = ((long long)blockIdx.x * (WARPS / WPR) + group) * R;
+    const int pieces = K >> 3;
+    const bf16* wr[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) wr[r] = w + (size_t)min(row0 + r, (long long)N - 1) * ldw;   // rows past the end repeat the last, unused
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int m = 0; m < M; m++) acc[r][m] = 0.f;
+
+    constexpr int STEP = 32 * WPR;
+    bool waited = false;
+    for (int c = part * 32 + lane; c < pieces; c += STEP * U) {
+        uint4 wv[U][R];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int r = 0; r < R; r++)
+                wv[u][r] = (c + STEP * u < pieces) ? load_stream(wr[r] + (size_t)(c + STEP * u) * 8) : make_uint4(0, 0, 0, 0);
+        if (!waited) { ti_pdl_sync(); x = ti_dependent(x); waited = true; }      // x is the work of the kernel before this one
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int cc = min(c + STEP * u, pieces - 1);
+            uint4 xv[M];
+#pragma unroll
+            for (int m = 0; m < M; m++) xv[m] = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + (size_t)cc * 8);
+#pragma unroll
+            for (int r = 0; r < R; r++) fma_piece<M>(acc[r], wv[u][r], xv);
+        }
+    }
+    if (!waited) ti_pdl_sync();
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int m = 0; m < M; m++) acc[r][m] = warp_sum(acc[r][m]);
+    if (WPR > 1) {
+        if (lane == 0)
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int m = 0; m < M; m++) part_sum[(warp * R + r) * M + m] = acc[r][m];
+        __syncthreads();
+        if (part != 0 || lane != 0) return;
+#pragma unroll
+        for (int p = 1; p < WPR; p++)          // in the order of the parts, whichever warp finished first
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int m = 0; m < M; m++) acc[r][m] += part_sum[((warp + p) * R + r) * M + m];
+    } else if (lane != 0) {
+        return;
+    }
+    if (GATED) {
+#pragma unroll
+        for (int r = 0; r < R; r += 2) {
+            if (row0 + r + 1 >= N) break;
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const float g = acc[r][m], up = acc[r + 1][m];
+                out[(size_t)m * ldo + (size_t)((row0 + r) >> 1)] = from_f32<OutT>(up * (g / (1.f + expf(-g))));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            if (row0 + r >= N) break;
+#pragma unroll
+            for (int m = 0; m < M; m++) out[(size_t)m * ldo + (size_t)(row0 + r)] = from_f32<OutT>(acc[r][m]);
+        }
+    }
+}
+
+struct Args {
+    const bf16* x; const bf16* w; void* out; int N, K; long long ldx, ldw, ldo; cudaStream_t stream;
+};
+
+template <int M, int R, int WPR, bool GATED, typename OutT>
+int launch(const Args& a) {
+    constexpr int U = R == 2 ? 4 : 2;          // 128 bytes of weights in flight per lane either way
+    const long long groups = ((long long)a.N + R - 1) / R;
+    const long long blocks = (groups + WARPS / WPR - 1) / (WARPS / WPR);
+    TI_REQUIRE(blocks <= 0x7FFFFFFFll, "linear (few tokens): %d rows of weights are too many", a.N);
+    TI_CUDA(ti_launch(gemv_kernel<M, R, U, WPR, GATED, OutT>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, a.stream, a.x, a.w,
+                      (OutT*)a.out, a.N, a.K, a.ldx, a.ldw, a.ldo));
+    TI_CHECK_LAUNCH("linear (few tokens)");
+    return 0;
+}
+
+template <int M, int R, bool GATED, typename OutT>
+int launch_wpr(const Args& a, int wpr) {
+    switch (wpr) {
+        case 1: return launch<M, R, 1, GATED, OutT>(a);
+        case 2: return launch<M, R, 2, GATED, OutT>(a);
+        case 4: return launch<M, R, 4, GATED, OutT>(a);
+        default: return launch<M, R, 8, GATED, OutT>(a);
+    }
+}
+
+template <int M, bool GATED, typename OutT>
+int launch_r(const Args& a, int rows, int wpr) {
+    return rows == 4 ? launch_wpr<M, 4, GATED, OutT>(a, wpr) : launch_wpr<M, 2, GATED, OutT>(a, wpr);
+}
+
+template <int M>
+int launch_m(const Args& a, int out_f32, int gated, int rows, int wpr) {
+    if (gated) return launch_r<M, true, bf16>(a, rows, wpr);
+    if (out_f32) return launch_r<M, false, float>(a, rows, wpr);
+    return launch_r<M, false, bf16>(a, rows, wpr);
+}
+}  // namespace
+
+// x[M, K] (row stride ldx), w[N, K] (row stride ldw), both bfloat16, M 1 or 2; out[M, N]
+// bfloat16 or float32.  With `gated`, w's rows are (gate_0, up_0, gate_1, up_1, ...) and out is
+// [M, N / 2] = up * gate / (1 + exp(-gate)) in bfloat16.  K and the strides are multiples of 8
+// elements and the operands 16-byte aligned.  `sms`: the device's multiprocessors; the rows
+// per warp and the warps per row are chosen so that about 32 warps per SM have work.
+extern "C" int ti_linear_gemv(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
+                              long long ldw, long long ldo, int out_f32, int gated, int sms, cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    TI_REQUIRE(M >= 1 && M <= 2 && N > 0 && K > 0, "linear (few tokens): bad sizes M=%d N=%d K=%d", M, N, K);
+    TI_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "linear (few tokens): K and the row strides must be multiples of 8 elements");
+    TI_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+               "linear (few tokens): operands must be 16-byte aligned");
+    TI_REQUIRE(!gated || (N % 2 == 0 && !out_f32), "linear (few tokens): a gated product needs an even number of weight rows and a bfloat16 result");
+    // Measured on the shapes of 4B- and 32B-sized layers: with at least half of 32 warps per SM
+    // from two rows per warp, one warp per pair of rows is best.  With fewer rows, several warps
+    // share a pair so that the device fills, as long as a lane keeps a full round of loads; and
+    // when the contraction is still long then, four rows per warp halve the reads of x.
+    const long long target = 32ll * (sms > 0 ? sms : 1);
+    const long long pairs = ((long long)N + 1) / 2;
+    const int pieces = K >> 3;
+    int rows = 2, wpr = 1;
+    if (pairs * 2 < target) {
+        while (wpr < WARPS && pairs * wpr < target && pieces >= 32 * (wpr * 2) * 4) wpr *= 2;
+        if (pieces >= 32 * wpr * 8) rows = 4;
+    } else if (M == 2 && pairs >= 8 * target) {
+        rows = 4;
+    }
+    Args a{(const bf16*)x, (const bf16*)w, out, N, K, ldx, ldw, ldo, stream};
+    return M == 1 ? launch_m<1>(a, out_f32, gated, rows, wpr) : launch_m<2>(a, out_f32, gated, rows, wpr);
+}

@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(AB) argmax_kernel(const float* __restrict__ lo
     __shared__ float bv[AB / 32];
     __shared__ int bi[AB / 32];
     ti_pdl_sync();
+    logits = ti_dependent(logits);
     const int row = blockIdx.x;
     const float* x = logits + (size_t)row * ld;
     const int lo = blockIdx.y * per, hi = min(V, lo + per);

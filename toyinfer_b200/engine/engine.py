@@ -14,7 +14,9 @@ buffers refreshed before each replay.
 """
 from __future__ import annotations
 
+import gc
 import os
+import weakref
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -233,16 +235,25 @@ class Engine:
 
 
 class _DecodeGraph:
-    """A decode step of ``bucket`` sequences captured into a CUDA graph."""
+    """A decode step of ``bucket`` sequences captured into a CUDA graph.  It refers to its
+    engine weakly: engine and graphs then form no cycle, and both are released (with their
+    device memory) when the last reference to the engine goes, not at some later collection."""
 
     def __init__(self, engine: Engine, bucket: int):
-        self.engine = engine
+        self._engine = weakref.ref(engine)
         self.bucket = bucket
         self.buf = BatchBuffers(bucket, bucket, engine.device)
         self.rows = torch.arange(bucket, dtype=torch.int32, device=engine.device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.launches = 0
+
+    @property
+    def engine(self) -> Engine:
+        e = self._engine()
+        if e is None:
+            raise RuntimeError("the engine of this captured step is gone")
+        return e
 
     def _body(self, batch: StepBatch) -> torch.Tensor:
         e = self.engine
@@ -265,9 +276,18 @@ class _DecodeGraph:
             self.launches = K.launch_count - before
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()
-            # the capture only records; nothing runs until the first replay
-            with torch.cuda.graph(g):
-                self.logits = self._body(batch)
+            # The capture only records; nothing runs until the first replay.  No collection of
+            # Python garbage may fall into it: objects that own device memory, events or other
+            # graphs would be destroyed in the middle of the capture, which ends it with an error.
+            gc.collect()
+            was_enabled = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(g):
+                    self.logits = self._body(batch)
+            finally:
+                if was_enabled:
+                    gc.enable()
             self.graph = g
             return out
         self.graph.replay()

@@ -1,8 +1,9 @@
 """Which matrix-product kernel runs a given shape.
 
 bfloat16 operands whose rows are 16-byte aligned go to the tcgen05 kernel (the weights play
-the 128-row operand when there are at most 64 tokens); everything else, and the whole
-32-bit engine, runs on the CUDA-core kernels.
+the 128-row operand when there are at most 64 tokens), or, for one or two tokens, to a
+kernel that only streams the weights; everything else, and the whole 32-bit engine, runs on
+the CUDA-core kernels.
 """
 from __future__ import annotations
 
@@ -13,6 +14,9 @@ import torch
 from . import _call, _code, _ptr, _stream
 from .lib import library
 
+# Up to this many tokens the product is a plain read of the weights on the CUDA cores
+# (measured faster than the tensor-core kernel with its split contraction).
+GEMV_MAX_TOKENS = 2
 _tickets = {}
 _sm_counts = {}
 
@@ -41,6 +45,10 @@ def run(x, w, out, M, N, K, ldx, ldw, gated: bool = False) -> None:
     """``gated``: only for shapes the tensor-core kernel takes (see tc_eligible)."""
     lib = library()
     out_f32 = 1 if (out.dtype == torch.float32 and x.dtype != torch.float32) else 0
+    if tc_eligible(x, w, K, ldx, ldw) and M <= GEMV_MAX_TOKENS:
+        _call(lib.ti_linear_gemv, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, 1 if gated else 0,
+              sm_count(x.device), _stream())
+        return
     if tc_eligible(x, w, K, ldx, ldw):
         swap, bn, splits, n_tiles = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
         ws = ctypes.c_longlong()
