@@ -208,6 +208,45 @@ def test_linear_few_tokens(K, monkeypatch, M, N, K_):
         assert gated.shape == (M, N // 2)
 
 
+@pytest.mark.parametrize("M", [1, 2, 8])
+def test_products_back_to_back_read_what_the_kernel_before_wrote(K, M):
+    """Kernels are launched so that each may start while the one before it still runs and must
+    wait before it reads that kernel's results.  A chain norm -> product -> norm -> product ...
+    whose buffers are reused at the same addresses, replayed from a CUDA graph (no gaps between
+    the kernels), must give what the same chain gives with a device-wide wait after every kernel."""
+    H, N, n = 4096, 2560, 24
+    g = torch.Generator(device="cuda").manual_seed(3)
+    hs = [torch.randn(M, H, generator=g, device="cuda").to(torch.bfloat16) for _ in range(n)]
+    wn = (1 + 0.1 * torch.randn(H, generator=g, device="cuda")).to(torch.bfloat16)
+    w = (torch.randn(N, H, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
+
+    def chain(sync):
+        outs = []
+        for h in hs:
+            x = K.rmsnorm(h, wn, 1e-6)
+            if sync:
+                torch.cuda.synchronize()
+            y = K.linear(x, w)
+            if sync:
+                torch.cuda.synchronize()
+            outs.append(y)
+            del x
+        return outs
+
+    want = [o.clone() for o in chain(True)]
+    chain(False)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        got = chain(False)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    K.check_status()
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+
+
 def test_linear_strided_input_and_tail(K):
     buf = torch.full((9, 500), 3.0, dtype=torch.float32, device="cuda")
     x = randn(9, 120, seed=15)
