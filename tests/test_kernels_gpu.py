@@ -162,8 +162,12 @@ def test_linear(K, dtype, M, N, K_):
     (1, 151936, 2560, True),       # head for one row, float32 logits
     (33, 1000, 264, False), (16, 128, 64, False), (65, 136, 72, True), (129, 250, 200, False),
 ])
-def test_linear_tensor_cores_at_model_sizes(K, M, N, K_, f32):
-    """The tcgen05 kernel against a float32 product of the same bfloat16 operands."""
+def test_linear_tensor_cores_at_model_sizes(K, monkeypatch, M, N, K_, f32):
+    """The tcgen05 kernel against a float32 product of the same bfloat16 operands (the kernels
+    that otherwise take up to 8 tokens are switched off here)."""
+    import toyinfer_b200.kernels.gemm as gemm
+    monkeypatch.setattr(gemm, "GEMV_MAX_TOKENS", 0)
+    monkeypatch.setattr(gemm, "SKINNY_MAX_TOKENS", 0)
     g = torch.Generator(device="cuda").manual_seed(5)
     x = torch.randn(M, K_, generator=g, device="cuda").to(torch.bfloat16)
     w = (torch.randn(N, K_, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
@@ -190,6 +194,36 @@ def test_linear_few_tokens(K, monkeypatch, M, N, K_):
     import toyinfer_b200.kernels.gemm as gemm
     monkeypatch.setattr(gemm, "GEMV_MAX_TOKENS", 2)
     g = torch.Generator(device="cuda").manual_seed(9)
+    xb = torch.randn(M, K_ + 16, generator=g, device="cuda").to(torch.bfloat16)
+    wb = (torch.randn(N, K_ + 8, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
+    x, w = xb[:, 8:8 + K_], wb[:, :K_]
+    before = K.launch_count
+    got = K.linear(x, w)
+    got32 = K.linear(x, w, out_dtype=torch.float32)
+    assert K.launch_count == before + 2
+    want = x.float() @ w.float().T
+    torch.testing.assert_close(got32, want, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(got.float(), want.to(torch.bfloat16).float(), rtol=1.6e-2, atol=4e-3)
+    if N % 2 == 0:
+        gated = K.linear_swiglu(x, w)
+        gate, up = want[:, 0::2], want[:, 1::2]
+        torch.testing.assert_close(gated.float(), (up * gate / (1 + torch.exp(-gate))).to(torch.bfloat16).float(),
+                                   rtol=3e-2, atol=4e-3)
+        assert gated.shape == (M, N // 2)
+
+
+@pytest.mark.parametrize("M", [1, 3, 5, 8, 9, 13, 16])
+@pytest.mark.parametrize("N,K_", [(6144, 2560), (2560, 9728), (2560, 4096), (19456, 2560), (7, 8), (333, 200), (2, 4104),
+                                  (50000, 72), (100, 1024), (30, 20000)])
+def test_linear_small_batch(K, monkeypatch, M, N, K_):
+    """The small-batch product (operands straight from global memory into mma.sync) against a
+    float32 product: bfloat16 and float32 results, the gated form, row counts that are no
+    multiple of 16, contractions that are no multiple of 32, rows shared by several warps, and
+    operands inside wider buffers."""
+    import toyinfer_b200.kernels.gemm as gemm
+    monkeypatch.setattr(gemm, "GEMV_MAX_TOKENS", 0)
+    monkeypatch.setattr(gemm, "SKINNY_MAX_TOKENS", 16)
+    g = torch.Generator(device="cuda").manual_seed(11)
     xb = torch.randn(M, K_ + 16, generator=g, device="cuda").to(torch.bfloat16)
     wb = (torch.randn(N, K_ + 8, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
     x, w = xb[:, 8:8 + K_], wb[:, :K_]

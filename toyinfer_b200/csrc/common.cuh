@@ -132,6 +132,20 @@ static inline cudaError_t ti_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The same without the attribute: the kernel starts when everything before it in the stream
+// has finished (its ti_pdl_sync() then returns at once).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ti_launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                          Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.numAttrs = 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename F>
 static inline int ti_dispatch_dtype(int dtype, F&& f) {
     // f is called with a value of the element type

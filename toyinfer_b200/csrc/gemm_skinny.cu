@@ -1,0 +1,212 @@
+// out[M, N] = x[M, K] w[N, K]^T for a handful of tokens (up to 16), bfloat16 operands,
+// float32 accumulation on the tensor cores, operands loaded straight from global memory into
+// the MMA's registers.
+//
+// With few tokens the product is a read of the weights; what decides its time is how many
+// bytes are in flight and how little happens between a kernel's start and its first load.
+// This kernel has no shared-memory pipeline to fill, no tensor memory to allocate and no
+// split contraction to add up in a second pass:
+//   * a warp owns 16 rows of w and walks K in steps of 64.  Lane (g, t) = (lane / 4, lane % 4)
+//     loads 32 bytes (16 consecutive k) of rows g and g + 8 at k offset 16 t, and 32 bytes of
+//     token g of x at the same offset: four lanes read one whole 128-byte line of a row.  The
+//     contraction does not care in which order k is visited, so each 8 of those elements feed
+//     two m16n8k16 MMAs as they lie: the MMA's k index (2t, 2t+1, 2t+8, 2t+9) stands for the
+//     lane's elements (0, 1, 2, 3), then (4, 5, 6, 7) — the same renaming on both operands.  No
+//     ldmatrix, no transposition, every load 16 bytes;
+//   * loads run UNROLL steps (128 bytes of weights per lane) ahead of the MMAs; the first ones
+//     are issued before the wait for the kernel before this one, which produces x;
+//   * where the matrix has too few rows to occupy the SMs, the warps of a block share a
+//     row group and each takes a slice of K; their partial sums meet in shared memory and are
+//     added in slice order.
+// x is read from L1/L2 by every warp (at most 16 tokens: it stays resident).
+//
+// Launch: the kernel signals at its start that its successor may be scheduled, like every
+// kernel here, but is itself launched without the programmatic attribute, so it starts when its
+// predecessor has finished.  Measured in a 36-layer decode step at 8 sequences: started early
+// (its blocks loading weights and then waiting beside the predecessor's) the step took 4.4-4.9 ms;
+// started after the predecessor 2.8-2.9 ms; the tcgen05 kernel in its place 3.0 ms.
+//
+// The reference has no counterpart: it decodes one sequence with one block per output row
+// (src/decode.cu:201-298) and has no batch dimension; this is that product for a small batch.
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+namespace {
+constexpr int UNROLL = 2;
+
+__device__ __forceinline__ uint4 load_stream(const bf16* p) {     // read once: no L1 allocation
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+struct Args {
+    const bf16* x; const bf16* w; void* out;
+    int M, N, K;
+    long long ldx, ldw, ldo;
+};
+
+// NT: token tiles of 8 (1 or 2); WARPS per block; WPR: warps that share a group of 16 rows.
+template <int NT, int WARPS, int WPR, bool GATED, typename OutT>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel(Args a) {
+    ti_pdl_trigger();
+    __shared__ float part[WPR > 1 ? WARPS * NT * 4 * 32 : 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int group = warp / WPR, slice = warp % WPR;
+    const long long r0 = ((long long)blockIdx.x * (WARPS / WPR) + group) * 16;
+    const int steps = (a.K + 63) >> 6;
+    const int per = (steps + WPR - 1) / WPR;
+    const int s0 = slice * per, s1 = min(steps, s0 + per);
+    // rows past the end repeat the last row; their sums are never stored
+    const bf16* w_lo = a.w + (size_t)min(r0 + g, (long long)a.N - 1) * a.ldw + 16 * t;
+    const bf16* w_hi = a.w + (size_t)min(r0 + g + 8, (long long)a.N - 1) * a.ldw + 16 * t;
+    const bf16* x = a.x;
+    float c[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; n++) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+
+    bool waited = false;
+    for (int s = s0; s < s1; s += UNROLL) {
+        uint4 wl[UNROLL][2], wh[UNROLL][2];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int k = (s + u) * 64 + 16 * t + 8 * h;
+                const bool ok = s + u < s1 && k < a.K;          // K is a multiple of 8: a piece is whole or absent
+                wl[u][h] = ok ? load_stream(w_lo + (size_t)(s + u) * 64 + 8 * h) : make_uint4(0, 0, 0, 0);
+                wh[u][h] = ok ? load_stream(w_hi + (size_t)(s + u) * 64 + 8 * h) : make_uint4(0, 0, 0, 0);
+            }
+        if (!waited) { ti_pdl_sync(); x = ti_dependent(x); waited = true; }      // x is the work of the kernel before this one
+        // every piece of x of these steps is asked for before the first MMA: whether it comes from
+        // L1 or (when a neighbour's shared memory leaves no L1) from L2, the warp waits once
+        uint4 xv[UNROLL][2][NT];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int k = (s + u) * 64 + 16 * t + 8 * h;
+                const bool ok = s + u < s1 && k < a.K;
+#pragma unroll
+                for (int n = 0; n < NT; n++) {
+                    const int tok = min(n * 8 + g, a.M - 1);        // tokens past the end repeat the last; never stored
+                    xv[u][h][n] = ok ? *reinterpret_cast<const uint4*>(x + (size_t)tok * a.ldx + k) : make_uint4(0, 0, 0, 0);
+                }
+            }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const uint32_t a1[4] = {wl[u][h].x, wh[u][h].x, wl[u][h].y, wh[u][h].y};
+                const uint32_t a2[4] = {wl[u][h].z, wh[u][h].z, wl[u][h].w, wh[u][h].w};
+#pragma unroll
+                for (int n = 0; n < NT; n++) {
+                    mma_bf16(c[n], a1, xv[u][h][n].x, xv[u][h][n].y);
+                    mma_bf16(c[n], a2, xv[u][h][n].z, xv[u][h][n].w);
+                }
+            }
+    }
+    if (!waited) ti_pdl_sync();
+
+    if (WPR > 1) {
+#pragma unroll
+        for (int n = 0; n < NT; n++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) part[((warp * NT + n) * 4 + e) * 32 + lane] = c[n][e];
+        __syncthreads();
+        if (slice != 0) return;
+#pragma unroll
+        for (int p = 1; p < WPR; p++)
+#pragma unroll
+            for (int n = 0; n < NT; n++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) c[n][e] += part[(((warp + p) * NT + n) * 4 + e) * 32 + lane];
+    }
+    // c[n][0..1]: row r0 + g, tokens n*8 + 2t, 2t + 1;  c[n][2..3]: row r0 + g + 8, same tokens
+    OutT* out = (OutT*)a.out;
+#pragma unroll
+    for (int n = 0; n < NT; n++) {
+        if (GATED) {
+            // rows come in (gate, up) pairs: the partner row lives four lanes away
+            float other[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) other[e] = __shfl_xor_sync(0xffffffffu, c[n][e], 4);
+            if ((g & 1) == 0) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const long long row = r0 + g + (e >> 1) * 8;
+                    const int tok = n * 8 + 2 * t + (e & 1);
+                    if (row + 1 < a.N && tok < a.M) {
+                        const float gate = c[n][e], up = other[e];
+                        out[(size_t)tok * a.ldo + (size_t)(row >> 1)] = from_f32<OutT>(up * (gate / (1.f + expf(-gate))));
+                    }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const long long row = r0 + g + (e >> 1) * 8;
+                const int tok = n * 8 + 2 * t + (e & 1);
+                if (row < a.N && tok < a.M) out[(size_t)tok * a.ldo + (size_t)row] = from_f32<OutT>(c[n][e]);
+            }
+        }
+    }
+}
+
+template <int NT, int WARPS, int WPR, bool GATED, typename OutT>
+int launch(const Args& a, cudaStream_t stream) {
+    const long long groups = ((long long)a.N + 15) / 16;
+    const long long blocks = (groups + WARPS / WPR - 1) / (WARPS / WPR);
+    TI_REQUIRE(blocks <= 0x7FFFFFFFll, "linear (small batch): %d rows of weights are too many", a.N);
+    TI_CUDA(ti_launch_after(skinny_kernel<NT, WARPS, WPR, GATED, OutT>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, a));
+    TI_CHECK_LAUNCH("linear (small batch)");
+    return 0;
+}
+
+template <int NT, bool GATED, typename OutT>
+int launch_wpr(const Args& a, int wpr, cudaStream_t stream) {
+    switch (wpr) {
+        case 1: return launch<NT, 8, 1, GATED, OutT>(a, stream);
+        case 2: return launch<NT, 8, 2, GATED, OutT>(a, stream);
+        case 4: return launch<NT, 8, 4, GATED, OutT>(a, stream);
+        case 8: return launch<NT, 8, 8, GATED, OutT>(a, stream);
+        default: return launch<NT, 16, 16, GATED, OutT>(a, stream);
+    }
+}
+
+template <int NT>
+int launch_nt(const Args& a, int out_f32, int gated, int wpr, cudaStream_t stream) {
+    if (gated) return launch_wpr<NT, true, bf16>(a, wpr, stream);
+    if (out_f32) return launch_wpr<NT, false, float>(a, wpr, stream);
+    return launch_wpr<NT, false, bf16>(a, wpr, stream);
+}
+
+}  // namespace
+
+// x[M, K] (row stride ldx), w[N, K] (row stride ldw), both bfloat16, M from 1 to 16; out[M, N]
+// bfloat16 or float32.  With `gated`, w's rows are (gate_0, up_0, gate_1, up_1, ...) and out is
+// [M, N / 2] = up * gate / (1 + exp(-gate)) in bfloat16.  K and the strides are multiples of 8
+// elements and the operands 16-byte aligned.  `sms`: the device's multiprocessors.
+extern "C" int ti_linear_skinny(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
+                                long long ldw, long long ldo, int out_f32, int gated, int sms, cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    TI_REQUIRE(M >= 1 && M <= 16 && N > 0 && K > 0, "linear (small batch): bad sizes M=%d N=%d K=%d", M, N, K);
+    TI_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "linear (small batch): K and the row strides must be multiples of 8 elements");
+    TI_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+               "linear (small batch): operands must be 16-byte aligned");
+    TI_REQUIRE(!gated || (N % 2 == 0 && !out_f32), "linear (small batch): a gated product needs an even number of weight rows and a bfloat16 result");
+    // Warps per row group, measured on the shapes of 4B- and 32B-sized layers: what counts is
+    // how many warps have loads in flight, so a group's contraction is cut into 8 slices
+    // whenever each slice keeps two steps, and into 16 (blocks of 16 warps, registers capped
+    // so that two fit an SM) when the matrix has too few rows to give every SM 16 warps.
+    const long long target = 16ll * (sms > 0 ? sms : 1);
+    const long long groups = ((long long)N + 15) / 16;
+    const int steps = (K + 63) / 64;
+    int wpr = 1;
+    while (wpr < 8 && steps >= (wpr * 2) * UNROLL) wpr *= 2;
+    if (wpr == 8 && groups * 8 < target && steps >= 16 * UNROLL) wpr = 16;
+    Args a{(const bf16*)x, (const bf16*)w, out, M, N, K, ldx, ldw, ldo};
+    return M <= 8 ? launch_nt<1>(a, out_f32, gated, wpr, stream) : launch_nt<2>(a, out_f32, gated, wpr, stream);
+}

@@ -1,8 +1,8 @@
 """Which matrix-product kernel runs a given shape.
 
 bfloat16 operands whose rows are 16-byte aligned go to the tcgen05 kernel (the weights play
-the 128-row operand when there are at most 64 tokens), or, for one or two tokens, to a
-kernel that only streams the weights; everything else, and the whole 32-bit engine, runs on
+the 128-row operand when there are at most 64 tokens), or, for up to 8 tokens, to kernels
+that only stream the weights (CUDA cores for one token, mma.sync beyond); everything else, and the whole 32-bit engine, runs on
 the CUDA-core kernels.
 """
 from __future__ import annotations
@@ -14,9 +14,11 @@ import torch
 from . import _call, _code, _ptr, _stream
 from .lib import library
 
-# Up to this many tokens the product is a plain read of the weights on the CUDA cores
-# (measured faster than the tensor-core kernel with its split contraction).
-GEMV_MAX_TOKENS = 2
+# Measured in whole decode steps of a 4B-shaped model (ms per step at 1 / 2 / 4 / 8 sequences):
+# tcgen05 swap-AB kernel 2.80 / 2.75 / 2.82 / 3.01, weight-streaming kernel 2.26 / 2.87 / - / -,
+# small-batch mma.sync kernel 2.41 / 2.51 / 2.63 / 2.88.
+GEMV_MAX_TOKENS = 1      # one token: a plain read of the weights on the CUDA cores
+SKINNY_MAX_TOKENS = 8    # up to this many: mma.sync with both operands loaded straight from global memory
 _tickets = {}
 _sm_counts = {}
 
@@ -47,6 +49,10 @@ def run(x, w, out, M, N, K, ldx, ldw, gated: bool = False) -> None:
     out_f32 = 1 if (out.dtype == torch.float32 and x.dtype != torch.float32) else 0
     if tc_eligible(x, w, K, ldx, ldw) and M <= GEMV_MAX_TOKENS:
         _call(lib.ti_linear_gemv, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, 1 if gated else 0,
+              sm_count(x.device), _stream())
+        return
+    if tc_eligible(x, w, K, ldx, ldw) and M <= SKINNY_MAX_TOKENS:
+        _call(lib.ti_linear_skinny, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, 1 if gated else 0,
               sm_count(x.device), _stream())
         return
     if tc_eligible(x, w, K, ldx, ldw):
