@@ -334,11 +334,11 @@ int launch(const tiattn::DecodeArgs& a, int n_seq, cudaStream_t stream) {
     TI_REQUIRE(status != nullptr, "attention_decode: no status word");
     const int g = a.n_heads / a.n_kv_heads;
     dim3 grid(n_seq, a.n_kv_heads * ((g + 15) / 16), a.n_splits);
-    TI_CUDA(ti_launch(attn_decode_mma_kernel<HD>, grid, dim3(THREADS), smem, stream, km, vm, a, status));
+    TI_CUDA(ti_launch_class<3>(attn_decode_mma_kernel<HD>, grid, dim3(THREADS), smem, stream, km, vm, a, status));
     TI_CHECK_LAUNCH("attention_decode (tensor cores)");
     if (a.n_splits > 1) {
         dim3 cgrid(n_seq, a.n_heads);
-        TI_CUDA(ti_launch(tiattn::attn_decode_combine_kernel<bf16>, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits));
+        TI_CUDA(ti_launch_class<4>(tiattn::attn_decode_combine_kernel<bf16>, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits));
         TI_CHECK_LAUNCH("attention_decode (combine)");
     }
     return 0;

@@ -113,12 +113,16 @@ __device__ __forceinline__ void ti_pdl_trigger() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-int ti_pdl_enabled();
+// Whether kernels of a class start early (programmatic serialization) or only when everything
+// before them in the stream has finished.  Classes: 0 everything not named below, 1 norms and
+// other row-wise kernels, 2 rotate-and-store, 3 decode attention, 4 its combine, 5 tcgen05 product.
+int ti_pdl_enabled(int cls);
 
-// Launches `kernel` with the programmatic-serialization attribute (see ti_pdl_sync).
-template <typename... KArgs, typename... Args>
-static inline cudaError_t ti_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                    Args&&... args) {
+// Launches `kernel` with the programmatic-serialization attribute (see ti_pdl_sync) when its
+// class has it switched on.
+template <int CLS, typename... KArgs, typename... Args>
+static inline cudaError_t ti_launch_class(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                          Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -128,8 +132,13 @@ static inline cudaError_t ti_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = ti_pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = ti_pdl_enabled(CLS) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ti_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+    return ti_launch_class<0>(kernel, grid, block, smem, stream, static_cast<Args&&>(args)...);
 }
 
 // The same without the attribute: the kernel starts when everything before it in the stream

@@ -93,9 +93,9 @@ extern "C" int ti_embed(const void* table, const int* ids, void* out, int M, int
         constexpr int V = vec_width<T>();
         const int threads = 128;
         if (H % V == 0 && aligned16(table) && aligned16(out))
-            TI_CUDA(ti_launch(embed_kernel<T, V>, dim3(M), dim3(threads), 0, stream, (const T*)table, ids, (T*)out, H, vocab));
+            TI_CUDA(ti_launch_class<1>(embed_kernel<T, V>, dim3(M), dim3(threads), 0, stream, (const T*)table, ids, (T*)out, H, vocab));
         else
-            TI_CUDA(ti_launch(embed_kernel<T, 1>, dim3(M), dim3(threads), 0, stream, (const T*)table, ids, (T*)out, H, vocab));
+            TI_CUDA(ti_launch_class<1>(embed_kernel<T, 1>, dim3(M), dim3(threads), 0, stream, (const T*)table, ids, (T*)out, H, vocab));
         TI_CHECK_LAUNCH("embed");
         return 0;
     });
@@ -154,10 +154,10 @@ static int launch_rmsnorm(void* x, const void* delta, const void* w, void* out, 
     if (H <= 256) threads = 64;
     else if (H <= 1024) threads = 128;
     if (vec)
-        TI_CUDA(ti_launch(rmsnorm_kernel<T, W, V, ADD>, dim3(M), dim3(threads), 0, stream, (T*)x, (const T*)delta,
+        TI_CUDA(ti_launch_class<1>(rmsnorm_kernel<T, W, V, ADD>, dim3(M), dim3(threads), 0, stream, (T*)x, (const T*)delta,
                           (const W*)w, (T*)out, H, x_stride, eps));
     else
-        TI_CUDA(ti_launch(rmsnorm_kernel<T, W, 1, ADD>, dim3(M), dim3(threads), 0, stream, (T*)x, (const T*)delta,
+        TI_CUDA(ti_launch_class<1>(rmsnorm_kernel<T, W, 1, ADD>, dim3(M), dim3(threads), 0, stream, (T*)x, (const T*)delta,
                           (const W*)w, (T*)out, H, x_stride, eps));
     TI_CHECK_LAUNCH("rmsnorm");
     return 0;
@@ -211,7 +211,7 @@ extern "C" int ti_gather_add(const void* h, const void* delta, const int* rows, 
     TI_REQUIRE(R > 0 && H > 0 && M > 0, "gather_add: bad sizes R=%d H=%d M=%d", R, H, M);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
-        TI_CUDA(ti_launch(gather_add_kernel<T>, dim3(R), dim3(256), 0, stream, (const T*)h, (const T*)delta, rows, (T*)out, H, M));
+        TI_CUDA(ti_launch_class<1>(gather_add_kernel<T>, dim3(R), dim3(256), 0, stream, (const T*)h, (const T*)delta, rows, (T*)out, H, M));
         TI_CHECK_LAUNCH("gather_add");
         return 0;
     });
@@ -262,18 +262,18 @@ extern "C" int ti_swiglu(const void* gu, void* out, int M, int I, int pairs, int
         if (pairs) {
             const long long n = (long long)M * I;
             const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
-            TI_CUDA(ti_launch(swiglu_pairs_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu, (T*)out, I, n));
+            TI_CUDA(ti_launch_class<1>(swiglu_pairs_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu, (T*)out, I, n));
             TI_CHECK_LAUNCH("swiglu");
             return 0;
         }
         if (I % V == 0 && aligned16(gu) && aligned16(out)) {
             const long long n = (long long)M * (I / V);
             const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
-            TI_CUDA(ti_launch(swiglu_kernel<T, V>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu, (T*)out, I, n));
+            TI_CUDA(ti_launch_class<1>(swiglu_kernel<T, V>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu, (T*)out, I, n));
         } else {
             const long long n = (long long)M * I;
             const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
-            TI_CUDA(ti_launch(swiglu_kernel<T, 1>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu, (T*)out, I, n));
+            TI_CUDA(ti_launch_class<1>(swiglu_kernel<T, 1>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu, (T*)out, I, n));
         }
         TI_CHECK_LAUNCH("swiglu");
         return 0;

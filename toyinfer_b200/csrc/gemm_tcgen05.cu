@@ -490,12 +490,12 @@ int launch(const CUtensorMap& am, const CUtensorMap& bm, const GemmArgs& g, cuda
     TI_REQUIRE(status != nullptr, "linear: no status word");
     dim3 grid((g.rows_a + BM - 1) / BM, (g.rows_b + BN - 1) / BN, g.splits);
     TI_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "linear: grid of %u x %u x %u is too large", grid.x, grid.y, grid.z);
-    TI_CUDA(ti_launch(gemm_tc_kernel<BN>, grid, dim3(THREADS), smem, stream, am, bm, g, status));
+    TI_CUDA(ti_launch_class<5>(gemm_tc_kernel<BN>, grid, dim3(THREADS), smem, stream, am, bm, g, status));
     TI_CHECK_LAUNCH("linear (tcgen05)");
     if (g.splits > 1 && !g.tickets) {
         const long long items = (long long)grid.x * grid.y * 4 * (BN / 16);
         const int warps = 4;
-        TI_CUDA(ti_launch(splitk_reduce_kernel<BN>, dim3((unsigned)((items + warps - 1) / warps)), dim3(warps * 32), 0, stream, g,
+        TI_CUDA(ti_launch_class<5>(splitk_reduce_kernel<BN>, dim3((unsigned)((items + warps - 1) / warps)), dim3(warps * 32), 0, stream, g,
                           (int)grid.x, (int)grid.y));
         TI_CHECK_LAUNCH("linear (tcgen05, split reduction)");
     }
@@ -514,7 +514,7 @@ int launch_persistent(const CUtensorMap& am, const CUtensorMap& bm, const GemmAr
     TI_REQUIRE(status != nullptr, "linear: no status word");
     const int tiles = ((g.rows_a + BM - 1) / BM) * ((g.rows_b + BN - 1) / BN);
     dim3 grid(tiles < sms ? tiles : sms);
-    TI_CUDA(ti_launch(gemm_tc_persistent_kernel<BN>, grid, dim3(THREADS), smem, stream, am, bm, g, status));
+    TI_CUDA(ti_launch_class<5>(gemm_tc_persistent_kernel<BN>, grid, dim3(THREADS), smem, stream, am, bm, g, status));
     TI_CHECK_LAUNCH("linear (tcgen05, persistent)");
     return 0;
 }

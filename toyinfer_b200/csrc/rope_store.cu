@@ -267,10 +267,10 @@ extern "C" int ti_qk_norm_rope_store(
         if (pairs) {
             const int w = 4;
             const int groups = M >= 1024 ? 1 : (per_tok + w - 1) / w;
-            TI_CUDA(ti_launch(rope_store_pairs_kernel<T>, dim3((unsigned)M, (unsigned)groups), dim3(w * 32), 0, stream, a));
+            TI_CUDA(ti_launch_class<2>(rope_store_pairs_kernel<T>, dim3((unsigned)M, (unsigned)groups), dim3(w * 32), 0, stream, a));
         }
         else
-            TI_CUDA(ti_launch(rope_store_kernel<T>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, a));
+            TI_CUDA(ti_launch_class<2>(rope_store_kernel<T>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, a));
         TI_CHECK_LAUNCH("qk_norm_rope_store");
         return 0;
     });

@@ -27,11 +27,12 @@ int load_encode() {
 }
 }  // namespace
 
-static int g_pdl = 1;
-int ti_pdl_enabled() { return g_pdl; }
+static unsigned g_pdl_mask = ~0u;
+int ti_pdl_enabled(int cls) { return (g_pdl_mask >> (cls & 31)) & 1u; }
 // 0 switches programmatic dependent launch off (every kernel then starts after the one before
-// it has ended), 1 switches it on again.
-extern "C" int ti_set_pdl(int on) { g_pdl = on ? 1 : 0; return 0; }
+// it has ended), 1 switches it on again; the mask form sets it per class of kernels (bit = class).
+extern "C" int ti_set_pdl(int on) { g_pdl_mask = on ? ~0u : 0u; return 0; }
+extern "C" int ti_set_pdl_mask(unsigned mask) { g_pdl_mask = mask; return 0; }
 
 int* ti_status_ptr() {
     int dev = 0;
