@@ -22,9 +22,12 @@
 //
 // Launch: the kernel signals at its start that its successor may be scheduled, like every
 // kernel here, but is itself launched without the programmatic attribute, so it starts when its
-// predecessor has finished.  Measured in a 36-layer decode step at 8 sequences: started early
-// (its blocks loading weights and then waiting beside the predecessor's) the step took 4.4-4.9 ms;
-// started after the predecessor 2.8-2.9 ms; the tcgen05 kernel in its place 3.0 ms.
+// predecessor has finished.  The reason is L1: every block reads all of x, and that is cheap
+// only while x sits in L1.  Blocks that start early land on SMs still configured for their
+// neighbours' large shared memory (attention, the tcgen05 product), with next to no L1 left.
+// Measured in a 36-layer decode step at 8 sequences: started early 4.4-4.9 ms; started after
+// the predecessor 2.8-2.9 ms; the same with the shared-memory carve-out forced to its maximum
+// 4.9 ms; the tcgen05 kernel in its place 3.0 ms.
 //
 // The reference has no counterpart: it decodes one sequence with one block per output row
 // (src/decode.cu:201-298) and has no batch dimension; this is that product for a small batch.
