@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -33,6 +34,9 @@ QWEN3_4B = {
     "vocab_size": 151936, "rope_theta": 1e6, "rms_norm_eps": 1e-6, "max_position_embeddings": 40960,
     "tie_word_embeddings": True,
 }
+QWEN3_8B = dict(QWEN3_4B, hidden_size=4096, intermediate_size=12288, tie_word_embeddings=False)
+QWEN3_32B = dict(QWEN3_4B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600,
+                 tie_word_embeddings=False)
 FULL_LAYERS = 36
 CONTEXT = 8192
 PREFILL_TOKENS = 2048
@@ -240,6 +244,41 @@ def run_ours(args):
     return out
 
 
+def run_workload(name: str):
+    """The two larger workloads that BASELINE.json describes, end to end through ``LLM.generate``
+    (host ids in, sampled ids out every step), random weights drawn on the device:
+    8b: 16 prompts of lengths uniform in [64, 4096], 256 greedy tokens each;
+    32b: 8 prompts of 2,048 tokens, 512 tokens each at temperature 0.7 with a fixed seed."""
+    import torch
+    from toyinfer_b200 import LLM, SamplingParams
+    if name == "8b":
+        cfg, n, new = QWEN3_8B, 16, 256
+        g = torch.Generator().manual_seed(8)
+        lens = torch.randint(64, 4097, (n,), generator=g).tolist()
+        params = SamplingParams(temperature=0.0)
+    else:
+        cfg, n, new = QWEN3_32B, 8, 512
+        lens = [2048] * n
+        params = SamplingParams(temperature=0.7, top_k=0, top_p=1.0, seed=32)
+    ctx = max(lens) + new
+    t0 = time.perf_counter()
+    llm = LLM(config=cfg, seed=0, dtype="bfloat16", max_seq_len=ctx, max_batch=n, max_tokens=sum((l + new + 63) // 64 * 64 for l in lens))
+    t_build = time.perf_counter() - t0
+    prompts = [random_tokens(l, cfg["vocab_size"], 900 + i) for i, l in enumerate(lens)]
+    llm.generate(prompts[:1], params, max_new_tokens=2, ignore_eos=True)       # warm-up
+    torch.cuda.synchronize()
+    out = llm.generate(prompts, params, max_new_tokens=new, ignore_eos=True)
+    st = llm.last_stats
+    assert all(len(r.tokens) == new for r in out)
+    return {"workload": name, "model": f"Qwen3-{name.upper()} shape, random weights, bfloat16", "layers": cfg["num_hidden_layers"],
+            "sequences": n, "prompt_tokens": st.prompt_tokens, "new_tokens_each": new,
+            "prefill_tokens_per_s": round(st.prompt_tokens / st.prefill_seconds, 1),
+            "decode_tokens_per_s": round(n * st.decode_steps / st.decode_seconds, 1),
+            "ms_per_decode_step": round(1e3 * st.decode_seconds / st.decode_steps, 3),
+            "weights_gb": round(2 * sum(math.prod(sp.shape) for sp in llm.engine.model.param_specs().values()) / 1e9, 1),
+            "build_seconds": round(t_build, 1), "through": "LLM.generate"}
+
+
 # ---------------------------------------------------------------------------
 # one kernel at a time, at the sizes of one layer of the benchmark model
 # ---------------------------------------------------------------------------
@@ -340,11 +379,16 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
                     "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K, attn_decode, attn_decode_b64, attn_decode_b1, attn_prefill")
+    ap.add_argument("--workload", default="", choices=["", "8b", "32b"],
+                    help="run one of the larger described workloads end to end instead (8B or 32B shape)")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--eager", action="store_true", help="with --kernel: plain launches instead of a graph replay")
     args = ap.parse_args()
     if args.kernel:
         print(json.dumps(run_kernel(args.kernel, args.reps, args.eager)))
+        return 0
+    if args.workload:
+        print(json.dumps(run_workload(args.workload)))
         return 0
     if args.impl == "reference":
         print(json.dumps({"impl": "reference",

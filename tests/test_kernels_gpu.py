@@ -156,6 +156,7 @@ def test_linear(K, dtype, M, N, K_):
     (2048, 2560, 9728, False),     # prefill, down projection (long contraction)
     (2048, 2560, 4096, False),     # prefill, output projection (tile width chosen to fill the SMs)
     (1000, 1536, 512, False), (777, 3000, 328, True),
+    (4741, 520, 264, False),       # more token tiles than one panel of the tile order, the last panel short
     (300, 2560, 4096, False),      # few tiles: the contraction is split
     (8, 19456, 2560, False),       # decode at batch 8, gate and up rows
     (64, 2560, 9728, False),       # decode at batch 64, split contraction

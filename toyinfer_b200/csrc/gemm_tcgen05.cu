@@ -314,6 +314,23 @@ template <int BN> constexpr int persistent_stages() {
     return n > 8 ? 8 : n;
 }
 
+// Order of the tiles of a many-token product.  Token tiles go in groups of PANEL: within a
+// group the token tile changes fastest, then the weight tile, so the blocks that run together
+// share few weight tiles and one panel of activations, and the panel (PANEL x 128 tokens x K,
+// some tens of MB at most) stays in L2 while the group sweeps over all weight tiles.  Without
+// the grouping every round of blocks would touch all token tiles: fine while the activations
+// fit L2 (2,048 tokens), a re-read of all of them per weight tile when they do not (16,384).
+constexpr int PANEL = 16;
+template <int BN>
+__device__ __forceinline__ void tile_origin(int tile, int tiles_a, int tiles_b, int& a0, int& b0) {
+    const int per_group = PANEL * tiles_b;
+    const int grp = tile / per_group, within = tile - grp * per_group;
+    const int first = grp * PANEL;
+    const int span = min(PANEL, tiles_a - first);
+    a0 = (first + within % span) * BM;
+    b0 = (within / span) * BN;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
@@ -354,7 +371,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const int a0 = (tile % tiles_a) * BM, b0 = (tile / tiles_a) * BN;   // neighbours share the weight tile
+                int a0, b0;
+                tile_origin<BN>(tile, tiles_a, tiles_b, a0, b0);
                 for (int kb = 0; kb < nkb; kb++, it++) {
                     const int s = it % STAGES;
                     if (!mbar_wait(&empty[s], (uint32_t)(((it / STAGES) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); ok = false; break; }
@@ -396,7 +414,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, n++) {
             const int buf = n & 1;
-            const int a0 = (tile % tiles_a) * BM, b0 = (tile / tiles_a) * BN;
+            int a0, b0;
+            tile_origin<BN>(tile, tiles_a, tiles_b, a0, b0);
             const int i = a0 + q * 32 + lane;
             if (!mbar_wait(&acc_full[buf], (uint32_t)((n >> 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
