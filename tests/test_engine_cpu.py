@@ -79,3 +79,24 @@ def test_unequal_batches_reuse_slots(cpu_engine, model_folders):
         assert eng.cache.slots.n_free == eng.cache.n_slots
         for g in eng.cache.kv_groups:
             assert g.pool.n_free == g.pool.n_pages
+
+
+def test_a_layers_keys_and_values_are_let_go_after_their_last_user(cpu_engine, monkeypatch):
+    """What a schedule entry leaves for entries that borrow its memory (this step's keys and
+    values) must not outlive its last user: kept until the step's end it pins every layer's
+    projection buffer (at 260,000 prompt tokens that was 3 GB per layer)."""
+    from toyinfer_b200.parts.attention import GQAAttention
+    eng = cpu_engine("B")
+    seen = []
+    inner = GQAAttention.forward
+
+    def forward(self, x, batch, mem, shared):
+        assert all(not d for d in seen), "an earlier entry's keys and values are still held"
+        seen.append(shared)
+        return inner(self, x, batch, mem, shared)
+
+    monkeypatch.setattr(GQAAttention, "forward", forward)
+    slot = eng.new_sequence()
+    eng.step([(slot, prompts_for("B", [9])[0])], None)
+    assert len(seen) == TINY["B"]["num_hidden_layers"] and all(not d for d in seen)
+    eng.end_sequence(slot)

@@ -124,9 +124,13 @@ class DecoderModel(Part):
         h = K.embed(self.embed, batch.token_ids)
         delta = None
         shared: List[dict] = [dict() for _ in self.schedule]
+        owners = [i if e.memory_of is None else e.memory_of for i, e in enumerate(self.schedule)]
+        last_use = {o: i for i, o in enumerate(owners)}
         for i, e in enumerate(self.schedule):
-            owner = i if e.memory_of is None else e.memory_of
+            owner = owners[i]
             h, delta = self.blocks[e.layer].forward(h, delta, batch, memories[owner], shared[owner])
+            if last_use[owner] == i:
+                shared[owner].clear()      # what an entry left for its borrowers (this step's keys and values) is let go
         return h, delta
 
     def logits(self, h, delta, rows: torch.Tensor) -> torch.Tensor:
