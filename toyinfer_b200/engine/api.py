@@ -136,4 +136,7 @@ class LLM:
                               dedicated_prefill=self.use_dedicated_prefill)
         out = loop.run(prompts, max_new_tokens)
         self.last_stats = loop.stats
+        if e.device.type == "cuda":
+            from .. import kernels as K
+            K.check_status()     # raises if a kernel gave up on a bounded wait: its tokens are not to be trusted
         return out
