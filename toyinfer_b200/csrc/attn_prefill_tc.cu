@@ -26,7 +26,7 @@
 #include <tuple>
 
 namespace {
-constexpr int BQ = 128, BKV = 64, THREADS = 192;
+constexpr int BQ = 128, BKV = 64, THREADS = 320;      // TMA warp, MMA warp, eight softmax warps
 
 struct Args {
     const int* cu_new; int n_heads, n_kv_heads; float scale; int window;
@@ -44,7 +44,9 @@ __device__ __forceinline__ float ex2(float x) {
 template <int HD> struct Smem {
     static constexpr int Q_BYTES = BQ * HD * 2, KV_BYTES = BKV * HD * 2;
     static constexpr int Q_OFF = 0, KV_OFF = Q_BYTES, BAR_OFF = KV_OFF + 4 * KV_BYTES;
-    static constexpr int TOTAL = BAR_OFF + 256;
+    static constexpr int MX_OFF = BAR_OFF + 256;          // row maxima of the two column halves, two tiles deep
+    static constexpr int L_OFF = MX_OFF + 2 * 2 * BQ * 4;  // row sums of the two column halves
+    static constexpr int TOTAL = L_OFF + 2 * BQ * 4;
 };
 
 template <int HD>
@@ -64,11 +66,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;      // [2]
     uint64_t* v_full = bars + 3;      // [2]
-    uint64_t* kv_empty = bars + 5;    // [2]
-    uint64_t* s_full = bars + 7;      // [2] scores of a tile are in tensor memory
-    uint64_t* p_full = bars + 9;      // [2] the softmax warps have replaced them by P
-    uint64_t* pv_done = bars + 11;    //     a tile's second product has finished (one phase per tile)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    uint64_t* k_empty = bars + 5;     // [2] a tile's first product has read its keys
+    uint64_t* v_empty = bars + 7;     // [2] a tile's second product has read its values
+    uint64_t* s_full = bars + 9;      // [2] scores of a tile are in tensor memory
+    uint64_t* p_full = bars + 11;     // [2] the softmax warps have replaced them by P
+    uint64_t* pv_done = bars + 13;    //     a tile's second product has finished (one phase per tile)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (smem_u32(smem) & 1023u) {       // the swizzled tiles need a 1024-byte aligned base
@@ -78,8 +81,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; s++) {
-            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1);
-            mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 4);
+            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 8);
         }
         mbar_init(pv_done, 1);
         mbar_fence_init();
@@ -110,17 +113,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
             for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(q_s + bx * QBOX, &q_map, h * HD + bx * 64, tok0 + q0, q_full);
-            for (int j = 0; j < n_tiles; j++) {
+            // Keys run one tile ahead of values: the keys of tile j + 1 are asked for as soon as the
+            // first product of tile j - 1 has read that buffer, the values of tile j once the second
+            // product of tile j - 2 has read theirs.
+            auto load_k = [&](int j) -> bool {
                 const int s = j & 1;
-                if (!mbar_wait(&kv_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); break; }
-                const int y = tok0 + (kt_lo + j) * BKV;
+                if (!mbar_wait(&k_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); return false; }
                 unsigned char* ks = kv_s + (size_t)s * 2 * KV_BYTES;
                 mbar_expect_tx(&k_full[s], KV_BYTES);
 #pragma unroll
-                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + bx * KBOX, &k_map, kvh * HD + bx * 64, y, &k_full[s]);
+                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + bx * KBOX, &k_map, kvh * HD + bx * 64, tok0 + (kt_lo + j) * BKV, &k_full[s]);
+                return true;
+            };
+            auto load_v = [&](int j) -> bool {
+                const int s = j & 1;
+                if (!mbar_wait(&v_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); return false; }
+                unsigned char* vs = kv_s + (size_t)s * 2 * KV_BYTES + KV_BYTES;
                 mbar_expect_tx(&v_full[s], KV_BYTES);
 #pragma unroll
-                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + KV_BYTES + bx * KBOX, &v_map, kvh * HD + bx * 64, y, &v_full[s]);
+                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(vs + bx * KBOX, &v_map, kvh * HD + bx * 64, tok0 + (kt_lo + j) * BKV, &v_full[s]);
+                return true;
+            };
+            bool ok = n_tiles > 0 && load_k(0);
+            for (int j = 0; j < n_tiles && ok; j++) {
+                if (j + 1 < n_tiles) ok = load_k(j + 1);
+                if (ok) ok = load_v(j);
             }
         }
     } else if (active && warp == 1) {
@@ -135,6 +152,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     tc_mma_bf16(tmem + (j & 1) * S_COLS, smem_desc_sw128(qa + (kk >> 2) * QBOX + (kk & 3) * 32),
                                 smem_desc_sw128(ka + (kk >> 2) * KBOX + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
                 tc_commit(&s_full[j & 1]);
+                tc_commit(&k_empty[j & 1]);      // the keys have been read once these products are through
             };
             bool ok = mbar_wait(q_full, 0) && mbar_wait(&k_full[0], 0);
             if (!ok) ti_report(status, TI_STATUS_TMA_WAIT);
@@ -162,40 +180,48 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 for (int kk = 0; kk < BKV / 16; kk++)        // 16 positions per step
                     tc_mma_bf16_ts(tmem + O_COL, p_tmem + kk * 8, smem_desc_mn_sw128(va + kk * 16 * 128, KBOX),
                                    idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-                tc_commit(&kv_empty[j & 1]);     // the stage's K and V have been read
+                tc_commit(&v_empty[j & 1]);      // the values have been read
                 tc_commit(pv_done);              // and O holds this tile's contribution
             }
         }
     } else if (active) {
-        // ---- softmax: one thread per query row
-        const int qd = warp & 3;
+        // ---- softmax: two threads per query row (= TMEM lane), each with 32 of the tile's 64
+        // positions.  Warps 2-5 take the first 32 columns, warps 6-9 the second; warp w and w + 4
+        // share the lanes 32 * (w % 4) .. + 31, the quarter of tensor memory a warp may touch.
+        // The halves meet once per tile, for the row maximum (shared memory, a barrier of their
+        // own); sums stay apart until the end.  A thread that saw a wait run out keeps going
+        // through the barriers without touching anything, so that nobody is left waiting for it.
+        const int qd = warp & 3, half = (warp - 2) >> 2;
         const int r = qd * 32 + lane;
         const int qi = q0 + r;
         const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
         const float scale2 = a.scale * 1.4426950408889634f;
+        float* mx_s = reinterpret_cast<float*>(smem + L::MX_OFF);      // [tile parity][half][row]
+        float* l_s = reinterpret_cast<float*>(smem + L::L_OFF);        // [half][row]
+        constexpr int HALF = BKV / 2;
         float m_used = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles; j++) {
             const int sb = j & 1;
-            if (!mbar_wait(&s_full[sb], (uint32_t)((j >> 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            if (ok && !mbar_wait(&s_full[sb], (uint32_t)((j >> 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
             tc_fence_after();
-            const int k0 = (kt_lo + j) * BKV;
-            const bool edge = a.window > 0 || k0 + BKV - 1 > q0 + qd * 32 || k0 + BKV > n;
+            const int k0 = (kt_lo + j) * BKV + half * HALF;
+            const bool edge = a.window > 0 || k0 + HALF - 1 > q0 + qd * 32 || k0 + HALF > n;
             const uint32_t s_addr = tmem + sb * S_COLS + lane_base;
-            // the row's 64 scores, in base-2 units
-            float v[BKV];
-            {
-                float lo[32], hi[32];
-                tmem_ld32(s_addr, lo);
-                tmem_ld32(s_addr + 32, hi);
+            // this thread's 32 scores of the row, in base-2 units
+            float v[HALF];
+            if (ok) {
+                tmem_ld32(s_addr + half * HALF, v);
 #pragma unroll
-                for (int e = 0; e < 32; e++) { v[e] = lo[e] * scale2; v[32 + e] = hi[e] * scale2; }
+                for (int e = 0; e < HALF; e++) v[e] *= scale2;
+            } else {
+#pragma unroll
+                for (int e = 0; e < HALF; e++) v[e] = -INFINITY;
             }
             if (edge) {
 #pragma unroll
-                for (int e = 0; e < BKV; e++) {
+                for (int e = 0; e < HALF; e++) {
                     const int kj = k0 + e;
                     const bool vis = kj <= qi && kj < n && (a.window <= 0 || kj > qi - a.window);
                     v[e] = vis ? v[e] : -INFINITY;
@@ -203,11 +229,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int e = 0; e < BKV; e += 4) {
+            for (int e = 0; e < HALF; e += 4) {
                 mx4[0] = fmaxf(mx4[0], v[e]); mx4[1] = fmaxf(mx4[1], v[e + 1]);
                 mx4[2] = fmaxf(mx4[2], v[e + 2]); mx4[3] = fmaxf(mx4[3], v[e + 3]);
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            mx_s[(sb * 2 + half) * BQ + r] = mx;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            mx = fmaxf(mx, mx_s[(sb * 2 + (half ^ 1)) * BQ + r]);
             float alpha = 1.f, m_new = m_used;
             if (mx > m_used + 8.f || (m_used == -INFINITY && mx > -INFINITY)) {
                 m_new = mx;
@@ -215,9 +244,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             }
             const float m_sub = m_new > -INFINITY ? m_new : 0.f;      // masked scores stay -inf, 2^-inf = 0
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t pk[BKV / 2];
+            uint32_t pk[HALF / 2];
 #pragma unroll
-            for (int e = 0; e < BKV; e += 4) {
+            for (int e = 0; e < HALF; e += 4) {
                 const float p0 = ex2(v[e] - m_sub), p1 = ex2(v[e + 1] - m_sub);
                 const float p2 = ex2(v[e + 2] - m_sub), p3 = ex2(v[e + 3] - m_sub);
                 sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
@@ -227,39 +256,45 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             }
             // Every tile's completion is waited for, in order (a parity wait can only tell one phase
             // from the next); by now the previous tile's second product has long been issued.
-            if (j > 0 && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            if (ok && j > 0 && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                // O may be touched: the previous tile's second product has finished
-                tc_fence_after();
+            if (ok) {
+                if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                    // O may be touched: the previous tile's second product has finished.  Each half
+                    // rescales its 64 of the row's 128 columns.
+                    tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < HD / 32; c++) {
-                    float o[32];
-                    tmem_ld32(tmem + O_COL + lane_base + c * 32, o);
+                    for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); c++) {
+                        float o[32];
+                        tmem_ld32(tmem + O_COL + lane_base + c * 32, o);
 #pragma unroll
-                    for (int e = 0; e < 32; e++) o[e] *= alpha;
-                    tmem_st32(tmem + O_COL + lane_base + c * 32, o);
+                        for (int e = 0; e < 32; e++) o[e] *= alpha;
+                        tmem_st32(tmem + O_COL + lane_base + c * 32, o);
+                    }
                 }
+                // P over the scores: this thread's 32 values as 16 columns of bfloat16 pairs
+                tmem_st16_bits(s_addr + half * (HALF / 2), pk);
+                l_run = l_run * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                m_used = m_new;
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[sb]);
             }
-            // P over the scores just read: this row's 64 values as 32 columns of bfloat16 pairs
-            tmem_st32_bits(s_addr, pk);
-            l_run = l_run * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            m_used = m_new;
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[sb]);
         }
         if (ok && n_tiles > 0) {
             if (!mbar_wait(pv_done, (uint32_t)((n_tiles - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
         }
+        // the row's sum: both halves'
+        l_s[half * BQ + r] = l_run;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        l_run += l_s[(half ^ 1) * BQ + r];
         if (ok) {
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             bf16* orow = (bf16*)a.out + (size_t)(tok0 + qi) * a.o_stride + (size_t)h * HD;
 #pragma unroll 1
-            for (int c = 0; c < HD / 32; c++) {
+            for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); c++) {
                 float o[32];
                 tmem_ld32(tmem + O_COL + lane_base + c * 32, o);
                 if (qi < n) {
