@@ -39,6 +39,32 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Two floats in one 64-bit register pair, for the packed float32 instructions of sm_100: the
+// softmax warps are bound by how many instructions they issue, and these do two elements each.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 // Shared memory of a block (all dynamic, so that two blocks fit an SM): the query tile, two
 // stages of (K tile, V tile), then the mbarriers.
 template <int HD> struct Smem {
@@ -209,12 +235,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const int k0 = (kt_lo + j) * BKV + half * HALF;
             const bool edge = a.window > 0 || k0 + HALF - 1 > q0 + qd * 32 || k0 + HALF > n;
             const uint32_t s_addr = tmem + sb * S_COLS + lane_base;
-            // this thread's 32 scores of the row, in base-2 units
+            // this thread's 32 scores of the row, as the product left them (the scale comes later)
             float v[HALF];
             if (ok) {
                 tmem_ld32(s_addr + half * HALF, v);
-#pragma unroll
-                for (int e = 0; e < HALF; e++) v[e] *= scale2;
             } else {
 #pragma unroll
                 for (int e = 0; e < HALF; e++) v[e] = -INFINITY;
@@ -227,13 +251,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     v[e] = vis ? v[e] : -INFINITY;
                 }
             }
+            // row maximum in base-2 units (the scale is positive): three-input maxima, four chains
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int e = 0; e < HALF; e += 4) {
-                mx4[0] = fmaxf(mx4[0], v[e]); mx4[1] = fmaxf(mx4[1], v[e + 1]);
-                mx4[2] = fmaxf(mx4[2], v[e + 2]); mx4[3] = fmaxf(mx4[3], v[e + 3]);
+            for (int e = 0; e < HALF; e += 8) {
+                mx4[0] = max3(mx4[0], v[e], v[e + 1]); mx4[1] = max3(mx4[1], v[e + 2], v[e + 3]);
+                mx4[2] = max3(mx4[2], v[e + 4], v[e + 5]); mx4[3] = max3(mx4[3], v[e + 6], v[e + 7]);
             }
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
             mx_s[(sb * 2 + half) * BQ + r] = mx;
             asm volatile("bar.sync 1, 256;" ::: "memory");
             mx = fmaxf(mx, mx_s[(sb * 2 + (half ^ 1)) * BQ + r]);
@@ -243,17 +268,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 alpha = ex2(m_used - m_new);        // 0 when nothing was visible before
             }
             const float m_sub = m_new > -INFINITY ? m_new : 0.f;      // masked scores stay -inf, 2^-inf = 0
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            // p = 2^(s * scale - m): one packed multiply-add per two scores, two exponentials, one
+            // packed add into the sums, one conversion to a bfloat16 pair
+            const unsigned long long sc2 = pack2(scale2, scale2), nm2 = pack2(-m_sub, -m_sub);
+            unsigned long long sum2[2] = {0ull, 0ull};
             uint32_t pk[HALF / 2];
 #pragma unroll
             for (int e = 0; e < HALF; e += 4) {
-                const float p0 = ex2(v[e] - m_sub), p1 = ex2(v[e + 1] - m_sub);
-                const float p2 = ex2(v[e + 2] - m_sub), p3 = ex2(v[e + 3] - m_sub);
-                sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
+                float x0, x1, x2, x3;
+                unpack2(fma2(pack2(v[e], v[e + 1]), sc2, nm2), x0, x1);
+                unpack2(fma2(pack2(v[e + 2], v[e + 3]), sc2, nm2), x2, x3);
+                const float p0 = ex2(x0), p1 = ex2(x1), p2 = ex2(x2), p3 = ex2(x3);
+                sum2[0] = add2(sum2[0], pack2(p0, p1));
+                sum2[1] = add2(sum2[1], pack2(p2, p3));
                 __nv_bfloat162 t0 = __floats2bfloat162_rn(p0, p1), t1 = __floats2bfloat162_rn(p2, p3);
                 pk[e >> 1] = *reinterpret_cast<uint32_t*>(&t0);
                 pk[(e >> 1) + 1] = *reinterpret_cast<uint32_t*>(&t1);
             }
+            float sum4[4];
+            unpack2(sum2[0], sum4[0], sum4[1]);
+            unpack2(sum2[1], sum4[2], sum4[3]);
             // Every tile's completion is waited for, in order (a parity wait can only tell one phase
             // from the next); by now the previous tile's second product has long been issued.
             if (ok && j > 0 && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
