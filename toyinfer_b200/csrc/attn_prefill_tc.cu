@@ -170,13 +170,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         if (lane == 0) {
             constexpr uint32_t idesc_s = instr_desc_bf16(BKV, false);    // S: N = positions, K tile K-major
             constexpr uint32_t idesc_o = instr_desc_bf16(HD, true);      // O: N = head elements, V tile MN-major
-            const uint32_t qa = smem_u32(q_s);
+            // The one thread that issues the products is on the block's critical path: descriptors
+            // are made once; inside the loop a descriptor is a base plus a constant (the address
+            // field counts 16-byte units and cannot overflow within shared memory).
+            const uint64_t q_desc = smem_desc_sw128(smem_u32(q_s));
+            const uint64_t k_desc0 = smem_desc_sw128(smem_u32(kv_s)), k_desc1 = smem_desc_sw128(smem_u32(kv_s + 2 * KV_BYTES));
+            const uint64_t v_desc0 = smem_desc_mn_sw128(smem_u32(kv_s + KV_BYTES), KBOX);
+            const uint64_t v_desc1 = smem_desc_mn_sw128(smem_u32(kv_s + 3 * KV_BYTES), KBOX);
             auto issue_s = [&](int j) {       // S_j = Q K_j^T into score buffer j & 1
-                const uint32_t ka = smem_u32(kv_s + (size_t)(j & 1) * 2 * KV_BYTES);
+                const uint64_t kd = (j & 1) ? k_desc1 : k_desc0;
+                const uint32_t d = tmem + (j & 1) * S_COLS;
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; kk++)      // 64 columns per box, 32 bytes per step of 16
-                    tc_mma_bf16(tmem + (j & 1) * S_COLS, smem_desc_sw128(qa + (kk >> 2) * QBOX + (kk & 3) * 32),
-                                smem_desc_sw128(ka + (kk >> 2) * KBOX + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
+                    tc_mma_bf16(d, q_desc + (uint64_t)(((kk >> 2) * QBOX + (kk & 3) * 32) >> 4),
+                                kd + (uint64_t)(((kk >> 2) * KBOX + (kk & 3) * 32) >> 4), idesc_s, kk > 0 ? 1u : 0u);
                 tc_commit(&s_full[j & 1]);
                 tc_commit(&k_empty[j & 1]);      // the keys have been read once these products are through
             };
@@ -200,11 +207,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     ti_report(status, TI_STATUS_PIPE_WAIT); ok = false; break;
                 }
                 tc_fence_after();
-                const uint32_t va = smem_u32(kv_s + (size_t)(j & 1) * 2 * KV_BYTES + KV_BYTES);
+                const uint64_t vd = (j & 1) ? v_desc1 : v_desc0;
                 const uint32_t p_tmem = tmem + (j & 1) * S_COLS;       // P: two bfloat16 per column, 8 columns per step
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; kk++)        // 16 positions per step
-                    tc_mma_bf16_ts(tmem + O_COL, p_tmem + kk * 8, smem_desc_mn_sw128(va + kk * 16 * 128, KBOX),
+                    tc_mma_bf16_ts(tmem + O_COL, p_tmem + kk * 8, vd + (uint64_t)((kk * 16 * 128) >> 4),
                                    idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                 tc_commit(&v_empty[j & 1]);      // the values have been read
                 tc_commit(pv_done);              // and O holds this tile's contribution
