@@ -105,6 +105,31 @@ def test_long_decoding(model_folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_decoding_across_a_length_class(tmp_path, dtype):
+    """Decode steps are captured per class of sequence lengths (powers of two from 1,024): a
+    sequence that grows from 1,000 to 1,050 positions moves from one captured step to the next,
+    with another sequence of 30 positions beside it; both must follow the plain implementation."""
+    from toyinfer_b200.weights import write_model_folder
+    cfg = dict(TINY["A"], max_position_embeddings=2304)
+    folder = write_model_folder(cfg, 17, str(tmp_path / "long"))
+    eng = make_engine(folder, dtype, max_tokens=4096, max_batch=2)
+    g = torch.Generator().manual_seed(4)
+    long_ids = torch.randint(0, cfg["vocab_size"], (1050,), generator=g).tolist()
+    short_ids = torch.randint(0, cfg["vocab_size"], (80,), generator=g).tolist()
+    want_long, want_short = plain_logits(folder, long_ids, dtype), plain_logits(folder, short_ids, dtype)
+    a, b = eng.new_sequence(), eng.new_sequence()
+    eng.step([(a, long_ids[:1000]), (b, short_ids[:30])], [[], []])
+    got_a, got_b = [], []
+    for t in range(50):
+        out = eng.step([(a, [long_ids[1000 + t]]), (b, [short_ids[30 + t]])], [[0], [0]])
+        got_a.append(out[0:1].clone())
+        got_b.append(out[1:2].clone())
+    assert len({cls for (_, cls) in eng._graphs}) == 2
+    assert_logits_close(torch.cat(got_a), want_long[1000:1050], dtype, "across a length class, long")
+    assert_logits_close(torch.cat(got_b), want_short[30:80], dtype, "across a length class, short")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_padding_and_company_change_nothing(model_folders, dtype):
     """A request's logits are the same alone, in a batch of 3 (padded to 4 by the graph's
     bucket) and in a batch of 5 (padded to 8), beyond rounding."""

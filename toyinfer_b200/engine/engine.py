@@ -71,7 +71,7 @@ class Engine:
         self.memories = self.cache.views(len(model.schedule))
         self.use_cuda_graph = bool(use_cuda_graph) and self.device.type == "cuda"
         self._eager_bufs: Dict[Tuple[int, int], BatchBuffers] = {}
-        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}     # (batch bucket, length class) -> captured step
         self.graph_replays = 0
 
     # -- construction -----------------------------------------------------------
@@ -208,13 +208,19 @@ class Engine:
     # -- accounting for measurements ----------------------------------------------------
     def launches_per_step(self, n_seq: int) -> int:
         """Kernels that one captured decode step of ``n_seq`` sequences launches."""
-        g = self._graphs.get(_bucket(n_seq, self.max_batch))
+        g = self._graph_of_bucket(_bucket(n_seq, self.max_batch))
         return g.launches if g is not None else 0
 
     def decode_metadata_bytes(self, n_seq: int) -> int:
         """Bytes copied host to device before each decode step of ``n_seq`` sequences."""
-        g = self._graphs.get(_bucket(n_seq, self.max_batch))
+        g = self._graph_of_bucket(_bucket(n_seq, self.max_batch))
         return g.buf.total * 4 if g is not None else 0
+
+    def _graph_of_bucket(self, bucket: int):
+        for (b, _), g in self._graphs.items():
+            if b == bucket:
+                return g
+        return None
 
     # -- helpers ----------------------------------------------------------------------
     def _eager_batch(self, mode, slots, starts, tokens) -> StepBatch:
@@ -228,9 +234,17 @@ class Engine:
     def _decode_graph(self, slots, starts, tokens, token_source=None) -> torch.Tensor:
         n = len(slots)
         b = _bucket(n, self.max_batch)
-        g = self._graphs.get(b)
+        # Launch shapes that depend on how long sequences are (how the keys of a sequence are split
+        # over blocks) are planned for a class of lengths, not for the engine's limit: powers of two
+        # from 1,024 positions up.  A batch that grows past its class moves to the next graph.
+        longest = max(starts) + 1
+        cls = 1024
+        while cls < longest:
+            cls <<= 1
+        cls = min(cls, self.max_seq_len)
+        g = self._graphs.get((b, cls))
         if g is None:
-            g = self._graphs[b] = _DecodeGraph(self, b)
+            g = self._graphs[(b, cls)] = _DecodeGraph(self, b, cls)
         return g.run(slots, starts, tokens, token_source)
 
 
@@ -239,9 +253,10 @@ class _DecodeGraph:
     engine weakly: engine and graphs then form no cycle, and both are released (with their
     device memory) when the last reference to the engine goes, not at some later collection."""
 
-    def __init__(self, engine: Engine, bucket: int):
+    def __init__(self, engine: Engine, bucket: int, plan_len: int):
         self._engine = weakref.ref(engine)
         self.bucket = bucket
+        self.plan_len = plan_len
         self.buf = BatchBuffers(bucket, bucket, engine.device)
         self.rows = torch.arange(bucket, dtype=torch.int32, device=engine.device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -264,7 +279,7 @@ class _DecodeGraph:
         e = self.engine
         pad = self.bucket - len(slots)
         batch = fill_batch(self.buf, "extend", slots, starts, tokens, e.cache.scratch_slot,
-                           e.max_seq_len, pad_seqs=pad)
+                           self.plan_len, pad_seqs=pad)
         if token_source is not None:
             batch.token_ids[:len(slots)].copy_(token_source)      # after the upload, before the replay
         if self.graph is None:
