@@ -1,6 +1,6 @@
 """Generation through the entry point and the command line on the GPU: greedy tokens
 equal the plain implementation's; sampled tokens follow the fixed seed whatever the
-batch; the BASELINE workloads of the two tiny configurations."""
+batch; the workloads named for the two tiny configurations (three greedy prompts, four sampled ones)."""
 from __future__ import annotations
 
 import json

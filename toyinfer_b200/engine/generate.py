@@ -175,13 +175,13 @@ class GenerationLoop:
                     drawn = st.read(handle)
                 else:
                     drawn = st.sample(logits, draw_keys, draw_steps)
-                verdict = {}
+                goes_on = {}
                 for (i, slot), tok in zip(drawing, drawn):
-                    verdict[i] = self._accept(results[i], len(prompts[i]), int(tok), max_new)
+                    goes_on[i] = self._accept(results[i], len(prompts[i]), int(tok), max_new)
                     last[i] = int(tok)
                 nxt = []
                 for i, slot in live:
-                    if verdict.get(i, True):
+                    if goes_on.get(i, True):
                         nxt.append((i, slot))
                     else:
                         st.end_sequence(slot)
