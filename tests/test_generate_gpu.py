@@ -136,3 +136,18 @@ def test_command_line(model_folders):
     r2 = subprocess.run(cmd + ["--use_dedicated_prefill", "0"], capture_output=True, text=True, timeout=300)
     assert r2.returncode == 0, r2.stderr
     assert [json.loads(l)["tokens"] for l in r2.stdout.splitlines() if l.startswith("{")] == [l["tokens"] for l in lines]
+
+
+def test_command_line_with_random_weights(tmp_path):
+    """--random takes a config.json alone; the same seed draws the same weights, so two runs
+    print the same tokens."""
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(TINY["B"]))
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "toyinfer"), "--random", str(cfg_path), "--seed", "5", "--max_seq_len", "128",
+           "--dtype", "float32", "--temperature", "0", "--prompt_ids", "3,1,4,1,5;9,2,6", "--max_new_tokens", "5", "--ignore_eos", "1"]
+    runs = []
+    for _ in range(2):
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr
+        runs.append([json.loads(l)["tokens"] for l in r.stdout.splitlines() if l.startswith("{")])
+    assert runs[0] == runs[1] and [len(t) for t in runs[0]] == [5, 5]

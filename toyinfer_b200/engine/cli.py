@@ -7,6 +7,7 @@ search (--beam_size above 1 is refused).
 
     bin/toyinfer --model_dir DIR --max_seq_len 4096 --prompt_ids "1,2,3;4,5" --max_new_tokens 32
     bin/toyinfer --model_dir DIR --max_seq_len 8192 --bench long
+    bin/toyinfer --random config.json --seed 3 --max_seq_len 8192 --bench short
 """
 from __future__ import annotations
 
@@ -41,7 +42,9 @@ def _prompts(text: str) -> List[List[int]]:
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="toyinfer", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--model_dir", required=True, help="Model dir (config.json + safetensors)")
+    ap.add_argument("--model_dir", default="", help="Model dir (config.json + safetensors)")
+    ap.add_argument("--random", default="", metavar="CONFIG_JSON",
+                    help="instead of --model_dir: a config.json alone; weights are drawn from --seed on the device")
     ap.add_argument("--max_seq_len", type=int, default=0, help="Maximum inference context window "
                     "(0: the model's max_position_embeddings)")
     ap.add_argument("--thinking", type=_flag, default=True, help="accepted for compatibility; selects a chat "
@@ -76,14 +79,22 @@ def main(argv=None) -> int:
     if args.beam_size != 1:
         print("toyinfer: beam search is not part of this library (--beam_size must be 1)", file=sys.stderr)
         return 2
+    if bool(args.model_dir) == bool(args.random):
+        print("toyinfer: give either --model_dir or --random CONFIG_JSON", file=sys.stderr)
+        return 2
     if not args.bench and not args.prompt_ids:
         print("toyinfer: give --prompt_ids or --bench short|long", file=sys.stderr)
         return 2
     import torch
     from .. import LLM, SamplingParams
 
-    llm = LLM(args.model_dir, dtype=args.dtype, max_seq_len=args.max_seq_len or None, max_batch=args.max_batch,
-              enable_cuda_graph=args.enable_cuda_graph, use_dedicated_prefill=args.use_dedicated_prefill)
+    common = dict(dtype=args.dtype, max_seq_len=args.max_seq_len or None, max_batch=args.max_batch,
+                  enable_cuda_graph=args.enable_cuda_graph, use_dedicated_prefill=args.use_dedicated_prefill)
+    if args.random:
+        with open(args.random) as f:
+            llm = LLM(config=json.load(f), seed=args.seed, **common)
+    else:
+        llm = LLM(args.model_dir, **common)
     vocab = llm.engine.spec.vocab_size
     max_new = args.max_new_tokens
     ignore_eos = args.ignore_eos
