@@ -132,11 +132,16 @@ def attention_decode(q, mem, scale, window, batch):
     return out
 
 
+def attention_decode_step(q, k, v, q_w, k_w, eps, tables, mem, scale, window, batch):
+    qk_norm_rope_store(q, k, v, q_w, k_w, eps, tables, batch, mem if k is not None else None)
+    return attention_decode(q, mem, scale, window, batch)
+
+
 def argmax(logits):
     return torch.argmax(logits, dim=1).to(torch.int32)
 
 
 def install(monkeypatch) -> None:
     for name in ("embed", "rmsnorm", "add_rmsnorm", "gather_add", "linear", "swiglu", "linear_swiglu", "qk_norm_rope_store",
-                 "attention_prefill", "attention_decode", "argmax"):
+                 "attention_prefill", "attention_decode", "attention_decode_step", "argmax"):
         monkeypatch.setattr(K, name, globals()[name])

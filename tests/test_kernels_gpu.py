@@ -487,6 +487,63 @@ def test_attention_decode(K, dtype, nh, nkv, hd, window):
             torch.testing.assert_close(got[s], want, **ATT_TOL[dtype])
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,norm", [(32, 8, 128, 0, "bf16"), (8, 1, 128, 100, "f32"), (16, 1, 64, 0, "bf16"),
+                                                   (40, 8, 128, 0, None), (4, 4, 64, 70, "bf16")])
+@pytest.mark.parametrize("rotate", [True, False])
+def test_attention_decode_step_one_kernel_equals_two(K, nh, nkv, hd, window, norm, rotate):
+    """The decode kernel with norm, rotation and cache store folded in against the rotate-and-store
+    kernel followed by the plain decode kernel: the same output and the same cache, bit for bit
+    (both round at the same places).  Lengths at the start, the end and the middle of a page, a
+    ring that has wrapped, several split counts, and a layer that borrows its memory (no k, v)."""
+    from toyinfer_b200.kernels import attention
+    dtype = torch.bfloat16
+    lens = [1, 64, 65, 300, 129, 128]
+    B = len(lens)
+    g = torch.Generator(device="cuda").manual_seed(77)
+    mem = make_mem(dtype, B, nkv, hd, pages=30, window=window, dirty=0.0)
+    free = list(range(30, 0, -1))
+    for s, n in enumerate(lens):
+        need = (min(n, mem.ring_rows) if mem.ring_rows else n) + 63 >> 6
+        hist_k = torch.randn(n, nkv, hd, generator=g, device="cuda").to(dtype)
+        hist_v = torch.randn(n, nkv, hd, generator=g, device="cuda").to(dtype)
+        fill_cache(mem, s, [free.pop() for _ in range(need)], hist_k, hist_v)
+    qkv = torch.randn(B, (nh + 2 * nkv) * hd + 8, generator=g, device="cuda").to(dtype)      # rows wider than needed: strided views
+    wdt = {"bf16": torch.bfloat16, "f32": torch.float32, None: None}[norm]
+    q_w = (1 + 0.1 * torch.randn(hd, generator=g, device="cuda")).to(wdt) if wdt else None
+    k_w = (1 + 0.1 * torch.randn(hd, generator=g, device="cuda")).to(wdt) if wdt else None
+    pos = torch.arange(400, device="cuda", dtype=torch.float32)[:, None] * torch.exp(
+        -torch.arange(hd // 2, device="cuda", dtype=torch.float32) / (hd // 2) * math.log(1e4))[None, :]
+    tables = (torch.cos(pos).contiguous(), torch.sin(pos).contiguous(), hd) if rotate else None
+    scale = 1.0 / math.sqrt(hd)
+
+    def views(buf):
+        q = buf[:, :nh * hd].view(B, nh, hd)
+        k = buf[:, nh * hd:(nh + nkv) * hd].view(B, nkv, hd)
+        v = buf[:, (nh + nkv) * hd:(nh + 2 * nkv) * hd].view(B, nkv, hd)
+        return q, k, v
+
+    for plan in (64, 4096):
+        for borrow in (False, True):
+            batch = make_batch("extend", list(range(B)), [n - 1 for n in lens], [1] * B, plan_len=plan)
+            mem_a = type(mem)(mem.k_pages.clone(), mem.v_pages.clone(), mem.page_table, nkv, hd, window, mem.ring_rows)
+            mem_b = type(mem)(mem.k_pages.clone(), mem.v_pages.clone(), mem.page_table, nkv, hd, window, mem.ring_rows)
+            qa, ka, va = views(qkv.clone())
+            qb, kb, vb = views(qkv.clone())
+            if borrow:
+                ka = va = kb = vb = None
+            assert attention.decode_fused_eligible(qb, kb, vb, q_w, k_w, tables, mem_b)
+            K.qk_norm_rope_store(qa, ka, va, q_w, k_w, 1e-6, tables, batch, None if borrow else mem_a)
+            want = K.attention_decode(qa, mem_a, scale, window, batch)
+            before = K.launch_count
+            got = K.attention_decode_step(qb, kb, vb, q_w, k_w, 1e-6, tables, mem_b, scale, window, batch)
+            assert K.launch_count - before <= 2
+            K.check_status()
+            assert torch.equal(got, want), (plan, borrow)
+            assert torch.equal(mem_a.k_pages, mem_b.k_pages) and torch.equal(mem_a.v_pages, mem_b.v_pages)
+            if not borrow:
+                assert not torch.equal(mem_b.k_pages, mem.k_pages)      # something was stored
+
+
 @pytest.mark.parametrize("dtype", DT)
 def test_attention_decode_far_key(K, dtype):
     nh, nkv, hd, n, far = 8, 2, 64, 700, 3

@@ -35,10 +35,65 @@ __device__ __forceinline__ float ex2(float x) {      // 2^x, the hardware's appr
     return y;
 }
 
+// The new token's projections as the product before this kernel left them: not yet normed,
+// rotated or stored.  With FUSED the kernel does that itself (formulas and rounding as in
+// rope_store.cu: per-head RMS norm rounded to bfloat16, then the rotation of pairs i, i + hd/2,
+// rounded again), so that one kernel fewer stands between the projection and the attention.
+// k and v are null for a layer that reads another layer's memory.
+struct FuseArgs {
+    const bf16* q; const bf16* k; const bf16* v;        // [B, heads, hd], [B, kv_heads, hd] twice
+    long long q_stride, k_stride, v_stride;             // elements between consecutive sequences
+    const void* q_w; const void* k_w; int w_is_f32; float eps;   // norm weights [hd] or null
+    const float* cos_t; const float* sin_t; int max_pos;         // rotary tables [max_pos, hd/2] or null
+    bf16* k_pages; bf16* v_pages;                       // the cache, writable
+};
+
+// One warp: norm (when w is given) and rotation (when cs is given) of one head; bfloat16 result to dst.
 template <int HD>
+__device__ __forceinline__ void norm_rotate_head(const bf16* x, const void* w, int w_is_f32, float eps,
+                                                 const float* cs, const float* sn, bf16* dst, int lane) {
+    constexpr int half = HD / 2;
+    float r = 1.f;
+    if (w) {
+        float ss = 0.f;
+        for (int i = lane * 2; i < HD; i += 64) {
+            const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + i));
+            ss = fmaf(t.x, t.x, ss);
+            ss = fmaf(t.y, t.y, ss);
+        }
+        ss = warp_sum(ss);
+        r = rsqrtf(fmaf(ss, 1.0f / (float)HD, eps));
+    }
+    for (int i = lane * 2; i < half; i += 64) {
+        float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + i));
+        float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + i + half));
+        if (w) {
+            float2 wl, wh;
+            if (w_is_f32) {
+                wl = *reinterpret_cast<const float2*>((const float*)w + i);
+                wh = *reinterpret_cast<const float2*>((const float*)w + i + half);
+            } else {
+                wl = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>((const bf16*)w + i));
+                wh = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>((const bf16*)w + i + half));
+            }
+            lo.x = __bfloat162float(__float2bfloat16_rn(lo.x * r * wl.x)); lo.y = __bfloat162float(__float2bfloat16_rn(lo.y * r * wl.y));
+            hi.x = __bfloat162float(__float2bfloat16_rn(hi.x * r * wh.x)); hi.y = __bfloat162float(__float2bfloat16_rn(hi.y * r * wh.y));
+        }
+        if (cs) {
+            const float2 c = *reinterpret_cast<const float2*>(cs + i), sv = *reinterpret_cast<const float2*>(sn + i);
+            const float2 nlo = make_float2(lo.x * c.x - hi.x * sv.x, lo.y * c.y - hi.y * sv.y);
+            const float2 nhi = make_float2(hi.x * c.x + lo.x * sv.x, hi.y * c.y + lo.y * sv.y);
+            lo = nlo; hi = nhi;
+        }
+        *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(lo.x, lo.y);
+        *reinterpret_cast<__nv_bfloat162*>(dst + i + half) = __floats2bfloat162_rn(hi.x, hi.y);
+    }
+}
+
+template <int HD, bool FUSED>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                       tiattn::DecodeArgs a, int* status) {
+                       tiattn::DecodeArgs a, FuseArgs f, int* status) {
     ti_pdl_trigger();
     constexpr int TILE_BYTES = TILE * HD * 2;          // one of K or V
     constexpr int KSTEPS = HD / 16, NT = HD / 8;
@@ -47,6 +102,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full[STAGES];
     __shared__ int s_abort;
+    __shared__ __align__(16) bf16 q_s[FUSED ? 16 * HD : 8];       // the block's query heads, normed and rotated
+    __shared__ __align__(16) bf16 kv_new[FUSED ? 2 * HD : 8];     // the new token's key and value of this kv head
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) mbar_init(&full[s], 1);
@@ -92,20 +149,58 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
     };
     // The tile that holds the newest position is being written by the kernel before this one;
     // every other tile may be requested right away, while that kernel still runs.
+    // (With FUSED nobody writes the cache before this kernel does: every tile may come early; the
+    // newest position's line is put into the tile by hand below.)
     const int newest_tile = (L - 1) / TILE;
     unsigned early = 0;
     if (t == 0)
         for (int i = 0; i < STAGES - 1 && i < my_n; i++)
-            if (my_lo + i != newest_tile) { issue(i); early |= 1u << i; }
+            if (FUSED || my_lo + i != newest_tile) { issue(i); early |= 1u << i; }
     ti_pdl_sync();
     if (t == 0)
         for (int i = 0; i < STAGES - 1 && i < my_n; i++)
             if (!((early >> i) & 1u)) issue(i);
 
+    const bool store_new = FUSED && f.k != nullptr;
+    const bool has_newest = L > 0 && newest_tile >= my_lo && newest_tile < my_lo + my_n;
+    if (FUSED) {
+        const bf16* fq = ti_dependent(f.q);
+        const bf16* fk = ti_dependent(f.k);
+        const bf16* fv = ti_dependent(f.v);
+        int pos = max(L - 1, 0);
+        if (pos >= f.max_pos) pos = f.max_pos - 1;
+        const float* cs = f.cos_t ? f.cos_t + (size_t)pos * (HD / 2) : nullptr;
+        const float* sn = f.sin_t ? f.sin_t + (size_t)pos * (HD / 2) : nullptr;
+        for (int item = warp; item < rows + 2; item += THREADS / 32) {
+            if (item < rows)
+                norm_rotate_head<HD>(fq + (size_t)b * f.q_stride + (size_t)(h0 + item) * HD, f.q_w, f.w_is_f32, f.eps, cs, sn,
+                                     q_s + item * HD, lane);
+            else if (item == rows && store_new)
+                norm_rotate_head<HD>(fk + (size_t)b * f.k_stride + (size_t)kvh * HD, f.k_w, f.w_is_f32, f.eps, cs, sn, kv_new, lane);
+            else if (item == rows + 1 && store_new)
+                for (int i = lane * 2; i < HD; i += 64)
+                    *reinterpret_cast<__nv_bfloat162*>(kv_new + HD + i) =
+                        *reinterpret_cast<const __nv_bfloat162*>(fv + (size_t)b * f.v_stride + (size_t)kvh * HD + i);
+        }
+        __syncthreads();
+        // the new key and value go to their line of the cache, for the steps to come: one block per
+        // (sequence, kv head) does it, the one whose tiles include the newest position
+        if (store_new && has_newest && grp == 0 && t < 2 * (HD / 8)) {
+            const int row = a.ring_rows > 0 ? (L - 1) % a.ring_rows : L - 1;
+            const int pidx = row / TILE;
+            const int page = pidx < a.table_width ? a.page_table[(size_t)slot * a.table_width + pidx] : -1;
+            if (page >= 0 && page < a.n_pages) {
+                const bool is_v = t >= HD / 8;
+                const int c = (is_v ? t - HD / 8 : t) * 8;
+                bf16* dst = (is_v ? f.v_pages : f.k_pages) + (((size_t)page * a.n_kv_heads + kvh) * TILE + row % TILE) * HD + c;
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(kv_new + (is_v ? HD : 0) + c);
+            }
+        }
+    }
     // the queries as A fragments: row lane/4 (and +8) is a query head, zero beyond `rows`
     uint32_t qf[KSTEPS][4];
     {
-        const bf16* q = (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)h0 * HD;
+        const bf16* q = FUSED ? q_s : (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)h0 * HD;
         const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ks++) {
@@ -138,7 +233,19 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
         const uint32_t vbase = kbase + TILE_BYTES;
         const int p0 = (my_lo + i) * TILE;
         const int key0 = warp * 16;                      // this warp's positions within the tile
-        const bool edge = p0 < lo || p0 + TILE > L;      // some positions of the tile are out of range
+        const bool patched = store_new && my_lo + i == newest_tile;
+        const bool edge = p0 < lo || p0 + TILE > L || patched;      // some positions of the tile are out of range (or written by hand)
+        if (patched) {
+            // the newest position's key and value are not in the cache the tile was read from
+            const int rr = (L - 1) - p0;
+            if (warp == rr / 16 && lane < 2 * (HD / 8)) {
+                const bool is_v = lane >= HD / 8;
+                const int c = (is_v ? lane - HD / 8 : lane) * 8;
+                *reinterpret_cast<uint4*>(smem + (size_t)stage * 2 * TILE_BYTES + (is_v ? TILE_BYTES : 0) + tile_offset<HD>(rr, c)) =
+                    *reinterpret_cast<const uint4*>(kv_new + (is_v ? HD : 0) + c);
+            }
+            __syncwarp();
+        }
 
         if (edge) {
             // lines outside [lo, L) may hold anything: clear this warp's such value rows
@@ -316,14 +423,14 @@ int page_map(const void* pages, long long rows, int hd, CUtensorMap* out) {
     return 0;
 }
 
-template <int HD>
-int launch(const tiattn::DecodeArgs& a, int n_seq, cudaStream_t stream) {
+template <int HD, bool FUSED>
+int launch(const tiattn::DecodeArgs& a, const FuseArgs& f, int n_seq, cudaStream_t stream) {
     constexpr size_t stage_bytes = 2 * TILE * HD * 2;
     constexpr size_t merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * sizeof(float);
     constexpr size_t smem = (STAGES * stage_bytes > merge_bytes ? STAGES * stage_bytes : merge_bytes) + 1024;
     static bool configured = false;
     if (!configured) {
-        TI_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TI_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<HD, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
     CUtensorMap km, vm;
@@ -334,7 +441,7 @@ int launch(const tiattn::DecodeArgs& a, int n_seq, cudaStream_t stream) {
     TI_REQUIRE(status != nullptr, "attention_decode: no status word");
     const int g = a.n_heads / a.n_kv_heads;
     dim3 grid(n_seq, a.n_kv_heads * ((g + 15) / 16), a.n_splits);
-    TI_CUDA(ti_launch_class<3>(attn_decode_mma_kernel<HD>, grid, dim3(THREADS), smem, stream, km, vm, a, status));
+    TI_CUDA(ti_launch_class<3>(attn_decode_mma_kernel<HD, FUSED>, grid, dim3(THREADS), smem, stream, km, vm, a, f, status));
     TI_CHECK_LAUNCH("attention_decode (tensor cores)");
     if (a.n_splits > 1) {
         dim3 cgrid(n_seq, a.n_heads);
@@ -369,5 +476,52 @@ extern "C" int ti_attn_decode_mma(const void* q, long long q_stride, const void*
     a.seq_slot = seq_slot; a.seq_len = seq_len; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.hd = head_dim;
     a.window = window; a.n_splits = n_splits; a.scale = scale; a.out = out; a.o_stride = o_stride;
     a.part_o = part_o; a.part_ml = part_ml;
-    return head_dim == 64 ? launch<64>(a, n_seq, stream) : launch<128>(a, n_seq, stream);
+    FuseArgs f = {};
+    return head_dim == 64 ? launch<64, false>(a, f, n_seq, stream) : launch<128, false>(a, f, n_seq, stream);
+}
+
+// The same with the step before it folded in: q[B, heads, hd], k and v[B, kv_heads, hd] are the
+// projection's output for the one new token of each sequence (position seq_len - 1).  Per head:
+// RMS norm with q_w / k_w (null: none; float32 or bfloat16), rotation by the float32 tables
+// cos, sin [max_pos, hd/2] (null: none), then k and v are written to their line of the cache and
+// the attention runs.  k and v null: a layer that reads another's memory; only q is prepared.
+extern "C" int ti_attn_decode_fused(const void* q, const void* k, const void* v, long long q_stride, long long k_stride,
+                                    long long v_stride, const void* q_w, const void* k_w, int w_is_f32, float eps,
+                                    const float* cos_t, const float* sin_t, int max_pos,
+                                    void* k_pages, void* v_pages, const int* page_table, int table_width, int page_size,
+                                    int ring_rows, int n_pages, const int* seq_slot, const int* seq_len, int n_seq,
+                                    int n_heads, int n_kv_heads, int head_dim, float scale, int window, int n_splits,
+                                    void* out, long long o_stride, float* part_o, float* part_ml, int dtype,
+                                    cudaStream_t stream) {
+    if (n_seq == 0) return 0;
+    TI_REQUIRE(dtype == TI_BF16, "attention_decode (fused): bfloat16 only");
+    TI_REQUIRE(head_dim == 64 || head_dim == 128, "attention_decode (fused): head size %d is not 64 or 128", head_dim);
+    TI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_decode: bad head counts");
+    TI_REQUIRE(page_size == TILE, "attention_decode: pages of %d positions, this kernel works on %d", page_size, TILE);
+    TI_REQUIRE(ring_rows % page_size == 0, "attention_decode: ring of %d rows is not whole pages", ring_rows);
+    TI_REQUIRE(window == 0 || ring_rows == 0 || ring_rows >= window, "attention_decode: ring smaller than the window");
+    TI_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention_decode: bad split count %d", n_splits);
+    TI_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_decode: split results need scratch memory");
+    TI_REQUIRE(q != nullptr && (k == nullptr) == (v == nullptr), "attention_decode (fused): queries are needed; keys and values go together");
+    TI_REQUIRE((cos_t == nullptr) == (sin_t == nullptr) && (!cos_t || max_pos > 0), "attention_decode (fused): cos and sin tables go together");
+    auto ok4 = [](const void* p, long long stride) { return (reinterpret_cast<uintptr_t>(p) & 3) == 0 && stride % 2 == 0; };
+    TI_REQUIRE(ok4(q, q_stride) && ok4(k, k_stride) && ok4(v, v_stride) && ok4(q_w, 0) && ok4(k_w, 0),
+               "attention_decode (fused): projections and norm weights must be 4-byte aligned with even strides");
+    TI_REQUIRE((reinterpret_cast<uintptr_t>(cos_t) & 7) == 0 && (reinterpret_cast<uintptr_t>(sin_t) & 7) == 0,
+               "attention_decode (fused): rotary tables must be 8-byte aligned");
+    TI_REQUIRE((reinterpret_cast<uintptr_t>(k_pages) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_pages) & 15) == 0,
+               "attention_decode (fused): cache pages must be 16-byte aligned");
+    tiattn::DecodeArgs a;
+    a.q = q; a.q_stride = q_stride; a.k_pages = k_pages; a.v_pages = v_pages; a.page_table = page_table;
+    a.table_width = table_width; a.page_size = page_size; a.ring_rows = ring_rows; a.n_pages = n_pages;
+    a.seq_slot = seq_slot; a.seq_len = seq_len; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.hd = head_dim;
+    a.window = window; a.n_splits = n_splits; a.scale = scale; a.out = out; a.o_stride = o_stride;
+    a.part_o = part_o; a.part_ml = part_ml;
+    FuseArgs f;
+    f.q = (const bf16*)q; f.k = (const bf16*)k; f.v = (const bf16*)v;
+    f.q_stride = q_stride; f.k_stride = k_stride; f.v_stride = v_stride;
+    f.q_w = q_w; f.k_w = k_w; f.w_is_f32 = w_is_f32; f.eps = eps;
+    f.cos_t = cos_t; f.sin_t = sin_t; f.max_pos = max_pos > 0 ? max_pos : 1;
+    f.k_pages = (bf16*)k_pages; f.v_pages = (bf16*)v_pages;
+    return head_dim == 64 ? launch<64, true>(a, f, n_seq, stream) : launch<128, true>(a, f, n_seq, stream);
 }

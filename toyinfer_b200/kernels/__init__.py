@@ -254,6 +254,26 @@ def attention_decode(q, mem, scale: float, window: int, batch) -> torch.Tensor:
     return out
 
 
+def attention_decode_step(q, k, v, q_w, k_w, eps, tables, mem, scale: float, window: int, batch) -> torch.Tensor:
+    """The attention of a step in which every sequence goes on by one token, from the projection's
+    output: q[B, heads, d], k and v[B, kv_heads, d] (None for a layer that reads another's memory)
+    get their per-head norm (weights q_w, k_w or None) and rotation (``tables`` or None), k and v
+    go to the cache, and q attends over it.  One kernel where the decode kernel can do all of it
+    (see attention.decode_fused_eligible), else the rotate-and-store kernel and then the attention.
+    q, k and v may be changed in place."""
+    _need_cuda(q, k, v, q_w, k_w, what="attention_decode_step")
+    from . import attention
+    if attention.decode_fused_eligible(q, k, v, q_w, k_w, tables, mem):
+        B, nh, hd = q.shape
+        if k is not None and (k.shape != v.shape or k.shape[0] != B or k.shape[2] != hd or k.shape[1] != mem.n_kv_heads):
+            raise KernelError("attention_decode_step: k and v do not fit the queries or the cache")
+        out = torch.empty((B, nh, hd), dtype=q.dtype, device=q.device)
+        attention.decode_fused(q, k, v, q_w, k_w, float(eps), tables, mem, out, float(scale), int(window), batch)
+        return out
+    qk_norm_rope_store(q, k, v, q_w, k_w, eps, tables, batch, mem if k is not None else None)
+    return attention_decode(q, mem, scale, window, batch)
+
+
 _argmax_scratch = {}
 
 

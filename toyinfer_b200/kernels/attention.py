@@ -50,3 +50,48 @@ def decode(q, mem, out, scale, window, batch) -> None:
           _ptr(batch.seq_slot), _ptr(batch.seq_len), B, nh, nkv, hd, scale, window, splits,
           _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _code(q, "attention_decode"), _stream(),
           launches=2 if splits > 1 else 1)
+
+
+def decode_fused_eligible(q, k, v, q_w, k_w, tables, mem) -> bool:
+    """Whether the decode kernel can take the projection's output as it is (norm, rotation and
+    cache store folded in): bfloat16, heads of 64 or 128, a rotation over the whole head."""
+    hd = q.shape[2]
+    if q.dtype != torch.bfloat16 or hd not in (64, 128) or mem.page_size != 64:
+        return False
+    if tables is not None and (tables[2] != hd or tables[0].dtype != torch.float32):
+        return False
+    for t in (q, k, v):
+        if t is not None and (t.stride(2) != 1 or t.stride(1) != hd or t.stride(0) % 2 or t.data_ptr() % 4):
+            return False
+    for w in (q_w, k_w):
+        if w is not None and (w.dtype not in (torch.bfloat16, torch.float32) or not w.is_contiguous() or w.data_ptr() % 4):
+            return False
+    if q_w is not None and k_w is not None and q_w.dtype != k_w.dtype:
+        return False
+    return mem.k_pages.dtype == torch.bfloat16 and mem.k_pages.is_contiguous()
+
+
+def decode_fused(q, k, v, q_w, k_w, eps, tables, mem, out, scale, window, batch) -> None:
+    B, nh, hd = q.shape
+    nkv = mem.n_kv_heads
+    span = batch.plan_len if window <= 0 else min(batch.plan_len, window + mem.page_size)
+    splits = decode_splits(B, nkv, span, mem.page_size, sm_count(q.device))
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((B, nh, splits, 2), dtype=torch.float32, device=q.device)
+    cos = sin = None
+    max_pos = 0
+    if tables is not None:
+        cos, sin, _ = tables
+        max_pos = cos.shape[0]
+        if batch.max_pos_after > max_pos:
+            raise KernelError(f"attention_decode: position {batch.max_pos_after - 1} is beyond the rotary tables' {max_pos}")
+    w = q_w if q_w is not None else k_w
+    pt = mem.page_table
+    _call(library().ti_attn_decode_fused, _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0) if k is not None else 0,
+          v.stride(0) if v is not None else 0, _ptr(q_w), _ptr(k_w), 1 if (w is not None and w.dtype == torch.float32) else 0,
+          float(eps), _ptr(cos), _ptr(sin), max_pos, _ptr(mem.k_pages), _ptr(mem.v_pages), _ptr(pt), pt.shape[1],
+          mem.page_size, mem.ring_rows, mem.k_pages.shape[0], _ptr(batch.seq_slot), _ptr(batch.seq_len), B, nh, nkv, hd,
+          scale, window, splits, _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _code(q, "attention_decode"),
+          _stream(), launches=2 if splits > 1 else 1)

@@ -121,6 +121,11 @@ class GQAAttention(Mixer):
         else:
             k = v = None
         tables = self.pos.rotary_tables() if self.pos is not None else None
+        if batch.mode == "extend" and (self.pos is None or tables is not None):
+            # one token each: norm, rotation, cache store and attention from the projection's output
+            a = K.attention_decode_step(q, k, v, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0, tables, mem,
+                                        self.scale, self.window, batch)
+            return K.linear(a.view(M, self.q_dim), self.w_o)
         if self.pos is not None and tables is None:
             # a position encoding without rotary tables works on q and k itself
             # norms, then the part's own encoding, then the store
