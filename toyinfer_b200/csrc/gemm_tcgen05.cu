@@ -563,7 +563,18 @@ extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* b
     const bool sw = M <= 64;
     const int rows_a = sw ? N : M, rows_b = sw ? M : N;
     int b;
-    if (sw) b = rows_b <= 16 ? 16 : rows_b <= 32 ? 32 : 64;
+    if (sw) {
+        b = rows_b <= 16 ? 16 : rows_b <= 32 ? 32 : 64;
+        // A matrix with few row tiles is split along the contraction, and the block that adds a
+        // tile's partial sums does so in rounds whose number grows with the tile's width.  While
+        // the blocks still fit the SMs once, such a product takes its tokens in two tiles of half
+        // the width (measured at 64 tokens: 2560 x 4096 16.5 -> 12.1 us, 6144 x 2560 14.9 -> 13.0,
+        // 2560 x 9728 21.2 -> 18.5; at 32 tokens 2560 x 4096 11.7 -> 9.9); the weights' second
+        // reader finds them in L2.
+        const int row_tiles = (rows_a + BM - 1) / BM;
+        if (b == 64 && row_tiles * 2 <= sms) b = 32;
+        else if (b == 32 && rows_b > 16 && row_tiles * 4 <= sms) b = 16;
+    }
     else b = rows_b >= 256 ? wide_tile(rows_a, rows_b, sms) : rows_b > 64 ? 128 : rows_b > 32 ? 64 : rows_b > 16 ? 32 : 16;
     const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + b - 1) / b);
     const int nkb = (K + BK - 1) / BK;
