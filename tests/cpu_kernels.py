@@ -37,7 +37,7 @@ def gather_add(h, delta, rows):
     return out.to(h.dtype)
 
 
-def linear(x, w, out_dtype=None):
+def linear(x, w, out_dtype=None, after_attention=False):
     return (x.float() @ w.float().T).to(out_dtype or x.dtype)
 
 

@@ -20,17 +20,15 @@
 //     added in slice order.
 // x is read from L1/L2 by every warp (at most 16 tokens: it stays resident).
 //
-// Launch: the kernel signals at its start that its successor may be scheduled, like every
-// kernel here, but is itself launched without the programmatic attribute, so it starts when its
-// predecessor has finished.  The reason is L1: every block reads all of x, and that is cheap
-// only while x sits in L1.  Blocks that start early land on SMs still configured for their
-// neighbours' large shared memory (attention, the tcgen05 product), with next to no L1 left.
-// Measured in a 36-layer decode step at 8 sequences: started early 4.4-4.9 ms; started after
-// the predecessor 2.8-2.9 ms; the same with the shared-memory carve-out forced to its maximum
-// 4.9 ms; the tcgen05 kernel in its place 3.0 ms.
-//
-// The reference has no counterpart: it decodes one sequence with one block per output row
-// (src/decode.cu:201-298) and has no batch dimension; this is that product for a small batch.
+// Launch: every block reads all of x, and that is cheap only while x sits in L1.  Blocks that
+// start while a kernel with large shared memory is still on the SMs (decode attention: 100 KB
+// per block) find the SMs configured with next to no L1, and the configuration stays while
+// kernels keep overlapping.  So the product that follows such a kernel is launched `late_start`:
+// without the programmatic attribute, when its predecessor has finished and the SMs have
+// drained; the other products of a layer start early like every kernel here.  Measured in a
+// 36-layer decode step at 8 sequences of 8,192: all late 3.78 ms, all early 5.40, early except
+// after the attention 3.69; late with the shared-memory carve-out forced to its maximum 4.9 at
+// 2,048 positions against 2.8; the tcgen05 kernel in this one's place 3.0 against 2.8.
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -159,31 +157,34 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel
 }
 
 template <int NT, int WARPS, int WPR, bool GATED, typename OutT>
-int launch(const Args& a, cudaStream_t stream) {
+int launch(const Args& a, bool late_start, cudaStream_t stream) {
     const long long groups = ((long long)a.N + 15) / 16;
     const long long blocks = (groups + WARPS / WPR - 1) / (WARPS / WPR);
     TI_REQUIRE(blocks <= 0x7FFFFFFFll, "linear (small batch): %d rows of weights are too many", a.N);
-    TI_CUDA(ti_launch_after(skinny_kernel<NT, WARPS, WPR, GATED, OutT>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, a));
+    if (late_start)
+        TI_CUDA(ti_launch_after(skinny_kernel<NT, WARPS, WPR, GATED, OutT>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, a));
+    else
+        TI_CUDA(ti_launch(skinny_kernel<NT, WARPS, WPR, GATED, OutT>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, a));
     TI_CHECK_LAUNCH("linear (small batch)");
     return 0;
 }
 
 template <int NT, bool GATED, typename OutT>
-int launch_wpr(const Args& a, int wpr, cudaStream_t stream) {
+int launch_wpr(const Args& a, int wpr, bool late_start, cudaStream_t stream) {
     switch (wpr) {
-        case 1: return launch<NT, 8, 1, GATED, OutT>(a, stream);
-        case 2: return launch<NT, 8, 2, GATED, OutT>(a, stream);
-        case 4: return launch<NT, 8, 4, GATED, OutT>(a, stream);
-        case 8: return launch<NT, 8, 8, GATED, OutT>(a, stream);
-        default: return launch<NT, 16, 16, GATED, OutT>(a, stream);
+        case 1: return launch<NT, 8, 1, GATED, OutT>(a, late_start, stream);
+        case 2: return launch<NT, 8, 2, GATED, OutT>(a, late_start, stream);
+        case 4: return launch<NT, 8, 4, GATED, OutT>(a, late_start, stream);
+        case 8: return launch<NT, 8, 8, GATED, OutT>(a, late_start, stream);
+        default: return launch<NT, 16, 16, GATED, OutT>(a, late_start, stream);
     }
 }
 
 template <int NT>
-int launch_nt(const Args& a, int out_f32, int gated, int wpr, cudaStream_t stream) {
-    if (gated) return launch_wpr<NT, true, bf16>(a, wpr, stream);
-    if (out_f32) return launch_wpr<NT, false, float>(a, wpr, stream);
-    return launch_wpr<NT, false, bf16>(a, wpr, stream);
+int launch_nt(const Args& a, int out_f32, int gated, int wpr, bool late_start, cudaStream_t stream) {
+    if (gated) return launch_wpr<NT, true, bf16>(a, wpr, late_start, stream);
+    if (out_f32) return launch_wpr<NT, false, float>(a, wpr, late_start, stream);
+    return launch_wpr<NT, false, bf16>(a, wpr, late_start, stream);
 }
 
 }  // namespace
@@ -191,9 +192,11 @@ int launch_nt(const Args& a, int out_f32, int gated, int wpr, cudaStream_t strea
 // x[M, K] (row stride ldx), w[N, K] (row stride ldw), both bfloat16, M from 1 to 16; out[M, N]
 // bfloat16 or float32.  With `gated`, w's rows are (gate_0, up_0, gate_1, up_1, ...) and out is
 // [M, N / 2] = up * gate / (1 + exp(-gate)) in bfloat16.  K and the strides are multiples of 8
-// elements and the operands 16-byte aligned.  `sms`: the device's multiprocessors.
+// elements and the operands 16-byte aligned.  `sms`: the device's multiprocessors.  `late_start`:
+// see the note on launching at the top of this file.
 extern "C" int ti_linear_skinny(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
-                                long long ldw, long long ldo, int out_f32, int gated, int sms, cudaStream_t stream) {
+                                long long ldw, long long ldo, int out_f32, int gated, int sms, int late_start,
+                                cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     TI_REQUIRE(M >= 1 && M <= 16 && N > 0 && K > 0, "linear (small batch): bad sizes M=%d N=%d K=%d", M, N, K);
     TI_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "linear (small batch): K and the row strides must be multiples of 8 elements");
@@ -211,5 +214,5 @@ extern "C" int ti_linear_skinny(const void* x, const void* w, void* out, int M, 
     while (wpr < 8 && steps >= (wpr * 2) * UNROLL) wpr *= 2;
     if (wpr == 8 && groups * 8 < target && steps >= 16 * UNROLL) wpr = 16;
     Args a{(const bf16*)x, (const bf16*)w, out, M, N, K, ldx, ldw, ldo};
-    return M <= 8 ? launch_nt<1>(a, out_f32, gated, wpr, stream) : launch_nt<2>(a, out_f32, gated, wpr, stream);
+    return M <= 8 ? launch_nt<1>(a, out_f32, gated, wpr, late_start != 0, stream) : launch_nt<2>(a, out_f32, gated, wpr, late_start != 0, stream);
 }

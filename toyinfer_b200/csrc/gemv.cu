@@ -10,9 +10,8 @@
 // pieces of x are the same for every warp and come from L1.  The first weights are requested
 // before the wait for the kernel before this one, which produces x.
 //
-// Launched without the programmatic attribute (it starts when its predecessor has finished;
-// measured faster in a whole decode step: 2.26 against 2.48 ms), while its own successor may
-// still be scheduled early.
+// Launched early like every kernel here, except `late_start` (without the programmatic
+// attribute) where it follows a kernel with large shared memory: see gemm_skinny.cu.
 //
 // The reference decodes one token through products of this kind, one block per output row
 // and two elements per load (src/decode.cu:201-298: gemv_bf16_kernel and its float-output
@@ -135,37 +134,41 @@ struct Args {
 };
 
 template <int M, int R, int WPR, bool GATED, typename OutT>
-int launch(const Args& a) {
+int launch(const Args& a, bool late_start) {
     constexpr int U = R == 2 ? 4 : 2;          // 128 bytes of weights in flight per lane either way
     const long long groups = ((long long)a.N + R - 1) / R;
     const long long blocks = (groups + WARPS / WPR - 1) / (WARPS / WPR);
     TI_REQUIRE(blocks <= 0x7FFFFFFFll, "linear (few tokens): %d rows of weights are too many", a.N);
-    TI_CUDA(ti_launch_after(gemv_kernel<M, R, U, WPR, GATED, OutT>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, a.stream, a.x, a.w,
-                      (OutT*)a.out, a.N, a.K, a.ldx, a.ldw, a.ldo));
+    if (late_start)
+        TI_CUDA(ti_launch_after(gemv_kernel<M, R, U, WPR, GATED, OutT>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, a.stream, a.x, a.w,
+                                (OutT*)a.out, a.N, a.K, a.ldx, a.ldw, a.ldo));
+    else
+        TI_CUDA(ti_launch(gemv_kernel<M, R, U, WPR, GATED, OutT>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, a.stream, a.x, a.w,
+                          (OutT*)a.out, a.N, a.K, a.ldx, a.ldw, a.ldo));
     TI_CHECK_LAUNCH("linear (few tokens)");
     return 0;
 }
 
 template <int M, int R, bool GATED, typename OutT>
-int launch_wpr(const Args& a, int wpr) {
+int launch_wpr(const Args& a, int wpr, bool late_start) {
     switch (wpr) {
-        case 1: return launch<M, R, 1, GATED, OutT>(a);
-        case 2: return launch<M, R, 2, GATED, OutT>(a);
-        case 4: return launch<M, R, 4, GATED, OutT>(a);
-        default: return launch<M, R, 8, GATED, OutT>(a);
+        case 1: return launch<M, R, 1, GATED, OutT>(a, late_start);
+        case 2: return launch<M, R, 2, GATED, OutT>(a, late_start);
+        case 4: return launch<M, R, 4, GATED, OutT>(a, late_start);
+        default: return launch<M, R, 8, GATED, OutT>(a, late_start);
     }
 }
 
 template <int M, bool GATED, typename OutT>
-int launch_r(const Args& a, int rows, int wpr) {
-    return rows == 4 ? launch_wpr<M, 4, GATED, OutT>(a, wpr) : launch_wpr<M, 2, GATED, OutT>(a, wpr);
+int launch_r(const Args& a, int rows, int wpr, bool late_start) {
+    return rows == 4 ? launch_wpr<M, 4, GATED, OutT>(a, wpr, late_start) : launch_wpr<M, 2, GATED, OutT>(a, wpr, late_start);
 }
 
 template <int M>
-int launch_m(const Args& a, int out_f32, int gated, int rows, int wpr) {
-    if (gated) return launch_r<M, true, bf16>(a, rows, wpr);
-    if (out_f32) return launch_r<M, false, float>(a, rows, wpr);
-    return launch_r<M, false, bf16>(a, rows, wpr);
+int launch_m(const Args& a, int out_f32, int gated, int rows, int wpr, bool late_start) {
+    if (gated) return launch_r<M, true, bf16>(a, rows, wpr, late_start);
+    if (out_f32) return launch_r<M, false, float>(a, rows, wpr, late_start);
+    return launch_r<M, false, bf16>(a, rows, wpr, late_start);
 }
 }  // namespace
 
@@ -175,7 +178,8 @@ int launch_m(const Args& a, int out_f32, int gated, int rows, int wpr) {
 // elements and the operands 16-byte aligned.  `sms`: the device's multiprocessors; the rows
 // per warp and the warps per row are chosen so that about 32 warps per SM have work.
 extern "C" int ti_linear_gemv(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
-                              long long ldw, long long ldo, int out_f32, int gated, int sms, cudaStream_t stream) {
+                              long long ldw, long long ldo, int out_f32, int gated, int sms, int late_start,
+                              cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     TI_REQUIRE(M >= 1 && M <= 2 && N > 0 && K > 0, "linear (few tokens): bad sizes M=%d N=%d K=%d", M, N, K);
     TI_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "linear (few tokens): K and the row strides must be multiples of 8 elements");
@@ -197,5 +201,5 @@ extern "C" int ti_linear_gemv(const void* x, const void* w, void* out, int M, in
         rows = 4;
     }
     Args a{(const bf16*)x, (const bf16*)w, out, N, K, ldx, ldw, ldo, stream};
-    return M == 1 ? launch_m<1>(a, out_f32, gated, rows, wpr) : launch_m<2>(a, out_f32, gated, rows, wpr);
+    return M == 1 ? launch_m<1>(a, out_f32, gated, rows, wpr, late_start != 0) : launch_m<2>(a, out_f32, gated, rows, wpr, late_start != 0);
 }

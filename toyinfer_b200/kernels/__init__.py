@@ -127,9 +127,13 @@ def gather_add(h: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tenso
     return out
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           after_attention: bool = False) -> torch.Tensor:
     """x[M, K] times w[N, K] transposed -> [M, N]; 32-bit accumulation.  ``out_dtype`` may
-    ask for float32 results from bfloat16 operands (the head)."""
+    ask for float32 results from bfloat16 operands (the head).  ``after_attention``: a hint
+    that x comes (through at most a tiny kernel) from an attention kernel with large shared
+    memory; the few-token kernels then start only when it has finished (a matter of speed, not
+    of results: csrc/gemm_skinny.cu)."""
     _need_cuda(x, w, what="linear")
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
         raise KernelError(f"linear: shapes {tuple(x.shape)} and {tuple(w.shape)} do not contract")
@@ -143,7 +147,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     ldx, ldw = _row_stride(x, "linear x"), _row_stride(w, "linear w")
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     from . import gemm
-    gemm.run(x, w, out, M, N, K, ldx, ldw)
+    gemm.run(x, w, out, M, N, K, ldx, ldw, late_start=after_attention)
     return out
 
 

@@ -43,17 +43,18 @@ def tc_eligible(x, w, K, ldx, ldw) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def run(x, w, out, M, N, K, ldx, ldw, gated: bool = False) -> None:
-    """``gated``: only for shapes the tensor-core kernel takes (see tc_eligible)."""
+def run(x, w, out, M, N, K, ldx, ldw, gated: bool = False, late_start: bool = False) -> None:
+    """``gated``: only for shapes the tensor-core kernel takes (see tc_eligible).  ``late_start``: the
+    few-token kernels start only when the kernel before them has finished (csrc/gemm_skinny.cu)."""
     lib = library()
     out_f32 = 1 if (out.dtype == torch.float32 and x.dtype != torch.float32) else 0
     if tc_eligible(x, w, K, ldx, ldw) and M <= GEMV_MAX_TOKENS:
         _call(lib.ti_linear_gemv, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, 1 if gated else 0,
-              sm_count(x.device), _stream())
+              sm_count(x.device), 1 if late_start else 0, _stream())
         return
     if tc_eligible(x, w, K, ldx, ldw) and M <= SKINNY_MAX_TOKENS:
         _call(lib.ti_linear_skinny, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, 1 if gated else 0,
-              sm_count(x.device), _stream())
+              sm_count(x.device), 1 if late_start else 0, _stream())
         return
     if tc_eligible(x, w, K, ldx, ldw):
         swap, bn, splits, n_tiles = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()

@@ -125,7 +125,7 @@ class GQAAttention(Mixer):
             # one token each: norm, rotation, cache store and attention from the projection's output
             a = K.attention_decode_step(q, k, v, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0, tables, mem,
                                         self.scale, self.window, batch)
-            return K.linear(a.view(M, self.q_dim), self.w_o)
+            return K.linear(a.view(M, self.q_dim), self.w_o, after_attention=True)
         if self.pos is not None and tables is None:
             # a position encoding without rotary tables works on q and k itself
             # norms, then the part's own encoding, then the store
@@ -145,7 +145,7 @@ class GQAAttention(Mixer):
             a = K.attention_prefill(q, k, v, self.scale, self.window, batch)
         else:
             a = K.attention_decode(q, mem, self.scale, self.window, batch)
-        return K.linear(a.view(M, self.q_dim), self.w_o)
+        return K.linear(a.view(M, self.q_dim), self.w_o, after_attention=True)
 
 
 register_part("mixer", "gqa_attention", GQAAttention)
