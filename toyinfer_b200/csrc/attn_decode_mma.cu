@@ -445,7 +445,9 @@ int launch(const tiattn::DecodeArgs& a, const FuseArgs& f, int n_seq, cudaStream
     TI_CHECK_LAUNCH("attention_decode (tensor cores)");
     if (a.n_splits > 1) {
         dim3 cgrid(n_seq, a.n_heads);
-        TI_CUDA(ti_launch_class<4>(tiattn::attn_decode_combine_kernel<bf16>, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits));
+        // started late: when it runs the attention blocks with their large shared memory are gone and the
+        // SMs have drained, so the products after it find an L1 (see gemm_skinny.cu) and may start early
+        TI_CUDA(ti_launch_after(tiattn::attn_decode_combine_kernel<bf16>, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits));
         TI_CHECK_LAUNCH("attention_decode (combine)");
     }
     return 0;

@@ -147,7 +147,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     ldx, ldw = _row_stride(x, "linear x"), _row_stride(w, "linear w")
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     from . import gemm
-    gemm.run(x, w, out, M, N, K, ldx, ldw, late_start=after_attention)
+    late = False
+    if after_attention:
+        from . import attention
+        late = not attention.last_decode_had_combine      # the combine kernel has already let the SMs drain
+    gemm.run(x, w, out, M, N, K, ldx, ldw, late_start=late)
     return out
 
 

@@ -33,7 +33,14 @@ def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int
     return max(1, min(want, (tiles + 1) // 2, 64))
 
 
+# Whether the last decode attention ended with its combine kernel (several splits).  That kernel
+# starts only when the attention blocks have left the SMs; without it, the product that follows
+# has to start late itself (kernels.linear(after_attention=True) asks here).
+last_decode_had_combine = False
+
+
 def decode(q, mem, out, scale, window, batch) -> None:
+    global last_decode_had_combine
     B, nh, hd = q.shape
     nkv = mem.n_kv_heads
     span = batch.plan_len if window <= 0 else min(batch.plan_len, window + mem.page_size)
@@ -44,7 +51,9 @@ def decode(q, mem, out, scale, window, batch) -> None:
         part_ml = torch.empty((B, nh, splits, 2), dtype=torch.float32, device=q.device)
     pt = mem.page_table
     lib = library()
-    fn = lib.ti_attn_decode_mma if (q.dtype == torch.bfloat16 and hd in (64, 128)) else lib.ti_attn_decode_simt
+    tensor_cores = q.dtype == torch.bfloat16 and hd in (64, 128)
+    last_decode_had_combine = tensor_cores and splits > 1
+    fn = lib.ti_attn_decode_mma if tensor_cores else lib.ti_attn_decode_simt
     _call(fn, _ptr(q), _row_stride(q, "q"), _ptr(mem.k_pages), _ptr(mem.v_pages),
           _ptr(pt), pt.shape[1], mem.page_size, mem.ring_rows, mem.k_pages.shape[0],
           _ptr(batch.seq_slot), _ptr(batch.seq_len), B, nh, nkv, hd, scale, window, splits,
@@ -72,6 +81,7 @@ def decode_fused_eligible(q, k, v, q_w, k_w, tables, mem) -> bool:
 
 
 def decode_fused(q, k, v, q_w, k_w, eps, tables, mem, out, scale, window, batch) -> None:
+    global last_decode_had_combine
     B, nh, hd = q.shape
     nkv = mem.n_kv_heads
     span = batch.plan_len if window <= 0 else min(batch.plan_len, window + mem.page_size)
@@ -80,6 +90,7 @@ def decode_fused(q, k, v, q_w, k_w, eps, tables, mem, out, scale, window, batch)
     if splits > 1:
         part_o = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((B, nh, splits, 2), dtype=torch.float32, device=q.device)
+    last_decode_had_combine = splits > 1
     cos = sin = None
     max_pos = 0
     if tables is not None:
