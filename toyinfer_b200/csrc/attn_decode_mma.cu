@@ -17,6 +17,7 @@
 // then written as this split's partial result (or the final one when there is one split).
 #include "attn_decode.cuh"
 #include "mma_utils.cuh"
+#include "rope_math.cuh"
 #include "tma.cuh"
 
 #include <map>
@@ -47,48 +48,6 @@ struct FuseArgs {
     const float* cos_t; const float* sin_t; int max_pos;         // rotary tables [max_pos, hd/2] or null
     bf16* k_pages; bf16* v_pages;                       // the cache, writable
 };
-
-// One warp: norm (when w is given) and rotation (when cs is given) of one head; bfloat16 result to dst.
-template <int HD>
-__device__ __forceinline__ void norm_rotate_head(const bf16* x, const void* w, int w_is_f32, float eps,
-                                                 const float* cs, const float* sn, bf16* dst, int lane) {
-    constexpr int half = HD / 2;
-    float r = 1.f;
-    if (w) {
-        float ss = 0.f;
-        for (int i = lane * 2; i < HD; i += 64) {
-            const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + i));
-            ss = fmaf(t.x, t.x, ss);
-            ss = fmaf(t.y, t.y, ss);
-        }
-        ss = warp_sum(ss);
-        r = rsqrtf(fmaf(ss, 1.0f / (float)HD, eps));
-    }
-    for (int i = lane * 2; i < half; i += 64) {
-        float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + i));
-        float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + i + half));
-        if (w) {
-            float2 wl, wh;
-            if (w_is_f32) {
-                wl = *reinterpret_cast<const float2*>((const float*)w + i);
-                wh = *reinterpret_cast<const float2*>((const float*)w + i + half);
-            } else {
-                wl = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>((const bf16*)w + i));
-                wh = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>((const bf16*)w + i + half));
-            }
-            lo.x = __bfloat162float(__float2bfloat16_rn(lo.x * r * wl.x)); lo.y = __bfloat162float(__float2bfloat16_rn(lo.y * r * wl.y));
-            hi.x = __bfloat162float(__float2bfloat16_rn(hi.x * r * wh.x)); hi.y = __bfloat162float(__float2bfloat16_rn(hi.y * r * wh.y));
-        }
-        if (cs) {
-            const float2 c = *reinterpret_cast<const float2*>(cs + i), sv = *reinterpret_cast<const float2*>(sn + i);
-            const float2 nlo = make_float2(lo.x * c.x - hi.x * sv.x, lo.y * c.y - hi.y * sv.y);
-            const float2 nhi = make_float2(hi.x * c.x + lo.x * sv.x, hi.y * c.y + lo.y * sv.y);
-            lo = nlo; hi = nhi;
-        }
-        *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(lo.x, lo.y);
-        *reinterpret_cast<__nv_bfloat162*>(dst + i + half) = __floats2bfloat162_rn(hi.x, hi.y);
-    }
-}
 
 template <int HD, bool FUSED>
 __global__ void __launch_bounds__(THREADS, 2)
@@ -169,18 +128,30 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
         const bf16* fv = ti_dependent(f.v);
         int pos = max(L - 1, 0);
         if (pos >= f.max_pos) pos = f.max_pos - 1;
-        const float* cs = f.cos_t ? f.cos_t + (size_t)pos * (HD / 2) : nullptr;
-        const float* sn = f.sin_t ? f.sin_t + (size_t)pos * (HD / 2) : nullptr;
-        for (int item = warp; item < rows + 2; item += THREADS / 32) {
-            if (item < rows)
-                norm_rotate_head<HD>(fq + (size_t)b * f.q_stride + (size_t)(h0 + item) * HD, f.q_w, f.w_is_f32, f.eps, cs, sn,
-                                     q_s + item * HD, lane);
-            else if (item == rows && store_new)
-                norm_rotate_head<HD>(fk + (size_t)b * f.k_stride + (size_t)kvh * HD, f.k_w, f.w_is_f32, f.eps, cs, sn, kv_new, lane);
-            else if (item == rows + 1 && store_new)
-                for (int i = lane * 2; i < HD; i += 64)
-                    *reinterpret_cast<__nv_bfloat162*>(kv_new + HD + i) =
-                        *reinterpret_cast<const __nv_bfloat162*>(fv + (size_t)b * f.v_stride + (size_t)kvh * HD + i);
+        // heads of this block's queries, then the kv head's key and value: hd / 16 lanes a head
+        constexpr int LPH = HD / 16, HPW = 32 / LPH;
+        const int sub = lane % LPH, ei = sub * 8;
+        float c[8] = {}, sn[8] = {};
+        if (f.cos_t) tirope::load_angles(f.cos_t + (size_t)pos * (HD / 2), f.sin_t + (size_t)pos * (HD / 2), ei, c, sn);
+        const int n_items = rows + (store_new ? 2 : 0);
+        for (int item0 = warp * HPW; item0 < n_items; item0 += (THREADS / 32) * HPW) {
+            const int item = item0 + lane / LPH;
+            const bool active = item < n_items;
+            const bool is_q = item < rows, is_v = item == rows + 1;
+            const bf16* src = is_q ? fq + (size_t)b * f.q_stride + (size_t)(h0 + item) * HD
+                            : !is_v ? fk + (size_t)b * f.k_stride + (size_t)kvh * HD
+                                    : fv + (size_t)b * f.v_stride + (size_t)kvh * HD;
+            bf16* dst = is_q ? q_s + item * HD : kv_new + (is_v ? HD : 0);
+            uint4 vlo = make_uint4(0, 0, 0, 0), vhi = vlo;
+            if (active) {
+                vlo = *reinterpret_cast<const uint4*>(src + ei);
+                vhi = *reinterpret_cast<const uint4*>(src + ei + HD / 2);
+            }
+            tirope::norm_rotate<HD>(vlo, vhi, active && !is_v, is_q ? f.q_w : f.k_w, f.w_is_f32, f.eps, f.cos_t != nullptr, c, sn, ei);
+            if (active) {
+                *reinterpret_cast<uint4*>(dst + ei) = vlo;
+                *reinterpret_cast<uint4*>(dst + ei + HD / 2) = vhi;
+            }
         }
         __syncthreads();
         // the new key and value go to their line of the cache, for the steps to come: one block per
@@ -506,11 +477,9 @@ extern "C" int ti_attn_decode_fused(const void* q, const void* k, const void* v,
     TI_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_decode: split results need scratch memory");
     TI_REQUIRE(q != nullptr && (k == nullptr) == (v == nullptr), "attention_decode (fused): queries are needed; keys and values go together");
     TI_REQUIRE((cos_t == nullptr) == (sin_t == nullptr) && (!cos_t || max_pos > 0), "attention_decode (fused): cos and sin tables go together");
-    auto ok4 = [](const void* p, long long stride) { return (reinterpret_cast<uintptr_t>(p) & 3) == 0 && stride % 2 == 0; };
-    TI_REQUIRE(ok4(q, q_stride) && ok4(k, k_stride) && ok4(v, v_stride) && ok4(q_w, 0) && ok4(k_w, 0),
-               "attention_decode (fused): projections and norm weights must be 4-byte aligned with even strides");
-    TI_REQUIRE((reinterpret_cast<uintptr_t>(cos_t) & 7) == 0 && (reinterpret_cast<uintptr_t>(sin_t) & 7) == 0,
-               "attention_decode (fused): rotary tables must be 8-byte aligned");
+    auto ok16 = [](const void* p, long long stride) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && stride % 8 == 0; };
+    TI_REQUIRE(ok16(q, q_stride) && ok16(k, k_stride) && ok16(v, v_stride) && ok16(q_w, 0) && ok16(k_w, 0) && ok16(cos_t, 0) && ok16(sin_t, 0),
+               "attention_decode (fused): projections, norm weights and rotary tables must be 16-byte aligned, strides multiples of 8");
     TI_REQUIRE((reinterpret_cast<uintptr_t>(k_pages) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_pages) & 15) == 0,
                "attention_decode (fused): cache pages must be 16-byte aligned");
     tiattn::DecodeArgs a;

@@ -13,7 +13,9 @@
 //   row  = pos                    (ring_rows == 0)
 //   row  = pos mod ring_rows      (windowed group; tokens older than the ring are not stored)
 //   page = page_table[slot][row / page_size], line row % page_size
-#include "common.cuh"
+#include "rope_math.cuh"
+
+#include <type_traits>
 
 struct RopeStoreArgs {
     void* q; void* k; void* v;
@@ -222,6 +224,76 @@ __global__ void rope_store_pairs_kernel(RopeStoreArgs a) {
     }
 }
 
+// bfloat16 heads of 64 or 128 elements with 16-byte aligned rows: a head is shared by hd / 16
+// lanes, each with 8 consecutive elements of the lower half and the 8 that pair with them in the
+// upper half (two 16-byte loads), so a warp works on four (or eight) heads at once and every
+// access is a full 16 bytes.  Same formulas and roundings as the kernels above; this is the form
+// that many-token steps run (2,048 tokens of a 4B-shaped layer: 38 us with two-element lanes).
+template <int HD>
+__global__ void rope_store_vec_kernel(RopeStoreArgs a) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    constexpr int LPH = HD / 16, HPW = 32 / LPH, half = HD / 2;
+    const int n_warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_q = a.q ? a.n_heads : 0;
+    const int heads_k = a.k ? a.n_kv_heads : 0;
+    const int heads_v = a.v ? a.n_kv_heads : 0;
+    const int per_tok = heads_q + heads_k + heads_v;
+    const int m = blockIdx.x;
+    int pos = a.tok_pos[m];
+    long long dst_off = -1;
+    if (a.k_pages) {
+        const int seq = a.tok_seq[m];
+        const int slot = a.seq_slot[seq];
+        int row = pos;
+        bool keep = pos >= 0;
+        if (a.ring_rows > 0) {
+            keep = keep && pos >= a.seq_len[seq] - a.ring_rows;
+            row = pos % a.ring_rows;
+        }
+        const int pidx = row / a.page_size;
+        if (keep && pidx < a.table_width) {
+            const int page = a.page_table[(size_t)slot * a.table_width + pidx];
+            if (page >= 0 && page < a.n_pages)
+                dst_off = ((long long)page * a.n_kv_heads * a.page_size + (row % a.page_size)) * HD;
+        }
+    }
+    if (pos < 0) pos = 0;
+    if (pos >= a.max_pos) pos = a.max_pos - 1;
+    const int sub = lane % LPH, i = sub * 8;
+    float c[8] = {}, sn[8] = {};
+    if (a.cos_t) tirope::load_angles(a.cos_t + (size_t)pos * half, a.sin_t + (size_t)pos * half, i, c, sn);
+    for (int item0 = (blockIdx.y * n_warps + warp) * HPW; item0 < per_tok; item0 += n_warps * gridDim.y * HPW) {
+        const int item = item0 + lane / LPH;
+        const bool active = item < per_tok;
+        int h = active ? item : 0, kind;  // 0 q, 1 k, 2 v
+        if (h < heads_q) kind = 0;
+        else if (h < heads_q + heads_k) { kind = 1; h -= heads_q; }
+        else { kind = 2; h -= heads_q + heads_k; }
+        bf16* x = kind == 0 ? (bf16*)a.q + (size_t)m * a.q_stride + (size_t)h * HD
+                : kind == 1 ? (bf16*)a.k + (size_t)m * a.k_stride + (size_t)h * HD
+                            : (bf16*)a.v + (size_t)m * a.v_stride + (size_t)h * HD;
+        bf16* dst = nullptr;
+        if (kind != 0 && dst_off >= 0)
+            dst = (bf16*)(kind == 1 ? a.k_pages : a.v_pages) + dst_off + (size_t)h * a.page_size * HD;
+        uint4 vlo = make_uint4(0, 0, 0, 0), vhi = vlo;
+        if (active) {
+            vlo = *reinterpret_cast<const uint4*>(x + i);
+            vhi = *reinterpret_cast<const uint4*>(x + i + half);
+        }
+        const bool apply = active && kind != 2;
+        tirope::norm_rotate<HD>(vlo, vhi, apply, kind == 0 ? a.q_w : a.k_w, a.w_is_f32, a.eps, a.cos_t != nullptr, c, sn, i);
+        if (apply) {
+            *reinterpret_cast<uint4*>(x + i) = vlo;
+            *reinterpret_cast<uint4*>(x + i + half) = vhi;
+        }
+        if (active && dst) {
+            *reinterpret_cast<uint4*>(dst + i) = vlo;
+            *reinterpret_cast<uint4*>(dst + i + half) = vhi;
+        }
+    }
+}
+
 extern "C" int ti_qk_norm_rope_store(
     void* q, void* k, void* v, long long q_stride, long long k_stride, long long v_stride,
     int n_heads, int n_kv_heads, int head_dim,
@@ -264,7 +336,21 @@ extern "C" int ti_qk_norm_rope_store(
         const bool pairs = head_dim % 4 == 0 && even(q, q_stride) && even(k, k_stride) && even(v, v_stride) &&
                            even(q_w, 0) && even(k_w, 0) && even(k_pages, 0) && even(v_pages, 0) &&
                            (reinterpret_cast<uintptr_t>(cos_t) % 8 == 0) && (reinterpret_cast<uintptr_t>(sin_t) % 8 == 0);
-        if (pairs) {
+        auto al16 = [&](const void* p, long long stride) { return !p || ((reinterpret_cast<uintptr_t>(p) & 15) == 0 && stride % 8 == 0); };
+        const bool vec = std::is_same<T, bf16>::value && (head_dim == 64 || head_dim == 128) && al16(q, q_stride) &&
+                         al16(k, k_stride) && al16(v, v_stride) && al16(q_w, 0) && al16(k_w, 0) && al16(k_pages, 0) &&
+                         al16(v_pages, 0) && al16(cos_t, 0) && al16(sin_t, 0);
+        if (vec) {
+            const int w = 4;
+            const int hpw = 32 / (head_dim / 16);
+            const int need = (per_tok + hpw - 1) / hpw;                 // warp-rounds per token
+            const int groups = M >= 1024 ? 1 : (need + w - 1) / w;
+            if (head_dim == 128)
+                TI_CUDA(ti_launch_class<2>(rope_store_vec_kernel<128>, dim3((unsigned)M, (unsigned)groups), dim3(w * 32), 0, stream, a));
+            else
+                TI_CUDA(ti_launch_class<2>(rope_store_vec_kernel<64>, dim3((unsigned)M, (unsigned)groups), dim3(w * 32), 0, stream, a));
+        }
+        else if (pairs) {
             const int w = 4;
             const int groups = M >= 1024 ? 1 : (per_tok + w - 1) / w;
             TI_CUDA(ti_launch_class<2>(rope_store_pairs_kernel<T>, dim3((unsigned)M, (unsigned)groups), dim3(w * 32), 0, stream, a));

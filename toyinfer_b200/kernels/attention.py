@@ -67,13 +67,14 @@ def decode_fused_eligible(q, k, v, q_w, k_w, tables, mem) -> bool:
     hd = q.shape[2]
     if q.dtype != torch.bfloat16 or hd not in (64, 128) or mem.page_size != 64:
         return False
-    if tables is not None and (tables[2] != hd or tables[0].dtype != torch.float32):
+    if tables is not None and (tables[2] != hd or tables[0].dtype != torch.float32 or tables[0].data_ptr() % 16
+                               or tables[1].data_ptr() % 16 or not tables[0].is_contiguous() or not tables[1].is_contiguous()):
         return False
     for t in (q, k, v):
-        if t is not None and (t.stride(2) != 1 or t.stride(1) != hd or t.stride(0) % 2 or t.data_ptr() % 4):
+        if t is not None and (t.stride(2) != 1 or t.stride(1) != hd or t.stride(0) % 8 or t.data_ptr() % 16):
             return False
     for w in (q_w, k_w):
-        if w is not None and (w.dtype not in (torch.bfloat16, torch.float32) or not w.is_contiguous() or w.data_ptr() % 4):
+        if w is not None and (w.dtype not in (torch.bfloat16, torch.float32) or not w.is_contiguous() or w.data_ptr() % 16):
             return False
     if q_w is not None and k_w is not None and q_w.dtype != k_w.dtype:
         return False
