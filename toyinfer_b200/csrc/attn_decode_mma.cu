@@ -395,7 +395,7 @@ int page_map(const void* pages, long long rows, int hd, CUtensorMap* out) {
 }
 
 template <int HD, bool FUSED>
-int launch(const tiattn::DecodeArgs& a, const FuseArgs& f, int n_seq, cudaStream_t stream) {
+int launch(const tiattn::DecodeArgs& a, const FuseArgs& f, int n_seq, bool combine_late, cudaStream_t stream) {
     constexpr size_t stage_bytes = 2 * TILE * HD * 2;
     constexpr size_t merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * sizeof(float);
     constexpr size_t smem = (STAGES * stage_bytes > merge_bytes ? STAGES * stage_bytes : merge_bytes) + 1024;
@@ -416,9 +416,14 @@ int launch(const tiattn::DecodeArgs& a, const FuseArgs& f, int n_seq, cudaStream
     TI_CHECK_LAUNCH("attention_decode (tensor cores)");
     if (a.n_splits > 1) {
         dim3 cgrid(n_seq, a.n_heads);
-        // started late: when it runs the attention blocks with their large shared memory are gone and the
-        // SMs have drained, so the products after it find an L1 (see gemm_skinny.cu) and may start early
-        TI_CUDA(ti_launch_after(tiattn::attn_decode_combine_kernel<bf16>, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits));
+        // Started late when the caller says so: by then the attention blocks with their large shared
+        // memory are gone and the SMs have drained, so that few-token products after it find an L1
+        // (see gemm_skinny.cu) and may start early.  Before the tcgen05 product (more tokens), which
+        // does not care about L1 and gains from starting early, it starts early like everything else.
+        if (combine_late)
+            TI_CUDA(ti_launch_after(tiattn::attn_decode_combine_kernel<bf16>, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits));
+        else
+            TI_CUDA(ti_launch_class<4>(tiattn::attn_decode_combine_kernel<bf16>, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits));
         TI_CHECK_LAUNCH("attention_decode (combine)");
     }
     return 0;
@@ -432,7 +437,7 @@ extern "C" int ti_attn_decode_mma(const void* q, long long q_stride, const void*
                                   int n_pages, const int* seq_slot, const int* seq_len, int n_seq,
                                   int n_heads, int n_kv_heads, int head_dim, float scale, int window,
                                   int n_splits, void* out, long long o_stride, float* part_o,
-                                  float* part_ml, int dtype, cudaStream_t stream) {
+                                  float* part_ml, int dtype, int combine_late, cudaStream_t stream) {
     if (n_seq == 0) return 0;
     TI_REQUIRE(dtype == TI_BF16, "attention_decode (tensor cores): bfloat16 only");
     TI_REQUIRE(head_dim == 64 || head_dim == 128, "attention_decode (tensor cores): head size %d is not 64 or 128", head_dim);
@@ -450,7 +455,7 @@ extern "C" int ti_attn_decode_mma(const void* q, long long q_stride, const void*
     a.window = window; a.n_splits = n_splits; a.scale = scale; a.out = out; a.o_stride = o_stride;
     a.part_o = part_o; a.part_ml = part_ml;
     FuseArgs f = {};
-    return head_dim == 64 ? launch<64, false>(a, f, n_seq, stream) : launch<128, false>(a, f, n_seq, stream);
+    return head_dim == 64 ? launch<64, false>(a, f, n_seq, combine_late != 0, stream) : launch<128, false>(a, f, n_seq, combine_late != 0, stream);
 }
 
 // The same with the step before it folded in: q[B, heads, hd], k and v[B, kv_heads, hd] are the
@@ -465,7 +470,7 @@ extern "C" int ti_attn_decode_fused(const void* q, const void* k, const void* v,
                                     int ring_rows, int n_pages, const int* seq_slot, const int* seq_len, int n_seq,
                                     int n_heads, int n_kv_heads, int head_dim, float scale, int window, int n_splits,
                                     void* out, long long o_stride, float* part_o, float* part_ml, int dtype,
-                                    cudaStream_t stream) {
+                                    int combine_late, cudaStream_t stream) {
     if (n_seq == 0) return 0;
     TI_REQUIRE(dtype == TI_BF16, "attention_decode (fused): bfloat16 only");
     TI_REQUIRE(head_dim == 64 || head_dim == 128, "attention_decode (fused): head size %d is not 64 or 128", head_dim);
@@ -494,5 +499,5 @@ extern "C" int ti_attn_decode_fused(const void* q, const void* k, const void* v,
     f.q_w = q_w; f.k_w = k_w; f.w_is_f32 = w_is_f32; f.eps = eps;
     f.cos_t = cos_t; f.sin_t = sin_t; f.max_pos = max_pos > 0 ? max_pos : 1;
     f.k_pages = (bf16*)k_pages; f.v_pages = (bf16*)v_pages;
-    return head_dim == 64 ? launch<64, true>(a, f, n_seq, stream) : launch<128, true>(a, f, n_seq, stream);
+    return head_dim == 64 ? launch<64, true>(a, f, n_seq, combine_late != 0, stream) : launch<128, true>(a, f, n_seq, combine_late != 0, stream);
 }

@@ -33,10 +33,16 @@ def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int
     return max(1, min(want, (tiles + 1) // 2, 64))
 
 
-# Whether the last decode attention ended with its combine kernel (several splits).  That kernel
-# starts only when the attention blocks have left the SMs; without it, the product that follows
-# has to start late itself (kernels.linear(after_attention=True) asks here).
+# Whether the last decode attention ended with a combine kernel that was started late, i.e. only
+# when the attention blocks had left the SMs.  If not, a few-token product that follows has to
+# start late itself (kernels.linear(after_attention=True) asks here).  The combine kernel is
+# started late exactly when the step is small enough for the few-token products.
 last_decode_had_combine = False
+
+
+def _combine_late(n_seq: int) -> bool:
+    from . import gemm
+    return n_seq <= max(gemm.SKINNY_MAX_TOKENS, gemm.GEMV_MAX_TOKENS)
 
 
 def decode(q, mem, out, scale, window, batch) -> None:
@@ -52,12 +58,14 @@ def decode(q, mem, out, scale, window, batch) -> None:
     pt = mem.page_table
     lib = library()
     tensor_cores = q.dtype == torch.bfloat16 and hd in (64, 128)
-    last_decode_had_combine = tensor_cores and splits > 1
+    late = _combine_late(B)
+    last_decode_had_combine = tensor_cores and splits > 1 and late
     fn = lib.ti_attn_decode_mma if tensor_cores else lib.ti_attn_decode_simt
+    extra = (1 if late else 0,) if tensor_cores else ()
     _call(fn, _ptr(q), _row_stride(q, "q"), _ptr(mem.k_pages), _ptr(mem.v_pages),
           _ptr(pt), pt.shape[1], mem.page_size, mem.ring_rows, mem.k_pages.shape[0],
           _ptr(batch.seq_slot), _ptr(batch.seq_len), B, nh, nkv, hd, scale, window, splits,
-          _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _code(q, "attention_decode"), _stream(),
+          _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _code(q, "attention_decode"), *extra, _stream(),
           launches=2 if splits > 1 else 1)
 
 
@@ -91,7 +99,8 @@ def decode_fused(q, k, v, q_w, k_w, eps, tables, mem, out, scale, window, batch)
     if splits > 1:
         part_o = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((B, nh, splits, 2), dtype=torch.float32, device=q.device)
-    last_decode_had_combine = splits > 1
+    late = _combine_late(B)
+    last_decode_had_combine = splits > 1 and late
     cos = sin = None
     max_pos = 0
     if tables is not None:
@@ -106,4 +115,4 @@ def decode_fused(q, k, v, q_w, k_w, eps, tables, mem, out, scale, window, batch)
           float(eps), _ptr(cos), _ptr(sin), max_pos, _ptr(mem.k_pages), _ptr(mem.v_pages), _ptr(pt), pt.shape[1],
           mem.page_size, mem.ring_rows, mem.k_pages.shape[0], _ptr(batch.seq_slot), _ptr(batch.seq_len), B, nh, nkv, hd,
           scale, window, splits, _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _code(q, "attention_decode"),
-          _stream(), launches=2 if splits > 1 else 1)
+          1 if late else 0, _stream(), launches=2 if splits > 1 else 1)
