@@ -81,33 +81,30 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel
                 wh[u][h] = ok ? load_stream(w_hi + (size_t)(s + u) * 64 + 8 * h) : make_uint4(0, 0, 0, 0);
             }
         if (!waited) { ti_pdl_sync(); x = ti_dependent(x); waited = true; }      // x is the work of the kernel before this one
-        // every piece of x of these steps is asked for before the first MMA: whether it comes from
-        // L1 or (when a neighbour's shared memory leaves no L1) from L2, the warp waits once
-        uint4 xv[UNROLL][2][NT];
+        // every piece of x of these steps (for one tile of 8 tokens at a time) is asked for before
+        // the tile's first MMA: the warp waits for x once per tile, not once per piece
 #pragma unroll
-        for (int u = 0; u < UNROLL; u++)
+        for (int n = 0; n < NT; n++) {
+            const int tok = min(n * 8 + g, a.M - 1);        // tokens past the end repeat the last; never stored
+            uint4 xv[UNROLL][2];
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int k = (s + u) * 64 + 16 * t + 8 * h;
-                const bool ok = s + u < s1 && k < a.K;
+            for (int u = 0; u < UNROLL; u++)
 #pragma unroll
-                for (int n = 0; n < NT; n++) {
-                    const int tok = min(n * 8 + g, a.M - 1);        // tokens past the end repeat the last; never stored
-                    xv[u][h][n] = ok ? *reinterpret_cast<const uint4*>(x + (size_t)tok * a.ldx + k) : make_uint4(0, 0, 0, 0);
+                for (int h = 0; h < 2; h++) {
+                    const int k = (s + u) * 64 + 16 * t + 8 * h;
+                    const bool ok = s + u < s1 && k < a.K;
+                    xv[u][h] = ok ? *reinterpret_cast<const uint4*>(x + (size_t)tok * a.ldx + k) : make_uint4(0, 0, 0, 0);
                 }
-            }
 #pragma unroll
-        for (int u = 0; u < UNROLL; u++)
+            for (int u = 0; u < UNROLL; u++)
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const uint32_t a1[4] = {wl[u][h].x, wh[u][h].x, wl[u][h].y, wh[u][h].y};
-                const uint32_t a2[4] = {wl[u][h].z, wh[u][h].z, wl[u][h].w, wh[u][h].w};
-#pragma unroll
-                for (int n = 0; n < NT; n++) {
-                    mma_bf16(c[n], a1, xv[u][h][n].x, xv[u][h][n].y);
-                    mma_bf16(c[n], a2, xv[u][h][n].z, xv[u][h][n].w);
+                for (int h = 0; h < 2; h++) {
+                    const uint32_t a1[4] = {wl[u][h].x, wh[u][h].x, wl[u][h].y, wh[u][h].y};
+                    const uint32_t a2[4] = {wl[u][h].z, wh[u][h].z, wl[u][h].w, wh[u][h].w};
+                    mma_bf16(c[n], a1, xv[u][h].x, xv[u][h].y);
+                    mma_bf16(c[n], a2, xv[u][h].z, xv[u][h].w);
                 }
-            }
+        }
     }
     if (!waited) ti_pdl_sync();
 
