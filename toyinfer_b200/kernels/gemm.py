@@ -2,8 +2,8 @@
 
 bfloat16 operands whose rows are 16-byte aligned go to the tcgen05 kernel (the weights play
 the 128-row operand when there are at most 64 tokens), or, for up to 8 tokens, to kernels
-that only stream the weights (CUDA cores for one token, mma.sync beyond); everything else, and the whole 32-bit engine, runs on
-the CUDA-core kernels.
+that only stream the weights (CUDA cores for one token, mma.sync beyond); everything else,
+and the whole 32-bit engine, runs on the CUDA-core kernels.
 """
 from __future__ import annotations
 
@@ -14,9 +14,10 @@ import torch
 from . import _call, _code, _ptr, _stream
 from .lib import library
 
-# Measured in whole decode steps of a 4B-shaped model (ms per step at 1 / 2 / 4 / 8 sequences):
-# tcgen05 swap-AB kernel 2.80 / 2.75 / 2.82 / 3.01, weight-streaming kernel 2.26 / 2.87 / - / -,
-# small-batch mma.sync kernel 2.41 / 2.51 / 2.63 / 2.88.
+# Measured in whole decode steps of a 4B-shaped model at 2,048 positions (ms per step at 1 / 2 / 4 / 8
+# sequences, every product of the step through the one kernel): tcgen05 swap-AB kernel 2.80 / 2.75 /
+# 2.82 / 3.01, weight-streaming kernel 2.26 / 2.87 / - / -, small-batch mma.sync kernel 2.41 / 2.51 /
+# 2.63 / 2.88; at 16 sequences the tcgen05 kernel 3.37 against 3.58.
 GEMV_MAX_TOKENS = 1      # one token: a plain read of the weights on the CUDA cores
 SKINNY_MAX_TOKENS = 8    # up to this many: mma.sync with both operands loaded straight from global memory
 _tickets = {}
