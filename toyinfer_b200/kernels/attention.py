@@ -26,11 +26,11 @@ def prefill(q, k, v, out, scale, window, batch) -> None:
 
 def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int) -> int:
     """Splits along the keys so that the grid has about two blocks per SM, but no split
-    shorter than two pages.  Depends only on the batch's padded size and the longest
+    shorter than four pages.  Depends only on the batch's padded size and the longest
     length the step was planned for, so that a captured launch stays valid."""
     tiles = max(1, (max_len + page - 1) // page)
     want = max(1, (2 * sms) // max(1, n_seq * n_kv_heads))
-    return max(1, min(want, (tiles + 1) // 2, 64))
+    return max(1, min(want, (tiles + 3) // 4, 64))
 
 
 # Whether the last decode attention ended with a combine kernel that was started late, i.e. only
