@@ -154,6 +154,31 @@ def time_decode(engine, batch, context, steps, warmup, seed=0):
             engine.end_sequence(s)
 
 
+def time_decode_range(engine, batch, start, end, seed=0):
+    """Mean decode step time while ``batch`` sequences grow from ``start`` to ``end`` positions
+    (tokens per second = batch / mean).  Token ids are chosen beforehand; timed on the device."""
+    import torch
+    vocab = engine.spec.vocab_size
+    slots = [engine.new_sequence() for _ in range(batch)]
+    try:
+        engine.step([(s, random_tokens(start, vocab, seed + i)) for i, s in enumerate(slots)], [[] for _ in slots])
+        steps = end - start
+        toks = [random_tokens(steps, vocab, seed + 2000 + i) for i in range(batch)]
+        for t in range(4):                          # warm-up (counts towards the lengths, not the time)
+            engine.step([(s, [toks[i][t]]) for i, s in enumerate(slots)], None)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for t in range(4, steps):
+            engine.step([(s, [toks[i][t]]) for i, s in enumerate(slots)], None)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (steps - 4)
+    finally:
+        for s in slots:
+            engine.end_sequence(s)
+
+
 def time_prefill(engine, tokens, reps=3):
     import torch
     vocab = engine.spec.vocab_size
@@ -235,6 +260,10 @@ def run_ours(args):
     out["prefill"] = {"value": round(PREFILL_TOKENS * 1000.0 / ms_pre, 1), "tokens": PREFILL_TOKENS,
                       "ms": round(ms_pre, 3), "frac": round(fl / (ms_pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
+    if args.range:
+        ms_r = time_decode_range(engine, batch, PREFILL_TOKENS, ctx)
+        out["range"] = {"from": PREFILL_TOKENS, "to": ctx, "batch": batch, "ms_per_step": round(ms_r, 4),
+                        "value": round(batch * 1000.0 / ms_r, 2), "unit": "tokens/s"}
     if not args.skip_points:
         pts = {}
         for b in (1, 64):
@@ -377,6 +406,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the named configuration (reported)")
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
+    ap.add_argument("--range", action="store_true",
+                    help="also the mean decode rate while the batch grows from 2,048 positions to --context (some 20 s more)")
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
                     "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K, attn_decode, attn_decode_b64, attn_decode_b1, attn_prefill")
     ap.add_argument("--workload", default="", choices=["", "8b", "32b"],
