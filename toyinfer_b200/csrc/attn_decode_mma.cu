@@ -66,10 +66,12 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) mbar_init(&full[s], 1);
-        s_abort = 0;
+        // once a wait has run out somewhere results are lost anyway: later blocks leave at once
+        s_abort = *reinterpret_cast<volatile int*>(status);
         mbar_fence_init();
     }
     __syncthreads();
+    if (s_abort) return;
 
     // What is read before ti_pdl_sync() below does not depend on the kernel just before this
     // one: the step's lengths, slots and page table were uploaded before the step's first

@@ -147,8 +147,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full[STAGES], empty[STAGES], acc_ready;
     __shared__ uint32_t tmem_slot;
-    __shared__ int s_last;
+    __shared__ int s_last, s_gave_up;
 
+    // Once a wait has run out somewhere, results are lost anyway: later blocks leave at once
+    // instead of each running into its own limits.
+    if (threadIdx.x == 0) s_gave_up = *reinterpret_cast<volatile int*>(status);
+    __syncthreads();
+    if (s_gave_up) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * BM, b0 = blockIdx.y * BN, split = blockIdx.z;
     const int nkb = (g.K + BK - 1) / BK;
@@ -344,7 +349,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
+    __shared__ int s_gave_up;
 
+    if (threadIdx.x == 0) s_gave_up = *reinterpret_cast<volatile int*>(status);      // see gemm_tc_kernel
+    __syncthreads();
+    if (s_gave_up) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_a = (g.rows_a + BM - 1) / BM, tiles_b = (g.rows_b + BN - 1) / BN;
     const int n_tiles = tiles_a * tiles_b;
