@@ -112,7 +112,8 @@ def test_swiglu(K, dtype, M, I):
 
 
 @pytest.mark.parametrize("dtype", DT)
-@pytest.mark.parametrize("M,I,K_", [(1, 128, 64), (8, 9728, 2560), (5, 200, 96), (70, 144, 80), (300, 1000, 264), (3, 50, 100)])
+@pytest.mark.parametrize("M,I,K_", [(1, 128, 64), (8, 9728, 2560), (5, 200, 96), (70, 144, 80), (300, 1000, 264), (3, 50, 100),
+                                    (1300, 1800, 264)])
 def test_linear_swiglu(K, dtype, M, I, K_):
     """Gate and up rows side by side in one matrix; the activation in the product's epilogue
     (tensor-core shapes) or in a kernel after it (the rest)."""
@@ -151,6 +152,16 @@ def test_linear(K, dtype, M, N, K_):
         torch.testing.assert_close(got32.cpu().double(), want, rtol=1e-3, atol=1e-4)
 
 
+def _planned_shared_tiles(M, N, K_):
+    import ctypes
+    from toyinfer_b200.kernels.gemm import sm_count
+    from toyinfer_b200.kernels.lib import library
+    swap, bn, splits, shared, ws = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_longlong()
+    library().ti_linear_tc_plan(M, N, K_, sm_count(torch.device("cuda", torch.cuda.current_device())), ctypes.byref(swap),
+                                ctypes.byref(bn), ctypes.byref(splits), ctypes.byref(ws), ctypes.byref(shared))
+    return shared.value if (not swap.value and splits.value == 1 and bn.value >= 128) else 0
+
+
 @pytest.mark.parametrize("M,N,K_,f32", [
     (2048, 6144, 2560, False),     # prefill, q/k/v rows of a 4B-shaped layer
     (2048, 2560, 9728, False),     # prefill, down projection (long contraction)
@@ -158,6 +169,7 @@ def test_linear(K, dtype, M, N, K_):
     (1000, 1536, 512, False), (777, 3000, 328, True),
     (4741, 520, 264, False),       # more token tiles than one panel of the tile order, the last panel short
     (300, 2560, 4096, False),      # few tiles: the contraction is split
+    (1300, 3600, 264, False),      # tiles for a round and a bit, shared out by contraction steps; short parts, ragged K
     (8, 19456, 2560, False),       # decode at batch 8, gate and up rows
     (64, 2560, 9728, False),       # decode at batch 64, split contraction
     (1, 151936, 2560, True),       # head for one row, float32 logits
@@ -174,6 +186,8 @@ def test_linear_tensor_cores_at_model_sizes(K, monkeypatch, M, N, K_, f32):
     w = (torch.randn(N, K_, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
     got = K.linear(x, w, out_dtype=torch.float32 if f32 else None)
     K.check_status()
+    if (M, N) in ((2048, 2560), (1300, 3600)):
+        assert _planned_shared_tiles(M, N, K_) > 0      # these are here for the tiles that two blocks share
     want = x.float() @ w.float().T
     if f32:
         torch.testing.assert_close(got, want, rtol=1e-3, atol=1e-3)

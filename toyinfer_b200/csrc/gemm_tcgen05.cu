@@ -10,7 +10,8 @@
 //     128-row MMA whatever the batch; the step is bound by that read.
 // The contraction may be split over blockIdx.z; partial tiles go to a float32 workspace and
 // the last block to finish a tile (a ticket per tile) adds them in split order, so the
-// result does not depend on timing.
+// result does not depend on timing.  The many-token kernel (one block per SM walking over
+// tiles) shares out the tiles of an uneven last round by contraction steps instead: TileWalk.
 //
 // Roles inside a block of 192 threads: warp 0 issues TMA loads into a ring of stages
 // (full/empty mbarriers), one lane of warp 1 issues the MMAs (four K = 16 steps per
@@ -34,6 +35,7 @@ struct GemmArgs {
     void* out; long long ld_out; int out_f32; int transposed;
     int splits; float* workspace; int* tickets;
     int gated;      // rows of the weight operand come in (gate, up) pairs: store up * silu(gate), half as many columns
+    int shared_tiles;   // many-token kernel: the first so many tiles are shared out by contraction steps (see TileWalk)
 };
 
 // kind::f16 instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M = 128
@@ -336,6 +338,60 @@ __device__ __forceinline__ void tile_origin(int tile, int tiles_a, int tiles_b, 
     b0 = (within / span) * BN;
 }
 
+// What a block of the many-token kernel does, in order.  The tiles seldom fill whole rounds of
+// blocks (2,048 x 2,560 outputs are 160 tiles of 128 x 256 for 148 SMs: two rounds, the second
+// nearly empty).  So the first `shared` tiles, between one and two rounds' worth, are not dealt
+// out tile by tile but as one row of shared * nkb contraction steps cut into equal parts, one per
+// block: a block finishes the tile its part starts in, takes whole tiles, and begins the tile
+// its part ends in.  The pieces of a tile that several blocks worked on go to a float32
+// workspace (two places per block: the piece at the start of its part and the one at its end), and the
+// block that brings a tile's second piece (a ticket per tile) adds the two and stores the tile.
+// The remaining tiles follow in whole rounds.
+struct Piece {
+    int tile, kb0, kb1;
+    bool whole;     // the whole contraction: stored straight from tensor memory
+    int place;      // else: which of the block's two places in the workspace takes it
+};
+struct TileWalk {
+    int nkb, n_tiles, next_whole, stride;
+    long long at, end;
+    bool first;
+    __device__ TileWalk(int shared, int n_tiles_, int nkb_) : nkb(nkb_), n_tiles(n_tiles_), first(true) {
+        const long long steps = (long long)shared * nkb_;
+        at = part_start(blockIdx.x, steps, gridDim.x);
+        end = part_start(blockIdx.x + 1, steps, gridDim.x);
+        next_whole = shared + blockIdx.x;
+        stride = gridDim.x;
+    }
+    __device__ static long long part_start(int block, long long steps, int blocks) { return (long long)block * steps / blocks; }
+    __device__ bool next(Piece& p) {
+        if (at < end) {
+            p.tile = (int)(at / nkb);
+            p.kb0 = (int)(at - (long long)p.tile * nkb);
+            const int len = (int)min((long long)(nkb - p.kb0), end - at);
+            p.kb1 = p.kb0 + len;
+            p.whole = len == nkb;
+            p.place = first ? 0 : 1;
+            first = false;
+            at += len;
+            return true;
+        }
+        if (next_whole < n_tiles) {
+            p.tile = next_whole; p.kb0 = 0; p.kb1 = nkb; p.whole = true; p.place = 0;
+            next_whole += stride;
+            return true;
+        }
+        return false;
+    }
+    // the block whose part holds contraction step `s` of the shared tiles
+    __device__ static int block_of(long long s, long long steps, int blocks) {
+        int b = (int)(s * blocks / steps);
+        while (b + 1 < blocks && part_start(b + 1, steps, blocks) <= s) b++;
+        while (b > 0 && part_start(b, steps, blocks) > s) b--;
+        return b;
+    }
+};
+
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
@@ -349,7 +405,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
-    __shared__ int s_gave_up;
+    __shared__ int s_gave_up, s_last;
 
     if (threadIdx.x == 0) s_gave_up = *reinterpret_cast<volatile int*>(status);      // see gemm_tc_kernel
     __syncthreads();
@@ -379,10 +435,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
         if (lane == 0) {
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            TileWalk walk(g.shared_tiles, n_tiles, nkb);
+            Piece p;
+            while (ok && walk.next(p)) {
                 int a0, b0;
-                tile_origin<BN>(tile, tiles_a, tiles_b, a0, b0);
-                for (int kb = 0; kb < nkb; kb++, it++) {
+                tile_origin<BN>(p.tile, tiles_a, tiles_b, a0, b0);
+                for (int kb = p.kb0; kb < p.kb1; kb++, it++) {
                     const int s = it % STAGES;
                     if (!mbar_wait(&empty[s], (uint32_t)(((it / STAGES) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); ok = false; break; }
                     unsigned char* sa = smem + (size_t)s * (A_BYTES + B_BYTES);
@@ -397,13 +455,15 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
             constexpr uint32_t idesc = instr_desc<BN>();
             int it = 0, n = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, n++) {
+            TileWalk walk(g.shared_tiles, n_tiles, nkb);
+            Piece p;
+            for (; ok && walk.next(p); n++) {
                 const int buf = n & 1;
                 // the epilogue must have drained this accumulator (its use before last)
                 if (!mbar_wait(&acc_empty[buf], (uint32_t)(((n >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); ok = false; break; }
                 tc_fence_after();
                 const uint32_t acc = tmem + buf * ACC_COLS;
-                for (int kb = 0; kb < nkb; kb++, it++) {
+                for (int kb = p.kb0; kb < p.kb1; kb++, it++) {
                     const int s = it % STAGES;
                     if (!mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1))) { ti_report(status, TI_STATUS_TMA_WAIT); ok = false; break; }
                     tc_fence_after();
@@ -411,7 +471,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
                     const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++)
-                        tc_mma_bf16(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        tc_mma_bf16(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > p.kb0 || k > 0) ? 1u : 0u);
                     tc_commit(&empty[s]);
                 }
                 if (ok) tc_commit(&acc_full[buf]);
@@ -421,23 +481,94 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
         const int q = warp & 3;
         int n = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, n++) {
+        TileWalk walk(g.shared_tiles, n_tiles, nkb);
+        Piece p;
+        const long long shared_steps = (long long)g.shared_tiles * nkb;
+        constexpr size_t TILE_FLOATS = (size_t)BM * BN;
+        for (; walk.next(p); n++) {
             const int buf = n & 1;
             int a0, b0;
-            tile_origin<BN>(tile, tiles_a, tiles_b, a0, b0);
+            tile_origin<BN>(p.tile, tiles_a, tiles_b, a0, b0);
             const int i = a0 + q * 32 + lane;
             if (!mbar_wait(&acc_full[buf], (uint32_t)((n >> 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem + buf * ACC_COLS + ((uint32_t)(q * 32) << 16);
+            if (p.whole) {
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                float r[16];
-                tmem_ld16(taddr + c, r);
-                store_chunk(g, i, b0, c, r, lane);
+                for (int c = 0; c < BN; c += 16) {
+                    float r[16];
+                    tmem_ld16(taddr + c, r);
+                    store_chunk(g, i, b0, c, r, lane);
+                }
+                // this warp has read its lanes of the accumulator: hand it back to the MMA warp
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                continue;
             }
-            // this warp has read its lanes of the accumulator: hand it back to the MMA warp
+            // A piece of a tile.  The blocks that hold this tile's pieces, by the cut of the steps:
+            const long long t0 = (long long)p.tile * nkb;
+            const int blk0 = TileWalk::block_of(t0, shared_steps, gridDim.x);
+            const int blk1 = TileWalk::block_of(t0 + nkb - 1, shared_steps, gridDim.x);
+            const int t = q * 32 + lane;
+            // Has the other block brought its piece already?  Then this block adds the tile up and
+            // its own piece never leaves tensor memory.  Else the piece goes to this block's place
+            // in the workspace (thread t keeps 16 columns as four float4, word v of chunk c at
+            // [(c / 16 * 4 + v) * 128 + t]), and the ticket says whether the other came meanwhile.
+            asm volatile("bar.sync 1, 128;" ::: "memory");      // everyone has read s_last of the piece before
+            if (threadIdx.x == 64) s_last = *reinterpret_cast<volatile int*>(&g.tickets[p.tile]) == blk1 - blk0;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            bool last = s_last != 0;
+            if (!last) {
+                float4* mine = reinterpret_cast<float4*>(g.workspace + ((size_t)blockIdx.x * 2 + p.place) * TILE_FLOATS) + t;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    float r[16];
+                    tmem_ld16(taddr + c, r);
+#pragma unroll
+                    for (int v = 0; v < 4; v++) mine[(size_t)(c / 4 + v) * BM] = make_float4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) s_last = atomicAdd(&g.tickets[p.tile], 1) == blk1 - blk0;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                last = s_last != 0;
+            }
+            if (last) {
+                if (threadIdx.x == 64) g.tickets[p.tile] = 0;   // ready for the next launch
+                __threadfence();
+                // A part is at least a tile long, so a tile has two pieces at most: this block's and one
+                // other.  Nothing runs beside this at the end of a kernel, so the other piece is fetched
+                // 128 columns at a time, all loads in flight together, before this block's own piece is
+                // read back and added (a sum of two, the same whichever block forms it).
+                const int other = blk0 == (int)blockIdx.x ? blk1 : blk0;
+                const int place = TileWalk::part_start(other, shared_steps, gridDim.x) >= t0 ? 0 : 1;   // first piece of its part, or last
+                const float4* ws = reinterpret_cast<const float4*>(g.workspace + ((size_t)other * 2 + place) * TILE_FLOATS) + t;
+                constexpr int GROUP = 8;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16 * GROUP) {
+                    float4 f[GROUP][4];
+#pragma unroll
+                    for (int u = 0; u < GROUP; u++)
+#pragma unroll
+                        for (int v = 0; v < 4; v++)
+                            f[u][v] = c0 + 16 * u < BN ? __ldcg(&ws[(size_t)((c0 + 16 * u) / 4 + v) * BM]) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int u = 0; u < GROUP; u++) {
+                        const int c = c0 + 16 * u;
+                        if (c >= BN) break;
+                        float r[16];
+                        tmem_ld16(taddr + c, r);
+#pragma unroll
+                        for (int v = 0; v < 4; v++) {
+                            r[4 * v] += f[u][v].x; r[4 * v + 1] += f[u][v].y; r[4 * v + 2] += f[u][v].z; r[4 * v + 3] += f[u][v].w;
+                        }
+                        store_chunk(g, i, b0, c, r, lane);
+                    }
+                }
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
@@ -529,6 +660,14 @@ int launch(const CUtensorMap& am, const CUtensorMap& bm, const GemmArgs& g, cuda
     }
     return 0;
 }
+// How many tiles of a many-token product are shared out by contraction steps (TileWalk): with
+// whole rounds of tiles, or less than one round, none; else the last round and the one before it,
+// so that every block's part is at least a tile long.
+int shared_tiles_of(int tiles, int sms) {
+    if (sms <= 0 || tiles < sms || tiles % sms == 0) return 0;
+    return sms + tiles % sms;
+}
+
 template <int BN>
 int launch_persistent(const CUtensorMap& am, const CUtensorMap& bm, const GemmArgs& g, int sms, cudaStream_t stream) {
     constexpr int STAGES = persistent_stages<BN>();
@@ -541,15 +680,16 @@ int launch_persistent(const CUtensorMap& am, const CUtensorMap& bm, const GemmAr
     int* status = ti_status_ptr();
     TI_REQUIRE(status != nullptr, "linear: no status word");
     const int tiles = ((g.rows_a + BM - 1) / BM) * ((g.rows_b + BN - 1) / BN);
-    dim3 grid(tiles < sms ? tiles : sms);
-    TI_CUDA(ti_launch_class<5>(gemm_tc_persistent_kernel<BN>, grid, dim3(THREADS), smem, stream, am, bm, g, status));
+    const int blocks = g.shared_tiles > 0 || tiles > sms ? sms : tiles;
+    TI_CUDA(ti_launch_class<5>(gemm_tc_persistent_kernel<BN>, dim3(blocks), dim3(THREADS), smem, stream, am, bm, g, status));
     TI_CHECK_LAUNCH("linear (tcgen05, persistent)");
     return 0;
 }
 
-// Weight rows per tile for many tokens: the width whose tiles fill whole rounds of `sms`
-// blocks best, wider tiles being a little more efficient per flop.
-int wide_tile(int rows_a, int rows_b, int sms) {
+// Weight rows per tile for many tokens.  Wider tiles are a little more efficient per flop; what
+// counts besides is how much of the last tile along the weights' rows is used, and, where the
+// tiles are dealt out whole (`whole_rounds`), how well they fill whole rounds of `sms` blocks.
+int wide_tile(int rows_a, int rows_b, int sms, bool whole_rounds, double* score_out = nullptr) {
     const int cand[9] = {256, 240, 224, 208, 192, 176, 160, 144, 128};
     const double mma_eff[9] = {1.0, 0.99, 0.98, 0.97, 0.96, 0.95, 0.94, 0.92, 0.90};
     int best = 256;
@@ -558,20 +698,23 @@ int wide_tile(int rows_a, int rows_b, int sms) {
         const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + cand[c] - 1) / cand[c]);
         const int rounds = (tiles + sms - 1) / sms;
         const double useful = (double)rows_b / (((rows_b + cand[c] - 1) / cand[c]) * (double)cand[c]);
-        const double score = mma_eff[c] * useful * tiles / ((double)rounds * sms);
+        double score = mma_eff[c] * useful;
+        if (whole_rounds) score *= tiles / ((double)rounds * sms);
         if (score > best_score + 1e-9) { best_score = score; best = cand[c]; }
     }
+    if (score_out) *score_out = best_score;
     return best;
 }
 }  // namespace
 
-// Bytes of float32 workspace ti_linear_tc needs for this shape (0: no split), and how it
-// splits.  `sms` blocks fill the device once.
+// Floats of workspace and tickets (`n_tiles`) ti_linear_tc needs for this shape (0: none), and
+// how it splits.  `sms` blocks fill the device once.
 extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* bn, int* splits, long long* ws_floats,
                                  int* n_tiles) {
     const bool sw = M <= 64;
     const int rows_a = sw ? N : M, rows_b = sw ? M : N;
     int b;
+    bool share = false;     // many tokens: tiles shared out by contraction steps
     if (sw) {
         b = rows_b <= 16 ? 16 : rows_b <= 32 ? 32 : 64;
         // A matrix with few row tiles is split along the contraction, and the block that adds a
@@ -584,7 +727,18 @@ extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* b
         if (b == 64 && row_tiles * 2 <= sms) b = 32;
         else if (b == 32 && rows_b > 16 && row_tiles * 4 <= sms) b = 16;
     }
-    else b = rows_b >= 256 ? wide_tile(rows_a, rows_b, sms) : rows_b > 64 ? 128 : rows_b > 32 ? 64 : rows_b > 16 ? 32 : 16;
+    else if (rows_b >= 256) {
+        // The width that fills whole rounds best.  Where even that leaves more than a tenth of the
+        // device idle (measured at 2,048 tokens: 2,560 weight rows do, 6,144 and 19,456 do not), the
+        // widest useful tile instead, with a part of the tiles shared out by contraction steps.
+        double score;
+        b = wide_tile(rows_a, rows_b, sms, true, &score);
+        if (score < 0.89) {
+            const int wide = wide_tile(rows_a, rows_b, sms, false);
+            if (((rows_a + BM - 1) / BM) * ((rows_b + wide - 1) / wide) >= sms) { b = wide; share = true; }
+        }
+    }
+    else b = rows_b > 64 ? 128 : rows_b > 32 ? 64 : rows_b > 16 ? 32 : 16;
     const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + b - 1) / b);
     const int nkb = (K + BK - 1) / BK;
     int sp = 1;
@@ -601,6 +755,12 @@ extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* b
     }
     *swap = sw; *bn = b; *splits = sp; *n_tiles = tiles;
     *ws_floats = sp > 1 ? (long long)sp * tiles * BM * b : 0;
+    if (!sw && sp == 1 && b >= 128) {
+        // the many-token kernel: two places per block for the pieces of shared tiles, a ticket per shared tile
+        const int shared = share ? shared_tiles_of(tiles, sms) : 0;
+        *n_tiles = shared;
+        *ws_floats = shared ? (long long)sms * 2 * BM * b : 0;
+    }
     return 0;
 }
 
@@ -608,7 +768,8 @@ extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* b
 // float32 with row stride ldo.  With `gated`, w's rows are (gate_0, up_0, gate_1, up_1, ...) and
 // out is [M, N / 2] = up * gate / (1 + exp(-gate)).  `workspace` (float32) and `tickets` (int32, zero before the
 // first use, left zero) as planned by ti_linear_tc_plan; tickets needs n_tiles entries and may be
-// null, in which case a second kernel adds the partial tiles.
+// null, in which case a second kernel adds the partial tiles of a split contraction, and the
+// many-token kernel deals out whole tiles only.
 extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                             long long ldw, long long ldo, int out_f32, int gated, int sms, float* workspace, int* tickets,
                             cudaStream_t stream) {
@@ -626,11 +787,13 @@ extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int 
     g.out = out; g.ld_out = ldo; g.out_f32 = out_f32; g.transposed = swap;
     g.splits = splits; g.workspace = workspace; g.tickets = tickets;
     g.gated = gated;
+    g.shared_tiles = 0;
     TI_REQUIRE(!gated || (N % 2 == 0 && !out_f32), "linear (tcgen05): a gated product needs an even number of weight rows and a bfloat16 result");
     CUtensorMap am, bm;
     if (int rc = operand_map(swap ? w : x, g.rows_a, K, swap ? ldw : ldx, BM, &am)) return rc;
     if (int rc = operand_map(swap ? x : w, g.rows_b, K, swap ? ldx : ldw, bn, &bm)) return rc;
     if (!swap && splits == 1 && bn >= 128) {
+        if (workspace && tickets) g.shared_tiles = tiles;       // as planned: 0 where whole tiles fill the rounds
         switch (bn) {
             case 128: return launch_persistent<128>(am, bm, g, sms, stream);
             case 144: return launch_persistent<144>(am, bm, g, sms, stream);

@@ -64,7 +64,7 @@ def run(x, w, out, M, N, K, ldx, ldw, gated: bool = False, late_start: bool = Fa
         lib.ti_linear_tc_plan(M, N, K, sms, ctypes.byref(swap), ctypes.byref(bn), ctypes.byref(splits),
                               ctypes.byref(ws), ctypes.byref(n_tiles))
         workspace = tickets = None
-        if splits.value > 1:
+        if ws.value > 0:
             workspace = torch.empty(ws.value, dtype=torch.float32, device=x.device)
             # tickets let the last block of a tile add the partial tiles itself; measured faster
             # than the separate reduction kernel the library falls back to without them
