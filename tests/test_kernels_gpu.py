@@ -198,6 +198,34 @@ def test_linear_tensor_cores_at_model_sizes(K, monkeypatch, M, N, K_, f32):
     assert torch.equal(got, got2)
 
 
+@pytest.mark.parametrize("M,N,K_,f32", [
+    (2048, 2560, 4096, False),     # 80 tiles of 256 x 256 for 74 pairs: all shared out by contraction steps
+    (2048, 6144, 2560, False),     # whole tiles in both forms
+    (1100, 3000, 328, True),       # ragged on every side; rows past the end in the pair's second block
+    (512, 19456, 264, False),      # two token tiles
+])
+def test_linear_many_tokens_on_one_and_on_two_sms_per_tile(K, M, N, K_, f32):
+    """The many-token tcgen05 kernel in both forms, one block per tile of 128 tokens and a pair of blocks
+    per tile of 256 (cta_group::2), against a float32 product of the same bfloat16 operands."""
+    from toyinfer_b200.kernels.lib import library
+    g = torch.Generator(device="cuda").manual_seed(6)
+    x = torch.randn(M, K_, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K_, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
+    want = x.float() @ w.float().T
+    try:
+        for mode in (1, 2):
+            library().ti_set_gemm_pair_mode(mode)
+            got = K.linear(x, w, out_dtype=torch.float32 if f32 else None)
+            K.check_status()
+            if f32:
+                torch.testing.assert_close(got, want, rtol=1e-3, atol=1e-3)
+            else:
+                torch.testing.assert_close(got.float(), want.to(torch.bfloat16).float(), rtol=1.6e-2, atol=4e-3)
+            assert torch.equal(got, K.linear(x, w, out_dtype=torch.float32 if f32 else None))
+    finally:
+        library().ti_set_gemm_pair_mode(0)
+
+
 @pytest.mark.parametrize("M", [1, 2])
 @pytest.mark.parametrize("N,K_", [(6144, 2560), (2560, 9728), (2560, 4096), (19456, 2560), (7, 8), (333, 200), (2, 4104),
                                   (151936, 64), (100, 1024), (30, 20000)])

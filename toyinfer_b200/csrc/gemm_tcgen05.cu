@@ -10,8 +10,9 @@
 //     128-row MMA whatever the batch; the step is bound by that read.
 // The contraction may be split over blockIdx.z; partial tiles go to a float32 workspace and
 // the last block to finish a tile (a ticket per tile) adds them in split order, so the
-// result does not depend on timing.  The many-token kernel (one block per SM walking over
-// tiles) shares out the tiles of an uneven last round by contraction steps instead: TileWalk.
+// result does not depend on timing.  The many-token kernel (every SM walking over tiles, alone
+// or as one of a pair on the two-SM MMA, cta_group::2) shares out the tiles of an uneven last
+// round by contraction steps instead: TileWalk.
 //
 // Roles inside a block of 192 threads: warp 0 issues TMA loads into a ring of stages
 // (full/empty mbarriers), one lane of warp 1 issues the MMAs (four K = 16 steps per
@@ -310,43 +311,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------
-// Many tokens: one block per SM walks over the output tiles (activations as the 128-row
-// operand, BN weight rows per tile).  Two accumulators in tensor memory: while the epilogue
-// warps read one back and store it, the MMA warp already fills the other, so the tensor
-// cores do not idle during a tile's epilogue.  The TMA ring runs on across tile borders.
+// Many tokens: every SM walks over output tiles (activations as the MMA's row operand, BN
+// weight rows per tile).  Two accumulators in tensor memory: while the epilogue warps read one
+// back and store it, the MMA warp already fills the other, so the tensor cores do not idle
+// during a tile's epilogue.  The TMA ring runs on across tile borders.
+//
+// Two forms.  One block per tile of 128 tokens; or (PAIR) the two blocks of a cluster on one
+// tile of 256 tokens with the two-SM MMA (cta_group::2): each loads its 128 tokens and BN / 2 of
+// the weight rows, so an SM takes in 32 KB per 64 steps of the contraction where a block on its
+// own takes 48 KB for the same arithmetic.  The block of rank 0 issues the MMAs for both; all
+// loads of a stage are counted on its `full` barrier; a commit frees the stage, and hands over
+// the accumulator, in both blocks at once; the epilogue warps of both report a drained
+// accumulator to rank 0.  Each block reads its own 128 rows of the result from its own tensor
+// memory.  "Unit" below is what works on a tile: a block, or a pair of them.
 // ---------------------------------------------------------------------------
-template <int BN> constexpr int persistent_stages() {
-    constexpr int per = BM * BK * 2 + BN * BK * 2;
+template <int BN, bool PAIR> constexpr int walk_stages() {
+    constexpr int per = BM * BK * 2 + (PAIR ? BN / 2 : BN) * BK * 2;
     constexpr int n = (196 * 1024) / per;
     return n > 8 ? 8 : n;
 }
 
-// Order of the tiles of a many-token product.  Token tiles go in groups of PANEL: within a
-// group the token tile changes fastest, then the weight tile, so the blocks that run together
-// share few weight tiles and one panel of activations, and the panel (PANEL x 128 tokens x K,
-// some tens of MB at most) stays in L2 while the group sweeps over all weight tiles.  Without
-// the grouping every round of blocks would touch all token tiles: fine while the activations
-// fit L2 (2,048 tokens), a re-read of all of them per weight tile when they do not (16,384).
-constexpr int PANEL = 16;
-template <int BN>
-__device__ __forceinline__ void tile_origin(int tile, int tiles_a, int tiles_b, int& a0, int& b0) {
-    const int per_group = PANEL * tiles_b;
+// Order of the tiles of a many-token product.  Token tiles go in groups of 2,048 tokens: within a
+// group the token tile changes fastest, then the weight tile, so the units that run together
+// share few weight tiles and one panel of activations, and the panel (2,048 tokens x K, some
+// tens of MB at most) stays in L2 while the group sweeps over all weight tiles.  Without the
+// grouping every round of units would touch all token tiles: fine while the activations fit L2
+// (2,048 tokens), a re-read of all of them per weight tile when they do not (16,384).
+constexpr int PANEL_TOKENS = 2048;
+__device__ __forceinline__ void tile_origin(int tile, int tiles_a, int tiles_b, int tile_rows, int bn, int& a0, int& b0) {
+    const int panel = PANEL_TOKENS / tile_rows;
+    const int per_group = panel * tiles_b;
     const int grp = tile / per_group, within = tile - grp * per_group;
-    const int first = grp * PANEL;
-    const int span = min(PANEL, tiles_a - first);
-    a0 = (first + within % span) * BM;
-    b0 = (within / span) * BN;
+    const int first = grp * panel;
+    const int span = min(panel, tiles_a - first);
+    a0 = (first + within % span) * tile_rows;
+    b0 = (within / span) * bn;
 }
 
-// What a block of the many-token kernel does, in order.  The tiles seldom fill whole rounds of
-// blocks (2,048 x 2,560 outputs are 160 tiles of 128 x 256 for 148 SMs: two rounds, the second
-// nearly empty).  So the first `shared` tiles, between one and two rounds' worth, are not dealt
-// out tile by tile but as one row of shared * nkb contraction steps cut into equal parts, one per
-// block: a block finishes the tile its part starts in, takes whole tiles, and begins the tile
-// its part ends in.  The pieces of a tile that several blocks worked on go to a float32
-// workspace (two places per block: the piece at the start of its part and the one at its end), and the
-// block that brings a tile's second piece (a ticket per tile) adds the two and stores the tile.
-// The remaining tiles follow in whole rounds.
+// What a unit does, in order.  The tiles seldom fill whole rounds of units (2,048 x 2,560
+// outputs are 160 tiles of 128 x 256 for 148 SMs: two rounds, the second nearly empty).  So the
+// first `shared` tiles, between one and two rounds' worth, are not dealt out tile by tile but as
+// one row of shared * nkb contraction steps cut into equal parts, one per unit: a unit finishes
+// the tile its part starts in, takes whole tiles, and begins the tile its part ends in.  A part
+// is at least a tile long, so a tile has two pieces at most.  Pieces go to a float32 workspace
+// (two places per block: the piece at the start of its part and the one at its end), and the
+// block that brings a tile's second piece (a ticket per tile and block of the unit) adds the two
+// and stores the tile.  The remaining tiles follow in whole rounds.
 struct Piece {
     int tile, kb0, kb1;
     bool whole;     // the whole contraction: stored straight from tensor memory
@@ -356,14 +366,14 @@ struct TileWalk {
     int nkb, n_tiles, next_whole, stride;
     long long at, end;
     bool first;
-    __device__ TileWalk(int shared, int n_tiles_, int nkb_) : nkb(nkb_), n_tiles(n_tiles_), first(true) {
+    __device__ TileWalk(int shared, int n_tiles_, int nkb_, int unit, int units) : nkb(nkb_), n_tiles(n_tiles_), first(true) {
         const long long steps = (long long)shared * nkb_;
-        at = part_start(blockIdx.x, steps, gridDim.x);
-        end = part_start(blockIdx.x + 1, steps, gridDim.x);
-        next_whole = shared + blockIdx.x;
-        stride = gridDim.x;
+        at = part_start(unit, steps, units);
+        end = part_start(unit + 1, steps, units);
+        next_whole = shared + unit;
+        stride = units;
     }
-    __device__ static long long part_start(int block, long long steps, int blocks) { return (long long)block * steps / blocks; }
+    __device__ static long long part_start(int unit, long long steps, int units) { return (long long)unit * steps / units; }
     __device__ bool next(Piece& p) {
         if (at < end) {
             p.tile = (int)(at / nkb);
@@ -383,22 +393,24 @@ struct TileWalk {
         }
         return false;
     }
-    // the block whose part holds contraction step `s` of the shared tiles
-    __device__ static int block_of(long long s, long long steps, int blocks) {
-        int b = (int)(s * blocks / steps);
-        while (b + 1 < blocks && part_start(b + 1, steps, blocks) <= s) b++;
-        while (b > 0 && part_start(b, steps, blocks) > s) b--;
-        return b;
+    // the unit whose part holds contraction step `s` of the shared tiles
+    __device__ static int unit_of(long long s, long long steps, int units) {
+        int u = (int)(s * units / steps);
+        while (u + 1 < units && part_start(u + 1, steps, units) <= s) u++;
+        while (u > 0 && part_start(u, steps, units) > s) u--;
+        return u;
     }
 };
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
-                          GemmArgs g, int* status) {
+gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
+                    GemmArgs g, int* status) {
     ti_pdl_trigger();
-    constexpr int STAGES = persistent_stages<BN>();
-    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr int STAGES = walk_stages<BN, PAIR>();
+    constexpr int B_ROWS = PAIR ? BN / 2 : BN;                  // weight rows this block loads
+    constexpr int TILE_ROWS = PAIR ? 2 * BM : BM;               // tokens of a tile
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = B_ROWS * BK * 2;
     constexpr uint32_t ACC_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;   // columns of one accumulator
     constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -407,23 +419,33 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
     __shared__ uint32_t tmem_slot;
     __shared__ int s_gave_up, s_last;
 
-    if (threadIdx.x == 0) s_gave_up = *reinterpret_cast<volatile int*>(status);      // see gemm_tc_kernel
-    __syncthreads();
-    if (s_gave_up) return;
+    if (!PAIR) {
+        // Once a wait has run out somewhere, results are lost anyway (see gemm_tc_kernel).  A pair
+        // has no such exit: its blocks must leave together.
+        if (threadIdx.x == 0) s_gave_up = *reinterpret_cast<volatile int*>(status);
+        __syncthreads();
+        if (s_gave_up) return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_a = (g.rows_a + BM - 1) / BM, tiles_b = (g.rows_b + BN - 1) / BN;
+    const int rank = PAIR ? (int)cluster_rank() : 0;
+    const int unit = PAIR ? blockIdx.x >> 1 : blockIdx.x, units = PAIR ? gridDim.x >> 1 : gridDim.x;
+    const int tiles_a = (g.rows_a + TILE_ROWS - 1) / TILE_ROWS, tiles_b = (g.rows_b + BN - 1) / BN;
     const int n_tiles = tiles_a * tiles_b;
     const int nkb = (g.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], PAIR ? 8 : 4); }   // epilogue warps of the unit
         mbar_fence_init();
+    }
+    if (PAIR) {
+        __syncthreads();
+        cluster_sync_all();         // the other block's barriers exist before anything arrives on them
     }
     if (warp == 1) {
         __syncwarp();
-        tmem_alloc(&tmem_slot, TMEM_COLS);
-        tmem_relinquish();
+        if (PAIR) { tmem_alloc_pair(&tmem_slot, TMEM_COLS); tmem_relinquish_pair(); }
+        else { tmem_alloc(&tmem_slot, TMEM_COLS); tmem_relinquish(); }
     }
     tc_fence_before();
     __syncthreads();
@@ -435,27 +457,36 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
         if (lane == 0) {
             int it = 0;
             bool ok = true;
-            TileWalk walk(g.shared_tiles, n_tiles, nkb);
+            TileWalk walk(g.shared_tiles, n_tiles, nkb, unit, units);
             Piece p;
             while (ok && walk.next(p)) {
                 int a0, b0;
-                tile_origin<BN>(p.tile, tiles_a, tiles_b, a0, b0);
+                tile_origin(p.tile, tiles_a, tiles_b, TILE_ROWS, BN, a0, b0);
+                a0 += rank * BM;
+                b0 += rank * B_ROWS;
                 for (int kb = p.kb0; kb < p.kb1; kb++, it++) {
                     const int s = it % STAGES;
                     if (!mbar_wait(&empty[s], (uint32_t)(((it / STAGES) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); ok = false; break; }
                     unsigned char* sa = smem + (size_t)s * (A_BYTES + B_BYTES);
-                    mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                    tma_load_2d(sa, &a_map, kb * BK, a0, &full[s]);
-                    tma_load_2d(sa + A_BYTES, &b_map, kb * BK, b0, &full[s]);
+                    if (PAIR) {
+                        if (rank == 0) mbar_expect_tx(&full[s], 2 * (A_BYTES + B_BYTES));
+                        const uint32_t bar = cluster_addr(&full[s], 0);
+                        tma_load_2d_pair(sa, &a_map, kb * BK, a0, bar);
+                        tma_load_2d_pair(sa + A_BYTES, &b_map, kb * BK, b0, bar);
+                    } else {
+                        mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                        tma_load_2d(sa, &a_map, kb * BK, a0, &full[s]);
+                        tma_load_2d(sa + A_BYTES, &b_map, kb * BK, b0, &full[s]);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc<BN>();
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
             int it = 0, n = 0;
             bool ok = true;
-            TileWalk walk(g.shared_tiles, n_tiles, nkb);
+            TileWalk walk(g.shared_tiles, n_tiles, nkb, unit, units);
             Piece p;
             for (; ok && walk.next(p); n++) {
                 const int buf = n & 1;
@@ -470,26 +501,39 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
                     const uint32_t sa = smem_u32(smem + (size_t)s * (A_BYTES + B_BYTES));
                     const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; k++)
-                        tc_mma_bf16(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > p.kb0 || k > 0) ? 1u : 0u);
-                    tc_commit(&empty[s]);
+                    for (int k = 0; k < BK / 16; k++) {
+                        const uint32_t accumulate = (kb > p.kb0 || k > 0) ? 1u : 0u;
+                        if (PAIR) tc_mma_bf16_pair(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accumulate);
+                        else tc_mma_bf16(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accumulate);
+                    }
+                    if (PAIR) tc_commit_pair(&empty[s]); else tc_commit(&empty[s]);
                 }
-                if (ok) tc_commit(&acc_full[buf]);
+                if (ok) { if (PAIR) tc_commit_pair(&acc_full[buf]); else tc_commit(&acc_full[buf]); }
             }
         }
     } else {
         const int q = warp & 3;
         int n = 0;
         bool ok = true;
-        TileWalk walk(g.shared_tiles, n_tiles, nkb);
+        TileWalk walk(g.shared_tiles, n_tiles, nkb, unit, units);
         Piece p;
         const long long shared_steps = (long long)g.shared_tiles * nkb;
-        constexpr size_t TILE_FLOATS = (size_t)BM * BN;
+        constexpr size_t TILE_FLOATS = (size_t)BM * BN;         // of one block's rows of a tile
+        const int blocks_per_unit = PAIR ? 2 : 1;
+        // this warp has read its lanes of the accumulator: hand it back to the MMA warp
+        auto release = [&](int buf) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(cluster_addr(&acc_empty[buf], 0));
+                else mbar_arrive(&acc_empty[buf]);
+            }
+        };
         for (; walk.next(p); n++) {
             const int buf = n & 1;
             int a0, b0;
-            tile_origin<BN>(p.tile, tiles_a, tiles_b, a0, b0);
-            const int i = a0 + q * 32 + lane;
+            tile_origin(p.tile, tiles_a, tiles_b, TILE_ROWS, BN, a0, b0);
+            const int i = a0 + rank * BM + q * 32 + lane;
             if (!mbar_wait(&acc_full[buf], (uint32_t)((n >> 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -502,27 +546,25 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
                     tmem_ld16(taddr + c, r);
                     store_chunk(g, i, b0, c, r, lane);
                 }
-                // this warp has read its lanes of the accumulator: hand it back to the MMA warp
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                release(buf);
                 continue;
             }
-            // A piece of a tile.  The blocks that hold this tile's pieces, by the cut of the steps:
+            // A piece of a tile.  The two units that hold this tile's pieces, by the cut of the steps:
             const long long t0 = (long long)p.tile * nkb;
-            const int blk0 = TileWalk::block_of(t0, shared_steps, gridDim.x);
-            const int blk1 = TileWalk::block_of(t0 + nkb - 1, shared_steps, gridDim.x);
+            const int u0 = TileWalk::unit_of(t0, shared_steps, units);
+            const int other = u0 == unit ? u0 + 1 : u0;
             const int t = q * 32 + lane;
-            // Has the other block brought its piece already?  Then this block adds the tile up and
+            int* ticket = &g.tickets[p.tile * blocks_per_unit + rank];
+            // Has the other unit brought its piece already?  Then this block adds the tile up and
             // its own piece never leaves tensor memory.  Else the piece goes to this block's place
             // in the workspace (thread t keeps 16 columns as four float4, word v of chunk c at
             // [(c / 16 * 4 + v) * 128 + t]), and the ticket says whether the other came meanwhile.
             asm volatile("bar.sync 1, 128;" ::: "memory");      // everyone has read s_last of the piece before
-            if (threadIdx.x == 64) s_last = *reinterpret_cast<volatile int*>(&g.tickets[p.tile]) == blk1 - blk0;
+            if (threadIdx.x == 64) s_last = *reinterpret_cast<volatile int*>(ticket) == 1;
             asm volatile("bar.sync 1, 128;" ::: "memory");
             bool last = s_last != 0;
             if (!last) {
-                float4* mine = reinterpret_cast<float4*>(g.workspace + ((size_t)blockIdx.x * 2 + p.place) * TILE_FLOATS) + t;
+                float4* mine = reinterpret_cast<float4*>(g.workspace + (((size_t)unit * 2 + p.place) * blocks_per_unit + rank) * TILE_FLOATS) + t;
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     float r[16];
@@ -532,20 +574,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
                 }
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (threadIdx.x == 64) s_last = atomicAdd(&g.tickets[p.tile], 1) == blk1 - blk0;
+                if (threadIdx.x == 64) s_last = atomicAdd(ticket, 1) == 1;
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 last = s_last != 0;
             }
             if (last) {
-                if (threadIdx.x == 64) g.tickets[p.tile] = 0;   // ready for the next launch
+                if (threadIdx.x == 64) *ticket = 0;             // ready for the next launch
                 __threadfence();
-                // A part is at least a tile long, so a tile has two pieces at most: this block's and one
-                // other.  Nothing runs beside this at the end of a kernel, so the other piece is fetched
-                // 128 columns at a time, all loads in flight together, before this block's own piece is
+                // Nothing runs beside this at the end of a kernel, so the other piece is fetched 128
+                // columns at a time, all loads in flight together, before this block's own piece is
                 // read back and added (a sum of two, the same whichever block forms it).
-                const int other = blk0 == (int)blockIdx.x ? blk1 : blk0;
-                const int place = TileWalk::part_start(other, shared_steps, gridDim.x) >= t0 ? 0 : 1;   // first piece of its part, or last
-                const float4* ws = reinterpret_cast<const float4*>(g.workspace + ((size_t)other * 2 + place) * TILE_FLOATS) + t;
+                const int place = TileWalk::part_start(other, shared_steps, units) >= t0 ? 0 : 1;   // first piece of its part, or last
+                const float4* ws = reinterpret_cast<const float4*>(g.workspace + (((size_t)other * 2 + place) * blocks_per_unit + rank) * TILE_FLOATS) + t;
                 constexpr int GROUP = 8;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 16 * GROUP) {
@@ -569,17 +609,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap a_map, const __gri
                     }
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            release(buf);
         }
     }
+    // A block of a pair neither leaves nor gives back its tensor memory while the other may
+    // still read its shared memory or arrive on its barriers.
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc(tmem, TMEM_COLS);
+        if (PAIR) tmem_dealloc_pair(tmem, TMEM_COLS); else tmem_dealloc(tmem, TMEM_COLS);
     }
 }
 
@@ -662,27 +703,50 @@ int launch(const CUtensorMap& am, const CUtensorMap& bm, const GemmArgs& g, cuda
 }
 // How many tiles of a many-token product are shared out by contraction steps (TileWalk): with
 // whole rounds of tiles, or less than one round, none; else the last round and the one before it,
-// so that every block's part is at least a tile long.
-int shared_tiles_of(int tiles, int sms) {
-    if (sms <= 0 || tiles < sms || tiles % sms == 0) return 0;
-    return sms + tiles % sms;
+// so that every unit's part is at least a tile long.
+int shared_tiles_of(int tiles, int units) {
+    if (units <= 0 || tiles < units || tiles % units == 0) return 0;
+    return units + tiles % units;
 }
 
-template <int BN>
-int launch_persistent(const CUtensorMap& am, const CUtensorMap& bm, const GemmArgs& g, int sms, cudaStream_t stream) {
-    constexpr int STAGES = persistent_stages<BN>();
-    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
+template <int BN, bool PAIR>
+int launch_walk(const CUtensorMap& am, const CUtensorMap& bm, const GemmArgs& g, int sms, cudaStream_t stream) {
+    constexpr int STAGES = walk_stages<BN, PAIR>();
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + (PAIR ? BN / 2 : BN) * BK * 2) + 1024;
     static bool configured = false;
     if (!configured) {
-        TI_CUDA(cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TI_CUDA(cudaFuncSetAttribute(gemm_tc_walk_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
     int* status = ti_status_ptr();
     TI_REQUIRE(status != nullptr, "linear: no status word");
-    const int tiles = ((g.rows_a + BM - 1) / BM) * ((g.rows_b + BN - 1) / BN);
-    const int blocks = g.shared_tiles > 0 || tiles > sms ? sms : tiles;
-    TI_CUDA(ti_launch_class<5>(gemm_tc_persistent_kernel<BN>, dim3(blocks), dim3(THREADS), smem, stream, am, bm, g, status));
-    TI_CHECK_LAUNCH("linear (tcgen05, persistent)");
+    const int tile_rows = PAIR ? 2 * BM : BM;
+    const int tiles = ((g.rows_a + tile_rows - 1) / tile_rows) * ((g.rows_b + BN - 1) / BN);
+    const int all_units = PAIR ? sms / 2 : sms;
+    const int units = g.shared_tiles > 0 || tiles > all_units ? all_units : tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(PAIR ? 2 * units : units);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (PAIR) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 2;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        n_attr++;
+    }
+    if (ti_pdl_enabled(5)) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        n_attr++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    TI_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_walk_kernel<BN, PAIR>, am, bm, g, status));
+    TI_CHECK_LAUNCH(PAIR ? "linear (tcgen05, two SMs per tile)" : "linear (tcgen05, tile walk)");
     return 0;
 }
 
@@ -707,15 +771,32 @@ int wide_tile(int rows_a, int rows_b, int sms, bool whole_rounds, double* score_
 }
 }  // namespace
 
-// Floats of workspace and tickets (`n_tiles`) ti_linear_tc needs for this shape (0: none), and
-// how it splits.  `sms` blocks fill the device once.
-extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* bn, int* splits, long long* ws_floats,
-                                 int* n_tiles) {
-    const bool sw = M <= 64;
-    const int rows_a = sw ? N : M, rows_b = sw ? M : N;
+// For tests and measurements: 0 lets the plan choose, 1 keeps many-token products on one SM per
+// tile, 2 puts them on two wherever there are enough tiles.
+static int g_pair_mode = 0;
+extern "C" void ti_set_gemm_pair_mode(int mode) { g_pair_mode = mode; }
+
+namespace {
+struct Plan {
+    bool swap;          // few tokens: the weights are the MMA's row operand
+    int bn;             // rows of the other operand per tile
+    int splits;         // of the contraction, over blockIdx.z (the one-tile-per-block kernel)
+    bool walk;          // the many-token kernel
+    bool pair;          // ... on two SMs per tile
+    int shared;         // ... tiles shared out by contraction steps
+    int tiles;
+    long long ws_floats;
+    int tickets;
+};
+
+Plan make_plan(int M, int N, int K, int sms) {
+    Plan p = {};
+    p.swap = M <= 64;
+    const int rows_a = p.swap ? N : M, rows_b = p.swap ? M : N;
+    const int nkb = (K + BK - 1) / BK;
     int b;
     bool share = false;     // many tokens: tiles shared out by contraction steps
-    if (sw) {
+    if (p.swap) {
         b = rows_b <= 16 ? 16 : rows_b <= 32 ? 32 : 64;
         // A matrix with few row tiles is split along the contraction, and the block that adds a
         // tile's partial sums does so in rounds whose number grows with the tile's width.  While
@@ -728,22 +809,37 @@ extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* b
         else if (b == 32 && rows_b > 16 && row_tiles * 4 <= sms) b = 16;
     }
     else if (rows_b >= 256) {
-        // The width that fills whole rounds best.  Where even that leaves more than a tenth of the
-        // device idle (measured at 2,048 tokens: 2,560 weight rows do, 6,144 and 19,456 do not), the
-        // widest useful tile instead, with a part of the tiles shared out by contraction steps.
-        double score;
-        b = wide_tile(rows_a, rows_b, sms, true, &score);
-        if (score < 0.89) {
-            const int wide = wide_tile(rows_a, rows_b, sms, false);
-            if (((rows_a + BM - 1) / BM) * ((rows_b + wide - 1) / wide) >= sms) { b = wide; share = true; }
+        // Two SMs per tile of 256 x 256 where that wastes little at the edges and there is at least
+        // a tile per pair; what the rounds leave over is shared out by contraction steps.
+        const int pairs = sms / 2;
+        const long long tiles_a2 = (rows_a + 2 * BM - 1) / (2 * BM), tiles_b2 = (rows_b + 255) / 256;
+        const double useful = ((double)rows_a / (tiles_a2 * 2 * BM)) * ((double)rows_b / (tiles_b2 * 256));
+        if (g_pair_mode != 1 && pairs > 0 && tiles_a2 * tiles_b2 >= pairs && (useful >= 0.93 || g_pair_mode == 2)) {
+            p.pair = true;
+            b = 256;
+            // Sharing costs about as much as a dozen steps of the contraction (measured at 2,048
+            // tokens: 6,144 weight rows x 2,560 gain nothing from it, 19,456 x 2,560 gain 8 %).
+            const long long tiles2 = tiles_a2 * tiles_b2;
+            const long long idle_steps = ((tiles2 + pairs - 1) / pairs) * nkb - tiles2 * nkb / pairs;
+            share = idle_steps > 20;
+        } else {
+            // The width that fills whole rounds best.  Where even that leaves more than a tenth of the
+            // device idle (measured at 2,048 tokens: 2,560 weight rows do, 6,144 and 19,456 do not), the
+            // widest useful tile instead, with a part of the tiles shared out by contraction steps.
+            double score;
+            b = wide_tile(rows_a, rows_b, sms, true, &score);
+            if (score < 0.89) {
+                const int wide = wide_tile(rows_a, rows_b, sms, false);
+                if (((rows_a + BM - 1) / BM) * ((rows_b + wide - 1) / wide) >= sms) { b = wide; share = true; }
+            }
         }
     }
     else b = rows_b > 64 ? 128 : rows_b > 32 ? 64 : rows_b > 16 ? 32 : 16;
-    const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + b - 1) / b);
-    const int nkb = (K + BK - 1) / BK;
+    const int tile_rows = p.pair ? 2 * BM : BM;
+    const int tiles = ((rows_a + tile_rows - 1) / tile_rows) * ((rows_b + b - 1) / b);
     int sp = 1;
     const int want = sms;        // measured: between 1.0 and 1.5 blocks per SM is best for all four decode shapes
-    if (tiles < want) {
+    if (tiles < want && !p.pair) {
         sp = (want + tiles / 2) / tiles;
         if (sp < 1) sp = 1;
         const int max_sp = nkb / 4 > 0 ? nkb / 4 : 1;       // at least four 64-wide blocks per split
@@ -753,14 +849,26 @@ extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* b
         const int per = (nkb + sp - 1) / sp;
         sp = (nkb + per - 1) / per;
     }
-    *swap = sw; *bn = b; *splits = sp; *n_tiles = tiles;
-    *ws_floats = sp > 1 ? (long long)sp * tiles * BM * b : 0;
-    if (!sw && sp == 1 && b >= 128) {
-        // the many-token kernel: two places per block for the pieces of shared tiles, a ticket per shared tile
-        const int shared = share ? shared_tiles_of(tiles, sms) : 0;
-        *n_tiles = shared;
-        *ws_floats = shared ? (long long)sms * 2 * BM * b : 0;
+    p.bn = b; p.splits = sp; p.tiles = tiles;
+    p.ws_floats = sp > 1 ? (long long)sp * tiles * BM * b : 0;
+    p.tickets = sp > 1 ? tiles : 0;
+    p.walk = !p.swap && sp == 1 && b >= 128;
+    if (p.walk) {
+        // two places per block for the pieces of shared tiles, a ticket per shared tile and block of a unit
+        p.shared = share ? shared_tiles_of(tiles, p.pair ? sms / 2 : sms) : 0;
+        p.ws_floats = p.shared ? (long long)sms * 2 * BM * b : 0;
+        p.tickets = p.shared * (p.pair ? 2 : 1);
     }
+    return p;
+}
+}  // namespace
+
+// Floats of workspace and tickets (`n_tiles`) ti_linear_tc needs for this shape (0: none), and
+// how it splits.  `sms` blocks fill the device once.
+extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* bn, int* splits, long long* ws_floats,
+                                 int* n_tiles) {
+    const Plan p = make_plan(M, N, K, sms);
+    *swap = p.swap; *bn = p.bn; *splits = p.splits; *ws_floats = p.ws_floats; *n_tiles = p.tickets;
     return 0;
 }
 
@@ -778,32 +886,31 @@ extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int 
     TI_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "linear (tcgen05): K and the row strides must be multiples of 8 elements");
     TI_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
                "linear (tcgen05): operands must be 16-byte aligned");
-    int swap, bn, splits, tiles;
-    long long ws;
-    ti_linear_tc_plan(M, N, K, sms, &swap, &bn, &splits, &ws, &tiles);
+    const Plan p = make_plan(M, N, K, sms);
+    const int swap = p.swap, bn = p.bn, splits = p.splits;
     TI_REQUIRE(splits == 1 || workspace, "linear (tcgen05): a split contraction needs a workspace");
     GemmArgs g;
     g.rows_a = swap ? N : M; g.rows_b = swap ? M : N; g.K = K;
     g.out = out; g.ld_out = ldo; g.out_f32 = out_f32; g.transposed = swap;
     g.splits = splits; g.workspace = workspace; g.tickets = tickets;
     g.gated = gated;
-    g.shared_tiles = 0;
+    g.shared_tiles = p.walk && workspace && tickets ? p.shared : 0;      // without them: whole tiles only
     TI_REQUIRE(!gated || (N % 2 == 0 && !out_f32), "linear (tcgen05): a gated product needs an even number of weight rows and a bfloat16 result");
     CUtensorMap am, bm;
     if (int rc = operand_map(swap ? w : x, g.rows_a, K, swap ? ldw : ldx, BM, &am)) return rc;
-    if (int rc = operand_map(swap ? x : w, g.rows_b, K, swap ? ldx : ldw, bn, &bm)) return rc;
-    if (!swap && splits == 1 && bn >= 128) {
-        if (workspace && tickets) g.shared_tiles = tiles;       // as planned: 0 where whole tiles fill the rounds
+    if (int rc = operand_map(swap ? x : w, g.rows_b, K, swap ? ldx : ldw, p.pair ? bn / 2 : bn, &bm)) return rc;
+    if (p.pair) return launch_walk<256, true>(am, bm, g, sms, stream);
+    if (p.walk) {
         switch (bn) {
-            case 128: return launch_persistent<128>(am, bm, g, sms, stream);
-            case 144: return launch_persistent<144>(am, bm, g, sms, stream);
-            case 160: return launch_persistent<160>(am, bm, g, sms, stream);
-            case 176: return launch_persistent<176>(am, bm, g, sms, stream);
-            case 192: return launch_persistent<192>(am, bm, g, sms, stream);
-            case 208: return launch_persistent<208>(am, bm, g, sms, stream);
-            case 224: return launch_persistent<224>(am, bm, g, sms, stream);
-            case 240: return launch_persistent<240>(am, bm, g, sms, stream);
-            default: return launch_persistent<256>(am, bm, g, sms, stream);
+            case 128: return launch_walk<128, false>(am, bm, g, sms, stream);
+            case 144: return launch_walk<144, false>(am, bm, g, sms, stream);
+            case 160: return launch_walk<160, false>(am, bm, g, sms, stream);
+            case 176: return launch_walk<176, false>(am, bm, g, sms, stream);
+            case 192: return launch_walk<192, false>(am, bm, g, sms, stream);
+            case 208: return launch_walk<208, false>(am, bm, g, sms, stream);
+            case 224: return launch_walk<224, false>(am, bm, g, sms, stream);
+            case 240: return launch_walk<240, false>(am, bm, g, sms, stream);
+            default: return launch_walk<256, false>(am, bm, g, sms, stream);
         }
     }
     switch (bn) {
