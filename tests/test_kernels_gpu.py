@@ -255,6 +255,46 @@ def test_linear_few_tokens(K, monkeypatch, M, N, K_):
         assert gated.shape == (M, N // 2)
 
 
+@pytest.mark.parametrize("norm_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("N,K_,gated,with_delta", [(6144, 2560, False, True), (19456, 2560, True, True), (2560, 5120, False, False),
+                                                   (333, 200, False, True), (70, 1032, True, True), (51200, 5120, True, True)])
+def test_linear_with_the_norm_inside(K, N, K_, gated, with_delta, norm_dtype):
+    """One token's product that forms its own input, rmsnorm(h + delta) * g, against the norm kernel
+    followed by the product: the same bits where the norm kernel sums in the same order (bfloat16
+    weights, rows longer than 1,024), else within a rounding of the input; and the sum it leaves."""
+    g = torch.Generator(device="cuda").manual_seed(11)
+    h = torch.randn(1, K_, generator=g, device="cuda").to(torch.bfloat16)
+    delta = (torch.randn(1, K_, generator=g, device="cuda") * 0.5).to(torch.bfloat16) if with_delta else None
+    gw = (1 + 0.1 * torch.randn(K_, generator=g, device="cuda")).to(norm_dtype)
+    w = (torch.randn(N, K_, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
+    eps = 1e-5
+    h_sum = (h.float() + delta.float()).to(torch.bfloat16) if with_delta else h.clone()
+    x = K.rmsnorm(h_sum, gw, eps)
+    want = K.linear_swiglu(x, w) if gated else K.linear(x, w)
+    pending = K.pending_norm(h.clone(), delta, gw, eps)
+    assert pending is not None
+    got = K.linear_swiglu(pending, w) if gated else K.linear(pending, w)
+    K.check_status()
+    assert torch.equal(pending.hidden(), h_sum)
+    if norm_dtype == torch.bfloat16 and K_ > 1024:
+        assert torch.equal(got, want)
+    else:
+        torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    # used a second time, the input is formed by the norm kernel from the sum that exists now
+    again = K.linear(pending, w[: N // 2])
+    torch.testing.assert_close(again.float(), K.linear(x, w[: N // 2]).float(), rtol=2e-2, atol=2e-2)
+
+
+def test_pending_norm_is_refused_where_no_product_can_use_it(K):
+    h = torch.zeros(2, 64, dtype=torch.bfloat16, device="cuda")
+    w = torch.ones(64, dtype=torch.bfloat16, device="cuda")
+    assert K.pending_norm(h, None, w, 1e-6) is None                       # two tokens
+    assert K.pending_norm(h[:1].float(), None, w.float(), 1e-6) is None   # float32
+    assert K.pending_norm(h[:1, :60], None, w[:60], 1e-6) is None         # rows of 60 elements: no multiple of 8
+    p = K.pending_norm(h[:1], None, w, 1e-6)
+    assert p is not None and torch.equal(p.hidden(), h[:1])               # nothing to add: the hidden state is h
+
+
 @pytest.mark.parametrize("M", [1, 3, 5, 8, 9, 13, 16])
 @pytest.mark.parametrize("N,K_", [(6144, 2560), (2560, 9728), (2560, 4096), (19456, 2560), (7, 8), (333, 200), (2, 4104),
                                   (50000, 72), (100, 1024), (30, 20000)])

@@ -113,6 +113,82 @@ def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: floa
     return out
 
 
+class PendingNorm:
+    """An input that is not formed yet: rmsnorm(h + delta) * weight (delta may be None).
+
+    ``linear`` and ``linear_swiglu`` take it in place of a tensor.  For one bfloat16 token the
+    product's kernel forms the input itself, in every block, and the step has a kernel less;
+    otherwise ``tensor()`` runs the norm kernel.  Either way the sum h + delta exists afterwards:
+    ``hidden()`` returns it (h itself, updated in place, or a new tensor).  Made by
+    ``pending_norm``, which says first whether the product can use it.
+    """
+
+    def __init__(self, h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float):
+        self.h, self.delta, self.weight, self.eps = h, delta, weight, float(eps)
+        self._x: Optional[torch.Tensor] = None
+        self._hidden: Optional[torch.Tensor] = None
+
+    shape = property(lambda self: self.h.shape)
+    dtype = property(lambda self: self.h.dtype)
+    device = property(lambda self: self.h.device)
+
+    def tensor(self) -> torch.Tensor:
+        """The normalised input as a tensor (the norm kernel runs once)."""
+        if self._x is None:
+            if self._hidden is not None:            # a product has formed the sum already
+                self._x = rmsnorm(self._hidden, self.weight, self.eps)
+            elif self.delta is None:
+                self._x = rmsnorm(self.h, self.weight, self.eps)
+                self._hidden = self.h
+            else:
+                self._x = add_rmsnorm(self.h, self.delta, self.weight, self.eps)
+                self._hidden = self.h
+        return self._x
+
+    def hidden(self) -> torch.Tensor:
+        """h + delta, rounded once."""
+        if self._hidden is None:
+            self.tensor()
+        return self._hidden
+
+
+def pending_norm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float) -> Optional[PendingNorm]:
+    """A PendingNorm if a product can form this input itself (one bfloat16 token on a CUDA device,
+    dense, rows of a multiple of 8 up to 24,576 elements), else None."""
+    from . import gemm
+    if not (h.is_cuda and h.dtype == torch.bfloat16 and h.dim() == 2 and h.is_contiguous() and weight.is_contiguous()):
+        return None
+    M, H = h.shape
+    if M < 1 or M > gemm.GEMV_MAX_TOKENS or M != 1 or H % 8 or H > 24576 or weight.shape != (H,):
+        return None
+    if weight.dtype not in (torch.bfloat16, torch.float32):
+        return None
+    if delta is not None and (delta.shape != h.shape or delta.dtype != h.dtype or not delta.is_contiguous()):
+        return None
+    return PendingNorm(h, delta, weight, eps)
+
+
+def _linear_pending(x: PendingNorm, w: torch.Tensor, gated: bool) -> Optional[torch.Tensor]:
+    """The product with the norm inside, or None if this weight does not allow it."""
+    from . import gemm
+    h = x.h
+    H = h.shape[1]
+    if x._x is not None or x._hidden is not None or w.dtype != torch.bfloat16 or w.dim() != 2 or w.shape[1] != H:
+        return None
+    ldw = w.stride(0)
+    if w.stride(1) != 1 or ldw % 8 or w.data_ptr() % 16 or h.shape[0] > gemm.GEMV_MAX_TOKENS:
+        return None
+    if any(t is not None and t.data_ptr() % 16 for t in (h, x.delta, x.weight)):
+        return None
+    N = w.shape[0]
+    out = torch.empty((1, N // 2 if gated else N), dtype=h.dtype, device=h.device)
+    h_out = torch.empty_like(h) if x.delta is not None else None
+    _call(library().ti_linear_gemv_normed, _ptr(h), _ptr(x.delta), _ptr(x.weight), 1 if x.weight.dtype == torch.float32 else 0,
+          x.eps, _ptr(h_out), _ptr(w), _ptr(out), N, H, ldw, 1 if gated else 0, gemm.sm_count(h.device), _stream())
+    x._hidden = h_out if h_out is not None else h
+    return out
+
+
 def gather_add(h: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
     """out[r] = h[rows[r]] + delta[rows[r]] (delta may be None)."""
     _need_cuda(h, delta, rows, what="gather_add")
@@ -133,7 +209,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     ask for float32 results from bfloat16 operands (the head).  ``after_attention``: a hint
     that x comes (through at most a tiny kernel) from an attention kernel with large shared
     memory; the few-token kernels then start only when it has finished (a matter of speed, not
-    of results: csrc/gemm_skinny.cu)."""
+    of results: csrc/gemm_skinny.cu).  x may be a PendingNorm."""
+    if isinstance(x, PendingNorm):
+        out = _linear_pending(x, w, gated=False) if out_dtype in (None, x.dtype) else None
+        if out is not None:
+            return out
+        x = x.tensor()
     _need_cuda(x, w, what="linear")
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
         raise KernelError(f"linear: shapes {tuple(x.shape)} and {tuple(w.shape)} do not contract")
@@ -170,7 +251,12 @@ def swiglu(gu: torch.Tensor, pairs: bool = False) -> torch.Tensor:
 def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor) -> torch.Tensor:
     """x[M, K] times w_pairs[2*I, K] (rows gate_0, up_0, gate_1, up_1, ...) followed by the
     gated activation -> [M, I].  The activation runs in the product's epilogue where the
-    tensor-core kernel takes the shape, else as a kernel of its own."""
+    tensor-core kernel takes the shape, else as a kernel of its own.  x may be a PendingNorm."""
+    if isinstance(x, PendingNorm):
+        out = _linear_pending(x, w_pairs, gated=True) if w_pairs.dim() == 2 and w_pairs.shape[0] % 2 == 0 else None
+        if out is not None:
+            return out
+        x = x.tensor()
     _need_cuda(x, w_pairs, what="linear_swiglu")
     if x.dim() != 2 or w_pairs.dim() != 2 or x.shape[1] != w_pairs.shape[1] or w_pairs.shape[0] % 2:
         raise KernelError(f"linear_swiglu: shapes {tuple(x.shape)} and {tuple(w_pairs.shape)} do not fit")

@@ -36,6 +36,7 @@ def _declare(lib) -> None:
         "ti_linear_tc": [P, P, P, I, I, I, L, L, L, I, I, I, P, P, P],
         "ti_linear_gemv": [P, P, P, I, I, I, L, L, L, I, I, I, I, P],
         "ti_linear_skinny": [P, P, P, I, I, I, L, L, L, I, I, I, I, P],
+        "ti_linear_gemv_normed": [P, P, P, I, F, P, P, P, I, I, L, I, I, P],
         "ti_linear_tc_plan": [I, I, I, I, P, P, P, P, P],
         "ti_read_status": [P],
         "ti_argmax": [P, L, I, I, I, P, P, P, P],

@@ -97,6 +97,8 @@ class GQAAttention(Mixer):
             if self.own_kv:
                 self.k_norm_w = tensors.pop(self.names["k_norm"])
 
+    takes_pending_norm = True       # x goes into K.linear first, and nowhere else
+
     def memory_request(self):
         if not self.own_kv:
             return None

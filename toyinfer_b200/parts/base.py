@@ -112,6 +112,11 @@ class Norm(Part):
     def add_forward(self, h: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
         raise NotImplementedError
 
+    def add_pending(self, h: torch.Tensor, delta: Optional[torch.Tensor]):
+        """As add_forward, but may leave the work to the reader's first product: a
+        kernels.PendingNorm instead of a tensor (only for readers that say takes_pending_norm)."""
+        return self.add_forward(h, delta)
+
 
 class PositionEncoding(Part):
     def rotary_tables(self) -> Optional[Tuple[torch.Tensor, torch.Tensor, int]]:
@@ -122,6 +127,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    takes_pending_norm = False      # forward() may be given a kernels.PendingNorm, used by K.linear first
+
     def memory_request(self):
         return None
 
@@ -130,6 +137,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_pending_norm = False      # as for Mixer
+
     def forward(self, x, batch) -> torch.Tensor:
         raise NotImplementedError
 

@@ -12,6 +12,7 @@ from typing import Dict, Optional
 
 import torch
 
+from .. import kernels as K
 from .base import Block, BuildContext, ParamSpec, PartSpec, build_part, register_part
 
 
@@ -38,10 +39,16 @@ class PreNormBlock(Block):
             c.bind(tensors)
 
     def forward(self, h, delta, batch, mem, shared):
-        x = self.norm_in.add_forward(h, delta)           # h += delta (if any); x = norm(h)
+        # h += delta (if any); x = norm(h) -- at once, or inside the reader's first product
+        x = self.norm_in.add_pending(h, delta) if self.mixer.takes_pending_norm else self.norm_in.add_forward(h, delta)
         a = self.mixer.forward(x, batch, mem, shared)
-        x = self.norm_post.add_forward(h, a)             # h += a; x = norm(h)
+        if isinstance(x, K.PendingNorm):
+            h = x.hidden()
+        # h += a; x = norm(h)
+        x = self.norm_post.add_pending(h, a) if self.feed_forward.takes_pending_norm else self.norm_post.add_forward(h, a)
         m = self.feed_forward.forward(x, batch)
+        if isinstance(x, K.PendingNorm):
+            h = x.hidden()
         return h, m
 
 

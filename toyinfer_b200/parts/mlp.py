@@ -41,6 +41,8 @@ class SwiGLU(FeedForward):
         del g, u
         self.w_down = tensors.pop(self.names["down"]).contiguous()
 
+    takes_pending_norm = True       # x goes into K.linear_swiglu, and nowhere else
+
     def forward(self, x, batch) -> torch.Tensor:
         z = K.linear_swiglu(x, self.w_gate_up)    # [M, inter]
         return K.linear(z, self.w_down)

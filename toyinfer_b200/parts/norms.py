@@ -38,5 +38,9 @@ class RMSNorm(Norm):
             return K.rmsnorm(h, self.weight, self.eps)
         return K.add_rmsnorm(h, delta, self.weight, self.eps)
 
+    def add_pending(self, h: torch.Tensor, delta: Optional[torch.Tensor]):
+        pending = K.pending_norm(h, delta, self.weight, self.eps)
+        return pending if pending is not None else self.add_forward(h, delta)
+
 
 register_part("norm", "rmsnorm", RMSNorm)
