@@ -38,6 +38,8 @@ def gather_add(h, delta, rows):
 
 
 def linear(x, w, out_dtype=None, after_attention=False):
+    if isinstance(x, K.PendingNorm):
+        x = x.tensor()
     return (x.float() @ w.float().T).to(out_dtype or x.dtype)
 
 
@@ -49,6 +51,18 @@ def swiglu(gu, pairs=False):
 
 def linear_swiglu(x, w_pairs):
     return swiglu(linear(x, w_pairs), pairs=True)
+
+
+class PendingOutOfPlace(K.PendingNorm):
+    """A pending norm whose sum lands in a new tensor, as after the product that forms its own
+    input; h itself stays as it was."""
+
+    def tensor(self):
+        if self._x is None:
+            summed = self.h if self.delta is None else (self.h.float() + self.delta.float()).to(self.h.dtype)
+            self._hidden = summed.clone()
+            self._x = rmsnorm(self._hidden, self.weight, self.eps)
+        return self._x
 
 
 def _norm_heads(x, w, eps):

@@ -100,3 +100,35 @@ def test_a_layers_keys_and_values_are_let_go_after_their_last_user(cpu_engine, m
     eng.step([(slot, prompts_for("B", [9])[0])], None)
     assert len(seen) == TINY["B"]["num_hidden_layers"] and all(not d for d in seen)
     eng.end_sequence(slot)
+
+
+def test_a_norm_left_to_the_readers_product_changes_no_result(cpu_engine, model_folders, monkeypatch):
+    """Single-token steps with the norm handed on as a kernels.PendingNorm (the sum h + delta then
+    lands in a new tensor, and the block must go on with that one) give the logits of plain steps."""
+    import toyinfer_b200.kernels as K
+    name = "B"
+    ids = prompts_for(name, [40], seed=3)[0]
+
+    def run(eng):
+        slot = eng.new_sequence()
+        got = [eng.step([(slot, ids[:8])], [[7]])]
+        for t in range(8, len(ids)):
+            got.append(eng.step([(slot, [ids[t]])], [[0]]).clone())
+        eng.end_sequence(slot)
+        return torch.cat(got)
+
+    plain_steps = run(cpu_engine(name))
+    made = []
+
+    def pending_norm(h, delta, weight, eps):
+        if h.shape[0] != 1:
+            return None
+        made.append(1)
+        return cpu_kernels.PendingOutOfPlace(h, delta, weight, eps)
+
+    monkeypatch.setattr(K, "pending_norm", pending_norm)
+    pending_steps = run(cpu_engine(name))
+    assert len(made) == 2 * TINY[name]["num_hidden_layers"] * (len(ids) - 8)      # both norms of every layer, every single-token step
+    assert torch.equal(pending_steps, plain_steps)
+    want = _plain_logits(model_folders[name], ids)
+    torch.testing.assert_close(pending_steps, want[7:], rtol=1e-4, atol=1e-5)
