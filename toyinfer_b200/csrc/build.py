@@ -112,8 +112,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     th = threading.Thread(target=ticker, daemon=True)
     th.start()
     try:
-        with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
-            futs = [pool.submit(_compile_one, nvcc, s, o, verbose) for s, o in zip(srcs, objs)]
+        # the longest compiles start first; the text a file pulls in from this folder stands for its time
+        order = sorted(range(len(srcs)), key=lambda i: -_text_size(srcs[i]))
+        with ThreadPoolExecutor(max_workers=min(max(4, os.cpu_count() or 4), len(srcs))) as pool:
+            futs = [pool.submit(_compile_one, nvcc, srcs[i], objs[i], verbose) for i in order]
             for f in futs:
                 f.result()
         tmp = lib + f".tmp{os.getpid()}"
@@ -128,6 +130,22 @@ def build(force: bool = False, verbose: bool = False) -> str:
         done.set()
     _say(f"built {LIB_NAME} in {time.time() - t0:.0f} s")
     return lib
+
+
+def _text_size(path: str, seen=None) -> int:
+    """Bytes of a source file and of the headers of this folder that it includes."""
+    seen = set() if seen is None else seen
+    if path in seen or not os.path.isfile(path):
+        return 0
+    seen.add(path)
+    with open(path, errors="replace") as f:
+        text = f.read()
+    total = len(text)
+    for line in text.splitlines():
+        line = line.strip()
+        if line.startswith('#include "'):
+            total += _text_size(os.path.join(HERE, line.split('"')[1]), seen)
+    return total
 
 
 def ensure_built() -> str:
