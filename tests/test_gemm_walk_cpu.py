@@ -1,0 +1,89 @@
+"""The order in which the many-token matrix product deals out its tiles, checked on the host: the
+library's own walk (the code the kernels run, compiled for the host too) is traced for many shapes
+and the properties the kernels rely on are checked.  Needs nvcc to build the library, no GPU."""
+from __future__ import annotations
+
+import ctypes
+import random
+import shutil
+
+import pytest
+
+pytestmark = pytest.mark.skipif(shutil.which("nvcc") is None, reason="the kernel library cannot be built without nvcc")
+
+
+def _trace(M, N, K, sms):
+    from toyinfer_b200.kernels.lib import library
+    lib = library()
+    cap = 1 << 16
+    rows = (ctypes.c_int * (cap * 8))()
+    units, tiles, pair = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    fn = lib.ti_gemm_walk_trace
+    fn.restype = ctypes.c_int
+    n = fn(M, N, K, sms, rows, cap, ctypes.byref(units), ctypes.byref(tiles), ctypes.byref(pair))
+    assert n <= cap
+    out = [tuple(rows[i * 8:(i + 1) * 8]) for i in range(n)]
+    return out, units.value, tiles.value, bool(pair.value)
+
+
+def _check(M, N, K, sms):
+    rows, units, tiles, pair = _trace(M, N, K, sms)
+    if not rows:
+        return None
+    nkb = (K + 63) // 64
+    covered = {}
+    per_tile = {}
+    per_unit = {}
+    for unit, tile, kb0, kb1, whole, place, other, other_place in rows:
+        assert 0 <= unit < units and 0 <= tile < tiles and 0 <= kb0 < kb1 <= nkb
+        assert bool(whole) == (kb0 == 0 and kb1 == nkb)
+        for kb in range(kb0, kb1):
+            assert (tile, kb) not in covered, "a step of the contraction is done twice"
+            covered[(tile, kb)] = unit
+        per_tile.setdefault(tile, []).append((unit, kb0, kb1, place, other, other_place))
+        per_unit.setdefault(unit, []).append((tile, kb0, kb1, whole, place))
+    assert len(covered) == tiles * nkb, "a step of the contraction is left out"
+    shared = 0
+    for tile, pieces in per_tile.items():
+        if len(pieces) == 1:
+            continue
+        shared += 1
+        assert len(pieces) == 2, "a tile in more than two pieces"
+        (ua, a0, a1, pa, oa, opa), (ub, b0, b1, pb, ob, opb) = sorted(pieces, key=lambda p: p[1])
+        assert a0 == 0 and a1 == b0 and b1 == nkb                # the pieces meet
+        assert ub == ua + 1                                      # neighbours in the cut
+        assert (oa, opa) == (ub, pb) and (ob, opb) == (ua, pa)   # each finds the other's piece where it was put
+    for unit, pieces in per_unit.items():
+        places = [(p[4]) for p in pieces if not p[3]]
+        assert len(places) <= 2 and len(set(places)) == len(places), "two pieces of a unit in one place"
+    # work is even: no unit has more than a step over its share of the shared tiles, plus whole rounds
+    steps = [sum(k1 - k0 for _, k0, k1, _, _ in per_unit.get(u, [])) for u in range(units)]
+    assert max(steps) - min(steps) <= nkb
+    return shared, pair
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 2560, 4096), (2048, 2560, 9728), (2048, 6144, 2560), (2048, 19456, 2560),
+                                   (1300, 3600, 264), (16384, 19456, 2560), (8192, 12288, 4096), (512, 19456, 264),
+                                   (1100, 3000, 328), (777, 3000, 328), (2048, 151936, 2560), (4741, 520, 264)])
+def test_every_step_once_and_pieces_meet(M, N, K):
+    _check(M, N, K, 148)
+
+
+def test_the_layer_shapes_with_2560_columns_are_shared_out():
+    shared, pair = _check(2048, 2560, 4096, 148)
+    assert pair and shared > 0
+    shared, pair = _check(1300, 3600, 264, 148)
+    assert not pair and shared > 0
+
+
+def test_random_shapes_and_device_sizes():
+    rng = random.Random(7)
+    walked = 0
+    for _ in range(300):
+        sms = rng.choice([148, 132, 108, 64, 37, 2, 1])
+        M = rng.choice([65, 129, 300, 512, 640, 1000, 2048, 3000, 5000, 9000])
+        N = rng.choice([256, 520, 1000, 2560, 3600, 6144, 12288, 19456])
+        K = rng.choice([64, 72, 264, 1000, 2560, 4096, 9728])
+        if _check(M, N, K, sms) is not None:
+            walked += 1
+    assert walked > 100

@@ -23,6 +23,7 @@
 // Contraction and rounding are those of the reference's projections (src/decode.cu:202-236,
 // src/prefill.cu:124-161): bfloat16 operands, float32 accumulation, one rounding of the result.
 #include "gemm_tcgen05.cuh"
+#include "gemm_tile_walk.cuh"
 
 #include <map>
 #include <mutex>
@@ -220,4 +221,37 @@ extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int 
     if (p.pair) return launch_walk_pair(bn, am, bm, g, sms, stream);
     if (p.walk) return launch_walk_single(bn, am, bm, g, sms, stream);
     return launch_tile(bn, am, bm, g, stream);
+}
+
+// For tests: what every unit of a many-token product of this shape does, as the kernel will walk
+// it.  Rows of 8 ints: unit, tile, first step, end step, whole tile (0/1), place of the piece, and
+// for a piece of a shared tile the unit and place of the other piece as the adding block works
+// them out (else -1).  Returns the number of rows (at most max_rows are written); *units_out and
+// *tiles_out receive the number of units and tiles, *pair_out whether two SMs take a tile.
+extern "C" int ti_gemm_walk_trace(int M, int N, int K, int sms, int* rows, int max_rows, int* units_out, int* tiles_out,
+                                  int* pair_out) {
+    const Plan p = make_plan(M, N, K, sms);
+    *pair_out = p.pair ? 1 : 0;
+    *tiles_out = p.tiles;
+    *units_out = 0;
+    if (!p.walk) return 0;
+    const int all_units = p.pair ? sms / 2 : sms;
+    const int units = p.shared > 0 || p.tiles > all_units ? all_units : p.tiles;
+    const int nkb = (K + BK - 1) / BK;
+    *units_out = units;
+    int n = 0;
+    for (int u = 0; u < units; u++) {
+        TileWalk walk(p.shared, p.tiles, nkb, u, units);
+        Piece piece;
+        while (walk.next(piece)) {
+            if (n < max_rows) {
+                int* r = rows + (size_t)n * 8;
+                r[0] = u; r[1] = piece.tile; r[2] = piece.kb0; r[3] = piece.kb1; r[4] = piece.whole ? 1 : 0; r[5] = piece.place;
+                r[6] = r[7] = -1;
+                if (!piece.whole) TileWalk::other_piece(piece.tile, nkb, u, (long long)p.shared * nkb, units, r[6], r[7]);
+            }
+            n++;
+        }
+    }
+    return n;
 }

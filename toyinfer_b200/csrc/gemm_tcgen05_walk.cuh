@@ -3,6 +3,7 @@
 #pragma once
 
 #include "gemm_tcgen05.cuh"
+#include "gemm_tile_walk.cuh"
 
 namespace tigemm {
 namespace {
@@ -43,60 +44,6 @@ __device__ __forceinline__ void tile_origin(int tile, int tiles_a, int tiles_b, 
     a0 = (first + within % span) * tile_rows;
     b0 = (within / span) * bn;
 }
-
-// What a unit does, in order.  The tiles seldom fill whole rounds of units (2,048 x 2,560
-// outputs are 160 tiles of 128 x 256 for 148 SMs: two rounds, the second nearly empty).  So the
-// first `shared` tiles, between one and two rounds' worth, are not dealt out tile by tile but as
-// one row of shared * nkb contraction steps cut into equal parts, one per unit: a unit finishes
-// the tile its part starts in, takes whole tiles, and begins the tile its part ends in.  A part
-// is at least a tile long, so a tile has two pieces at most.  Pieces go to a float32 workspace
-// (two places per block: the piece at the start of its part and the one at its end), and the
-// block that brings a tile's second piece (a ticket per tile and block of the unit) adds the two
-// and stores the tile.  The remaining tiles follow in whole rounds.
-struct Piece {
-    int tile, kb0, kb1;
-    bool whole;     // the whole contraction: stored straight from tensor memory
-    int place;      // else: which of the block's two places in the workspace takes it
-};
-struct TileWalk {
-    int nkb, n_tiles, next_whole, stride;
-    long long at, end;
-    bool first;
-    __device__ TileWalk(int shared, int n_tiles_, int nkb_, int unit, int units) : nkb(nkb_), n_tiles(n_tiles_), first(true) {
-        const long long steps = (long long)shared * nkb_;
-        at = part_start(unit, steps, units);
-        end = part_start(unit + 1, steps, units);
-        next_whole = shared + unit;
-        stride = units;
-    }
-    __device__ static long long part_start(int unit, long long steps, int units) { return (long long)unit * steps / units; }
-    __device__ bool next(Piece& p) {
-        if (at < end) {
-            p.tile = (int)(at / nkb);
-            p.kb0 = (int)(at - (long long)p.tile * nkb);
-            const int len = (int)min((long long)(nkb - p.kb0), end - at);
-            p.kb1 = p.kb0 + len;
-            p.whole = len == nkb;
-            p.place = first ? 0 : 1;
-            first = false;
-            at += len;
-            return true;
-        }
-        if (next_whole < n_tiles) {
-            p.tile = next_whole; p.kb0 = 0; p.kb1 = nkb; p.whole = true; p.place = 0;
-            next_whole += stride;
-            return true;
-        }
-        return false;
-    }
-    // the unit whose part holds contraction step `s` of the shared tiles
-    __device__ static int unit_of(long long s, long long steps, int units) {
-        int u = (int)(s * units / steps);
-        while (u + 1 < units && part_start(u + 1, steps, units) <= s) u++;
-        while (u > 0 && part_start(u, steps, units) > s) u--;
-        return u;
-    }
-};
 
 template <int BN, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -246,9 +193,8 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
                 continue;
             }
             // A piece of a tile.  The two units that hold this tile's pieces, by the cut of the steps:
-            const long long t0 = (long long)p.tile * nkb;
-            const int u0 = TileWalk::unit_of(t0, shared_steps, units);
-            const int other = u0 == unit ? u0 + 1 : u0;
+            int other, other_place;
+            TileWalk::other_piece(p.tile, nkb, unit, shared_steps, units, other, other_place);
             const int t = q * 32 + lane;
             int* ticket = &g.tickets[p.tile * blocks_per_unit + rank];
             // Has the other unit brought its piece already?  Then this block adds the tile up and
@@ -280,8 +226,7 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
                 // Nothing runs beside this at the end of a kernel, so the other piece is fetched 128
                 // columns at a time, all loads in flight together, before this block's own piece is
                 // read back and added (a sum of two, the same whichever block forms it).
-                const int place = TileWalk::part_start(other, shared_steps, units) >= t0 ? 0 : 1;   // first piece of its part, or last
-                const float4* ws = reinterpret_cast<const float4*>(g.workspace + (((size_t)other * 2 + place) * blocks_per_unit + rank) * TILE_FLOATS) + t;
+                const float4* ws = reinterpret_cast<const float4*>(g.workspace + (((size_t)other * 2 + other_place) * blocks_per_unit + rank) * TILE_FLOATS) + t;
                 constexpr int GROUP = 8;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 16 * GROUP) {
