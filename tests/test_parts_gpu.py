@@ -106,6 +106,47 @@ def test_feed_forward_part(dtype):
     torch.testing.assert_close(got, want, **tol(dtype))
 
 
+@pytest.mark.parametrize("hidden,inter", [(96, 200), (2560, 1000)])
+def test_norm_left_to_the_feed_forwards_product(hidden, inter):
+    """One bfloat16 token: the norm part hands a pending norm on, the feed-forward's first product
+    forms the input itself, and the sum h + delta comes back as the new hidden state; against the
+    plain implementation, and against the same parts with the norm kernel (same bits for rows longer
+    than 1,024, where both sum in the same order)."""
+    import toyinfer_b200.kernels as K
+    from toyinfer_b200.parts import PartSpec, build_part
+    dtype = torch.bfloat16
+    n = build_part("norm", PartSpec("rmsnorm", {"size": hidden, "eps": 1e-6}), ctx_for(dtype, hidden), "n.")
+    f = build_part("feed_forward", PartSpec("swiglu", {"intermediate_size": inter}), ctx_for(dtype, hidden), "m.")
+    wn = bind_random(n, 4, dtype)["n.weight"]
+    w = bind_random(f, 5, dtype)
+    g = torch.Generator().manual_seed(6)
+    h = torch.randn(1, hidden, generator=g).to(dtype)
+    d = (0.5 * torch.randn(1, hidden, generator=g)).to(dtype)
+    assert f.takes_pending_norm
+    h_dev = h.to(DEV)
+    pending = n.add_pending(h_dev, d.to(DEV))
+    assert isinstance(pending, K.PendingNorm)
+    got = f.forward(pending, None)
+    r = torch.bfloat16
+    hs = plain.rnd(h.double() + d.double(), r)
+    x = plain.rms_norm(hs, wn, 1e-6, r)
+    gate, up = plain.linear(x, w["m.gate_proj.weight"], r), plain.linear(x, w["m.up_proj.weight"], r)
+    want = plain.linear(plain.swiglu(gate, up, r), w["m.down_proj.weight"], r)
+    torch.testing.assert_close(got.cpu().double(), want, **tol(dtype))
+    torch.testing.assert_close(pending.hidden().cpu().double(), hs, rtol=0, atol=0)
+    assert torch.equal(h_dev.cpu(), h)                       # the sum went to a new tensor
+    h2 = h.to(DEV)
+    apart = f.forward(n.add_forward(h2, d.to(DEV)), None)    # norm kernel, then the products
+    assert torch.equal(h2, pending.hidden())
+    if hidden > 1024:
+        assert torch.equal(apart, got)
+    else:
+        torch.testing.assert_close(apart.float(), got.float(), **tol(dtype))
+    # more than one token: the norm part does the work itself
+    two = n.add_pending(torch.zeros(2, hidden, dtype=dtype, device=DEV), torch.zeros(2, hidden, dtype=dtype, device=DEV))
+    assert isinstance(two, torch.Tensor)
+
+
 def plain_attention_layer(x, w, p, nh, nkv, hd, eps, theta, window, r, positions=None, rope_fn=None):
     T = x.shape[0]
     q = plain.linear(x, w[p + "q_proj.weight"], r).view(T, nh, hd)
