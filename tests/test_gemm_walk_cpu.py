@@ -76,6 +76,40 @@ def test_the_layer_shapes_with_2560_columns_are_shared_out():
     assert not pair and shared > 0
 
 
+def _plan(M, N, K, sms):
+    from toyinfer_b200.kernels.lib import library
+    swap, bn, splits, tickets, ws = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_longlong()
+    library().ti_linear_tc_plan(M, N, K, sms, ctypes.byref(swap), ctypes.byref(bn), ctypes.byref(splits), ctypes.byref(ws),
+                                ctypes.byref(tickets))
+    return bool(swap.value), bn.value, splits.value, ws.value, tickets.value
+
+
+@pytest.mark.parametrize("sms", [148, 132, 37])
+def test_the_plan_asks_for_the_workspace_and_tickets_the_walk_uses(sms):
+    rng = random.Random(11)
+    for _ in range(200):
+        M = rng.choice([1, 8, 16, 33, 64, 65, 300, 512, 1300, 2048, 5000])
+        N = rng.choice([128, 520, 2560, 3600, 6144, 19456])
+        K = rng.choice([64, 264, 2560, 4096, 9728])
+        swap, bn, splits, ws, tickets = _plan(M, N, K, sms)
+        assert bn % 16 == 0 and 16 <= bn <= 256 and splits >= 1
+        rows, units, tiles, pair = _trace(M, N, K, sms)
+        if splits > 1:
+            assert not rows                                   # a split contraction runs one block per tile
+            rows_a, rows_b = (N, M) if swap else (M, N)
+            n_tiles = -(-rows_a // 128) * -(-rows_b // bn)
+            assert ws == splits * n_tiles * 128 * bn and tickets == n_tiles
+            continue
+        pieces = [r for r in rows if not r[4]]
+        if not pieces:          # whole tiles only (also when the cuts fall on tile borders, as with one step per tile)
+            continue
+        blocks = 2 if pair else 1
+        assert units * blocks <= sms
+        # a place for every piece: (unit, place, block of the unit), a tile's rows of one block in each
+        assert ws >= units * 2 * blocks * 128 * bn
+        assert tickets >= (max(r[1] for r in pieces) + 1) * blocks
+
+
 def test_random_shapes_and_device_sizes():
     rng = random.Random(7)
     walked = 0
