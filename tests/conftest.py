@@ -26,7 +26,7 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
-# Three tiny configurations that differ in every size and option.
+# Tiny configurations that differ in every size and option.
 TINY = {
     # heads 4 over 2 kv heads of 16, q_dim == hidden, tied head, theta 1e4, eps 1e-6
     "A": {
@@ -50,8 +50,22 @@ TINY = {
         "tie_word_embeddings": False, "use_sliding_window": True, "sliding_window": 40,
         "max_window_layers": 1,
     },
+    # heads of 128 (the size the bfloat16 tensor-core attention kernels take), 4 over 2 kv heads
+    "D": {
+        "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 256,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 320,
+        "vocab_size": 520, "rope_theta": 1e6, "rms_norm_eps": 1e-6, "max_position_embeddings": 1280,
+        "tie_word_embeddings": False, "eos_token_id": 3,
+    },
+    # heads of 64, 6 over 3 kv heads, a window of 64 (a ring with no slack) on the second layer
+    "E": {
+        "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 192,
+        "num_attention_heads": 6, "num_key_value_heads": 3, "head_dim": 64, "intermediate_size": 136,
+        "vocab_size": 410, "rope_theta": 1e5, "rms_norm_eps": 1e-5, "max_position_embeddings": 512,
+        "tie_word_embeddings": True, "layer_types": ["full_attention", "sliding_attention"], "sliding_window": 64,
+    },
 }
-SEEDS = {"A": 11, "B": 22, "C": 33}
+SEEDS = {"A": 11, "B": 22, "C": 33, "D": 44, "E": 55}
 
 
 @pytest.fixture(scope="session")

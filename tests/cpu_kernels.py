@@ -130,6 +130,28 @@ def attention_prefill(q, k, v, scale, window, batch):
     return out
 
 
+def attention_chunk(q, k, v, mem, scale, window, batch):
+    out = torch.empty_like(q)
+    cu, starts, slots = batch.cu_new.tolist(), batch.seq_start.tolist(), batch.seq_slot.tolist()
+    for b in range(batch.n_seq):
+        t0, t1, st = cu[b], cu[b + 1], starts[b]
+        for i in range(t1 - t0):
+            pos = st + i
+            lo = max(0, pos - window + 1) if window > 0 else 0
+            ks, vs = [], []
+            for p in range(lo, pos + 1):
+                if p >= st:
+                    ks.append(k[t0 + p - st])
+                    vs.append(v[t0 + p - st])
+                else:
+                    row = p % mem.ring_rows if mem.ring_rows else p
+                    page = int(mem.page_table[slots[b], row // mem.page_size])
+                    ks.append(mem.k_pages[page, :, row % mem.page_size, :])
+                    vs.append(mem.v_pages[page, :, row % mem.page_size, :])
+            out[t0 + i] = _attend(q[t0 + i], torch.stack(ks), torch.stack(vs), scale, lo).to(q.dtype)
+    return out
+
+
 def attention_decode(q, mem, scale, window, batch):
     out = torch.empty_like(q)
     slots, lens = batch.seq_slot.tolist(), batch.seq_len.tolist()
@@ -157,5 +179,5 @@ def argmax(logits):
 
 def install(monkeypatch) -> None:
     for name in ("embed", "rmsnorm", "add_rmsnorm", "gather_add", "linear", "swiglu", "linear_swiglu", "qk_norm_rope_store",
-                 "attention_prefill", "attention_decode", "attention_decode_step", "argmax"):
+                 "attention_prefill", "attention_chunk", "attention_decode", "attention_decode_step", "argmax"):
         monkeypatch.setattr(K, name, globals()[name])

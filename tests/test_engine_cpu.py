@@ -54,6 +54,44 @@ def test_last_tokens_one_by_one(cpu_engine, model_folders, name):
     torch.testing.assert_close(got, want[head - 1:], rtol=1e-4, atol=1e-5)
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_a_prompt_cut_into_pieces(cpu_engine, model_folders, name):
+    """A sequence fed 7, 64, 1 tokens, then the rest, then 16 + 16 more: every place's logits are
+    those of the whole sequence.  In C the pieces are longer than the window's ring has slack."""
+    eng = cpu_engine(name)
+    n = 230 if name == "C" else 120
+    ids = prompts_for(name, [n], seed=2)[0]
+    want = _plain_logits(model_folders[name], ids)
+    slot = eng.new_sequence()
+    cuts = [0, 7, 71, 72, n - 32, n - 16, n]
+    got = []
+    for a, b in zip(cuts, cuts[1:]):
+        got.append(eng.step([(slot, ids[a:b])], [list(range(b - a))]).clone())
+        assert eng.length(slot) == b
+    torch.testing.assert_close(torch.cat(got), want, rtol=1e-4, atol=1e-5)
+    eng.end_sequence(slot)
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_a_prompt_joins_sequences_that_decode(cpu_engine, model_folders, name):
+    """Two sequences decode; a third starts beside them with its whole prompt in the same step, and
+    one of the first two goes on by five tokens at once in the step after."""
+    eng = cpu_engine(name)
+    a, b, c = prompts_for(name, [90, 45, 70], seed=5)
+    wa, wb, wc = (_plain_logits(model_folders[name], x) for x in (a, b, c))
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    eng.step([(sa, a[:80]), (sb, b[:30])], [[], []])
+    out = eng.step([(sa, [a[80]]), (sb, [b[30]])], None)
+    torch.testing.assert_close(out, torch.stack([wa[80], wb[30]]), rtol=1e-4, atol=1e-5)
+    sc = eng.new_sequence()
+    out = eng.step([(sa, [a[81]]), (sc, c[:60]), (sb, [b[31]])], [[0], [0, 59], [0]])
+    torch.testing.assert_close(out, torch.stack([wa[81], wc[0], wc[59], wb[31]]), rtol=1e-4, atol=1e-5)
+    out = eng.step([(sa, a[82:87]), (sc, [c[60]]), (sb, [b[32]])], [[4], [0], [0]])
+    torch.testing.assert_close(out, torch.stack([wa[86], wc[60], wb[32]]), rtol=1e-4, atol=1e-5)
+    out = eng.step([(sa, [a[87]]), (sc, [c[61]]), (sb, [b[33]])], None)
+    torch.testing.assert_close(out, torch.stack([wa[87], wc[61], wb[33]]), rtol=1e-4, atol=1e-5)
+
+
 def test_unequal_batches_reuse_slots(cpu_engine, model_folders):
     name = "C"
     eng = cpu_engine(name, max_tokens=64 * 8)

@@ -545,6 +545,72 @@ def fill_cache(mem, slot, pages, k, v):
 
 
 @pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (5, 1, 48, 40), (8, 4, 64, 0), (8, 2, 128, 0), (4, 4, 128, 64),
+                                               (6, 2, 64, 100), (2, 1, 256, 0)])
+def test_attention_chunk(K, dtype, nh, nkv, hd, window):
+    """New tokens after positions in the cache: (positions held, new tokens) per sequence covers a
+    sequence that starts, single tokens, a start in the middle and at the end of a page, runs of
+    new tokens longer than a window's ring, and a ring that has wrapped.  Cache lines that no
+    query may read hold NaN; so do the lines where this step's own tokens will go."""
+    cases = [(0, 70), (64, 1), (65, 40), (300, 1), (129, 130), (1, 1), (200, 200), (127, 2)]
+    mem = make_mem(dtype, len(cases), nkv, hd, pages=40, window=window, dirty=float("nan"))
+    free = list(range(40, 0, -1))
+    scale = 1.0 / math.sqrt(hd)
+    ks = [randn(st + n, nkv, hd, seed=130 + i).to(dtype) for i, (st, n) in enumerate(cases)]
+    vs = [randn(st + n, nkv, hd, seed=140 + i).to(dtype) for i, (st, n) in enumerate(cases)]
+    qs = [randn(st + n, nh, hd, seed=150 + i).to(dtype) for i, (st, n) in enumerate(cases)]
+    for s, (st, n) in enumerate(cases):
+        total = st + n
+        need = (min(total, mem.ring_rows) if mem.ring_rows else total) + 63 >> 6
+        pages = [free.pop() for _ in range(need)]
+        if st:
+            fill_cache(mem, s, pages, dev(ks[s][:st]), dev(vs[s][:st]))
+        else:
+            for i, pg in enumerate(pages):
+                mem.page_table[s, i] = pg
+    batch = make_batch("mixed", list(range(len(cases))), [st for st, _ in cases], [n for _, n in cases])
+    q = torch.cat([qs[s][st:] for s, (st, _) in enumerate(cases)])
+    k = torch.cat([ks[s][st:] for s, (st, _) in enumerate(cases)])
+    v = torch.cat([vs[s][st:] for s, (st, _) in enumerate(cases)])
+    got = K.attention_chunk(dev(q), dev(k), dev(v), mem, scale, window, batch).cpu().double()
+    K.check_status()
+    o = 0
+    for s, (st, n) in enumerate(cases):
+        want = plain_attention_seq(qs[s], ks[s], vs[s], scale, window, dtype)[st:]
+        torch.testing.assert_close(got[o:o + n], want, **ATT_TOL[dtype], msg=lambda m: f"sequence {s} {cases[s]}: {m}")
+        o += n
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attention_chunk_far_key_in_the_cache(K, dtype, hd):
+    """One key far back in the cache dominates every new token's scores; with a window only the
+    new tokens that still see it return its value."""
+    nh, nkv, st, n, far, W = 4, 2, 500, 90, 449, 128
+    k = randn(st + n, nkv, hd, seed=160, scale=0.1)
+    v = randn(st + n, nkv, hd, seed=161)
+    q = randn(st + n, nh, hd, seed=162, scale=0.1)
+    k[far] = 0
+    k[far, :, 3] = 40.0
+    q[:, :, 3] = 40.0
+    q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    scale = 1.0 / math.sqrt(hd)
+    for window in (0, W):
+        mem = make_mem(dtype, 1, nkv, hd, pages=12, window=window, dirty=float("nan"))
+        fill_cache(mem, 0, list(range(1, 11)), dev(k[:st]), dev(v[:st]))
+        batch = make_batch("mixed", [0], [st], [n])
+        got = K.attention_chunk(dev(q[st:]), dev(k[st:]), dev(v[st:]), mem, scale, window, batch).cpu().double()
+        want = plain_attention_seq(q, k, v, scale, window, dtype)[st:]
+        torch.testing.assert_close(got, want, **ATT_TOL[dtype])
+        sees = [i for i in range(n) if window == 0 or far > st + i - window]
+        for i in (sees[0], sees[-1]):
+            torch.testing.assert_close(got[i, 0], v[far, 0].double(), rtol=1e-2, atol=1e-2)
+        if window:
+            blind = far + window - st
+            assert (got[blind, 0] - v[far, 0].double()).abs().max() > 0.1
+
+
+@pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 32, 0), (5, 1, 48, 40), (32, 8, 128, 0),
                                                (8, 1, 128, 100), (2, 2, 256, 0), (16, 1, 64, 0)])
 def test_attention_decode(K, dtype, nh, nkv, hd, window):

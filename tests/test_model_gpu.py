@@ -1,7 +1,12 @@
 """The engine on the GPU against the plain implementation, in float32 and bfloat16:
 each request alone and whole; with the last 32 tokens one by one; in batches of unequal
 lengths whose shorter requests end earlier, batch after batch so that slots are used
-again; long decoding; the first tokens of a sequence; graph replay against eager steps."""
+again; long decoding; the first tokens of a sequence; a prompt cut into pieces; a prompt
+that starts beside sequences that decode; graph replay against eager steps.
+
+Configurations A, B and C have heads of 16, 32 and 48 (the CUDA-core attention kernels in
+both precisions); D (heads of 128) and E (heads of 64, a window equal to its ring) put the
+bfloat16 tensor-core attention kernels under the same schedules."""
 from __future__ import annotations
 
 import pytest
@@ -12,7 +17,8 @@ from helpers import assert_logits_close, plain_logits
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["A", "B", "C"]
+NAMES = ["A", "B", "C", "D", "E"]
+WINDOWED = ("C", "E")
 
 
 def make_engine(folder, dtype, **kw):
@@ -26,7 +32,7 @@ def make_engine(folder, dtype, **kw):
 @pytest.mark.parametrize("name", NAMES)
 def test_each_request_alone_and_whole(model_folders, name, dtype):
     eng = make_engine(model_folders[name], dtype)
-    lens = [1, 2, 17, 64, 65, 100] if name != "C" else [1, 40, 41, 130, 200]
+    lens = [1, 2, 17, 64, 65, 100] if name not in WINDOWED else [1, 40, 41, 130, 200]
     for i, ids in enumerate(prompts_for(name, lens, seed=3)):
         slot = eng.new_sequence()
         got = eng.step([(slot, ids)], [list(range(len(ids)))])
@@ -39,7 +45,7 @@ def test_each_request_alone_and_whole(model_folders, name, dtype):
 @pytest.mark.parametrize("name", NAMES)
 def test_last_32_tokens_one_by_one(model_folders, name, dtype, graph):
     eng = make_engine(model_folders[name], dtype, use_cuda_graph=graph)
-    n = {"A": 100, "B": 77, "C": 190}[name]
+    n = {"A": 100, "B": 77, "C": 190, "D": 150, "E": 200}[name]
     ids = prompts_for(name, [n], seed=4)[0]
     want = plain_logits(model_folders[name], ids, dtype)
     slot = eng.new_sequence()
@@ -91,9 +97,56 @@ def test_unequal_batches_one_after_another(model_folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_long_decoding(model_folders, dtype):
-    """More than 200 single-token steps after a short prompt (ring wrapped three times)."""
-    name = "C"
+@pytest.mark.parametrize("name", NAMES)
+def test_a_prompt_cut_into_pieces(model_folders, name, dtype):
+    """A sequence fed 7, 64, 1 tokens, a long piece, then 16 + 16 more: every place's logits are
+    those of the whole sequence.  With a window the pieces are longer than its ring has slack."""
+    eng = make_engine(model_folders[name], dtype)
+    n = {"A": 120, "B": 200, "C": 300, "D": 400, "E": 330}[name]
+    ids = prompts_for(name, [n], seed=8)[0]
+    want = plain_logits(model_folders[name], ids, dtype)
+    slot = eng.new_sequence()
+    cuts = [0, 7, 71, 72, n - 32, n - 16, n]
+    got = []
+    for a, b in zip(cuts, cuts[1:]):
+        got.append(eng.step([(slot, ids[a:b])], [list(range(b - a))]).clone())
+        assert eng.length(slot) == b
+    assert_logits_close(torch.cat(got), want, dtype, f"{name} in pieces")
+    # and the same again in the slot's next use, cut elsewhere
+    eng.end_sequence(slot)
+    slot = eng.new_sequence()
+    got = [eng.step([(slot, ids[a:b])], [list(range(b - a))]).clone() for a, b in ((0, 65), (65, 66), (66, n))]
+    assert_logits_close(torch.cat(got), want, dtype, f"{name} in pieces, second use of the slot")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_a_prompt_joins_sequences_that_decode(model_folders, name, dtype):
+    """Two sequences decode; a third starts beside them with its whole prompt in the same step;
+    then one of the first two goes on by five tokens at once while the others go on by one."""
+    eng = make_engine(model_folders[name], dtype)
+    la = 110 if name == "A" else 150          # A holds 128 positions
+    h = la - 20
+    a, b, c = prompts_for(name, [la, 45, 100], seed=9)
+    wa, wb, wc = (plain_logits(model_folders[name], x, dtype) for x in (a, b, c))
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    eng.step([(sa, a[:h]), (sb, b[:30])], [[], []])
+    out = eng.step([(sa, [a[h]]), (sb, [b[30]])], None).clone()
+    assert_logits_close(out, torch.stack([wa[h], wb[30]]), dtype, f"{name} before the join")
+    sc = eng.new_sequence()
+    out = eng.step([(sa, [a[h + 1]]), (sc, c[:80]), (sb, [b[31]])], [[0], [0, 79], [0]]).clone()
+    assert_logits_close(out, torch.stack([wa[h + 1], wc[0], wc[79], wb[31]]), dtype, f"{name} the join")
+    out = eng.step([(sa, a[h + 2:h + 7]), (sc, [c[80]]), (sb, [b[32]])], [[4], [0], [0]]).clone()
+    assert_logits_close(out, torch.stack([wa[h + 6], wc[80], wb[32]]), dtype, f"{name} five at once")
+    out = eng.step([(sa, [a[h + 7]]), (sc, [c[81]]), (sb, [b[33]])], None).clone()
+    assert_logits_close(out, torch.stack([wa[h + 7], wc[81], wb[33]]), dtype, f"{name} after the join")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["C", "E"])
+def test_long_decoding(model_folders, name, dtype):
+    """More than 200 single-token steps after a short prompt (ring wrapped three times; in E
+    the ring has no slack: the newest position overwrites the one that just left the window)."""
     eng = make_engine(model_folders[name], dtype)
     ids = prompts_for(name, [300], seed=6)[0]
     want = plain_logits(model_folders[name], ids, dtype)
@@ -151,14 +204,19 @@ def test_padding_and_company_change_nothing(model_folders, dtype):
         torch.testing.assert_close(outs[0], outs[2], rtol=1e-5, atol=1e-6)
 
 
-def test_step_refuses_mixed_batches(model_folders):
+def test_step_refuses_what_it_cannot_run(model_folders):
     from toyinfer_b200.engine import StepError
     eng = make_engine(model_folders["A"], "float32")
     a, b = eng.new_sequence(), eng.new_sequence()
     eng.step([(a, [1, 2, 3])], None)
     with pytest.raises(StepError):
-        eng.step([(a, [4]), (b, [1, 2])], None)     # one goes on, one starts
-    with pytest.raises(StepError):
-        eng.step([(a, [4, 5])], None)               # goes on by two
-    with pytest.raises(StepError):
         eng.step([(b, [10 ** 6])], None)            # token outside the vocabulary
+    with pytest.raises(StepError):
+        eng.step([(a, [4]), (a, [5])], None)        # a slot twice
+    with pytest.raises(StepError):
+        eng.step([(a, [])], None)                   # no token
+    with pytest.raises(StepError):
+        eng.step([(a, [1] * 200)], None)            # beyond the model's positions
+    with pytest.raises(StepError):
+        eng.step([(a, None), (b, [1, 2])], None, token_source=torch.zeros(2, dtype=torch.int32, device="cuda"))
+    assert eng.length(a) == 3 and eng.length(b) == 0    # nothing was changed

@@ -1,6 +1,7 @@
 """bin/trace_run as a user runs it: a subprocess fed JSON lines, logits files compared
 with the plain implementation; whole requests, the last 32 tokens one by one, unequal
-batches with early ends and reused slots."""
+batches with early ends and reused slots, and a request fed in pieces beside one that
+goes on token by token."""
 from __future__ import annotations
 
 import json
@@ -36,7 +37,7 @@ def read_step(out_dir, step, vocab):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "C"])
+@pytest.mark.parametrize("name", ["A", "C", "D"])
 def test_trace_whole_then_one_by_one_then_batches(model_folders, tmp_path, name, dtype):
     folder, V = model_folders[name], TINY[name]["vocab_size"]
     a, b, c, d = prompts_for(name, [90, 150 if name == "C" else 100, 3, 41], seed=30)
@@ -76,6 +77,20 @@ def test_trace_whole_then_one_by_one_then_batches(model_folders, tmp_path, name,
             end.append("a2")
         steps.append({"step": n0 + 1 + t, "entries": entries, "end": end})
         checks.append((n0 + 1 + t, chk))
+    # request e in pieces of 20, 64 and the rest, while f starts with the second piece and then
+    # goes on one token at a time
+    e, f = prompts_for(name, [len(b), 30], seed=31)
+    n1 = len(steps)
+    steps.append({"step": n1, "entries": [{"id": "e", "tokens": e[:20], "want": [19]}], "end": []})
+    checks.append((n1, [(e, [19])]))
+    steps.append({"step": n1 + 1, "entries": [{"id": "e", "tokens": e[20:84], "want": [0, 63]},
+                                              {"id": "f", "tokens": f[:28], "want": [27]}], "end": []})
+    checks.append((n1 + 1, [(e, [20, 83]), (f, [27])]))
+    steps.append({"step": n1 + 2, "entries": [{"id": "f", "tokens": [f[28]], "want": [0]},
+                                              {"id": "e", "tokens": e[84:], "want": [len(e) - 85]}], "end": ["e"]})
+    checks.append((n1 + 2, [(f, [28]), (e, [len(e) - 1])]))
+    steps.append({"step": n1 + 3, "entries": [{"id": "f", "tokens": [f[29]], "want": [0]}], "end": ["f"]})
+    checks.append((n1 + 3, [(f, [29])]))
     out = str(tmp_path / "out")
     run_trace(folder, dtype, steps, out, max_tokens=64 * 6)
     for step, parts in checks:

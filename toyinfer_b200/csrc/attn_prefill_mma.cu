@@ -1,7 +1,10 @@
-// Causal grouped-query attention over the tokens of one step (sequences that start at
-// position 0), bfloat16, tensor cores, tiles brought in by TMA.  Same contract and formulas
-// as attn_prefill_simt.cu (reference: src/prefill.cu:224-379); this is the kernel the
-// bfloat16 engine runs prompts with for head sizes 64 and 128.
+// Causal grouped-query attention of the tokens of one step, bfloat16, tensor cores, tiles
+// brought in by TMA.  Same contract, formulas and two forms as attn_prefill_simt.cu (reference:
+// src/prefill.cu:224-379): sequences that start at position 0 (the kernel the bfloat16 engine runs
+// prompts of head size 64 with), and, PAGED, new tokens after `seq_start[b]` positions kept in the
+// paged cache.  In the second form a block first walks the sequence's pages below the start (a page
+// is 64 positions x head_dim of one kv head, one tile) and then the step's own keys and values;
+// one online softmax runs over both.
 //
 // Grid (query tiles of 64 taken from the last to the first, heads, sequences), 128 threads,
 // two blocks per SM.  q, k and v are strided views of the projection's output
@@ -32,12 +35,15 @@ __device__ __forceinline__ float ex2(float x) {      // 2^x, the hardware's appr
 struct PrefillArgs {
     const int* cu_new; int n_heads, n_kv_heads; float scale; int window;
     void* out; long long o_stride;
+    // PAGED form: where the positions before the step's tokens are kept
+    const int* seq_start; const int* seq_slot; const int* page_table; int table_width, ring_rows, n_pages;
 };
 
-template <int HD>
+template <int HD, bool PAGED>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                        const __grid_constant__ CUtensorMap v_map, PrefillArgs a, int* status) {
+                        const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap kp_map,
+                        const __grid_constant__ CUtensorMap vp_map, PrefillArgs a, int* status) {
     ti_pdl_trigger();
     constexpr int TILE_BYTES = BKV * HD * 2;
     constexpr int KSTEPS = HD / 16, NT = HD / 8;
@@ -65,16 +71,38 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
     const int kvh = h / (a.n_heads / a.n_kv_heads);
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
 
+    // The step's own keys, counted from the sequence's first new token: tiles kt_lo .. kt_hi.
     const int last_q = min(q0 + BQ, n) - 1;
     const int kt_lo = a.window > 0 ? max(0, q0 - a.window + 1) / BKV : 0;
     const int kt_hi = last_q / BKV;
-    const int n_tiles = kt_hi - kt_lo + 1;
+    // PAGED: the sequence's positions below `start`, one page a tile, pages pt_lo .. pt_lo + n_old - 1,
+    // before the step's own.  lo_blk is the oldest position any query of this block reads.
+    const int start = PAGED ? a.seq_start[b] : 0;
+    const int slot = PAGED ? a.seq_slot[b] : 0;
+    const int lo_blk = (PAGED && a.window > 0) ? max(0, start + q0 - a.window + 1) : 0;
+    const int pt_lo = lo_blk / BKV;
+    const int n_old = (PAGED && lo_blk < start) ? (start - 1) / BKV - pt_lo + 1 : 0;
+    const int n_tiles = n_old + kt_hi - kt_lo + 1;
 
     auto issue = [&](int i) {
-        const int y = tok0 + (kt_lo + i) * BKV;
         unsigned char* dst = kv_s + (size_t)(i % STAGES) * 2 * TILE_BYTES;
         uint64_t* bar = &full[i % STAGES];
         mbar_expect_tx(bar, 2 * TILE_BYTES);
+        if (PAGED && i < n_old) {
+            const int p0 = (pt_lo + i) * BKV;
+            const int row0 = a.ring_rows > 0 ? p0 % a.ring_rows : p0;
+            const int pidx = row0 / BKV;
+            int page = pidx < a.table_width ? a.page_table[(size_t)slot * a.table_width + pidx] : 0;
+            if (page < 0 || page >= a.n_pages) page = 0;
+            const int y = (page * a.n_kv_heads + kvh) * BKV;
+#pragma unroll
+            for (int bx = 0; bx < HD / 64; bx++) {
+                tma_load_2d(dst + bx * (BKV * 128), &kp_map, bx * 64, y, bar);
+                tma_load_2d(dst + TILE_BYTES + bx * (BKV * 128), &vp_map, bx * 64, y, bar);
+            }
+            return;
+        }
+        const int y = tok0 + (kt_lo + i - n_old) * BKV;
 #pragma unroll
         for (int bx = 0; bx < HD / 64; bx++) {
             tma_load_2d(dst + bx * (BKV * 128), &k_map, kvh * HD + bx * 64, y, bar);
@@ -124,7 +152,26 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
             s_abort = 1;
         }
         const uint32_t kb = smem_u32(kv_s + (size_t)stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
-        const int k0 = (kt_lo + i) * BKV;
+        // Key positions are counted from the step's first token of this sequence: a page of older
+        // positions starts at a negative k0.  `limit` is where the tile's valid keys end.
+        const bool old = PAGED && i < n_old;
+        const int k0 = old ? (pt_lo + i) * BKV - start : (kt_lo + i - n_old) * BKV;
+        const int limit = old ? 0 : n;
+        bool patched = false;
+        if (old && (k0 + BKV > 0 || k0 + start < lo_blk)) {
+            // lines of the page outside [lo_blk, start) may hold anything (this step's tokens, an
+            // older turn of the ring, a former owner's): their value rows are cleared, so that a
+            // probability of zero times whatever stands there cannot make a NaN
+            unsigned char* vt = kv_s + (size_t)stage * 2 * TILE_BYTES + TILE_BYTES;
+            for (int r = warp; r < BKV; r += THREADS / 32) {
+                const int p = k0 + start + r;
+                if (p < lo_blk || p >= start)
+                    for (int d = lane * 8; d < HD; d += 256)
+                        *reinterpret_cast<uint4*>(vt + swizzled_offset<BKV>(r, d)) = make_uint4(0, 0, 0, 0);
+            }
+            patched = true;
+            __syncthreads();
+        }
 
         float s[8][4];
 #pragma unroll
@@ -142,7 +189,7 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
                 }
         }
         // scale and mask
-        const bool edge = a.window > 0 || k0 + BKV - 1 > q0 + warp * 16 || k0 + BKV > n;
+        const bool edge = a.window > 0 || k0 + BKV - 1 > q0 + warp * 16 || k0 + BKV > limit;
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < 8; nt++)
@@ -152,7 +199,7 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
                 if (edge) {
                     const int kj = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int qi = qi0 + (e >> 1) * 8;
-                    const bool ok = kj <= qi && kj < n && (a.window <= 0 || kj > qi - a.window);
+                    const bool ok = kj <= qi && kj < limit && (a.window <= 0 || kj > qi - a.window);
                     v = ok ? v : -INFINITY;
                 }
                 s[nt][e] = v;
@@ -201,6 +248,7 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
                 }
             }
         }
+        if (patched) fence_proxy_async();   // this stage was written by threads; a TMA load will overwrite it
         __syncthreads();    // the stage may be refilled
         if (s_abort) {
             if (t == 0)
@@ -250,20 +298,36 @@ int view_map(const void* ptr, long long rows, long long cols, long long stride, 
     return 0;
 }
 
-template <int HD>
-int launch(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillArgs& a, int n_seq, int max_new,
-           cudaStream_t stream) {
+template <int HD, bool PAGED>
+int launch(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const CUtensorMap& kpm, const CUtensorMap& vpm,
+           const PrefillArgs& a, int n_seq, int max_new, cudaStream_t stream) {
     constexpr size_t smem = (size_t)BKV * HD * 2 * (1 + 2 * STAGES) + 1024;
     static bool configured = false;
     if (!configured) {
-        TI_CUDA(cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TI_CUDA(cudaFuncSetAttribute(attn_prefill_mma_kernel<HD, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
     int* status = ti_status_ptr();
     TI_REQUIRE(status != nullptr, "attention_prefill: no status word");
     dim3 grid((max_new + BQ - 1) / BQ, a.n_heads, n_seq);
-    TI_CUDA(ti_launch(attn_prefill_mma_kernel<HD>, grid, dim3(THREADS), smem, stream, qm, km, vm, a, status));
-    TI_CHECK_LAUNCH("attention_prefill (tensor cores)");
+    TI_CUDA(ti_launch(attn_prefill_mma_kernel<HD, PAGED>, grid, dim3(THREADS), smem, stream, qm, km, vm, kpm, vpm, a, status));
+    TI_CHECK_LAUNCH(PAGED ? "attention_chunk (tensor cores)" : "attention_prefill (tensor cores)");
+    return 0;
+}
+
+int check_and_map(const char* what, const void* q, const void* k, const void* v, const void* out, long long q_stride,
+                  long long k_stride, long long v_stride, long long o_stride, int n_seq, int n_tokens, int n_heads,
+                  int n_kv_heads, int head_dim, CUtensorMap* qm, CUtensorMap* km, CUtensorMap* vm) {
+    TI_REQUIRE(head_dim == 64 || head_dim == 128, "%s (tensor cores): head size %d is not 64 or 128", what, head_dim);
+    TI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "%s: bad head counts", what);
+    TI_REQUIRE(n_seq <= 65535 && n_heads <= 65535, "%s: too many sequences or heads for one launch", what);
+    TI_REQUIRE(q_stride % 8 == 0 && k_stride % 8 == 0 && v_stride % 8 == 0 && o_stride % 2 == 0,
+               "%s (tensor cores): token strides must be multiples of 8 elements", what);
+    TI_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0 &&
+               (reinterpret_cast<uintptr_t>(out) & 3) == 0, "%s (tensor cores): misaligned operands", what);
+    if (int rc = view_map(q, n_tokens, (long long)n_heads * head_dim, q_stride, qm)) return rc;
+    if (int rc = view_map(k, n_tokens, (long long)n_kv_heads * head_dim, k_stride, km)) return rc;
+    if (int rc = view_map(v, n_tokens, (long long)n_kv_heads * head_dim, v_stride, vm)) return rc;
     return 0;
 }
 }  // namespace
@@ -274,20 +338,44 @@ extern "C" int ti_attn_prefill_mma(const void* q, const void* k, const void* v, 
                                    const int* cu_new, int n_seq, int max_new, int n_tokens, int n_heads, int n_kv_heads,
                                    int head_dim, float scale, int window, cudaStream_t stream) {
     if (n_seq == 0 || max_new == 0) return 0;
-    TI_REQUIRE(head_dim == 64 || head_dim == 128, "attention_prefill (tensor cores): head size %d is not 64 or 128", head_dim);
-    TI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_prefill: bad head counts");
-    TI_REQUIRE(n_seq <= 65535 && n_heads <= 65535, "attention_prefill: too many sequences or heads for one launch");
-    TI_REQUIRE(q_stride % 8 == 0 && k_stride % 8 == 0 && v_stride % 8 == 0 && o_stride % 2 == 0,
-               "attention_prefill (tensor cores): token strides must be multiples of 8 elements");
-    TI_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0 &&
-               (reinterpret_cast<uintptr_t>(out) & 3) == 0, "attention_prefill (tensor cores): misaligned operands");
     CUtensorMap qm, km, vm;
-    if (int rc = view_map(q, n_tokens, (long long)n_heads * head_dim, q_stride, &qm)) return rc;
-    if (int rc = view_map(k, n_tokens, (long long)n_kv_heads * head_dim, k_stride, &km)) return rc;
-    if (int rc = view_map(v, n_tokens, (long long)n_kv_heads * head_dim, v_stride, &vm)) return rc;
-    PrefillArgs a;
+    if (int rc = check_and_map("attention_prefill", q, k, v, out, q_stride, k_stride, v_stride, o_stride, n_seq, n_tokens,
+                               n_heads, n_kv_heads, head_dim, &qm, &km, &vm)) return rc;
+    PrefillArgs a = {};
     a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = window;
     a.out = out; a.o_stride = o_stride;
-    return head_dim == 64 ? launch<64>(qm, km, vm, a, n_seq, max_new, stream)
-                          : launch<128>(qm, km, vm, a, n_seq, max_new, stream);
+    return head_dim == 64 ? launch<64, false>(qm, km, vm, km, vm, a, n_seq, max_new, stream)
+                          : launch<128, false>(qm, km, vm, km, vm, a, n_seq, max_new, stream);
+}
+
+// The same for new tokens after `seq_start[b]` positions that the cache holds (pages of 64
+// positions, bfloat16); arguments as ti_attn_chunk_simt.
+extern "C" int ti_attn_chunk_mma(const void* q, const void* k, const void* v, void* out,
+                                 long long q_stride, long long k_stride, long long v_stride, long long o_stride,
+                                 const int* cu_new, const int* seq_start, const int* seq_slot, int n_seq, int max_new,
+                                 int n_tokens, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                 const void* k_pages, const void* v_pages, const int* page_table, int table_width,
+                                 int page_size, int ring_rows, int n_pages, cudaStream_t stream) {
+    if (n_seq == 0 || max_new == 0) return 0;
+    TI_REQUIRE(k_pages && v_pages && page_table && seq_start && seq_slot && table_width > 0 && n_pages > 0,
+               "attention_chunk: incomplete cache description");
+    TI_REQUIRE(page_size == BKV, "attention_chunk (tensor cores): pages of %d positions, this kernel works on %d", page_size, BKV);
+    TI_REQUIRE(ring_rows % page_size == 0, "attention_chunk: ring of %d rows is not whole pages", ring_rows);
+    TI_REQUIRE(ring_rows == 0 || (window > 0 && ring_rows >= window),
+               "attention_chunk: a ring of %d rows needs a window of at most as many positions (got %d)", ring_rows, window);
+    TI_REQUIRE(((reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages)) & 15) == 0,
+               "attention_chunk (tensor cores): cache pages must be 16-byte aligned");
+    CUtensorMap qm, km, vm, kpm, vpm;
+    if (int rc = check_and_map("attention_chunk", q, k, v, out, q_stride, k_stride, v_stride, o_stride, n_seq, n_tokens,
+                               n_heads, n_kv_heads, head_dim, &qm, &km, &vm)) return rc;
+    const long long rows = (long long)n_pages * n_kv_heads * BKV;
+    if (int rc = view_map(k_pages, rows, head_dim, head_dim, &kpm)) return rc;
+    if (int rc = view_map(v_pages, rows, head_dim, head_dim, &vpm)) return rc;
+    PrefillArgs a = {};
+    a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = window;
+    a.out = out; a.o_stride = o_stride;
+    a.seq_start = seq_start; a.seq_slot = seq_slot; a.page_table = page_table; a.table_width = table_width;
+    a.ring_rows = ring_rows; a.n_pages = n_pages;
+    return head_dim == 64 ? launch<64, true>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream)
+                          : launch<128, true>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream);
 }

@@ -68,7 +68,8 @@ class BatchBuffers:
 
 @dataclass
 class StepBatch:
-    mode: str                 # "start": every sequence begins at position 0; "extend": one new token each
+    mode: str                 # "start": every sequence begins at position 0; "extend": one new token each;
+                              # "mixed": any start and any number of new tokens per sequence
     n_seq: int                # sequences, padding included
     n_tok: int                # tokens, padding included
     n_real_seq: int

@@ -1,16 +1,20 @@
 """The step function: runs exactly the tokens it is given, as one batch, from the cache.
 
-``Engine.step(entries, want)`` takes for each sequence its slot and its next tokens.
-Either every sequence of the step starts at position 0 (prompts of unequal lengths, all
-in one step) or every sequence goes on by one token.  It returns float32 logits
-[wanted, vocab] for the wanted places, in the order of the entries.  Finished sequences
-are simply absent from the next step; ``end_sequence`` gives their slot and pages back.
+``Engine.step(entries, want)`` takes for each sequence its slot and its next tokens: any
+number of them (at least one), following whatever the sequence holds already.  Prompts of
+unequal lengths in one step, one token each, a prompt fed in pieces, a prompt beside
+sequences that decode: all are one call, and all give the same logits beyond rounding.
+It returns float32 logits [wanted, vocab] for the wanted places, in the order of the
+entries.  Finished sequences are simply absent from the next step; ``end_sequence`` gives
+their slot and pages back.
 
 The reference has two entry points for one sequence, ``prefill(ids, n)`` and
-``forward(id, pos)`` (include/transformer.h:110-111); its decode body is captured once
-into a CUDA graph and replayed (src/transformer.cpp:647-669).  Here a decode step is
-captured per batch-size bucket; the graph reads slots, lengths and token ids from device
-buffers refreshed before each replay.
+``forward(id, pos)`` (include/transformer.h:110-111), and cannot continue a sequence by
+more than one token (its prefill writes cache rows [0, n) at positions 0..n-1,
+src/transformer.cpp:393-398, src/prefill.cu:185-208).  Its decode body is captured once
+into a CUDA graph and replayed (src/transformer.cpp:647-669).  Here a step in which every
+sequence goes on by one token is captured per batch-size bucket; the graph reads slots,
+lengths and token ids from device buffers refreshed before each replay.
 """
 from __future__ import annotations
 
@@ -156,13 +160,13 @@ class Engine:
                 if not (0 <= tok < self.spec.vocab_size):
                     raise StepError(f"slot {s}: token id {tok} is outside the vocabulary of {self.spec.vocab_size}")
         starts = [self.cache.length[s] for s in slots]
+        # two special cases have faster kernels; everything else is the general form
         if all(st == 0 for st in starts) and token_source is None:
             mode = "start"
         elif all(len(t) == 1 for t in tokens):
             mode = "extend"
         else:
-            raise StepError("the sequences of a step either all start at their first token or all "
-                            "go on by one token")
+            mode = "mixed"
         if want is None:
             want = [[len(t) - 1] for t in tokens]
         if len(want) != n:

@@ -337,6 +337,24 @@ def attention_prefill(q, k, v, scale: float, window: int, batch) -> torch.Tensor
     return out
 
 
+def attention_chunk(q, k, v, mem, scale: float, window: int, batch) -> torch.Tensor:
+    """Causal attention of a step whose sequences go on from any position by any number of
+    tokens: sequence b's new tokens take positions ``seq_start[b]`` onwards; keys and values at
+    positions below the start are read from ``mem`` (what earlier steps stored), the others are
+    the step's own k and v[M, kv_heads, d] (normed and rotated; whether they are stored yet does
+    not matter).  q[M, heads, d] -> [M, heads, d]."""
+    _need_cuda(q, k, v, what="attention_chunk")
+    M, nh, hd = q.shape
+    if k.shape != v.shape or k.shape[0] != M or k.shape[2] != hd or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise KernelError("attention_chunk: q, k and v do not fit together")
+    if (mem.n_kv_heads, mem.head_dim) != (k.shape[1], hd):
+        raise KernelError("attention_chunk: the cache does not fit these keys")
+    out = torch.empty((M, nh, hd), dtype=q.dtype, device=q.device)
+    from . import attention
+    attention.chunk(q, k, v, mem, out, float(scale), int(window), batch)
+    return out
+
+
 def attention_decode(q, mem, scale: float, window: int, batch) -> torch.Tensor:
     """One query per sequence over the cache (the new token's key already stored).
     q[B, heads, d] -> [B, heads, d]."""

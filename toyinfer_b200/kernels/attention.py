@@ -24,6 +24,27 @@ def prefill(q, k, v, out, scale, window, batch) -> None:
           _code(q, "attention_prefill"), _stream())
 
 
+def chunk(q, k, v, mem, out, scale, window, batch) -> None:
+    """New tokens after positions that the cache holds: keys below a sequence's start come from
+    ``mem``'s pages, the rest from k and v."""
+    M, nh, hd = q.shape
+    qs, ks, vs = _row_stride(q, "q"), _row_stride(k, "k"), _row_stride(v, "v")
+    pt = mem.page_table
+    if mem.k_pages.dtype != q.dtype or not mem.k_pages.is_contiguous() or not mem.v_pages.is_contiguous():
+        raise KernelError("attention_chunk: the cache pages do not fit these queries")
+    cache = (_ptr(mem.k_pages), _ptr(mem.v_pages), _ptr(pt), pt.shape[1], mem.page_size, mem.ring_rows, mem.k_pages.shape[0])
+    if (q.dtype == torch.bfloat16 and hd in (64, 128) and mem.page_size == 64 and qs % 8 == 0 and ks % 8 == 0 and vs % 8 == 0
+            and out.stride(0) % 2 == 0 and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0
+            and mem.k_pages.data_ptr() % 16 == 0 and mem.v_pages.data_ptr() % 16 == 0):
+        _call(library().ti_attn_chunk_mma, _ptr(q), _ptr(k), _ptr(v), _ptr(out), qs, ks, vs, out.stride(0),
+              _ptr(batch.cu_new), _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seq, batch.max_new, M, nh,
+              k.shape[1], hd, scale, window, *cache, _stream())
+        return
+    _call(library().ti_attn_chunk_simt, _ptr(q), _ptr(k), _ptr(v), _ptr(out), qs, ks, vs, out.stride(0),
+          _ptr(batch.cu_new), _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seq, batch.max_new, nh,
+          k.shape[1], hd, scale, window, *cache, _code(q, "attention_chunk"), _stream())
+
+
 def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int) -> int:
     """Splits along the keys so that the grid has about two blocks per SM, but no split
     shorter than four pages.  Depends only on the batch's padded size and the longest

@@ -14,9 +14,16 @@ src/prefill.cu:224-379); then o = Wo a (src/transformer.cpp:574-577).
 Parameters choose everything: head counts, head size, norm on or off and its eps,
 the window, the name of the position encoding, whether the layer has keys and
 values of its own (``own_kv``) or reads those of the entry it borrows memory from,
-and the softmax scale.  A step whose sequences all start at position 0 attends over
-the keys and values computed in the step; a step that extends each sequence by one
-token attends over the cache.
+and the softmax scale.
+
+A step may continue each sequence from any position by any number of tokens
+(``batch.mode == "mixed"``): a token's keys are then the sequence's earlier positions,
+read from the cache, and the step's own tokens up to itself.  Two special cases have
+kernels of their own: every sequence starts at position 0 (``"start"``: all keys are the
+step's own) and every sequence goes on by one token (``"extend"``: the new key is stored
+and all keys are read from the cache).  In a group that keeps a window of positions in a
+ring, a step's keys are stored only after the step's attention has read the positions
+they overwrite.
 """
 from __future__ import annotations
 
@@ -128,25 +135,38 @@ class GQAAttention(Mixer):
             a = K.attention_decode_step(q, k, v, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0, tables, mem,
                                         self.scale, self.window, batch)
             return K.linear(a.view(M, self.q_dim), self.w_o, after_attention=True)
+        # In a ring, a long enough run of new keys overwrites positions that the run's first
+        # queries still read: such a step stores after its attention.
+        store_first = self.own_kv and not (batch.mode == "mixed" and mem.ring_rows > 0)
         if self.pos is not None and tables is None:
-            # a position encoding without rotary tables works on q and k itself
+            # a position encoding without rotary tables works on q and k itself:
             # norms, then the part's own encoding, then the store
             K.qk_norm_rope_store(q, k, None, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0,
                                  None, batch, None)
             self.pos.apply(q, k, batch.tok_pos)
-            if self.own_kv:
+            if store_first:
                 K.qk_norm_rope_store(None, k, v, None, None, 0.0, None, batch, mem)
         else:
             K.qk_norm_rope_store(q, k, v, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0,
-                                 tables, batch, mem if self.own_kv else None)
-        if batch.mode == "start":
+                                 tables, batch, mem if store_first else None)
+        if batch.mode == "extend":
+            a = K.attention_decode(q, mem, self.scale, self.window, batch)
+        else:
             if self.own_kv:
                 shared["k_new"], shared["v_new"] = k, v
             else:
                 k, v = shared["k_new"], shared["v_new"]
-            a = K.attention_prefill(q, k, v, self.scale, self.window, batch)
-        else:
-            a = K.attention_decode(q, mem, self.scale, self.window, batch)
+            if batch.mode == "start":
+                a = K.attention_prefill(q, k, v, self.scale, self.window, batch)
+            else:
+                a = K.attention_chunk(q, k, v, mem, self.scale, self.window, batch)
+            if self.own_kv and not store_first:
+                def store(k=k, v=v):
+                    K.qk_norm_rope_store(None, k, v, None, None, 0.0, None, batch, mem)
+                if "deferred" in shared:        # entries that borrow this memory still have to read it
+                    shared["deferred"].append(store)
+                else:
+                    store()
         return K.linear(a.view(M, self.q_dim), self.w_o, after_attention=True)
 
 

@@ -15,9 +15,19 @@ Families and what each must provide:
 ``Mixer``           ``memory_request()`` says what the cache must keep for it (keys
                     and values, all or a window; a fixed-size state; nothing) and
                     ``forward(x, batch, mem, shared) -> y`` mixes ``x[M, hidden]``
-                    along each sequence.  ``shared`` is a dict that lives for one
+                    along each sequence.  Sequence b of the step brings
+                    ``batch.seq_new[b]`` tokens that follow ``batch.seq_start[b]``
+                    positions already in ``mem``; any mix of the two is allowed, and a
+                    mixer must be right for all of them.  ``batch.mode`` names two
+                    special cases a mixer may run faster: ``"start"`` (every start is
+                    0) and ``"extend"`` (one token each; device tensors only, since
+                    such a step may be captured into a CUDA graph); anything else is
+                    ``"mixed"``.  ``shared`` is a dict that lives for one
                     step and belongs to the schedule entry that owns ``mem``; an
                     entry that borrows another entry's memory gets the owner's dict.
+                    When it holds a list ``"deferred"``, later entries still read
+                    ``mem``: a write that would destroy what they read is appended
+                    there as a callable instead of being done.
 ``FeedForward``     ``forward(x, batch) -> y`` per token.
 ``Block``           owns norm(s), a mixer and a feed-forward and arranges them;
                     ``forward(h, delta, batch, mem, shared) -> (h, delta)`` where the

@@ -126,10 +126,15 @@ class DecoderModel(Part):
         shared: List[dict] = [dict() for _ in self.schedule]
         owners = [i if e.memory_of is None else e.memory_of for i, e in enumerate(self.schedule)]
         last_use = {o: i for i, o in enumerate(owners)}
+        for o, last in last_use.items():
+            if last != o:
+                shared[o]["deferred"] = []     # writes to the memory that must wait for its last reader
         for i, e in enumerate(self.schedule):
             owner = owners[i]
             h, delta = self.blocks[e.layer].forward(h, delta, batch, memories[owner], shared[owner])
             if last_use[owner] == i:
+                for fn in shared[owner].get("deferred", ()):
+                    fn()
                 shared[owner].clear()      # what an entry left for its borrowers (this step's keys and values) is let go
         return h, delta
 
