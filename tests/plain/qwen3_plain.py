@@ -2,8 +2,10 @@
 
 This file is the oracle of the tests.  It shares no code with toyinfer_b200: it reads
 config.json as a dict, reads safetensors with its own few lines, and computes every
-part with elementary torch operations on the CPU in float64.  Each function cites the
-lines of the reference (wiketool/ToyInfer) whose formula it restates.
+part with elementary torch operations in float64, on the device its inputs live on (the
+CPU in most tests; a GPU when weights of real layer sizes are handed in on one, where the
+same operations run in seconds).  Each function cites the lines of the reference
+(wiketool/ToyInfer) whose formula it restates.
 
 The reference's model code is CUDA only (every op is a __global__ kernel) and its host
 program needs third-party sources that are not in its tree, so it cannot run on a
@@ -80,7 +82,7 @@ def rnd(x: torch.Tensor, rounding: Optional[torch.dtype]) -> torch.Tensor:
 # ---------------------------------------------------------------------------
 def embedding(table: torch.Tensor, ids: Sequence[int]) -> torch.Tensor:
     """h[t] = E[id_t], no scale (src/prefill.cu:17-21, src/transformer.cpp:641-644)."""
-    return table.to(F64)[torch.tensor(list(ids), dtype=torch.long)]
+    return table[torch.tensor(list(ids), dtype=torch.long, device=table.device)].to(F64)
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float, rounding=None) -> torch.Tensor:
@@ -122,8 +124,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, w
     maximum subtracted (src/decode.cu:488-531); o = sum p v (src/decode.cu:618-627)."""
     T, nh, d = q.shape
     g = nh // k.shape[1]
-    out = torch.zeros(T, nh, d, dtype=F64)
-    pos = torch.arange(T)
+    out = torch.zeros(T, nh, d, dtype=F64, device=q.device)
+    pos = torch.arange(T, device=q.device)
     visible = pos[None, :] <= pos[:, None]
     if window > 0:
         visible &= pos[None, :] > pos[:, None] - window
@@ -170,7 +172,7 @@ def decoder_layer(h: torch.Tensor, w: Dict[str, torch.Tensor], cfg: dict, layer:
     v = linear(x, w[p + "self_attn.v_proj.weight"], rounding).view(T, nkv, hd)
     q = rms_norm(q, w[p + "self_attn.q_norm.weight"], eps, rounding)
     k = rms_norm(k, w[p + "self_attn.k_norm.weight"], eps, rounding)
-    ang = rope_angles(hd, cfg["rope_theta"], range(T))
+    ang = rope_angles(hd, cfg["rope_theta"], range(T)).to(h.device)
     q, k = rope(q, ang, rounding), rope(k, ang, rounding)
     a = attention(q, k, v, 1.0 / math.sqrt(hd), layer_window(cfg, layer), rounding)
     o = linear(a.reshape(T, nh * hd), w[p + "self_attn.o_proj.weight"], rounding)
@@ -182,15 +184,19 @@ def decoder_layer(h: torch.Tensor, w: Dict[str, torch.Tensor], cfg: dict, layer:
     return rnd(h + m, rounding)
 
 
-def forward(w: Dict[str, torch.Tensor], cfg: dict, ids: Sequence[int], rounding=None) -> torch.Tensor:
-    """Logits [T, vocab] (float64) of every position of one whole sequence: embedding,
-    layers, final norm, head (src/transformer.cpp:345-470).  The head is the embedding
-    table when ``tie_word_embeddings`` is true (the reference always ties,
-    src/qwen.cpp:482-483) and ``lm_head.weight`` otherwise; its output is not rounded
-    (float32 logits, src/decode.cu:251-286)."""
+def forward(w: Dict[str, torch.Tensor], cfg: dict, ids: Sequence[int], rounding=None,
+            rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Logits [T, vocab] (float64) of every position of one whole sequence (or of the
+    positions in ``rows`` only): embedding, layers, final norm, head
+    (src/transformer.cpp:345-470).  The head is the embedding table when
+    ``tie_word_embeddings`` is true (the reference always ties, src/qwen.cpp:482-483) and
+    ``lm_head.weight`` otherwise; its output is not rounded (float32 logits,
+    src/decode.cu:251-286)."""
     h = rnd(embedding(w["model.embed_tokens.weight"], ids), rounding)
     for layer in range(cfg["num_hidden_layers"]):
         h = decoder_layer(h, w, cfg, layer, rounding)
+    if rows is not None:
+        h = h[torch.tensor(list(rows), dtype=torch.long, device=h.device)]
     x = rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"], rounding)
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return linear(x, head, None)

@@ -529,6 +529,65 @@ def test_attention_prefill_far_key_and_window_edge(K, dtype):
             assert (got[first_blind, 0] - v[far, 0].double()).abs().max() > 0.1
 
 
+def plain_attention_on_gpu(q, k, v, scale, window, dtype):
+    """The plain function with its float64 operations on the GPU: for sequences of thousands of
+    positions, where the CPU would take minutes."""
+    return plain.attention(q.double().cuda(), k.double().cuda(), v.double().cuda(), scale, window, rnd_mode(dtype)).cpu()
+
+
+@pytest.mark.parametrize("news,window", [([2048], 0), ([1025, 4097], 0), ([3000, 70], 1000)])
+def test_attention_prefill_tcgen05_at_long_lengths(K, news, window):
+    """The tcgen05 kernel (head size 128) at the lengths prompts have in practice: 16 to 65 key
+    tiles per query tile, lengths one past a tile's end, two sequences in one launch."""
+    dtype, nh, nkv, hd = torch.bfloat16, 4, 2, 128
+    M = sum(news)
+    qkv = randn(M, (nh + 2 * nkv) * hd, seed=27).to(dtype)
+    g = dev(qkv)
+    q = g[:, : nh * hd].view(M, nh, hd)
+    k = g[:, nh * hd: (nh + nkv) * hd].view(M, nkv, hd)
+    v = g[:, (nh + nkv) * hd:].view(M, nkv, hd)
+    batch = make_batch("start", list(range(len(news))), [0] * len(news), news)
+    scale = 1.0 / math.sqrt(hd)
+    got = K.attention_prefill(q, k, v, scale, window, batch).cpu().double()
+    K.check_status()
+    o = 0
+    for n in news:
+        want = plain_attention_on_gpu(q[o:o + n], k[o:o + n], v[o:o + n], scale, window, dtype)
+        torch.testing.assert_close(got[o:o + n], want, **ATT_TOL[dtype])
+        o += n
+
+
+@pytest.mark.parametrize("n,far", [(300, 17), (300, 290), (2048, 5), (2048, 2000), (2048, 1029)])
+def test_attention_prefill_tcgen05_far_key(K, n, far):
+    """Head size 128 (the tcgen05 kernel, which rescales its output only when a row's maximum has
+    grown by more than 2^8): one key dominates, early in the row (the maximum is set in the first
+    tile and never moves) or late (every row that sees it has accumulated many tiles at a maximum
+    near 0 and must rescale by far more than 2^8 at once).  A second key, between the crowd and the
+    dominating one, sits before it and dominates the rows between them, so that the late case
+    rescales twice."""
+    dtype, nh, nkv, hd = torch.bfloat16, 4, 2, 128
+    q = randn(n, nh, hd, seed=123, scale=0.1)
+    k = randn(n, nkv, hd, seed=124, scale=0.1)
+    v = randn(n, nkv, hd, seed=125)
+    k[far] = 0
+    k[far, :, 0] = 40.0
+    mid = far // 2
+    k[mid] = 0
+    k[mid, :, 0] = 6.0           # score 240 * scale: about 21 above the crowd, about 2^30 in weight
+    q[:, :, 0] = 40.0
+    q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    batch = make_batch("start", [0], [0], [n])
+    scale = 1.0 / math.sqrt(hd)
+    got = K.attention_prefill(dev(q), dev(k), dev(v), scale, 0, batch).cpu().double()
+    K.check_status()
+    want = plain_attention_on_gpu(q, k, v, scale, 0, dtype)
+    torch.testing.assert_close(got, want, **ATT_TOL[dtype])
+    for i in (far, n - 1):
+        torch.testing.assert_close(got[i, 0], v[far, 0].double(), rtol=1e-2, atol=1e-2)
+    if mid > 0 and far - 1 > mid:
+        torch.testing.assert_close(got[far - 1, 0], v[mid, 0].double(), rtol=0.05, atol=0.05)
+
+
 def fill_cache(mem, slot, pages, k, v):
     """k, v [n, kv_heads, hd] into the given pages of a slot (ring-aware)."""
     from toyinfer_b200.cache.manager import PAGE
@@ -690,6 +749,67 @@ def test_attention_decode_step_one_kernel_equals_two(K, nh, nkv, hd, window, nor
             assert torch.equal(mem_a.k_pages, mem_b.k_pages) and torch.equal(mem_a.v_pages, mem_b.v_pages)
             if not borrow:
                 assert not torch.equal(mem_b.k_pages, mem.k_pages)      # something was stored
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_attention_decode_tensor_cores_at_long_lengths(K, fused):
+    """The tensor-core decode kernel (and its form with norm, rotation and store folded in)
+    against the plain implementation at the lengths of real contexts: page tables over a hundred
+    entries wide, up to 64 live splits and their combine, a batch of very unequal lengths.  The
+    plans of 8,192 and 40,960 positions give different split counts for the same data."""
+    from toyinfer_b200.parts.rope import rotary_tables
+    dtype, nh, nkv, hd, eps = torch.bfloat16, 8, 2, 128, 1e-6
+    lens = [8192, 64, 1, 3000, 2048, 4100]
+    B = len(lens)
+    n_pages = sum((n + 63) // 64 for n in lens)
+    mem = make_mem(dtype, B, nkv, hd, pages=n_pages, dirty=float("nan"))
+    free = list(range(n_pages, 0, -1))
+    ks = [randn(n, nkv, hd, seed=230 + i).to(dtype) for i, n in enumerate(lens)]
+    vs = [randn(n, nkv, hd, seed=240 + i).to(dtype) for i, n in enumerate(lens)]
+    q = randn(B, nh, hd, seed=250).to(dtype)
+    scale = 1.0 / math.sqrt(hd)
+    r = rnd_mode(dtype)
+    want = []
+    if fused:
+        # the cache holds all positions but the newest; the step brings that one unformed
+        q_w = (1 + randn(hd, seed=251, scale=0.1)).to(dtype)
+        k_w = (1 + randn(hd, seed=252, scale=0.1)).to(dtype)
+        cos, sin = rotary_tables(hd, 1e6, 8192)
+        for s, n in enumerate(lens):
+            ang = plain.rope_angles(hd, 1e6, [n - 1])
+            qn = plain.rope(plain.rms_norm(q[s:s + 1].double(), q_w, eps, r), ang, r)
+            kn = plain.rope(plain.rms_norm(ks[s][n - 1:n].double(), k_w, eps, r), ang, r)
+            kk = torch.cat([ks[s][:n - 1].double(), kn])
+            qq = torch.zeros(n, nh, hd, dtype=torch.float64)
+            qq[-1] = qn[0]
+            want.append(plain_attention_on_gpu(qq, kk, vs[s], scale, 0, dtype)[-1])
+    else:
+        for s, n in enumerate(lens):
+            qq = torch.zeros(n, nh, hd, dtype=dtype)
+            qq[-1] = q[s]
+            want.append(plain_attention_on_gpu(qq, ks[s], vs[s], scale, 0, dtype)[-1])
+    for s, n in enumerate(lens):
+        held = n - 1 if fused else n
+        pages = [free.pop() for _ in range((n + 63) // 64)]
+        if held:
+            fill_cache(mem, s, pages, dev(ks[s][:held]), dev(vs[s][:held]))
+        else:
+            mem.page_table[s, 0] = pages[0]
+    k_clean, v_clean = mem.k_pages.clone(), mem.v_pages.clone()
+    for plan in (8192, 40960):
+        mem.k_pages.copy_(k_clean)
+        mem.v_pages.copy_(v_clean)
+        batch = make_batch("extend", list(range(B)), [n - 1 for n in lens], [1] * B, plan_len=plan)
+        if fused:
+            k_new = torch.stack([ks[s][n - 1] for s, n in enumerate(lens)])
+            v_new = torch.stack([vs[s][n - 1] for s, n in enumerate(lens)])
+            got = K.attention_decode_step(dev(q).clone(), dev(k_new), dev(v_new), dev(q_w), dev(k_w), eps,
+                                          (dev(cos), dev(sin), hd), mem, scale, 0, batch).cpu().double()
+        else:
+            got = K.attention_decode(dev(q), mem, scale, 0, batch).cpu().double()
+        K.check_status()
+        for s in range(B):
+            torch.testing.assert_close(got[s], want[s], **ATT_TOL[dtype], msg=lambda m: f"plan {plan}, length {lens[s]}: {m}")
 
 
 @pytest.mark.parametrize("dtype", DT)

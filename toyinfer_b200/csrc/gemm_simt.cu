@@ -7,6 +7,12 @@
 // rows once and multiplies them with all M activation rows, so decode at a small
 // batch is bound by the read of W.
 //
+// Sums of thousands of 32-bit products are kept short: the tiled kernel adds up 128
+// consecutive k in one register and then moves that partial sum into a second one, so
+// that rounding errors grow with the square root of K/128 + 128 rather than of K (with
+// K = 9,728 a plain running sum alone put logits 1.5e-5 off the exact value; the few-row
+// kernel's sums are short already: a lane's share of the row, then a tree over the warp).
+//
 // Same contraction as the reference's src/decode.cu:202-236 (one token) and
 // src/prefill.cu:124-161 (one block per output element, W re-read for every token);
 // weights are [out, in] row-major, no bias.
@@ -17,6 +23,7 @@
 // ---------------------------------------------------------------------------
 namespace {
 constexpr int BM = 128, BN = 128, BK = 16, PAD = 4, TILE_THREADS = 256;
+constexpr int FLUSH_TILES = 8;      // partial sums over FLUSH_TILES * BK = 128 k are moved into the totals
 
 template <typename T, typename OT>
 __global__ void __launch_bounds__(TILE_THREADS)
@@ -30,14 +37,15 @@ gemm_tile_kernel(const T* __restrict__ X, const T* __restrict__ W, OT* __restric
     const int t = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int ty = t / 16, tx = t % 16;
-    float acc[8][8];
+    float acc[8][8], total[8][8];
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+        for (int j = 0; j < 8; j++) acc[i][j] = total[i][j] = 0.f;
 
     // loader mapping: 256 threads cover 64 rows x 4 groups of 4 k; two passes for 128 rows
     const int lr = t / 4, lk = (t % 4) * 4;
+    int since_flush = 0;
     for (int k0 = 0; k0 < K; k0 += BK) {
 #pragma unroll
         for (int p = 0; p < 2; p++) {
@@ -65,8 +73,19 @@ gemm_tile_kernel(const T* __restrict__ X, const T* __restrict__ W, OT* __restric
 #pragma unroll
                 for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
+        if (++since_flush == FLUSH_TILES) {
+            since_flush = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) { total[i][j] += acc[i][j]; acc[i][j] = 0.f; }
+        }
         __syncthreads();
     }
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] += total[i][j];
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
