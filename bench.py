@@ -409,12 +409,24 @@ def main() -> int:
     ap.add_argument("--range", action="store_true",
                     help="also the mean decode rate while the batch grows from 2,048 positions to --context (some 20 s more)")
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
-                    "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K, attn_decode, attn_decode_b64, attn_decode_b1, attn_prefill")
+                    "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K, attn_decode, attn_decode_b64, attn_decode_b1, attn_prefill; "
+                    "ref:all or ref:<case> times the reference's kernel recompiled for sm_100a beside this library's")
     ap.add_argument("--workload", default="", choices=["", "8b", "32b"],
                     help="run one of the larger described workloads end to end instead (8B or 32B shape)")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--eager", action="store_true", help="with --kernel: plain launches instead of a graph replay")
     args = ap.parse_args()
+    if args.kernel.startswith("ref:"):
+        # the reference's own kernels, recompiled for sm_100a, beside this library's (baseline/ref_kernels.py)
+        from baseline import ref_kernels
+        names = ref_kernels.CASES if args.kernel == "ref:all" else [args.kernel[4:]]
+        for n in names:
+            sampler = ClockSampler()
+            sampler.start()
+            row = ref_kernels.run(n, args.reps)
+            row["clocks"] = sampler.stop()
+            print(json.dumps(row), flush=True)
+        return 0
     if args.kernel:
         print(json.dumps(run_kernel(args.kernel, args.reps, args.eager)))
         return 0
