@@ -9,7 +9,12 @@ the whole batch.  ``value`` is decoded tokens per second over K steps timed on t
 device with CUDA events (token ids chosen beforehand, no host round trip inside);
 ``e2e`` is the same through the Python entry point ``LLM.generate`` (host token ids in,
 sampled token ids read back every step).  The line also carries a 2,048-token prefill,
-the decode step's share of the memory roofline, and decode rates at batch 1 and 64.
+the decode step's share of the memory roofline, and under ``points`` decode rates at
+batch 1 and 64, the mean rates while 1, 8 and 64 sequences grow from 2,048 to the context
+length (sampled at 13 lengths), 8 sequences at 32,768 positions, and 8 sequences at 8,192
+with the layer sizes of Qwen3-8B.  ``fp32_check`` is the float32 engine with two layers of
+the same sizes against the plain implementation of tests/plain (float64): the largest
+error of the logits of a 512-token prompt's last place and of 8 decoded places.
 Every decode step reads all weights (8 GB) and the live sequences' cache, far more than
 the 126 MB L2, so nothing is flushed between steps.
 """
@@ -39,6 +44,7 @@ QWEN3_32B = dict(QWEN3_4B, num_hidden_layers=64, hidden_size=5120, num_attention
                  tie_word_embeddings=False)
 FULL_LAYERS = 36
 CONTEXT = 8192
+LONG_CONTEXT = 32768
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -179,6 +185,81 @@ def time_decode_range(engine, batch, start, end, seed=0):
             engine.end_sequence(s)
 
 
+def time_decode_sampled_range(engine, batch, lo, hi, points=13, steps=16, warm=3, seed=0):
+    """Mean decode step time while ``batch`` sequences grow from ``lo`` to ``hi`` positions, sampled:
+    at ``points`` evenly spaced lengths the step is timed over ``steps`` steps that end there (after
+    ``warm`` untimed ones); between the samples the sequences are brought forward by whole pieces
+    of tokens (a step that continues every sequence by several hundred tokens).  The mean weighs
+    the two ends half (trapezoid rule): step time is close to linear in the length."""
+    import torch
+    vocab = engine.spec.vocab_size
+    slots = [engine.new_sequence() for _ in range(batch)]
+    times = []
+    try:
+        cur = 0
+        for j in range(points):
+            target = lo + (hi - lo) * j // (points - 1)
+            upto = target - steps - warm
+            engine.step([(s, random_tokens(upto - cur, vocab, seed + 31 * j + i)) for i, s in enumerate(slots)], [[] for _ in slots])
+            cur = upto
+            toks = [random_tokens(steps + warm, vocab, seed + 4000 + 31 * j + i) for i in range(batch)]
+            for t in range(warm):
+                engine.step([(s, [toks[i][t]]) for i, s in enumerate(slots)], None)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for t in range(warm, warm + steps):
+                engine.step([(s, [toks[i][t]]) for i, s in enumerate(slots)], None)
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) / steps)
+            cur = target
+        w = [0.5] + [1.0] * (points - 2) + [0.5]
+        return sum(x * y for x, y in zip(w, times)) / sum(w)
+    finally:
+        for s in slots:
+            engine.end_sequence(s)
+
+
+def fp32_check():
+    """The float32 engine (every kernel in true 32-bit) with two layers of the benchmark's sizes
+    against the plain implementation in float64, which gets the same tensors: a 512-token prompt,
+    then 8 tokens one by one.  The bound is the tests': |got - want| <= 1e-5 + 1e-4 |want|."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from plain import qwen3_plain as plain
+    from toyinfer_b200 import models  # noqa: F401
+    from toyinfer_b200.config import Qwen3Config, resolve_architecture
+    from toyinfer_b200.engine import Engine
+    from toyinfer_b200.parts.model import DecoderModel
+    from toyinfer_b200.weights import random_parameters
+    import toyinfer_b200.kernels as K
+    cfg = dict(QWEN3_4B, num_hidden_layers=2)
+    prompt, dec = 512, 8
+    spec = resolve_architecture("Qwen3ForCausalLM").describe(Qwen3Config.from_dict(dict(cfg)))
+    model = DecoderModel(spec, torch.float32, "cuda")
+    weights = random_parameters(model.param_specs(), 5, torch.bfloat16, "cuda")
+    model.bind({k: v.float() for k, v in weights.items()})
+    eng = Engine(model, max_tokens=1024, max_batch=1, max_seq_len=1024)
+    ids = random_tokens(prompt + dec, cfg["vocab_size"], 55)
+    slot = eng.new_sequence()
+    got = [eng.step([(slot, ids[:prompt])], None).clone()]
+    for t in range(prompt, prompt + dec):
+        got.append(eng.step([(slot, [ids[t]])], None).clone())
+    K.check_status()
+    got = torch.cat(got).double()
+    want = plain.forward(weights, cfg, ids, None, rows=list(range(prompt - 1, prompt + dec))).to(got.device)
+    err = (got - want).abs()
+    over = (err / (1e-5 + 1e-4 * want.abs())).max().item()
+    out = {"layers": 2, "prompt": prompt, "decoded": dec, "logits": int(got.numel()), "max_abs_err": float(f"{err.max().item():.3e}"),
+           "max_abs_logit": round(want.abs().max().item(), 3), "rtol": 1e-4, "atol": 1e-5, "worst_err_over_bound": round(over, 3),
+           "ok": bool(over <= 1.0), "against": "tests/plain/qwen3_plain.py in float64"}
+    eng.end_sequence(slot)
+    del eng, model, weights, got, want, err
+    torch.cuda.empty_cache()
+    return out
+
+
 def time_prefill(engine, tokens, reps=3):
     import torch
     vocab = engine.spec.vocab_size
@@ -209,9 +290,11 @@ def run_ours(args):
     cfg["num_hidden_layers"] = args.layers
     batch, ctx = args.batch, args.context
     K.library()
+    check = None if args.skip_points else fp32_check()
     big = max(batch, 64 if not args.skip_points else batch)
-    max_tokens = max(batch * (ctx + 64), (64 * (PREFILL_TOKENS + 256)) if not args.skip_points else 0)
-    llm = LLM(config=cfg, seed=0, dtype="bfloat16", max_seq_len=ctx, max_batch=big, max_tokens=max_tokens)
+    max_tokens = max(batch * (ctx + 64), (64 * (ctx + 64)) if not args.skip_points else 0)
+    limit = ctx if args.skip_points else max(ctx, LONG_CONTEXT)
+    llm = LLM(config=cfg, seed=0, dtype="bfloat16", max_seq_len=limit, max_batch=big, max_tokens=max_tokens)
     engine = llm.engine
 
     sampler = ClockSampler()
@@ -245,7 +328,7 @@ def run_ours(args):
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
             "tied": True, "global_batch": batch, "seq_len": ctx, "context": ctx, "prefill_tokens": PREFILL_TOKENS,
             "points_context": PREFILL_TOKENS, "parallelism": "single GPU", "l2": "inputs larger than L2, no flush",
-            "cuda_graph": True, "peaks": pk["source"],
+            "cuda_graph": True, "peaks": pk["source"], "range_points": "13 lengths from 2048 to context, 16 steps each",
         },
         "e2e": {"value": round(e2e_value, 2) if e2e_value else None, "unit": "tokens/s",
                 "steps": st.decode_steps, "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": batch * 4},
@@ -269,7 +352,23 @@ def run_ours(args):
         for b in (1, 64):
             ms_b, _ = time_decode(engine, b, PREFILL_TOKENS + args.steps + args.warmup, args.steps, args.warmup, seed=b)
             pts[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 2)
+        # tokens per second averaged over the lengths from the prompt's 2,048 positions to the context
+        for b in (1, 8, 64):
+            ms_b = time_decode_sampled_range(engine, b, PREFILL_TOKENS, ctx, seed=10 * b)
+            pts[f"range_b{b}"] = round(b * 1000.0 / ms_b, 2)
+        ms_l, _ = time_decode(engine, 8, LONG_CONTEXT, args.steps, args.warmup, seed=3)
+        pts[f"decode_b8_ctx{LONG_CONTEXT}"] = round(8 * 1000.0 / ms_l, 2)
+        pts[f"hbm_frac_b8_ctx{LONG_CONTEXT}"] = round(bytes_decode(cfg, 8, LONG_CONTEXT - args.steps / 2.0) / (ms_l * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        del engine
+        llm = None
+        torch.cuda.empty_cache()
+        # the same step with the layer sizes of Qwen3-8B (hidden 4,096, intermediate 12,288, untied head)
+        llm8 = LLM(config=dict(QWEN3_8B), seed=0, dtype="bfloat16", max_seq_len=ctx, max_batch=8, max_tokens=8 * (ctx + 64))
+        ms_8, _ = time_decode(llm8.engine, 8, ctx, args.steps, args.warmup, seed=4)
+        pts["shape8b_decode_b8"] = round(8 * 1000.0 / ms_8, 2)
+        pts["shape8b_hbm_frac_b8"] = round(bytes_decode(QWEN3_8B, 8, ctx - args.steps / 2.0) / (ms_8 * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         out["points"] = pts
+        out["fp32_check"] = check
     return out
 
 
