@@ -28,6 +28,9 @@ DRIVER = r'''
 #include "swiglu_test_common.h"
 #include "flash_attention_test_common.h"
 #include "precompute_freq_test_common.h"
+#include "gemv_test_common.h"
+#include "attention_test_common.h"
+#include "add_test_common.h"
 
 static std::vector<float> q(const std::vector<float>& v) { return kernel_test::to_float(kernel_test::to_bf16(v)); }
 static void dump(const char* name, const std::vector<float>& v, size_t n, bool last = false) {
@@ -75,7 +78,31 @@ int main() {
         precompute_freq_test::Case c; c.head_dim = 32; c.buffer_size = 16; c.theta = 1000000.0f;
         std::vector<float> init(16, 0.f);
         auto y = precompute_freq_test::build_expected(c, init);
-        printf(" \"inv_freq\": {\n  \"head_dim\": 32, \"theta\": 1000000.0,\n"); dump("y", y, 16, true); printf(" }\n");
+        printf(" \"inv_freq\": {\n  \"head_dim\": 32, \"theta\": 1000000.0,\n"); dump("y", y, 16, true); printf(" },\n");
+    }
+    {   // matrix times vector, 5 rows of 12: weights [out, in] row-major (src/decode.cu:202-236)
+        auto c = gemv_test::make_case("g", 5, 12, 5, 0.31f, 0.17f);
+        auto x = q(c.x), w = q(c.w);
+        auto y = gemv_test::reference_sum(c, x, w);
+        printf(" \"gemv\": {\n  \"rows\": 5, \"cols\": 12,\n"); dump("x", x, 12); dump("w", w, 60); dump("y", y, 5, true); printf(" },\n");
+    }
+    {   // one token's attention over cache rows 0..pos: scores, softmax, weighted values
+        // (src/decode.cu:401-432, :471-532, :598-628); 6 heads over 2 kv heads of 8, position 10 of 16 rows
+        auto c = attention_test::make_attention_case("g", 6, 2, 8, 10, 16, 0.27f, 0.19f);
+        auto qq = q(c.q), k = q(c.ks), v = q(c.vs);
+        std::vector<float> zeros(6 * 16, 0.f);
+        auto scores = attention_test::reference_qk_scores(c, qq, k, zeros);
+        auto probs = attention_test::reference_attention_score(c, qq, k);
+        auto o = attention_test::reference_attention_buffer(c, probs, v);
+        printf(" \"decode_attention\": {\n  \"heads\": 6, \"kv_heads\": 2, \"head_dim\": 8, \"pos\": 10, \"rows\": 16,\n");
+        dump("q", qq, qq.size()); dump("k", k, k.size()); dump("v", v, v.size()); dump("scores", scores, scores.size());
+        dump("probs", probs, probs.size()); dump("o", o, o.size(), true); printf(" },\n");
+    }
+    {   // residual sum, rounded to bfloat16 (src/decode.cu:7-22)
+        auto c = add_test::make_case("g", 50, 50, false, 0.21f, 0.33f, 0.0f);
+        auto r = q(c.residual), h = q(c.hidden);
+        auto y = add_test::apply_reference(h, r, 50);
+        printf(" \"residual_add\": {\n"); dump("residual", r, 50); dump("hidden", h, 50); dump("y", y, 50, true); printf(" }\n");
     }
     printf("}\n");
     return 0;
