@@ -151,3 +151,42 @@ def test_command_line_with_random_weights(tmp_path):
         assert r.returncode == 0, r.stderr
         runs.append([json.loads(l)["tokens"] for l in r.stdout.splitlines() if l.startswith("{")])
     assert runs[0] == runs[1] and [len(t) for t in runs[0]] == [5, 5]
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_detail_time_stages_add_up_to_the_steps(model_folders, graph):
+    """With detail_time every step is bracketed by CUDA events and, where a step runs as plain
+    launches, so are its stages (embedding, each layer's attention block and feed-forward block,
+    head).  The stages are back to back on the stream, so their device times add up to the step's
+    within 10 %.  Steps replayed from a CUDA graph are timed whole; their stages read N/A."""
+    from toyinfer_b200 import LLM, SamplingParams
+    from toyinfer_b200.engine.cli import detail_lines
+    name = "D"
+    layers = TINY[name]["num_hidden_layers"]
+    llm = LLM(model_folders[name], dtype="bfloat16", max_seq_len=512, max_batch=4, max_tokens=64 * 32,
+              enable_cuda_graph=graph, detail_time=True)
+    prompts = prompts_for(name, [300, 120, 41], seed=61)
+    llm.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=3, ignore_eos=True)      # warm-up: first launches
+    llm.engine.tracer.reset()
+    llm.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=9, ignore_eos=True)
+    rep = llm.timing_report()
+    n_pre, t_pre = rep["prefill_step"]
+    assert n_pre == 1 and t_pre > 0
+    assert rep["prefill.layer.attn_block"][0] == layers and rep["prefill.layer.mlp_block"][0] == layers
+    stages = sum(rep[k][1] for k in ("prefill.embed", "prefill.layer.attn_block", "prefill.layer.mlp_block", "prefill.head"))
+    assert abs(stages - t_pre) <= 0.10 * t_pre, (stages, t_pre)
+    inner = sum(rep[k][1] for k in ("prefill.mixer.qkv", "prefill.mixer.attention", "prefill.mixer.out"))
+    assert inner <= rep["prefill.layer.attn_block"][1] * 1.001
+    n_dec, t_dec = rep["decode_step"]
+    assert n_dec == llm.last_stats.decode_steps and t_dec > 0
+    assert rep["sample"][0] >= n_dec
+    lines = "\n".join(detail_lines(llm.last_stats, rep, graph))
+    if graph:
+        assert "decode.layer.attn_block" not in rep
+        assert "decode.layer.attn_block=N/A (CUDA graph enabled)" in lines
+    else:
+        assert rep["decode.layer.attn_block"][0] == layers * n_dec
+        stages = sum(rep[k][1] for k in ("decode.embed", "decode.layer.attn_block", "decode.layer.mlp_block", "decode.head"))
+        assert abs(stages - t_dec) <= 0.10 * t_dec, (stages, t_dec)
+        assert "N/A" not in lines
+    assert "prefill_total=" in lines and "decode_forward_total=" in lines

@@ -37,12 +37,14 @@ class _Stepper:
         return self.engine.step(entries, want)
 
     def sample(self, logits, keys, steps) -> List[int]:
-        return self.sampler.sample(logits, keys, steps).tolist()   # device -> host, waits for the step
+        with self.engine.tracer.range("sample"):
+            return self.sampler.sample(logits, keys, steps).tolist()   # device -> host, waits for the step
 
     # -- the next step started from tokens that are still on the device ---------------------
     def draw(self, logits, keys, steps):
         """Draws on the device; the handle is read later, beside whatever was started since."""
-        ids = self.sampler.sample(logits, keys, steps)
+        with self.engine.tracer.range("sample"):
+            ids = self.sampler.sample(logits, keys, steps)
         if ids.device.type != "cuda":
             return ids, None
         drawn = torch.cuda.Event()
@@ -89,7 +91,11 @@ class LLM:
     def __init__(self, model_dir: Optional[str] = None, *, config: Optional[dict] = None, seed: int = 0,
                  dtype="bfloat16", max_seq_len: Optional[int] = None, max_batch: int = 64,
                  max_tokens: Optional[int] = None, enable_cuda_graph: bool = True,
-                 use_dedicated_prefill: bool = True, device="cuda"):
+                 use_dedicated_prefill: bool = True, detail_time: bool = False, nvtx: bool = True, device="cuda"):
+        """``detail_time``: CUDA events around every step and, where steps run as plain launches
+        (prompts always; single-token steps with ``enable_cuda_graph=False``), around the stages of
+        every layer; ``timing_report()`` returns their sums.  ``nvtx``: NVTX ranges with the same
+        names, for a profiler's timeline."""
         if (model_dir is None) == (config is None):
             raise ValueError("give either model_dir or config (random weights)")
         from .. import models  # noqa: F401
@@ -112,12 +118,20 @@ class LLM:
         msl = int(min(max_seq_len or limit, limit))
         if max_tokens is None:
             max_tokens = default_max_tokens({}, model, max_batch, msl)
+        from ..tracing import Tracer
         self.engine = Engine(model, max_tokens=max_tokens, max_batch=max_batch, max_seq_len=msl,
-                             use_cuda_graph=enable_cuda_graph)
+                             use_cuda_graph=enable_cuda_graph,
+                             tracer=Tracer(nvtx=nvtx and model.device.type == "cuda", timing=detail_time))
         self.config = cfg
         self._stepper = _Stepper(self.engine, None)
         self.use_dedicated_prefill = use_dedicated_prefill
         self.last_stats: Optional[GenerationStats] = None
+
+    def timing_report(self):
+        """name -> (count, total device milliseconds) of the ranges timed since the last reset
+        (empty without ``detail_time``): ``prefill_step``, ``prefill.layer.attn_block``,
+        ``prefill.layer.mlp_block``, ``prefill.mixer.qkv`` ..., ``decode_step``, ``sample``."""
+        return self.engine.tracer.report()
 
     @property
     def stop_token_ids(self):

@@ -89,6 +89,7 @@ class StepBatch:
     host_slots: List[int] = field(default_factory=list)
     host_starts: List[int] = field(default_factory=list)
     host_new: List[int] = field(default_factory=list)
+    trace: object = None      # the engine's tracing.Tracer (parts wrap their stages in its ranges); None: no tracing
 
 
 def fill_batch(buf: BatchBuffers, mode: str, slots: Sequence[int], starts: Sequence[int],

@@ -56,7 +56,9 @@ def build_parser() -> argparse.ArgumentParser:
                          "so there is nothing left to put on side streams")
     ap.add_argument("--enable_cuda_graph", type=_flag, default=True,
                     help="Enable CUDA graph capture/replay for decode")
-    ap.add_argument("--detail_time", type=_flag, default=False, help="Print prefill and decode timings")
+    ap.add_argument("--detail_time", type=_flag, default=False,
+                    help="Print prefill and decode timings: device time of every step and, where steps are "
+                         "plain launches (prompts; decode with --enable_cuda_graph 0), of each layer's stages")
     ap.add_argument("--bench", default="", choices=["", "short", "long"],
                     help="Bench: a 64-token (short) or 4096-token (long) synthetic prompt, one turn")
     ap.add_argument("--temperature", type=float, default=0.6)
@@ -74,6 +76,36 @@ def build_parser() -> argparse.ArgumentParser:
     return ap
 
 
+def detail_lines(st, report, cuda_graph: bool) -> List[str]:
+    """The ``[detail]`` block in the reference's manner (src/engine_runtime.cpp:207-261): host totals
+    of the generation loop, then device times summed over steps and layers.  Stages inside a step
+    that was replayed from a CUDA graph cannot be timed; the reference prints N/A for them too."""
+    def ms(name):
+        n, total = report.get(name, (0, 0.0))
+        return n, total
+    out = []
+    pre = st.prompt_tokens / st.prefill_seconds if st.prefill_seconds else 0.0
+    dec = st.decode_seconds / st.decode_steps * 1e3 if st.decode_steps else 0.0
+    out.append(f"[detail] host: prefill {st.prefill_seconds * 1e3:.1f} ms ({pre:.0f} tok/s), decode {st.decode_steps} steps, "
+               f"{dec:.3f} ms/step, batches {st.batches}")
+    n, t = ms("prefill_step")
+    out.append(f"[detail] prefill_total={t:.3f} ms ({n} steps)")
+    for stage in ("embed", "layer.attn_block", "mixer.qkv", "mixer.attention", "mixer.out", "layer.mlp_block", "head"):
+        n, t = ms("prefill." + stage)
+        out.append(f"[detail] prefill.{stage}={t:.3f} ms ({n} ranges)")
+    n, t = ms("decode_step")
+    out.append(f"[detail] decode_forward_total={t:.3f} ms ({n} steps, {t / n if n else 0.0:.3f} ms each)")
+    for stage in ("layer.attn_block", "mixer.qkv", "mixer.attention", "mixer.out", "layer.mlp_block", "head"):
+        n, t = ms("decode." + stage)
+        if n == 0 and cuda_graph:
+            out.append(f"[detail] decode.{stage}=N/A (CUDA graph enabled)")
+        else:
+            out.append(f"[detail] decode.{stage}={t:.3f} ms ({n} ranges)")
+    n, t = ms("sample")
+    out.append(f"[detail] token_sample={t:.3f} ms ({n} draws, {t / n if n else 0.0:.3f} ms each)")
+    return out
+
+
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
     if args.beam_size != 1:
@@ -89,7 +121,8 @@ def main(argv=None) -> int:
     from .. import LLM, SamplingParams
 
     common = dict(dtype=args.dtype, max_seq_len=args.max_seq_len or None, max_batch=args.max_batch,
-                  enable_cuda_graph=args.enable_cuda_graph, use_dedicated_prefill=args.use_dedicated_prefill)
+                  enable_cuda_graph=args.enable_cuda_graph, use_dedicated_prefill=args.use_dedicated_prefill,
+                  detail_time=args.detail_time)
     if args.random:
         with open(args.random) as f:
             llm = LLM(config=json.load(f), seed=args.seed, **common)
@@ -116,10 +149,8 @@ def main(argv=None) -> int:
     print(f"[perf] prompt_tokens={st.prompt_tokens} generated_tokens={st.generated_tokens} "
           f"wall={wall:.3f}s tokens/s={total / wall:.2f}", file=sys.stderr)
     if args.detail_time:
-        pre = st.prompt_tokens / st.prefill_seconds if st.prefill_seconds else 0.0
-        dec = st.decode_seconds / st.decode_steps * 1e3 if st.decode_steps else 0.0
-        print(f"[detail] prefill {st.prefill_seconds * 1e3:.1f} ms ({pre:.0f} tok/s), decode {st.decode_steps} steps, "
-              f"{dec:.3f} ms/step, batches {st.batches}", file=sys.stderr)
+        for line in detail_lines(st, llm.timing_report(), args.enable_cuda_graph):
+            print(line, file=sys.stderr)
     return 0
 
 

@@ -28,6 +28,7 @@ import torch
 from ..cache import CacheError, CacheManager, PAGE, pages_for
 from ..config.registry import load_config
 from ..parts.model import DecoderModel, ModelSpec
+from ..tracing import Tracer
 from ..weights import load_parameters, random_parameters
 from .batch import BatchBuffers, StepBatch, fill_batch
 
@@ -59,8 +60,10 @@ def _bucket(n: int, cap: int) -> int:
 class Engine:
     def __init__(self, model: DecoderModel, max_tokens: int, max_batch: int = 64,
                  max_seq_len: Optional[int] = None, n_slots: Optional[int] = None,
-                 use_cuda_graph: bool = True):
+                 use_cuda_graph: bool = True, tracer: Optional[Tracer] = None):
         self.model = model
+        # NVTX ranges around steps and stages by default; device timers when the caller asks (tracing.py)
+        self.tracer = tracer if tracer is not None else Tracer(nvtx=torch.device(model.device).type == "cuda")
         self.spec: ModelSpec = model.spec
         self.device = model.device
         self.dtype = model.dtype
@@ -182,32 +185,36 @@ class Engine:
             self.cache.reserve(s, st + len(t))      # CacheError when the cache is full
         self.cache.flush()
 
+        logits = self._run(mode, slots, starts, tokens, want, token_source)
+        for s, st, t in zip(slots, starts, tokens):
+            self.cache.commit(s, st + len(t))
+        return logits
+
+    def _run(self, mode, slots, starts, tokens, want, token_source):
+        n = len(slots)
         if mode == "extend" and self.use_cuda_graph:
             logits_all = self._decode_graph(slots, starts, tokens, token_source)
             rows = [i for i, w in enumerate(want) if w]
             if not rows:
-                logits = None
-            elif len(rows) == n:
-                logits = logits_all[:n]
-            else:
-                logits = logits_all[torch.tensor(rows, device=self.device)]
-        else:
-            batch = self._eager_batch(mode, slots, starts, tokens)
-            if token_source is not None:
-                batch.token_ids[:n].copy_(token_source)
+                return None
+            if len(rows) == n:
+                return logits_all[:n]
+            return logits_all[torch.tensor(rows, device=self.device)]
+        batch = self._eager_batch(mode, slots, starts, tokens)
+        if token_source is not None:
+            batch.token_ids[:n].copy_(token_source)
+        rows, o = [], 0
+        for w, t in zip(want, tokens):
+            rows.extend(o + p for p in w)
+            o += len(t)
+        rows_dev = torch.tensor(rows, dtype=torch.int32, device=self.device) if rows else None
+        # the step's range holds the launches of the model only, not the host's preparation of the batch
+        with self.tracer.step("decode" if mode == "extend" else "prefill"):
             h, delta = self.model.forward_hidden(batch, self.memories)
-            rows, o = [], 0
-            for w, t in zip(want, tokens):
-                rows.extend(o + p for p in w)
-                o += len(t)
-            if rows:
-                rows_dev = torch.tensor(rows, dtype=torch.int32, device=self.device)
-                logits = self.model.logits(h, delta, rows_dev)
-            else:
-                logits = None
-        for s, st, t in zip(slots, starts, tokens):
-            self.cache.commit(s, st + len(t))
-        return logits
+            if rows_dev is None:
+                return None
+            with self.tracer.range("head"):
+                return self.model.logits(h, delta, rows_dev)
 
     # -- accounting for measurements ----------------------------------------------------
     def launches_per_step(self, n_seq: int) -> int:
@@ -233,7 +240,9 @@ class Engine:
         buf = self._eager_bufs.get(key)
         if buf is None:
             buf = self._eager_bufs[key] = BatchBuffers(key[0], key[1], self.device)
-        return fill_batch(buf, mode, slots, starts, tokens, self.cache.scratch_slot, self.max_seq_len)
+        batch = fill_batch(buf, mode, slots, starts, tokens, self.cache.scratch_slot, self.max_seq_len)
+        batch.trace = self.tracer
+        return batch
 
     def _decode_graph(self, slots, starts, tokens, token_source=None) -> torch.Tensor:
         n = len(slots)
@@ -277,13 +286,15 @@ class _DecodeGraph:
     def _body(self, batch: StepBatch) -> torch.Tensor:
         e = self.engine
         h, delta = e.model.forward_hidden(batch, e.memories)
-        return e.model.logits(h, delta, self.rows)
+        with e.tracer.range("head"):
+            return e.model.logits(h, delta, self.rows)
 
     def run(self, slots, starts, tokens, token_source=None) -> torch.Tensor:
         e = self.engine
         pad = self.bucket - len(slots)
         batch = fill_batch(self.buf, "extend", slots, starts, tokens, e.cache.scratch_slot,
                            self.plan_len, pad_seqs=pad)
+        batch.trace = e.tracer
         if token_source is not None:
             batch.token_ids[:len(slots)].copy_(token_source)      # after the upload, before the replay
         if self.graph is None:
@@ -291,7 +302,14 @@ class _DecodeGraph:
             # one-time set-up outside the capture
             from .. import kernels as K
             before = K.launch_count
-            out = self._body(batch)
+            # the stages inside this run and inside the capture are not timed: replays have none
+            was_capturing = e.tracer.capturing
+            with e.tracer.step("decode"):
+                e.tracer.capturing = True
+                try:
+                    out = self._body(batch)
+                finally:
+                    e.tracer.capturing = was_capturing
             self.launches = K.launch_count - before
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()
@@ -301,14 +319,17 @@ class _DecodeGraph:
             gc.collect()
             was_enabled = gc.isenabled()
             gc.disable()
+            e.tracer.capturing = True
             try:
                 with torch.cuda.graph(g):
                     self.logits = self._body(batch)
             finally:
+                e.tracer.capturing = was_capturing
                 if was_enabled:
                     gc.enable()
             self.graph = g
             return out
-        self.graph.replay()
+        with e.tracer.step("decode"):
+            self.graph.replay()
         e.graph_replays += 1
         return self.logits

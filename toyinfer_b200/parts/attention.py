@@ -32,6 +32,7 @@ from typing import Dict, Optional
 import torch
 
 from .. import kernels as K
+from ..tracing import ranged
 from .base import BuildContext, KVRequest, Mixer, ParamSpec, register_part
 from .norms import RMSNorm
 
@@ -122,19 +123,26 @@ class GQAAttention(Mixer):
                 f"{mem.n_kv_heads} kv heads of {mem.head_dim}"
             )
         M = x.shape[0]
-        qkv = K.linear(x, self.w_qkv)
+        with ranged(batch, "mixer.qkv"):
+            qkv = K.linear(x, self.w_qkv)
         q = qkv[:, : self.q_dim].view(M, nh, hd)
         if self.own_kv:
             k = qkv[:, self.q_dim : self.q_dim + self.kv_dim].view(M, nkv, hd)
             v = qkv[:, self.q_dim + self.kv_dim :].view(M, nkv, hd)
         else:
             k = v = None
+        with ranged(batch, "mixer.attention"):
+            a = self._attend(q, k, v, batch, mem, shared)
+        with ranged(batch, "mixer.out"):
+            return K.linear(a.view(M, self.q_dim), self.w_o, after_attention=True)
+
+    def _attend(self, q, k, v, batch, mem, shared) -> torch.Tensor:
+        """Per-head norm, position encoding, cache store and attention: q[M, heads, d] -> [M, heads, d]."""
         tables = self.pos.rotary_tables() if self.pos is not None else None
         if batch.mode == "extend" and (self.pos is None or tables is not None):
             # one token each: norm, rotation, cache store and attention from the projection's output
-            a = K.attention_decode_step(q, k, v, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0, tables, mem,
-                                        self.scale, self.window, batch)
-            return K.linear(a.view(M, self.q_dim), self.w_o, after_attention=True)
+            return K.attention_decode_step(q, k, v, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0, tables, mem,
+                                           self.scale, self.window, batch)
         # In a ring, a long enough run of new keys overwrites positions that the run's first
         # queries still read: such a step stores after its attention.
         store_first = self.own_kv and not (batch.mode == "mixed" and mem.ring_rows > 0)
@@ -150,24 +158,23 @@ class GQAAttention(Mixer):
             K.qk_norm_rope_store(q, k, v, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0,
                                  tables, batch, mem if store_first else None)
         if batch.mode == "extend":
-            a = K.attention_decode(q, mem, self.scale, self.window, batch)
+            return K.attention_decode(q, mem, self.scale, self.window, batch)
+        if self.own_kv:
+            shared["k_new"], shared["v_new"] = k, v
         else:
-            if self.own_kv:
-                shared["k_new"], shared["v_new"] = k, v
+            k, v = shared["k_new"], shared["v_new"]
+        if batch.mode == "start":
+            a = K.attention_prefill(q, k, v, self.scale, self.window, batch)
+        else:
+            a = K.attention_chunk(q, k, v, mem, self.scale, self.window, batch)
+        if self.own_kv and not store_first:
+            def store(k=k, v=v):
+                K.qk_norm_rope_store(None, k, v, None, None, 0.0, None, batch, mem)
+            if "deferred" in shared:        # entries that borrow this memory still have to read it
+                shared["deferred"].append(store)
             else:
-                k, v = shared["k_new"], shared["v_new"]
-            if batch.mode == "start":
-                a = K.attention_prefill(q, k, v, self.scale, self.window, batch)
-            else:
-                a = K.attention_chunk(q, k, v, mem, self.scale, self.window, batch)
-            if self.own_kv and not store_first:
-                def store(k=k, v=v):
-                    K.qk_norm_rope_store(None, k, v, None, None, 0.0, None, batch, mem)
-                if "deferred" in shared:        # entries that borrow this memory still have to read it
-                    shared["deferred"].append(store)
-                else:
-                    store()
-        return K.linear(a.view(M, self.q_dim), self.w_o, after_attention=True)
+                store()
+        return a
 
 
 register_part("mixer", "gqa_attention", GQAAttention)

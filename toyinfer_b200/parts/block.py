@@ -39,11 +39,25 @@ class PreNormBlock(Block):
             c.bind(tensors)
 
     def forward(self, h, delta, batch, mem, shared):
+        trace = getattr(batch, "trace", None)
+        if trace is not None and trace.active:
+            # the two stages the reference times per layer (src/transformer.cpp:363, :428, :511, :595)
+            with trace.range("layer.attn_block"):
+                h, a = self._mix(h, delta, batch, mem, shared)
+            with trace.range("layer.mlp_block"):
+                return self._feed(h, a, batch)
+        h, a = self._mix(h, delta, batch, mem, shared)
+        return self._feed(h, a, batch)
+
+    def _mix(self, h, delta, batch, mem, shared):
         # h += delta (if any); x = norm(h) -- at once, or inside the reader's first product
         x = self.norm_in.add_pending(h, delta) if self.mixer.takes_pending_norm else self.norm_in.add_forward(h, delta)
         a = self.mixer.forward(x, batch, mem, shared)
         if isinstance(x, K.PendingNorm):
             h = x.hidden()
+        return h, a
+
+    def _feed(self, h, a, batch):
         # h += a; x = norm(h)
         x = self.norm_post.add_pending(h, a) if self.feed_forward.takes_pending_norm else self.norm_post.add_forward(h, a)
         m = self.feed_forward.forward(x, batch)

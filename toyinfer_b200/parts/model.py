@@ -22,6 +22,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 import torch
 
 from .. import kernels as K
+from ..tracing import ranged
 from .base import BuildContext, ParamSpec, Part, PartSpec, build_part
 
 
@@ -121,7 +122,8 @@ class DecoderModel(Part):
     def forward_hidden(self, batch, memories: Sequence[Any]):
         """Runs the given tokens through all scheduled blocks.  Returns (h, delta):
         the hidden state is h + delta."""
-        h = K.embed(self.embed, batch.token_ids)
+        with ranged(batch, "embed"):
+            h = K.embed(self.embed, batch.token_ids)
         delta = None
         shared: List[dict] = [dict() for _ in self.schedule]
         owners = [i if e.memory_of is None else e.memory_of for i, e in enumerate(self.schedule)]
