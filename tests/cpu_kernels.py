@@ -15,8 +15,16 @@ import torch
 import toyinfer_b200.kernels as K
 
 
-def embed(table, ids):
-    return table[ids.long()].clone()
+def embed(table, ids, scale=1.0):
+    out = table[ids.long()].clone()
+    return out if scale == 1.0 else (out.float() * scale).to(table.dtype)
+
+
+def logit_scale_cap(logits, scale=1.0, cap=0.0):
+    logits.mul_(scale)
+    if cap > 0:
+        logits.copy_(cap * torch.tanh(logits / cap))
+    return logits
 
 
 def rmsnorm(x, w, eps):
@@ -37,7 +45,7 @@ def gather_add(h, delta, rows):
     return out.to(h.dtype)
 
 
-def linear(x, w, out_dtype=None, after_attention=False):
+def linear(x, w, out_dtype=None, late_start=False):
     if isinstance(x, K.PendingNorm):
         x = x.tensor()
     return (x.float() @ w.float().T).to(out_dtype or x.dtype)
@@ -178,6 +186,6 @@ def argmax(logits):
 
 
 def install(monkeypatch) -> None:
-    for name in ("embed", "rmsnorm", "add_rmsnorm", "gather_add", "linear", "swiglu", "linear_swiglu", "qk_norm_rope_store",
+    for name in ("embed", "logit_scale_cap", "rmsnorm", "add_rmsnorm", "gather_add", "linear", "swiglu", "linear_swiglu", "qk_norm_rope_store",
                  "attention_prefill", "attention_chunk", "attention_decode", "attention_decode_step", "argmax"):
         monkeypatch.setattr(K, name, globals()[name])

@@ -170,3 +170,61 @@ def test_a_norm_left_to_the_readers_product_changes_no_result(cpu_engine, model_
     assert torch.equal(pending_steps, plain_steps)
     want = _plain_logits(model_folders[name], ids)
     torch.testing.assert_close(pending_steps, want[7:], rtol=1e-4, atol=1e-5)
+
+
+def test_other_ends_of_a_model(cpu_engine, model_folders, monkeypatch):
+    """A description with an embedding multiplier, a logit scale and soft cap, and no final norm is
+    built from the shipped embedding and head parts (nothing in the library is edited) and follows
+    the same layers computed plainly with those ends."""
+    import math
+    from toyinfer_b200.config.registry import load_config
+    from toyinfer_b200.parts import PartSpec
+    from toyinfer_b200.parts.model import DecoderModel
+    from toyinfer_b200.weights import load_parameters
+    cpu_engine("A")          # installs the CPU stand-ins
+    folder = model_folders["B"]
+    arch, cfg = load_config(folder)
+    spec = arch.describe(cfg)
+    scale, lscale, cap = math.sqrt(cfg.hidden_size), 0.5, 3.0
+    spec.embedding = PartSpec("token_table", {"vocab_size": cfg.vocab_size, "scale": scale})
+    spec.head = PartSpec("linear", {"vocab_size": cfg.vocab_size, "norm": None, "tied": False, "scale": lscale, "softcap": cap})
+    model = DecoderModel(spec, torch.float32, "cpu")
+    assert "model.norm.weight" not in model.param_specs()
+    model.bind(load_parameters(model.param_specs(), folder, torch.float32, model.device, ignorable=("model.norm.weight",)))
+    eng = Engine(model, max_tokens=512, max_batch=2)
+    ids = prompts_for("B", [23], seed=12)[0]
+    slot = eng.new_sequence()
+    got = torch.cat([eng.step([(slot, ids[:20])], [list(range(20))]), eng.step([(slot, ids[20:])], [[0, 1, 2]])])
+    w, c = plain.read_weights(folder), plain.read_config(folder)
+    h = plain.embedding(w["model.embed_tokens.weight"], ids) * scale
+    for layer in range(c["num_hidden_layers"]):
+        h = plain.decoder_layer(h, w, c, layer)
+    logits = plain.linear(h, w["lm_head.weight"]) * lscale
+    want = cap * torch.tanh(logits / cap)
+    torch.testing.assert_close(got.double(), want, rtol=1e-4, atol=1e-5)
+
+
+def test_sizes_no_kernel_takes_are_refused_when_the_model_is_built():
+    """Before any weight is read: heads of 6 elements (the attention kernels want a multiple of 4)
+    and 40 query heads of 128 per kv head in float32 (beyond the CUDA-core decode kernel)."""
+    from toyinfer_b200 import models  # noqa: F401
+    from toyinfer_b200.config import Qwen3Config, resolve_architecture
+    from toyinfer_b200.kernels import KernelError
+    from toyinfer_b200.parts.model import DecoderModel
+    arch = resolve_architecture("Qwen3ForCausalLM")
+    cfg = dict(TINY["A"], head_dim=6)
+    with pytest.raises(KernelError, match="head size 6"):
+        DecoderModel(arch.describe(Qwen3Config.from_dict(cfg)), torch.float32, "cpu")
+    cfg = dict(TINY["A"], head_dim=128, num_attention_heads=40, num_key_value_heads=1)
+    with pytest.raises(KernelError, match="40 query heads per kv head"):
+        DecoderModel(arch.describe(Qwen3Config.from_dict(cfg)), torch.float32, "cpu")
+    DecoderModel(arch.describe(Qwen3Config.from_dict(cfg)), torch.bfloat16, "cpu")       # the tensor-core kernels take it
+
+
+def test_default_cache_size_asks_the_cache_for_bytes_per_token():
+    from toyinfer_b200.cache import bytes_per_token
+    from toyinfer_b200.parts import KVRequest, StateRequest
+    reqs = [KVRequest(2, 16), None, KVRequest(8, 128, window=64), StateRequest((5,), torch.float32)]
+    assert bytes_per_token(reqs, torch.bfloat16) == 2 * 2 * 16 * 2 + 2 * 8 * 128 * 2
+    assert bytes_per_token(reqs, torch.float32) == 2 * (2 * 2 * 16 * 2 + 2 * 8 * 128 * 2)
+    assert bytes_per_token([None, StateRequest((5,))], torch.float32) == 0

@@ -53,6 +53,22 @@ def test_temperature_sampling_tiny_b(model_folders):
     assert one_by_one == together
 
 
+def test_nucleus_sampling_without_top_k(model_folders):
+    """temperature 0.7, top_k off, top_p 0.9 (a common setting that needs the sampler's tiered kernel)
+    through the entry point: the plain sampler's tokens, alone and in a batch."""
+    from toyinfer_b200 import LLM, SamplingParams
+    f = model_folders["A"]
+    params = SamplingParams(temperature=0.7, top_k=0, top_p=0.9, seed=77)
+    prompts = prompts_for("A", [6, 21, 3], seed=57)
+    llm = LLM(f, dtype="float32", max_seq_len=128, max_batch=4, max_tokens=1024)
+    got = [r.tokens for r in llm.generate(prompts, params, max_new_tokens=10, ignore_eos=True)]
+    w, cfg = _plain(f)
+    for i, p in enumerate(prompts):
+        assert got[i] == plain.generate(w, cfg, p, 10, temperature=0.7, top_k=0, top_p=0.9, seed=77, key=i), i
+    llm2 = LLM(f, dtype="float32", max_seq_len=128, max_batch=1, max_tokens=1024)
+    assert [r.tokens for r in llm2.generate(prompts, params, max_new_tokens=10, ignore_eos=True)] == got
+
+
 def test_bfloat16_greedy_follows_its_own_logits(model_folders):
     """In bfloat16 near-ties may resolve differently from the plain result, so each drawn
     token is checked against the plain logits of the engine's own sequence: it must be the

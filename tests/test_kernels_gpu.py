@@ -671,9 +671,13 @@ def test_attention_chunk_far_key_in_the_cache(K, dtype, hd):
 
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 32, 0), (5, 1, 48, 40), (32, 8, 128, 0),
-                                               (8, 1, 128, 100), (2, 2, 256, 0), (16, 1, 64, 0)])
+                                               (8, 1, 128, 100), (2, 2, 256, 0), (16, 1, 64, 0),
+                                               (4, 2, 64, 64), (8, 2, 128, 128), (3, 1, 32, 64)])
 def test_attention_decode(K, dtype, nh, nkv, hd, window):
-    lens = [1, 64, 65, 300, 129]
+    """The last three cases have a window equal to its ring (whole pages, no slack): the newest
+    position has overwritten the one that just left the window, and the first and the newest tile
+    of a sequence are the same physical page."""
+    lens = [1, 64, 65, 300, 129, 100]
     mem = make_mem(dtype, len(lens), nkv, hd, pages=24, window=window, dirty=float("nan"))
     ks = [randn(n, nkv, hd, seed=30 + i).to(dtype) for i, n in enumerate(lens)]
     vs = [randn(n, nkv, hd, seed=40 + i).to(dtype) for i, n in enumerate(lens)]
@@ -695,7 +699,8 @@ def test_attention_decode(K, dtype, nh, nkv, hd, window):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,window,norm", [(32, 8, 128, 0, "bf16"), (8, 1, 128, 100, "f32"), (16, 1, 64, 0, "bf16"),
-                                                   (40, 8, 128, 0, None), (4, 4, 64, 70, "bf16")])
+                                                   (40, 8, 128, 0, None), (4, 4, 64, 70, "bf16"),
+                                                   (4, 2, 64, 64, "bf16"), (8, 2, 128, 128, "f32")])
 @pytest.mark.parametrize("rotate", [True, False])
 def test_attention_decode_step_one_kernel_equals_two(K, nh, nkv, hd, window, norm, rotate):
     """The decode kernel with norm, rotation and cache store folded in against the rotate-and-store
@@ -886,6 +891,77 @@ def test_sample_matches_plain(K, V, top_k, top_p, temp):
             assert got[r] in alt, (r, got[r], want, alt)
 
 
+def exact_picks(x, temp, top_k, top_p, u, slack):
+    """The sampling rule (plain.sample's) in float64, vectorised, for every combination of u and
+    top_p moved by -slack, 0, +slack: the set of tokens between the lowest and the highest rank
+    picked.  Two float32 implementations that add up thousands of probabilities in different
+    orders are each within rounding of the exact running sum, but not of each other's token when the
+    draw falls next to a boundary; `slack` is that rounding expressed in units of the running sum."""
+    xs = x.double() / temp
+    V = xs.numel()
+    neg, order = torch.sort(-xs, stable=True)          # larger first, lower index first among equals
+    k = top_k if 0 < top_k < V else V
+    p = torch.exp(-neg[:k] - (-neg[0]))
+    cum = torch.cumsum(p / p.sum(), 0)
+    ranks = []
+    for tp in (top_p - slack, top_p, top_p + slack):
+        over = (cum > tp).nonzero()
+        n = int(over[0]) + 1 if len(over) else k
+        for uu in (u - slack, u, u + slack):
+            coin = min(max(uu, 0.0), 1.0) * cum[n - 1]
+            hit = (cum[:n] > coin).nonzero()
+            ranks.append(int(hit[0]) if len(hit) else n - 1)
+    return set(order[min(ranks):max(ranks) + 1].tolist()), k
+
+
+@pytest.mark.parametrize("V,top_k,top_p,temp,scale,quantum", [
+    (300, 0, 0.9, 0.8, 3.0, 0),            # a nucleus over the whole (small) vocabulary
+    (5000, 0, 0.5, 1.3, 3.0, 0),           # the cut falls in the first tier of 1,024
+    (5000, 3000, 0.97, 1.0, 3.0, 0),       # more candidates than one sort holds: three tiers
+    (2000, 1500, 1.0, 0.7, 3.0, 0),        # top_k above 1,024 without top_p
+    (20000, 0, 0.9, 5.0, 3.0, 0),          # a flat distribution: the nucleus spans a dozen tiers
+    (6000, 0, 0.9, 2.0, 3.0, 0.5),         # values on a grid of 0.5: ties everywhere, also across tier boundaries
+    (6000, 2500, 0.8, 2.0, 3.0, 1.0),
+])
+def test_sample_any_top_k_and_top_p(K, V, top_k, top_p, temp, scale, quantum):
+    """The settings beyond one shared-memory sort (top_p without top_k, top_k above 1,024), draw by
+    draw: the token is the plain (float32) sampler's, or the exact rule's for a draw within the
+    rounding of a float32 running sum over the kept entries (4 standard deviations of a random walk
+    of n roundings of 2^-25 each)."""
+    R = 4
+    x = randn(R, V, seed=73, scale=scale)
+    if quantum:
+        x = torch.round(x / quantum) * quantum
+    keys = torch.arange(200, 200 + R, dtype=torch.int64)
+    steps = torch.arange(3, 3 + R, dtype=torch.int32)
+    for seed in (1234, 99):
+        got = K.sample(dev(x), temp, top_k, top_p, seed, dev(keys), dev(steps)).cpu().tolist()
+        for r in range(R):
+            u = plain.uniform_from(seed, int(keys[r]), int(steps[r]))
+            if got[r] == plain.sample(x[r], temp, top_k, top_p, u):
+                continue
+            n = top_k if 0 < top_k < V else V
+            allowed, _ = exact_picks(x[r], temp, top_k, top_p, u, 4 * math.sqrt(n) * 2.0 ** -25)
+            assert got[r] in allowed, (seed, r, got[r], allowed)
+
+
+def test_sample_nucleus_over_a_large_vocabulary(K):
+    """top_k off and top_p 0.95 at the vocabulary of the benchmark model: a peaked row (the nucleus is
+    a handful of tokens) and a flat one (tens of tiers)."""
+    V = 151936
+    x = randn(2, V, seed=74, scale=1.5)
+    x[0, 777] = 14.0
+    x[0, 90000] = 13.0
+    keys = torch.tensor([5, 6], dtype=torch.int64)
+    steps = torch.tensor([0, 9], dtype=torch.int32)
+    got = K.sample(dev(x), 0.6, 0, 0.95, 7, dev(keys), dev(steps)).cpu().tolist()
+    for r in range(2):
+        u = plain.uniform_from(7, int(keys[r]), int(steps[r]))
+        allowed, _ = exact_picks(x[r], 0.6, 0, 0.95, u, 4 * math.sqrt(V) * 2.0 ** -25)
+        assert got[r] in allowed, (r, got[r], allowed)
+    assert got[0] in (777, 90000)
+
+
 def test_sample_distribution(K):
     """Many draws from a small distribution land where softmax(logits / T) says."""
     V, n = 8, 20000
@@ -897,3 +973,47 @@ def test_sample_distribution(K):
     freq = torch.bincount(got.long(), minlength=V).double() / n
     p = torch.softmax(logits.double() / 0.7, 0)
     assert (freq - p).abs().max() < 0.015
+
+
+# ---------------------------------------------------------------------------
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_library_usable(K):
+    """Every device-side wait of the library is bounded; a wait that runs out records a code in the
+    status word and the kernel returns.  Here the library's test kernel waits, with a limit of
+    10,000 polls, on a barrier nothing arrives on: it must come back, check_status() must raise with
+    the code of a wait for a load, the scratch that kernels share (tickets) must be clear again even
+    if something had left a ticket set, the next product must be right, and the word must be clear."""
+    from toyinfer_b200.kernels import KernelError, gemm
+    K.check_status()
+    x = randn(40, 512, seed=300).to(torch.bfloat16)
+    w = randn(2560, 512, seed=301, scale=0.05).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    K.linear(dev(x), dev(w))                            # makes sure the ticket array exists
+    tickets = gemm._tickets_for(torch.device("cuda", torch.cuda.current_device()))
+    tickets[3] = 1                                      # as a product that gave up half-way would leave it
+    assert K.testing_wait_runs_out(10000) is True
+    with pytest.raises(KernelError, match="status 1: a wait for a TMA load ran out"):
+        K.check_status()
+    assert int(tickets.abs().sum()) == 0
+    got = K.linear(dev(x), dev(w)).cpu().double()
+    torch.testing.assert_close(got, want, rtol=1.6e-2, atol=2e-2)
+    K.check_status()                                    # clear: no second report
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_embed_scale_and_logit_scale_cap(K, dtype):
+    V, H, M = 50, 72, 9
+    table = randn(V, H, seed=310).to(dtype)
+    ids = torch.randint(0, V, (M,), generator=torch.Generator().manual_seed(311), dtype=torch.int32)
+    got = K.embed(dev(table), dev(ids), 8.5).cpu().double()
+    want = plain.rnd(table[ids.long()].double() * 8.5, rnd_mode(dtype))
+    torch.testing.assert_close(got, want, **tol(dtype))
+    logits = randn(5, 1003, seed=312, scale=20.0)
+    buf = torch.full((5, 1100), 7.0)
+    buf[:, :1003] = logits
+    g = dev(buf)
+    out = K.logit_scale_cap(g[:, :1003], 0.25, 30.0)
+    want = 30.0 * torch.tanh(logits.double() * 0.25 / 30.0)
+    torch.testing.assert_close(out.cpu().double(), want, rtol=2e-6, atol=2e-6)
+    assert torch.all(g[:, 1003:].cpu() == 7.0)          # the rows' tails are untouched
+    out = K.logit_scale_cap(dev(logits).clone(), 2.0, 0.0)
+    torch.testing.assert_close(out.cpu(), logits * 2.0, rtol=0, atol=0)

@@ -12,6 +12,9 @@ from __future__ import annotations
 from typing import List
 
 
+PAGE = 64  # positions per page: the one place this number stands
+
+
 class CacheError(RuntimeError):
     pass
 

@@ -31,9 +31,7 @@ import numpy as np
 import torch
 
 from ..parts.base import KVRequest, StateRequest
-from .allocators import CacheError, PagePool, SlotAllocator
-
-PAGE = 64  # positions per page
+from .allocators import PAGE, CacheError, PagePool, SlotAllocator
 
 
 def pages_for(n_tokens: int) -> int:
@@ -116,6 +114,13 @@ class _KVGroup:
         i = self.entries.index(entry)
         return KVView(self.k[i], self.v[i], self.table, self.req.n_kv_heads, self.req.head_dim,
                       self.req.window, self.ring_rows)
+
+
+def bytes_per_token(requests: Sequence[Any], dtype: torch.dtype) -> int:
+    """Bytes of cache that one position of one sequence takes, over all schedule entries' requests
+    (keys and values; fixed-size states do not grow with the length and count nothing here)."""
+    elem = torch.empty((), dtype=dtype).element_size()
+    return sum(2 * r.n_kv_heads * r.head_dim * elem for r in requests if isinstance(r, KVRequest))
 
 
 class CacheManager:

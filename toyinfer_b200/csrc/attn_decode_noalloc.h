@@ -13,7 +13,8 @@
 // Same arguments and result as ti_attn_decode_simt, minus the two scratch pointers.
 //   * n_seq * n_heads * n_splits * (head_dim + 2) must not exceed
 //     TI_NOALLOC_SCRATCH_FLOATS; a larger request is refused with a message
-//     (ti_last_error) and nothing is launched.
+//     (ti_last_error) and nothing is launched.  With n_splits == 1 no scratch is used and
+//     any size is taken.
 //   * The first call on a device looks up the array's device address (no allocation, but a
 //     runtime call that is not allowed while a stream is being captured): make that first
 //     call before any capture begins.

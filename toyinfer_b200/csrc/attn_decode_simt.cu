@@ -226,6 +226,10 @@ extern "C" int ti_attn_decode_noalloc(const void* q, long long q_stride, const v
                                       int n_splits, void* out, long long o_stride, int dtype, cudaStream_t stream) {
     if (n_seq == 0) return 0;
     TI_REQUIRE(n_seq > 0 && n_heads > 0 && head_dim > 0 && n_splits >= 1, "attention_decode (no allocation): bad sizes");
+    if (n_splits == 1)      // one split writes its result directly: no scratch is touched, and none is looked up
+        return ti_attn_decode_simt(q, q_stride, k_pages, v_pages, page_table, table_width, page_size, ring_rows, n_pages,
+                                   seq_slot, seq_len, n_seq, n_heads, n_kv_heads, head_dim, scale, window, 1, out,
+                                   o_stride, nullptr, nullptr, dtype, stream);
     const long long need = (long long)n_seq * n_heads * n_splits * (head_dim + 2);
     TI_REQUIRE(need <= (long long)TI_NOALLOC_SCRATCH_FLOATS,
                "attention_decode (no allocation): %d sequences x %d heads x %d splits x head size %d need %lld floats of "

@@ -60,11 +60,13 @@ template <typename T> constexpr int vec_width() { return 16 / sizeof(T); }
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // ---------------------------------------------------------------------------
-// embedding gather: out[m, :] = table[ids[m], :]; an id outside the table gives zeros
+// embedding gather: out[m, :] = table[ids[m], :] * scale; an id outside the table gives zeros.
+// The reference gathers without a scale (src/prefill.cu:17-21); with scale == 1 the row is
+// copied bit for bit, otherwise the product is formed in 32-bit and rounded once.
 // ---------------------------------------------------------------------------
 template <typename T, int V>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             T* __restrict__ out, int H, int vocab) {
+                             T* __restrict__ out, int H, int vocab, float scale) {
     ti_pdl_trigger();
     ti_pdl_sync();
     ids = ti_dependent(ids);
@@ -80,12 +82,16 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 #pragma unroll
             for (int j = 0; j < V; j++) x[j] = 0.f;
         }
+        if (scale != 1.0f) {
+#pragma unroll
+            for (int j = 0; j < V; j++) x[j] *= scale;
+        }
         store_vec<T, V>(dst + i, x);
     }
 }
 
 extern "C" int ti_embed(const void* table, const int* ids, void* out, int M, int H, int vocab,
-                        int dtype, cudaStream_t stream) {
+                        float scale, int dtype, cudaStream_t stream) {
     if (M == 0) return 0;
     TI_REQUIRE(M > 0 && H > 0 && vocab > 0, "embed: bad sizes M=%d H=%d vocab=%d", M, H, vocab);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
@@ -93,12 +99,39 @@ extern "C" int ti_embed(const void* table, const int* ids, void* out, int M, int
         constexpr int V = vec_width<T>();
         const int threads = 128;
         if (H % V == 0 && aligned16(table) && aligned16(out))
-            TI_CUDA(ti_launch_class<1>(embed_kernel<T, V>, dim3(M), dim3(threads), 0, stream, (const T*)table, ids, (T*)out, H, vocab));
+            TI_CUDA(ti_launch_class<1>(embed_kernel<T, V>, dim3(M), dim3(threads), 0, stream, (const T*)table, ids, (T*)out, H, vocab, scale));
         else
-            TI_CUDA(ti_launch_class<1>(embed_kernel<T, 1>, dim3(M), dim3(threads), 0, stream, (const T*)table, ids, (T*)out, H, vocab));
+            TI_CUDA(ti_launch_class<1>(embed_kernel<T, 1>, dim3(M), dim3(threads), 0, stream, (const T*)table, ids, (T*)out, H, vocab, scale));
         TI_CHECK_LAUNCH("embed");
         return 0;
     });
+}
+
+// ---------------------------------------------------------------------------
+// float32 logits in place: x <- x * scale, then with cap > 0 the soft cap x <- cap * tanh(x / cap).
+// (The reference has neither: its logits are the head product as it is, src/decode.cu:251-286.)
+// ---------------------------------------------------------------------------
+__global__ void logit_scale_cap_kernel(float* __restrict__ x, long long stride, int V, float scale, float cap) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    float* row = x + (size_t)blockIdx.y * stride;
+    const float inv = cap > 0.f ? 1.0f / cap : 0.f;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < V; i += gridDim.x * blockDim.x) {
+        float v = row[i] * scale;
+        if (cap > 0.f) v = cap * tanhf(v * inv);
+        row[i] = v;
+    }
+}
+
+extern "C" int ti_logit_scale_cap(float* logits, long long stride, int R, int V, float scale, float cap, cudaStream_t stream) {
+    if (R == 0 || V == 0) return 0;
+    TI_REQUIRE(R > 0 && V > 0 && stride >= V && R <= 65535, "logit_scale_cap: bad sizes R=%d V=%d stride=%lld", R, V, stride);
+    TI_REQUIRE(cap >= 0.f, "logit_scale_cap: the cap must not be negative");
+    const int threads = 256;
+    const int bx = (V + threads - 1) / threads < 256 ? (V + threads - 1) / threads : 256;
+    TI_CUDA(ti_launch_class<1>(logit_scale_cap_kernel, dim3(bx, R), dim3(threads), 0, stream, logits, stride, V, scale, cap));
+    TI_CHECK_LAUNCH("logit_scale_cap");
+    return 0;
 }
 
 // ---------------------------------------------------------------------------

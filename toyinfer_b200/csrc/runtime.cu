@@ -55,6 +55,37 @@ extern "C" int ti_read_status(int* out) {
     return 0;
 }
 
+// ---------------------------------------------------------------------------
+// A wait that runs out, on purpose and harmlessly: one block waits on an mbarrier in its own shared
+// memory that nothing ever arrives on, with the given (small) number of polls instead of
+// TI_SPIN_LIMIT, then does what every kernel of the library does when a wait gives up: it records
+// the code in the status word and returns.  Nothing faults, traps or waits without a limit; the
+// context stays usable.  For the test that checks how a run-out wait is reported; no product
+// kernel's limit changes.
+// ---------------------------------------------------------------------------
+namespace {
+__global__ void wait_runs_out_kernel(int* status, unsigned limit, int* gave_up) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const bool ok = mbar_wait_limited(&bar, 0, limit);
+    if (!ok) ti_report(status, TI_STATUS_TMA_WAIT);
+    if (threadIdx.x == 0 && gave_up) *gave_up = ok ? 0 : 1;
+}
+}  // namespace
+
+extern "C" int ti_test_wait_runs_out(unsigned limit, int* gave_up, cudaStream_t stream) {
+    TI_REQUIRE(limit >= 1 && limit <= (1u << 20), "wait test: the limit must be between 1 and 2^20 polls, got %u", limit);
+    int* status = ti_status_ptr();
+    TI_REQUIRE(status != nullptr, "wait test: no status word");
+    wait_runs_out_kernel<<<1, 32, 0, stream>>>(status, limit, gave_up);
+    TI_CHECK_LAUNCH("wait test");
+    return 0;
+}
+
 int ti_make_tensor_map_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                                uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols) {
     if (int rc = load_encode()) return rc;

@@ -12,7 +12,8 @@
 // step), so a sequence draws the same numbers in any batch.
 //
 // One block of 1024 threads per row.  Which of the two rules applies is the host's
-// decision; this file only refuses combinations it cannot run.
+// decision.  Three kernels: up to 1,024 candidates (one sort in shared memory), the whole
+// vocabulary without limits (one scan), and everything else tier by tier.
 #include "common.cuh"
 
 #include <climits>
@@ -267,6 +268,218 @@ __global__ void __launch_bounds__(SB) sample_topk_kernel(SampleArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// Any top_k and any top_p, in tiers of MAXK candidates.
+//
+// The rule is the one of the kernel above (the reference's, src/sampler.cpp:24-68): the kept
+// set is the k largest of x = logit / temperature (all of them when top_k is off), p = softmax
+// over the kept set, the sorted list is cut after the first entry at which the running sum
+// exceeds top_p, and a uniform draw times the sum at the cut picks the first entry whose
+// running sum exceeds it.  Entries are ordered by value, larger first, and by index among
+// equal values.  The sorted list is never formed as a whole: tier t holds the entries ranked
+// t * MAXK ... (t + 1) * MAXK - 1 in that order, found by radix selection of the two ranks that
+// bound it (integer counts only, so the result does not depend on the order in which threads
+// run), sorted in shared memory and walked by one thread with the running sum carried from tier
+// to tier.  A peaked distribution ends in the first tier; a flat one over a large vocabulary
+// walks many (a nucleus of 34,000 entries: 34 tiers).  The kept set's sum is formed first, in a
+// fixed order (a contiguous run of entries per thread, then a scan over the threads).
+// ---------------------------------------------------------------------------
+constexpr int MAX_TIERS = 1024;
+
+// Entries at or before a rank in sorted order: key > thr, or key == thr and index <= idx.
+struct Bound { unsigned thr; int idx; };
+
+__device__ __forceinline__ bool within(const Bound& b, unsigned key, int i) {
+    return key > b.thr || (key == b.thr && i <= b.idx);
+}
+
+// The bound of sorted rank `k` (1 <= k <= V): the k entries at or before it are exactly the k
+// first of the sorted order.  All threads call it and get the same answer.
+__device__ Bound select_rank(const float* x, int V, float temp, int k, int* hist, int* scan_i, unsigned* s_prefix,
+                             int* s_rem, int* s_idx) {
+    const int t = threadIdx.x;
+    unsigned prefix = 0, mask = 0;
+    int rem = k, at_thr = 0;
+    for (int pass = 3; pass >= 0; pass--) {
+        if (t < 256) hist[t] = 0;
+        __syncthreads();
+        for (int i = t; i < V; i += SB) {
+            const unsigned key = order_key(x[i] / temp);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> (8 * pass)) & 255], 1);
+        }
+        __syncthreads();
+        if (t == 0) {
+            int above = 0, bin = 255;
+            for (; bin > 0; bin--) {
+                if (above + hist[bin] >= rem) break;
+                above += hist[bin];
+            }
+            *s_prefix = prefix | ((unsigned)bin << (8 * pass));
+            s_rem[0] = rem - above;
+            s_rem[1] = hist[bin];
+        }
+        __syncthreads();
+        prefix = *s_prefix;
+        rem = s_rem[0];
+        at_thr = s_rem[1];
+        mask |= 0xFFu << (8 * pass);
+        __syncthreads();
+    }
+    Bound b{prefix, INT_MAX};
+    if (rem >= at_thr) return b;          // every entry equal to the threshold is inside
+    // only the `rem` lowest indices among the equal entries are inside: find the rem-th of them
+    const int chunk = (V + SB - 1) / SB;
+    const int lo = min(V, t * chunk), hi = min(V, lo + chunk);
+    int ties = 0;
+    for (int i = lo; i < hi; i++) ties += order_key(x[i] / temp) == prefix ? 1 : 0;
+    int total;
+    int rank = block_exclusive_scan<int>(ties, &total, scan_i);
+    if (rank < rem && rank + ties >= rem) {
+        for (int i = lo; i < hi; i++)
+            if (order_key(x[i] / temp) == prefix && ++rank == rem) { *s_idx = i; break; }
+    }
+    __syncthreads();
+    b.idx = *s_idx;
+    __syncthreads();
+    return b;
+}
+
+__global__ void __launch_bounds__(SB) sample_tiered_kernel(SampleArgs a) {
+    ti_pdl_trigger();
+    __shared__ int hist[256];
+    __shared__ float cval[MAXK];
+    __shared__ int cidx[MAXK];
+    __shared__ float tier_end[MAX_TIERS];
+    __shared__ int scan_i[33];
+    __shared__ float scan_f[33];
+    __shared__ float red[33];
+    __shared__ unsigned s_prefix;
+    __shared__ int s_rem[2], s_idx, s_count;
+    __shared__ int s_state[3];            // 0: cut found (1) or not, 1: tier to walk for the pick, 2: entries of the cut tier that are kept
+    __shared__ float s_coin;
+    ti_pdl_sync();
+    const int t = threadIdx.x, V = a.V;
+    const float* x = a.logits + (size_t)blockIdx.x * a.ld;
+    const float temp = a.temperature;
+    const int k_eff = (a.top_k <= 0 || a.top_k >= V) ? V : a.top_k;
+    const int chunk = (V + SB - 1) / SB;
+    const int lo = min(V, t * chunk), hi = min(V, lo + chunk);
+
+    // --- the maximum, and the kept set's sum of exp(x - max) in a fixed order
+    float mx = -INFINITY;
+    for (int i = t; i < V; i += SB) mx = fmaxf(mx, x[i] / temp);
+    mx = warp_max(mx);
+    if ((t & 31) == 0) red[t >> 5] = mx;
+    __syncthreads();
+    if (t < 32) {
+        float m2 = warp_max(red[t]);
+        if (t == 0) red[32] = m2;
+    }
+    __syncthreads();
+    mx = red[32];
+    Bound all{0u, INT_MAX};
+    const Bound kept = k_eff < V ? select_rank(x, V, temp, k_eff, hist, scan_i, &s_prefix, s_rem, &s_idx) : all;
+    float part = 0.f;
+    for (int i = lo; i < hi; i++) {
+        const float v = x[i] / temp;
+        if (k_eff == V || within(kept, order_key(v), i)) part += expf(v - mx);
+    }
+    float sum;
+    block_exclusive_scan<float>(part, &sum, scan_f);
+
+    // --- walk the tiers
+    const int n_tiers = (k_eff + MAXK - 1) / MAXK;
+    const float u = uniform_from(a.seed, (unsigned long long)a.keys[blockIdx.x], (unsigned long long)a.steps[blockIdx.x]);
+    if (t == 0) { s_state[0] = 0; s_state[1] = -1; s_state[2] = 0; }
+    Bound before = all;                   // rank tier * MAXK; unused for the first tier
+    int tier = 0;
+    bool picking = false;                 // second visit of an earlier tier, for the pick only
+    float acc = 0.f;                      // thread 0: the running sum at the start of the tier
+    while (true) {
+        const int first = tier * MAXK, m = min(MAXK, k_eff - first);
+        const Bound upto = first + m < V ? select_rank(x, V, temp, first + m, hist, scan_i, &s_prefix, s_rem, &s_idx) : all;
+        const bool open_end = first + m >= V;
+        if (t == 0) s_count = 0;
+        __syncthreads();
+        for (int i = lo; i < hi; i++) {
+            const float v = x[i] / temp;
+            const unsigned key = order_key(v);
+            if ((open_end || within(upto, key, i)) && (tier == 0 || !within(before, key, i))) {
+                const int p = atomicAdd(&s_count, 1);
+                if (p < MAXK) { cval[p] = v; cidx[p] = i; }
+            }
+        }
+        __syncthreads();
+        const int n = min(s_count, MAXK);      // == m unless the row holds NaNs
+        int n2 = 1;
+        while (n2 < n) n2 <<= 1;
+        for (int i = n + t; i < n2; i += SB) { cval[i] = -INFINITY; cidx[i] = INT_MAX; }
+        __syncthreads();
+        for (int size = 2; size <= n2; size <<= 1) {
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                for (int i = t; i < n2; i += SB) {
+                    const int j = i ^ stride;
+                    if (j > i) {
+                        const bool desc = (i & size) == 0;
+                        const float vi = cval[i], vj = cval[j];
+                        const int ii = cidx[i], ij = cidx[j];
+                        const bool i_first = vi > vj || (vi == vj && ii < ij);
+                        if (desc != i_first) { cval[i] = vj; cval[j] = vi; cidx[i] = ij; cidx[j] = ii; }
+                    }
+                }
+                __syncthreads();
+            }
+        }
+        for (int i = t; i < n; i += SB) cval[i] = expf(cval[i] - mx);
+        __syncthreads();
+        if (t == 0) {
+            if (!picking) {
+                // first visit: the running sum, until it passes top_p or the kept set ends
+                int cut = -1;
+                for (int i = 0; i < n; i++) {
+                    acc += cval[i] / sum;
+                    if (acc > a.top_p) { cut = i; break; }
+                }
+                tier_end[tier] = acc;
+                if (cut >= 0 || tier == n_tiers - 1) {
+                    s_state[0] = 1;
+                    s_state[2] = cut >= 0 ? cut + 1 : n;
+                    const float coin = u * acc;
+                    s_coin = coin;
+                    int tp = tier;                       // the first tier whose end passes the coin
+                    for (int j = 0; j < tier; j++)
+                        if (tier_end[j] > coin) { tp = j; break; }
+                    s_state[1] = tp;
+                }
+            }
+        }
+        __syncthreads();
+        if (s_state[0] && s_state[1] == tier) {
+            // the pick lies in the tier that is in shared memory now
+            if (t == 0) {
+                const int kept_here = picking ? n : s_state[2];
+                float run = tier > 0 ? tier_end[tier - 1] : 0.f;
+                int pick = kept_here > 0 ? cidx[kept_here - 1] : 0;
+                for (int i = 0; i < kept_here; i++) {
+                    run += cval[i] / sum;
+                    if (run > s_coin) { pick = cidx[i]; break; }
+                }
+                a.out[blockIdx.x] = pick;
+            }
+            return;
+        }
+        if (s_state[0]) {                 // the pick lies in an earlier tier: bring that one back
+            picking = true;
+            tier = s_state[1];
+            before = tier > 0 ? select_rank(x, V, temp, tier * MAXK, hist, scan_i, &s_prefix, s_rem, &s_idx) : all;
+        } else {
+            before = upto;
+            tier++;
+        }
+        __syncthreads();
+    }
+}
+
 // whole vocabulary, no top-k, no top-p: first index whose running probability exceeds u
 __global__ void __launch_bounds__(SB) sample_full_kernel(SampleArgs a) {
     ti_pdl_trigger();
@@ -354,12 +567,16 @@ extern "C" int ti_sample(const float* logits, long long ld, int R, int V, float 
     a.logits = logits; a.ld = ld; a.V = V; a.temperature = temperature; a.top_k = top_k;
     a.top_p = top_p; a.seed = seed; a.keys = keys; a.steps = steps; a.out = out;
     const bool k_off = top_k <= 0 || top_k >= V;
-    if (k_off) {
-        TI_REQUIRE(top_p >= 1.0f, "sample: top_p %g without a top_k of at most %d is not implemented", top_p, MAXK);
+    if (k_off && top_p >= 1.0f) {
         TI_CUDA(ti_launch(sample_full_kernel, dim3(R), dim3(SB), 0, stream, a));
-    } else {
-        TI_REQUIRE(top_k <= MAXK, "sample: top_k %d exceeds the %d candidates this kernel sorts", top_k, MAXK);
+    } else if (!k_off && top_k <= MAXK) {
         TI_CUDA(ti_launch(sample_topk_kernel, dim3(R), dim3(SB), 0, stream, a));
+    } else {
+        // top_p over the whole vocabulary, or more candidates than one sort holds: tier by tier
+        const long long kept = k_off ? V : top_k;
+        TI_REQUIRE(kept <= (long long)MAXK * MAX_TIERS, "sample: %lld candidates exceed the %d this kernel walks", kept,
+                   MAXK * MAX_TIERS);
+        TI_CUDA(ti_launch(sample_tiered_kernel, dim3(R), dim3(SB), 0, stream, a));
     }
     TI_CHECK_LAUNCH("sample");
     return 0;

@@ -70,11 +70,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait; false when it gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < TI_SPIN_LIMIT; i++)
+// Bounded wait; false when it gave up after `limit` polls.
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; i++)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    return mbar_wait_limited(bar, parity, TI_SPIN_LIMIT);
 }
 
 // One box of a 2-D tensor map into shared memory; x is the inner (contiguous) coordinate and

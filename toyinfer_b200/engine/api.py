@@ -76,15 +76,13 @@ class _Stepper:
 def default_max_tokens(engine_kw: dict, model, max_batch: int, max_seq_len: int) -> int:
     """Cache capacity when the caller gives none: what max_batch full sequences need,
     limited to 60 % of the device memory that is free once the weights are loaded."""
-    want = max_batch * ((max_seq_len + 63) // 64 * 64)
-    per_token = 0
-    for req in model.memory_requests():
-        if req is not None and hasattr(req, "n_kv_heads"):
-            per_token += 2 * req.n_kv_heads * req.head_dim * (2 if model.dtype == torch.bfloat16 else 4)
+    from ..cache import PAGE, bytes_per_token
+    want = max_batch * ((max_seq_len + PAGE - 1) // PAGE * PAGE)
+    per_token = bytes_per_token(model.memory_requests(), model.dtype)
     if model.device.type == "cuda" and per_token:
         free, _ = torch.cuda.mem_get_info(model.device)
-        want = min(want, max(64, int(free * 0.6) // per_token))
-    return max(64, want // 64 * 64)
+        want = min(want, max(PAGE, int(free * 0.6) // per_token))
+    return max(PAGE, want // PAGE * PAGE)
 
 
 class LLM:

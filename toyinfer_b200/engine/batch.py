@@ -89,6 +89,9 @@ class StepBatch:
     host_slots: List[int] = field(default_factory=list)
     host_starts: List[int] = field(default_factory=list)
     host_new: List[int] = field(default_factory=list)
+    # set by a mixer's attention kernels for the product after them: whether their last kernel was
+    # started only when the SMs had drained (kernels/attention.py); a matter of speed only
+    drained_after_attention: bool = False
     trace: object = None      # the engine's tracing.Tracer (parts wrap their stages in its ranges); None: no tracing
 
 

@@ -79,6 +79,10 @@ class Engine:
         self.use_cuda_graph = bool(use_cuda_graph) and self.device.type == "cuda"
         self._eager_bufs: Dict[Tuple[int, int], BatchBuffers] = {}
         self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}     # (batch bucket, length class) -> captured step
+        # All captured steps draw their intermediate buffers from one pool: steps run one at a time,
+        # so what one graph freed during its capture another may use.  Each graph still keeps its
+        # own [bucket, vocab] float32 logits (alive at the end of its capture).
+        self._graph_pool = None
         self.graph_replays = 0
 
     # -- construction -----------------------------------------------------------
@@ -321,7 +325,9 @@ class _DecodeGraph:
             gc.disable()
             e.tracer.capturing = True
             try:
-                with torch.cuda.graph(g):
+                if e._graph_pool is None:
+                    e._graph_pool = torch.cuda.graph_pool_handle()
+                with torch.cuda.graph(g, pool=e._graph_pool):
                     self.logits = self._body(batch)
             finally:
                 e.tracer.capturing = was_capturing

@@ -27,7 +27,7 @@ import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
-PAGE_ROUND = 64
+from ..cache.allocators import PAGE
 
 
 @dataclass
@@ -47,7 +47,7 @@ class GenerationStats:
 
 
 def _held(n: int) -> int:
-    return (n + PAGE_ROUND - 1) // PAGE_ROUND * PAGE_ROUND
+    return (n + PAGE - 1) // PAGE * PAGE
 
 
 def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_batch: int,

@@ -71,13 +71,25 @@ def _row_stride(t: torch.Tensor, what: str) -> int:
 
 
 # ---------------------------------------------------------------------------
-def embed(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+def embed(table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[m] = table[ids[m]] * scale (a copy when the scale is 1)."""
     _need_cuda(table, ids, what="embed")
     _i32(ids, "embed ids")
     V, H = table.shape
     out = torch.empty((ids.numel(), H), dtype=table.dtype, device=table.device)
-    _call(library().ti_embed, _ptr(table), _ptr(ids), _ptr(out), ids.numel(), H, V, _code(table, "embed"), _stream())
+    _call(library().ti_embed, _ptr(table), _ptr(ids), _ptr(out), ids.numel(), H, V, float(scale), _code(table, "embed"), _stream())
     return out
+
+
+def logit_scale_cap(logits: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torch.Tensor:
+    """In place on float32 logits [rows, vocab]: times ``scale``, then with ``cap`` > 0 the soft
+    cap ``cap * tanh(x / cap)``.  Returns its argument."""
+    _need_cuda(logits, what="logit_scale_cap")
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("logit_scale_cap: expected float32 [rows, vocab] with dense rows")
+    R, V = logits.shape
+    _call(library().ti_logit_scale_cap, _ptr(logits), logits.stride(0), R, V, float(scale), float(cap), _stream())
+    return logits
 
 
 def _wcode(x: torch.Tensor, w: torch.Tensor, what: str) -> int:
@@ -204,12 +216,12 @@ def gather_add(h: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tenso
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           after_attention: bool = False) -> torch.Tensor:
+           late_start: bool = False) -> torch.Tensor:
     """x[M, K] times w[N, K] transposed -> [M, N]; 32-bit accumulation.  ``out_dtype`` may
-    ask for float32 results from bfloat16 operands (the head).  ``after_attention``: a hint
-    that x comes (through at most a tiny kernel) from an attention kernel with large shared
-    memory; the few-token kernels then start only when it has finished (a matter of speed, not
-    of results: csrc/gemm_skinny.cu).  x may be a PendingNorm."""
+    ask for float32 results from bfloat16 operands (the head).  ``late_start``: a hint that x
+    comes from a kernel with large shared memory whose blocks may still be on the SMs; the
+    few-token kernels then start only when it has finished (a matter of speed, not of
+    results: csrc/gemm_skinny.cu).  x may be a PendingNorm."""
     if isinstance(x, PendingNorm):
         out = _linear_pending(x, w, gated=False) if out_dtype in (None, x.dtype) else None
         if out is not None:
@@ -228,11 +240,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     ldx, ldw = _row_stride(x, "linear x"), _row_stride(w, "linear w")
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     from . import gemm
-    late = False
-    if after_attention:
-        from . import attention
-        late = not attention.last_decode_had_combine      # the combine kernel has already let the SMs drain
-    gemm.run(x, w, out, M, N, K, ldx, ldw, late_start=late)
+    gemm.run(x, w, out, M, N, K, ldx, ldw, late_start=bool(late_start))
     return out
 
 
@@ -434,11 +442,37 @@ _STATUS = {1: "a wait for a TMA load ran out", 2: "a wait for tensor-core work r
            3: "a wait for a pipeline slot ran out"}
 
 
+def reset_scratch() -> None:
+    """Clears the device scratch that kernels keep between calls and expect to find zero: the
+    tickets by which the blocks of a split product find out who is last, and the words and tickets
+    of the argmax kernel.  A kernel that gave up on a wait may have left some of them set; every
+    later product that met such a ticket would add a stale piece or never write its tile."""
+    from . import gemm
+    for t in gemm._tickets.values():
+        t.zero_()
+    for word, tickets in _argmax_scratch.values():
+        word.zero_()
+        tickets.zero_()
+
+
 def check_status() -> None:
     """Waits for the device and raises if a kernel gave up on one of its bounded waits
-    since the last check (its results are then not to be trusted)."""
+    since the last check (its results are then not to be trusted).  The status word is clear
+    afterwards, and so is the scratch that the kernel may have left half-used."""
     v = ctypes.c_int(0)
     if library().ti_read_status(ctypes.byref(v)) != 0:
         raise KernelError(library().ti_last_error().decode("utf-8", "replace"))
     if v.value:
+        reset_scratch()
         raise KernelError(f"a kernel reported status {v.value}: {_STATUS.get(v.value, 'unknown')}")
+
+
+def testing_wait_runs_out(limit: int = 10000) -> bool:
+    """Launches the library's test kernel whose one bounded wait (``limit`` polls) is on a barrier
+    nothing arrives on.  Returns whether the wait gave up; the status word is then set, as after any
+    product kernel's run-out wait.  Faults nothing."""
+    from .lib import declare
+    fn = declare("ti_test_wait_runs_out", [ctypes.c_uint, ctypes.c_void_p, ctypes.c_void_p])
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _call(fn, int(limit), _ptr(flag), _stream())
+    return bool(flag.item())

@@ -9,6 +9,26 @@ from .gemm import sm_count
 from .lib import library
 
 
+def check_supported(n_heads: int, n_kv_heads: int, head_dim: int, dtype) -> None:
+    """Raises KernelError when no attention kernel of the library takes these sizes: the limits of
+    the CUDA-core kernels, which run whatever the tensor-core kernels (bfloat16, heads of 64 or
+    128) do not."""
+    if n_heads <= 0 or n_kv_heads <= 0 or n_heads % n_kv_heads:
+        raise KernelError(f"attention: {n_heads} heads over {n_kv_heads} kv heads")
+    if head_dim % 4 or head_dim < 4 or head_dim > 256:
+        raise KernelError(f"attention_prefill: head size {head_dim} not supported (multiples of 4 up to 256)")
+    group = n_heads // n_kv_heads
+    tensor_cores = dtype == torch.bfloat16 and head_dim in (64, 128)
+    if not tensor_cores:
+        if group * head_dim > 32 * 128:
+            raise KernelError(f"attention_decode: {group} query heads per kv head of size {head_dim} exceed this kernel's "
+                              f"{32 * 128} outputs per block")
+        smem = (group * head_dim + 64 * (head_dim + 1) + 64 * head_dim + group * 64 + 3 * group) * 4
+        if smem > 227 * 1024:
+            raise KernelError(f"attention_decode: {group} query heads per kv head of size {head_dim} need {smem} bytes "
+                              f"of shared memory")
+
+
 def prefill(q, k, v, out, scale, window, batch) -> None:
     M, nh, hd = q.shape
     qs, ks, vs = _row_stride(q, "q"), _row_stride(k, "k"), _row_stride(v, "v")
@@ -54,11 +74,12 @@ def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int
     return max(1, min(want, (tiles + 3) // 4, 64))
 
 
-# Whether the last decode attention ended with a combine kernel that was started late, i.e. only
-# when the attention blocks had left the SMs.  If not, a few-token product that follows has to
-# start late itself (kernels.linear(after_attention=True) asks here).  The combine kernel is
-# started late exactly when the step is small enough for the few-token products.
-last_decode_had_combine = False
+# A decode attention kernel with large shared memory leaves the SMs without an L1 for kernels that
+# start while its blocks still run (gemm_skinny.cu).  Its combine kernel, when there is one and the
+# step is small enough for the few-token products, is therefore started late: only when the
+# attention blocks have left the SMs.  Whether that happened is noted on the step's batch
+# (``batch.drained_after_attention``); if not, the product that follows starts late itself
+# (kernels.linear(late_start=...), which the mixer sets from the batch).
 
 
 def _combine_late(n_seq: int) -> bool:
@@ -67,7 +88,6 @@ def _combine_late(n_seq: int) -> bool:
 
 
 def decode(q, mem, out, scale, window, batch) -> None:
-    global last_decode_had_combine
     B, nh, hd = q.shape
     nkv = mem.n_kv_heads
     span = batch.plan_len if window <= 0 else min(batch.plan_len, window + mem.page_size)
@@ -80,7 +100,7 @@ def decode(q, mem, out, scale, window, batch) -> None:
     lib = library()
     tensor_cores = q.dtype == torch.bfloat16 and hd in (64, 128)
     late = _combine_late(B)
-    last_decode_had_combine = tensor_cores and splits > 1 and late
+    batch.drained_after_attention = tensor_cores and splits > 1 and late
     fn = lib.ti_attn_decode_mma if tensor_cores else lib.ti_attn_decode_simt
     extra = (1 if late else 0,) if tensor_cores else ()
     _call(fn, _ptr(q), _row_stride(q, "q"), _ptr(mem.k_pages), _ptr(mem.v_pages),
@@ -111,7 +131,6 @@ def decode_fused_eligible(q, k, v, q_w, k_w, tables, mem) -> bool:
 
 
 def decode_fused(q, k, v, q_w, k_w, eps, tables, mem, out, scale, window, batch) -> None:
-    global last_decode_had_combine
     B, nh, hd = q.shape
     nkv = mem.n_kv_heads
     span = batch.plan_len if window <= 0 else min(batch.plan_len, window + mem.page_size)
@@ -121,7 +140,7 @@ def decode_fused(q, k, v, q_w, k_w, eps, tables, mem, out, scale, window, batch)
         part_o = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((B, nh, splits, 2), dtype=torch.float32, device=q.device)
     late = _combine_late(B)
-    last_decode_had_combine = splits > 1 and late
+    batch.drained_after_attention = splits > 1 and late
     cos = sin = None
     max_pos = 0
     if tables is not None:

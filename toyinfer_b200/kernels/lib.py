@@ -19,7 +19,8 @@ def _declare(lib) -> None:
     lib.ti_last_error.restype = c_char_p
     lib.ti_last_error.argtypes = []
     sig = {
-        "ti_embed": [P, P, P, I, I, I, I, P],
+        "ti_embed": [P, P, P, I, I, I, F, I, P],
+        "ti_logit_scale_cap": [P, L, I, I, F, F, P],
         "ti_rmsnorm": [P, P, P, P, I, I, L, F, I, I, P],
         "ti_gather_add": [P, P, P, P, I, I, I, I, P],
         "ti_swiglu": [P, P, I, I, I, I, P],

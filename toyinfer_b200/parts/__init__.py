@@ -2,7 +2,9 @@
 from .base import (
     Block,
     BuildContext,
+    Embedding,
     FeedForward,
+    Head,
     KVRequest,
     Mixer,
     Norm,
@@ -16,11 +18,11 @@ from .base import (
     registered_parts,
     unregister_part,
 )
-from . import norms, rope, attention, mlp, block  # noqa: F401  (registration)
+from . import norms, rope, attention, mlp, block, ends  # noqa: F401  (registration)
 from .model import DecoderModel, LayerSpec, ModelSpec, ScheduleEntry
 
 __all__ = [
-    "Block", "BuildContext", "FeedForward", "KVRequest", "Mixer", "Norm", "ParamSpec", "Part",
+    "Block", "BuildContext", "Embedding", "FeedForward", "Head", "KVRequest", "Mixer", "Norm", "ParamSpec", "Part",
     "PartSpec", "PositionEncoding", "StateRequest", "build_part", "register_part",
     "registered_parts", "unregister_part", "DecoderModel", "LayerSpec", "ModelSpec", "ScheduleEntry",
 ]

@@ -107,6 +107,10 @@ class GQAAttention(Mixer):
 
     takes_pending_norm = True       # x goes into K.linear first, and nowhere else
 
+    def check_kernels(self, dtype) -> None:
+        from ..kernels import attention
+        attention.check_supported(self.n_heads, self.n_kv_heads, self.head_dim, dtype)
+
     def memory_request(self):
         if not self.own_kv:
             return None
@@ -134,7 +138,8 @@ class GQAAttention(Mixer):
         with ranged(batch, "mixer.attention"):
             a = self._attend(q, k, v, batch, mem, shared)
         with ranged(batch, "mixer.out"):
-            return K.linear(a.view(M, self.q_dim), self.w_o, after_attention=True)
+            # unless the attention's own last kernel waited for the SMs to drain, this product does
+            return K.linear(a.view(M, self.q_dim), self.w_o, late_start=not batch.drained_after_attention)
 
     def _attend(self, q, k, v, batch, mem, shared) -> torch.Tensor:
         """Per-head norm, position encoding, cache store and attention: q[M, heads, d] -> [M, heads, d]."""

@@ -29,6 +29,10 @@ Families and what each must provide:
                     ``mem``: a write that would destroy what they read is appended
                     there as a callable instead of being done.
 ``FeedForward``     ``forward(x, batch) -> y`` per token.
+``Embedding``       ``forward(token_ids[M]) -> h[M, hidden]`` and ``table()`` (the matrix a
+                    tied head reads).
+``Head``            ``forward(h, delta, rows) -> float32 logits [len(rows), vocab]`` of
+                    the tokens at ``rows``; the hidden state is ``h + delta``.
 ``Block``           owns norm(s), a mixer and a feed-forward and arranges them;
                     ``forward(h, delta, batch, mem, shared) -> (h, delta)`` where the
                     true hidden state is ``h + delta`` (``delta`` may be ``None``), so
@@ -80,6 +84,7 @@ class BuildContext:
     device: torch.device
     hidden_size: int
     positions: Dict[str, "PositionEncoding"] = field(default_factory=dict)
+    embedding: Optional["Embedding"] = None       # the model's embedding, once built (a tied head reads its table)
 
 
 class Part:
@@ -92,6 +97,11 @@ class Part:
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         pass
+
+    def check_kernels(self, dtype: torch.dtype) -> None:
+        """Raises (kernels.KernelError, with the kernel's own message) when the library's kernels
+        do not take this part's sizes in ``dtype``.  Called when a model is built, before weights
+        are read; a part that owns other parts passes the call on."""
 
 
 # ---------------------------------------------------------------------------
@@ -153,6 +163,22 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    def table(self) -> torch.Tensor:
+        raise NotImplementedError
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    def ignorable_names(self) -> Tuple[str, ...]:
+        return ()
+
+    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Block(Part):
     mixer: Mixer
 
@@ -163,7 +189,7 @@ class Block(Part):
 # ---------------------------------------------------------------------------
 # registries of implementations, one per family
 # ---------------------------------------------------------------------------
-FAMILIES = ("norm", "position", "mixer", "feed_forward", "block")
+FAMILIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
 _REGISTRY: Dict[str, Dict[str, Callable[..., Part]]] = {f: {} for f in FAMILIES}
 
 

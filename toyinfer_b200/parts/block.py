@@ -38,6 +38,10 @@ class PreNormBlock(Block):
         for c in self._children:
             c.bind(tensors)
 
+    def check_kernels(self, dtype) -> None:
+        for c in self._children:
+            c.check_kernels(dtype)
+
     def forward(self, h, delta, batch, mem, shared):
         trace = getattr(batch, "trace", None)
         if trace is not None and trace.active:

@@ -3,16 +3,17 @@
 ``ModelSpec`` holds what an architecture's ``describe(config)`` returns: the
 embedding, the position encodings, one ``LayerSpec`` per layer (arrangement, norm,
 mixer, feed-forward, each with its parameters), the schedule in which layers run,
-the final norm and the head.  The schedule is a list of ``ScheduleEntry``: an entry
+the final norm and the head (or, for models whose ends differ from the usual, an
+``embedding`` and a ``head`` part of their own: an embedding multiplier, a logit scale or
+soft cap, no final norm).  The schedule is a list of ``ScheduleEntry``: an entry
 names a layer (a layer may be named more than once: its weights are shared, each
 entry has memory of its own) and may borrow the memory of an earlier entry
 (``memory_of``), in which case its mixer reads what that entry stored.
 
-``DecoderModel`` runs: embedding gather (src/prefill.cu:6-22), the scheduled blocks,
-and for the rows whose logits are wanted the final norm and the head in 32-bit
-output (src/transformer.cpp:460-470, src/decode.cu:251-286).  The head is the
-embedding table when the model ties them (the reference always ties,
-src/qwen.cpp:482-483) and a matrix of its own otherwise.
+``DecoderModel`` runs: the embedding part (src/prefill.cu:6-22), the scheduled blocks,
+and for the rows whose logits are wanted the head part (parts/ends.py).  It also asks
+every part, at build time and before any weight is read, whether the library's kernels
+take its sizes (``Part.check_kernels``).
 """
 from __future__ import annotations
 
@@ -44,7 +45,7 @@ class ModelSpec:
     hidden_size: int
     max_positions: int
     layers: List[LayerSpec]
-    final_norm: PartSpec
+    final_norm: Optional[PartSpec]                      # None: the head reads the hidden state as it is
     schedule: Optional[List[ScheduleEntry]] = None      # default: every layer once, in order
     positions: Dict[str, PartSpec] = field(default_factory=dict)
     tie_head: bool = False
@@ -53,6 +54,21 @@ class ModelSpec:
     final_norm_prefix: str = "model.norm."
     stop_token_ids: Tuple[int, ...] = ()
     ignorable: Tuple[str, ...] = ()                     # tensors a checkpoint may hold that are not used
+    # The two ends as parts of their own; None: a plain token table (embed_name) and a linear head
+    # (final_norm under final_norm_prefix, tie_head, head_name) without scales.
+    embedding: Optional[PartSpec] = None
+    head: Optional[PartSpec] = None
+
+    def embedding_spec(self) -> PartSpec:
+        if self.embedding is not None:
+            return self.embedding
+        return PartSpec("token_table", {"vocab_size": self.vocab_size, "name": self.embed_name})
+
+    def head_spec(self) -> PartSpec:
+        if self.head is not None:
+            return self.head
+        return PartSpec("linear", {"vocab_size": self.vocab_size, "norm": self.final_norm, "tied": self.tie_head,
+                                   "name": self.head_name, "norm_prefix": self.final_norm_prefix})
 
     def run_order(self) -> List[ScheduleEntry]:
         if self.schedule is None:
@@ -69,8 +85,10 @@ class DecoderModel(Part):
         for name, pspec in spec.positions.items():
             ctx.positions[name] = build_part("position", pspec, ctx, "")
         self.ctx = ctx
+        self.embedding = build_part("embedding", spec.embedding_spec(), ctx, "")
+        ctx.embedding = self.embedding
         self.blocks = [build_part("block", ls.block, ctx, ls.prefix) for ls in spec.layers]
-        self.final_norm = build_part("norm", spec.final_norm, ctx, spec.final_norm_prefix)
+        self.head = build_part("head", spec.head_spec(), ctx, "")
         self.schedule = spec.run_order()
         for i, e in enumerate(self.schedule):
             if not (0 <= e.layer < len(self.blocks)):
@@ -80,35 +98,30 @@ class DecoderModel(Part):
                     raise ValueError(f"schedule entry {i} borrows memory of entry {e.memory_of}, which does not run before it")
                 if self.schedule[e.memory_of].memory_of is not None:
                     raise ValueError(f"schedule entry {i} borrows from entry {e.memory_of}, which itself borrows")
-        self.embed: Optional[torch.Tensor] = None
-        self.head: Optional[torch.Tensor] = None
+        # every part says now, before any weight is read, whether the kernels take its sizes
+        for part in [self.embedding, self.head, *self.ctx.positions.values(), *self.blocks]:
+            part.check_kernels(dtype)
 
     # -- parameters ---------------------------------------------------------
     def param_specs(self) -> Dict[str, ParamSpec]:
-        s = self.spec
-        out: Dict[str, ParamSpec] = {s.embed_name: ParamSpec((s.vocab_size, s.hidden_size))}
+        out: Dict[str, ParamSpec] = dict(self.embedding.param_specs())
         for b in self.blocks:
             out.update(b.param_specs())
         for p in self.ctx.positions.values():
             out.update(p.param_specs())
-        out.update(self.final_norm.param_specs())
-        if not s.tie_head:
-            out[s.head_name] = ParamSpec((s.vocab_size, s.hidden_size))
+        out.update(self.head.param_specs())
         return out
 
     def ignorable_names(self) -> Tuple[str, ...]:
-        extra = (self.spec.head_name,) if self.spec.tie_head else ()
-        return tuple(self.spec.ignorable) + extra
+        return tuple(self.spec.ignorable) + tuple(self.head.ignorable_names())
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        s = self.spec
-        self.embed = tensors.pop(s.embed_name)
-        self.head = self.embed if s.tie_head else tensors.pop(s.head_name)
+        self.embedding.bind(tensors)
         for p in self.ctx.positions.values():
             p.bind(tensors)
         for b in self.blocks:
             b.bind(tensors)
-        self.final_norm.bind(tensors)
+        self.head.bind(tensors)
 
     # -- what the cache must hold ---------------------------------------------
     def memory_requests(self) -> List[Any]:
@@ -123,7 +136,7 @@ class DecoderModel(Part):
         """Runs the given tokens through all scheduled blocks.  Returns (h, delta):
         the hidden state is h + delta."""
         with ranged(batch, "embed"):
-            h = K.embed(self.embed, batch.token_ids)
+            h = self.embedding.forward(batch.token_ids)
         delta = None
         shared: List[dict] = [dict() for _ in self.schedule]
         owners = [i if e.memory_of is None else e.memory_of for i, e in enumerate(self.schedule)]
@@ -142,6 +155,4 @@ class DecoderModel(Part):
 
     def logits(self, h, delta, rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] of the tokens at the given rows."""
-        x = K.gather_add(h, delta, rows)
-        x = self.final_norm.forward(x)
-        return K.linear(x, self.head, out_dtype=torch.float32)
+        return self.head.forward(h, delta, rows)

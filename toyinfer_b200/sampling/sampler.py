@@ -5,7 +5,9 @@ temperature, top-k and top-p as the reference orders them (src/sampler.cpp:24-68
 two differences: the temperature divides the logits once (the reference divides a
 second time inside the exponent, :38), and the uniform number is a function of
 (seed, sequence key, number of tokens the sequence has drawn), not of the clock (:57-60),
-so a sequence gets the same tokens whatever batch it runs in.
+so a sequence gets the same tokens whatever batch it runs in.  Every combination of top_k
+and top_p runs on the device: up to 1,024 candidates in one shared-memory sort, more (or
+top_p over the whole vocabulary) tier by tier (csrc/sampling.cu).
 """
 from __future__ import annotations
 
