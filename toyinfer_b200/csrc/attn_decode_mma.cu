@@ -15,10 +15,17 @@
 //   P = exp(S * scale - max), O += P V with P rounded to bfloat16 for the second product.
 // The four warps' maxima, sums and outputs are merged through shared memory at the end,
 // then written as this split's partial result (or the final one when there is one split).
+//
+// With CLUSTER the blocks of a sequence's kv head (its splits, up to 16) are launched as one
+// thread-block cluster and merge their partial results themselves, through distributed shared
+// memory: every block leaves its merged partial in its own shared memory, a cluster barrier makes
+// them visible, and each block then forms a slice of the final outputs from all blocks' partials
+// (read with ld.shared::cluster, added in split order).  No partial result goes through global
+// memory and no second kernel runs.
 #include "attn_decode.cuh"
 #include "mma_utils.cuh"
 #include "rope_math.cuh"
-#include "tma.cuh"
+#include "tcgen05.cuh"
 
 #include <map>
 #include <mutex>
@@ -49,7 +56,13 @@ struct FuseArgs {
     bf16* k_pages; bf16* v_pages;                       // the cache, writable
 };
 
-template <int HD, bool FUSED>
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_address) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_address) : "memory");
+    return v;
+}
+
+template <int HD, bool FUSED, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                        tiattn::DecodeArgs a, FuseArgs f, int* status) {
@@ -71,7 +84,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
         mbar_fence_init();
     }
     __syncthreads();
-    if (s_abort) return;
+    // (in a cluster every block goes on to the cluster's two barriers: it does no work, and the
+    // other blocks, which read the same word sooner or later, report what they see themselves)
+    const bool dead = s_abort != 0;
+    if (dead && !CLUSTER) return;
 
     // What is read before ti_pdl_sync() below does not depend on the kernel just before this
     // one: the step's lengths, slots and page table were uploaded before the step's first
@@ -90,7 +106,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
     const int n_tiles = L > 0 ? (L - 1) / TILE - tile_lo + 1 : 0;
     const int per = (n_tiles + a.n_splits - 1) / a.n_splits;
     const int my_lo = tile_lo + split * per;
-    const int my_n = max(0, min(my_lo + per, tile_lo + n_tiles) - my_lo);
+    const int my_n = dead ? 0 : max(0, min(my_lo + per, tile_lo + n_tiles) - my_lo);
 
     auto issue = [&](int i) {      // tile my_lo + i into stage i % STAGES; one thread calls this
         const int p0 = (my_lo + i) * TILE;
@@ -314,10 +330,11 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
         __syncthreads();                 // the stage may be refilled
         if (s_abort) {
             // give the loads still in flight a bounded time to land before the block's shared
-            // memory is released, then leave without a result
+            // memory is released (or used for the merge), then leave without a result
             if (t == 0)
                 for (int j = i + 1; j < my_n && j < i + STAGES; j++) mbar_wait(&full[j % STAGES], (uint32_t)((j / STAGES) & 1));
-            return;
+            if (!CLUSTER) return;
+            break;
         }
     }
     // back to natural-log units for the merge
@@ -349,6 +366,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
         }
     }
     __syncthreads();
+    float* fin_o = Lm + 4 * 16;                            // CLUSTER: this block's merged partial, [16 rows][HD]
+    float* fin_ml = fin_o + 16 * HD;                       //          and its (maximum, sum) per row
     for (int idx = t; idx < rows * HD; idx += THREADS) {
         const int r = idx / HD, d = idx - r * HD;
         float m = -INFINITY;
@@ -365,13 +384,40 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
             }
         }
         const int h = h0 + r;
-        if (a.n_splits == 1) {
+        if (CLUSTER) {
+            fin_o[idx] = acc;
+            if (d == 0) { fin_ml[r * 2] = m; fin_ml[r * 2 + 1] = l; }
+        } else if (a.n_splits == 1) {
             ((bf16*)a.out)[(size_t)b * a.o_stride + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
         } else {
             const size_t base = ((size_t)b * a.n_heads + h) * a.n_splits + split;
             a.part_o[base * HD + d] = acc;
             if (d == 0) { a.part_ml[base * 2] = m; a.part_ml[base * 2 + 1] = l; }
         }
+    }
+    if (CLUSTER) {
+        // every block's partial is in its shared memory: make them visible to the cluster, then
+        // each block forms its slice of the outputs from all of them, in split order
+        cluster_sync_all();
+        const int total = rows * HD, n = a.n_splits;
+        const int share = (total + n - 1) / n;
+        const int lo_idx = (int)cluster_rank() * share, hi_idx = min(total, lo_idx + share);
+        for (int idx = lo_idx + t; idx < hi_idx; idx += THREADS) {
+            const int r = idx / HD, d = idx - r * HD;
+            float m = -INFINITY;
+            for (int sp = 0; sp < n; sp++) m = fmaxf(m, ld_cluster_f32(cluster_addr(&fin_ml[r * 2], (uint32_t)sp)));
+            float l = 0.f, acc = 0.f;
+            for (int sp = 0; sp < n; sp++) {
+                const float ms = ld_cluster_f32(cluster_addr(&fin_ml[r * 2], (uint32_t)sp));
+                if (ms > -INFINITY) {       // a split that saw no key contributes nothing
+                    const float w = expf(ms - m);
+                    l = fmaf(ld_cluster_f32(cluster_addr(&fin_ml[r * 2 + 1], (uint32_t)sp)), w, l);
+                    acc = fmaf(ld_cluster_f32(cluster_addr(&fin_o[idx], (uint32_t)sp)), w, acc);
+                }
+            }
+            ((bf16*)a.out)[(size_t)b * a.o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        }
+        cluster_sync_all();     // nobody leaves while its shared memory may still be read
     }
 }
 
@@ -396,14 +442,20 @@ int page_map(const void* pages, long long rows, int hd, CUtensorMap* out) {
     return 0;
 }
 
+constexpr int MAX_CLUSTER = 16;      // blocks of one cluster; above 8 the kernel must opt in (non-portable size)
+
+// mode: 0 partial results through global memory and a combine kernel started like every kernel,
+// 1 the same with the combine kernel started late, 2 the splits as one cluster that merges itself.
 template <int HD, bool FUSED>
-int launch(const tiattn::DecodeArgs& a, const FuseArgs& f, int n_seq, bool combine_late, cudaStream_t stream) {
+int launch(const tiattn::DecodeArgs& a, const FuseArgs& f, int n_seq, int mode, cudaStream_t stream) {
     constexpr size_t stage_bytes = 2 * TILE * HD * 2;
-    constexpr size_t merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * sizeof(float);
+    constexpr size_t merge_bytes = (4 * 16 * HD + 2 * 4 * 16 + 16 * HD + 2 * 16) * sizeof(float);
     constexpr size_t smem = (STAGES * stage_bytes > merge_bytes ? STAGES * stage_bytes : merge_bytes) + 1024;
     static bool configured = false;
     if (!configured) {
-        TI_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<HD, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TI_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<HD, FUSED, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TI_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<HD, FUSED, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TI_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<HD, FUSED, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
         configured = true;
     }
     CUtensorMap km, vm;
@@ -414,7 +466,33 @@ int launch(const tiattn::DecodeArgs& a, const FuseArgs& f, int n_seq, bool combi
     TI_REQUIRE(status != nullptr, "attention_decode: no status word");
     const int g = a.n_heads / a.n_kv_heads;
     dim3 grid(n_seq, a.n_kv_heads * ((g + 15) / 16), a.n_splits);
-    TI_CUDA(ti_launch_class<3>(attn_decode_mma_kernel<HD, FUSED>, grid, dim3(THREADS), smem, stream, km, vm, a, f, status));
+    if (mode == 2) {
+        TI_REQUIRE(a.n_splits >= 2 && a.n_splits <= MAX_CLUSTER, "attention_decode (cluster): %d splits do not form a cluster of 2 to %d blocks",
+                   a.n_splits, MAX_CLUSTER);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        int n_attr = 0;
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = (unsigned)a.n_splits;
+        n_attr++;
+        if (ti_pdl_enabled(3)) {
+            attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+            n_attr++;
+        }
+        cfg.attrs = attr;
+        cfg.numAttrs = n_attr;
+        TI_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, FUSED, true>, km, vm, a, f, status));
+        TI_CHECK_LAUNCH("attention_decode (tensor cores, cluster)");
+        return 0;
+    }
+    TI_CUDA(ti_launch_class<3>(attn_decode_mma_kernel<HD, FUSED, false>, grid, dim3(THREADS), smem, stream, km, vm, a, f, status));
     TI_CHECK_LAUNCH("attention_decode (tensor cores)");
     if (a.n_splits > 1) {
         dim3 cgrid(n_seq, a.n_heads);
@@ -422,7 +500,7 @@ int launch(const tiattn::DecodeArgs& a, const FuseArgs& f, int n_seq, bool combi
         // memory are gone and the SMs have drained, so that few-token products after it find an L1
         // (see gemm_skinny.cu) and may start early.  Before the tcgen05 product (more tokens), which
         // does not care about L1 and gains from starting early, it starts early like everything else.
-        if (combine_late)
+        if (mode == 1)
             TI_CUDA(ti_launch_after(tiattn::attn_decode_combine_kernel<bf16>, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits));
         else
             TI_CUDA(ti_launch_class<4>(tiattn::attn_decode_combine_kernel<bf16>, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)a.out, a.o_stride, a.n_heads, HD, a.n_splits));
@@ -433,13 +511,14 @@ int launch(const tiattn::DecodeArgs& a, const FuseArgs& f, int n_seq, bool combi
 }  // namespace
 
 // bfloat16 only; head_dim 64 or 128; pages of 64 positions.  Same arguments as
-// ti_attn_decode_simt.
+// ti_attn_decode_simt, plus `mode`: how the splits' results are merged (see launch above; with
+// mode 2 no scratch is needed).
 extern "C" int ti_attn_decode_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                   const int* page_table, int table_width, int page_size, int ring_rows,
                                   int n_pages, const int* seq_slot, const int* seq_len, int n_seq,
                                   int n_heads, int n_kv_heads, int head_dim, float scale, int window,
                                   int n_splits, void* out, long long o_stride, float* part_o,
-                                  float* part_ml, int dtype, int combine_late, cudaStream_t stream) {
+                                  float* part_ml, int dtype, int mode, cudaStream_t stream) {
     if (n_seq == 0) return 0;
     TI_REQUIRE(dtype == TI_BF16, "attention_decode (tensor cores): bfloat16 only");
     TI_REQUIRE(head_dim == 64 || head_dim == 128, "attention_decode (tensor cores): head size %d is not 64 or 128", head_dim);
@@ -448,7 +527,7 @@ extern "C" int ti_attn_decode_mma(const void* q, long long q_stride, const void*
     TI_REQUIRE(ring_rows % page_size == 0, "attention_decode: ring of %d rows is not whole pages", ring_rows);
     TI_REQUIRE(window == 0 || ring_rows == 0 || ring_rows >= window, "attention_decode: ring smaller than the window");
     TI_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention_decode: bad split count %d", n_splits);
-    TI_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_decode: split results need scratch memory");
+    TI_REQUIRE(n_splits == 1 || mode == 2 || (part_o && part_ml), "attention_decode: split results need scratch memory");
     TI_REQUIRE((reinterpret_cast<uintptr_t>(q) & 3) == 0 && q_stride % 2 == 0, "attention_decode: queries must be 4-byte aligned");
     tiattn::DecodeArgs a;
     a.q = q; a.q_stride = q_stride; a.k_pages = k_pages; a.v_pages = v_pages; a.page_table = page_table;
@@ -457,7 +536,7 @@ extern "C" int ti_attn_decode_mma(const void* q, long long q_stride, const void*
     a.window = window; a.n_splits = n_splits; a.scale = scale; a.out = out; a.o_stride = o_stride;
     a.part_o = part_o; a.part_ml = part_ml;
     FuseArgs f = {};
-    return head_dim == 64 ? launch<64, false>(a, f, n_seq, combine_late != 0, stream) : launch<128, false>(a, f, n_seq, combine_late != 0, stream);
+    return head_dim == 64 ? launch<64, false>(a, f, n_seq, mode, stream) : launch<128, false>(a, f, n_seq, mode, stream);
 }
 
 // The same with the step before it folded in: q[B, heads, hd], k and v[B, kv_heads, hd] are the
@@ -472,7 +551,7 @@ extern "C" int ti_attn_decode_fused(const void* q, const void* k, const void* v,
                                     int ring_rows, int n_pages, const int* seq_slot, const int* seq_len, int n_seq,
                                     int n_heads, int n_kv_heads, int head_dim, float scale, int window, int n_splits,
                                     void* out, long long o_stride, float* part_o, float* part_ml, int dtype,
-                                    int combine_late, cudaStream_t stream) {
+                                    int mode, cudaStream_t stream) {
     if (n_seq == 0) return 0;
     TI_REQUIRE(dtype == TI_BF16, "attention_decode (fused): bfloat16 only");
     TI_REQUIRE(head_dim == 64 || head_dim == 128, "attention_decode (fused): head size %d is not 64 or 128", head_dim);
@@ -481,7 +560,7 @@ extern "C" int ti_attn_decode_fused(const void* q, const void* k, const void* v,
     TI_REQUIRE(ring_rows % page_size == 0, "attention_decode: ring of %d rows is not whole pages", ring_rows);
     TI_REQUIRE(window == 0 || ring_rows == 0 || ring_rows >= window, "attention_decode: ring smaller than the window");
     TI_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention_decode: bad split count %d", n_splits);
-    TI_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_decode: split results need scratch memory");
+    TI_REQUIRE(n_splits == 1 || mode == 2 || (part_o && part_ml), "attention_decode: split results need scratch memory");
     TI_REQUIRE(q != nullptr && (k == nullptr) == (v == nullptr), "attention_decode (fused): queries are needed; keys and values go together");
     TI_REQUIRE((cos_t == nullptr) == (sin_t == nullptr) && (!cos_t || max_pos > 0), "attention_decode (fused): cos and sin tables go together");
     auto ok16 = [](const void* p, long long stride) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && stride % 8 == 0; };
@@ -501,5 +580,5 @@ extern "C" int ti_attn_decode_fused(const void* q, const void* k, const void* v,
     f.q_w = q_w; f.k_w = k_w; f.w_is_f32 = w_is_f32; f.eps = eps;
     f.cos_t = cos_t; f.sin_t = sin_t; f.max_pos = max_pos > 0 ? max_pos : 1;
     f.k_pages = (bf16*)k_pages; f.v_pages = (bf16*)v_pages;
-    return head_dim == 64 ? launch<64, true>(a, f, n_seq, combine_late != 0, stream) : launch<128, true>(a, f, n_seq, combine_late != 0, stream);
+    return head_dim == 64 ? launch<64, true>(a, f, n_seq, mode, stream) : launch<128, true>(a, f, n_seq, mode, stream);
 }

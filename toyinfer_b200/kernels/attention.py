@@ -87,27 +87,39 @@ def _combine_late(n_seq: int) -> bool:
     return n_seq <= max(gemm.SKINNY_MAX_TOKENS, gemm.GEMV_MAX_TOKENS)
 
 
+MAX_CLUSTER = 16     # splits that the tensor-core decode kernel merges itself, as one thread-block cluster
+
+
+def _merge_mode(n_seq: int, splits: int, tensor_cores: bool) -> int:
+    """How the splits' partial results meet (csrc/attn_decode_mma.cu): 2 the splits of a kv head are
+    one cluster and merge through distributed shared memory (no scratch, no second kernel); else
+    through global scratch and a combine kernel, started late (1) or like every kernel (0)."""
+    if tensor_cores and 2 <= splits <= MAX_CLUSTER:
+        return 2
+    return 1 if _combine_late(n_seq) else 0
+
+
 def decode(q, mem, out, scale, window, batch) -> None:
     B, nh, hd = q.shape
     nkv = mem.n_kv_heads
     span = batch.plan_len if window <= 0 else min(batch.plan_len, window + mem.page_size)
     splits = decode_splits(B, nkv, span, mem.page_size, sm_count(q.device))
+    tensor_cores = q.dtype == torch.bfloat16 and hd in (64, 128)
+    mode = _merge_mode(B, splits, tensor_cores)
     part_o = part_ml = None
-    if splits > 1:
+    if splits > 1 and mode != 2:
         part_o = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((B, nh, splits, 2), dtype=torch.float32, device=q.device)
     pt = mem.page_table
     lib = library()
-    tensor_cores = q.dtype == torch.bfloat16 and hd in (64, 128)
-    late = _combine_late(B)
-    batch.drained_after_attention = tensor_cores and splits > 1 and late
+    batch.drained_after_attention = tensor_cores and splits > 1 and mode == 1
     fn = lib.ti_attn_decode_mma if tensor_cores else lib.ti_attn_decode_simt
-    extra = (1 if late else 0,) if tensor_cores else ()
+    extra = (mode,) if tensor_cores else ()
     _call(fn, _ptr(q), _row_stride(q, "q"), _ptr(mem.k_pages), _ptr(mem.v_pages),
           _ptr(pt), pt.shape[1], mem.page_size, mem.ring_rows, mem.k_pages.shape[0],
           _ptr(batch.seq_slot), _ptr(batch.seq_len), B, nh, nkv, hd, scale, window, splits,
           _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _code(q, "attention_decode"), *extra, _stream(),
-          launches=2 if splits > 1 else 1)
+          launches=2 if (splits > 1 and mode != 2) else 1)
 
 
 def decode_fused_eligible(q, k, v, q_w, k_w, tables, mem) -> bool:
@@ -135,12 +147,12 @@ def decode_fused(q, k, v, q_w, k_w, eps, tables, mem, out, scale, window, batch)
     nkv = mem.n_kv_heads
     span = batch.plan_len if window <= 0 else min(batch.plan_len, window + mem.page_size)
     splits = decode_splits(B, nkv, span, mem.page_size, sm_count(q.device))
+    mode = _merge_mode(B, splits, True)
     part_o = part_ml = None
-    if splits > 1:
+    if splits > 1 and mode != 2:
         part_o = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((B, nh, splits, 2), dtype=torch.float32, device=q.device)
-    late = _combine_late(B)
-    batch.drained_after_attention = splits > 1 and late
+    batch.drained_after_attention = splits > 1 and mode == 1
     cos = sin = None
     max_pos = 0
     if tables is not None:
@@ -155,4 +167,4 @@ def decode_fused(q, k, v, q_w, k_w, eps, tables, mem, out, scale, window, batch)
           float(eps), _ptr(cos), _ptr(sin), max_pos, _ptr(mem.k_pages), _ptr(mem.v_pages), _ptr(pt), pt.shape[1],
           mem.page_size, mem.ring_rows, mem.k_pages.shape[0], _ptr(batch.seq_slot), _ptr(batch.seq_len), B, nh, nkv, hd,
           scale, window, splits, _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _code(q, "attention_decode"),
-          1 if late else 0, _stream(), launches=2 if splits > 1 else 1)
+          mode, _stream(), launches=2 if (splits > 1 and mode != 2) else 1)
