@@ -177,3 +177,41 @@ def test_generation_through_the_engine_matches_plain(monkeypatch, model_folders)
     want = [plain.generate(w, cfg, p, 8, stop_ids=(stop, 7)) for p in prompts]
     assert [r.tokens for r in got] == want
     assert llm.engine.cache.slots.n_free == llm.engine.cache.n_slots
+
+
+def test_prompts_fed_in_pieces():
+    """prefill_chunk = 10: a step takes at most 10 prompt tokens in all, dealt out in request
+    order; a sequence whose prompt is done decodes beside the pieces of the others; the tokens
+    drawn are those of whole prompts."""
+    prompts = [[100 + j for j in range(4)], [200 + j for j in range(23)], [300 + j for j in range(7)]]
+    whole = ScriptedStepper()
+    want = GenerationLoop(whole, [], 8, 1000, 10 ** 6).run(prompts, 3)
+    st = ScriptedStepper()
+    loop = GenerationLoop(st, [], 8, 1000, 10 ** 6, prefill_chunk=10)
+    got = loop.run(prompts, 3)
+    assert [r.tokens for r in got] == [r.tokens for r in want]
+    # first step: 4 tokens of request 0 and 6 of request 1; request 2 waits
+    assert [(s, len(t)) for s, t in st.steps[0]] == [(0, 4), (1, 6)]
+    # second step: request 0 decodes, request 1 takes all 10 prompt tokens, request 2 still waits
+    assert [(s, len(t)) for s, t in st.steps[1]] == [(0, 1), (1, 10)]
+    # third: request 0 decodes, request 1 its last 7, request 2 gets the 3 that are left
+    assert [(s, len(t)) for s, t in st.steps[2]] == [(0, 1), (1, 7), (2, 3)]
+    assert loop.stats.prompt_tokens == 4 + 23 + 7
+    assert not st.live and sorted(st.ended) == [0, 1, 2]
+    with pytest.raises(ValueError):
+        GenerationLoop(st, [], 8, 1000, 10 ** 6, prefill_chunk=0)
+
+
+def test_prompts_in_pieces_on_the_engine(monkeypatch, model_folders):
+    """The same through the library's engine on the CPU stand-ins: greedy tokens with prompts fed
+    16 tokens a step equal those of whole prompts and the plain implementation's."""
+    from toyinfer_b200 import LLM, SamplingParams
+    cpu_kernels.install(monkeypatch)
+    prompts = prompts_for("C", [70, 3, 45], seed=91)
+    w, cfg = plain.read_weights(model_folders["C"]), plain.read_config(model_folders["C"])
+    want = [plain.generate(w, cfg, p, 5) for p in prompts]
+    for chunk in (None, 16):
+        llm = LLM(model_folders["C"], dtype="float32", device="cpu", max_seq_len=320, max_batch=4, max_tokens=1024,
+                  enable_cuda_graph=False, prefill_chunk=chunk)
+        got = llm.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=5, ignore_eos=True)
+        assert [r.tokens for r in got] == want, chunk

@@ -687,9 +687,17 @@ def test_attention_decode(K, dtype, nh, nkv, hd, window):
         fill_cache(mem, s, [free.pop() for _ in range(need)], dev(ks[s]), dev(vs[s]))
     q = randn(len(lens), nh, hd, seed=50).to(dtype)
     scale = 1.0 / math.sqrt(hd)
-    for plan in (64, 4096, 40960):     # different split counts must agree
+    from toyinfer_b200.kernels import attention
+    # different split counts must agree, and so must the two ways the tensor-core kernel's splits
+    # meet: as a cluster through distributed shared memory (the default) and through global scratch
+    # with the combine kernel (forced here)
+    for plan, mode in ((64, None), (4096, None), (40960, None), (4096, 1), (40960, 0)):
         batch = make_batch("extend", list(range(len(lens))), [n - 1 for n in lens], [1] * len(lens), plan_len=plan)
-        got = K.attention_decode(dev(q), mem, scale, window, batch).cpu().double()
+        attention.force_merge_mode = mode
+        try:
+            got = K.attention_decode(dev(q), mem, scale, window, batch).cpu().double()
+        finally:
+            attention.force_merge_mode = None
         K.check_status()
         for s, n in enumerate(lens):
             qq = torch.zeros(n, nh, hd, dtype=dtype)

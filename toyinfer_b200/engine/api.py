@@ -89,11 +89,13 @@ class LLM:
     def __init__(self, model_dir: Optional[str] = None, *, config: Optional[dict] = None, seed: int = 0,
                  dtype="bfloat16", max_seq_len: Optional[int] = None, max_batch: int = 64,
                  max_tokens: Optional[int] = None, enable_cuda_graph: bool = True,
-                 use_dedicated_prefill: bool = True, detail_time: bool = False, nvtx: bool = True, device="cuda"):
+                 use_dedicated_prefill: bool = True, prefill_chunk: Optional[int] = None,
+                 detail_time: bool = False, nvtx: bool = True, device="cuda"):
         """``detail_time``: CUDA events around every step and, where steps run as plain launches
         (prompts always; single-token steps with ``enable_cuda_graph=False``), around the stages of
         every layer; ``timing_report()`` returns their sums.  ``nvtx``: NVTX ranges with the same
-        names, for a profiler's timeline."""
+        names, for a profiler's timeline.  ``prefill_chunk``: the most prompt tokens one step takes
+        (prompts are then fed in pieces, so a step's activations stay bounded; None: whole prompts)."""
         if (model_dir is None) == (config is None):
             raise ValueError("give either model_dir or config (random weights)")
         from .. import models  # noqa: F401
@@ -123,6 +125,7 @@ class LLM:
         self.config = cfg
         self._stepper = _Stepper(self.engine, None)
         self.use_dedicated_prefill = use_dedicated_prefill
+        self.prefill_chunk = prefill_chunk
         self.last_stats: Optional[GenerationStats] = None
 
     def timing_report(self):
@@ -145,7 +148,7 @@ class LLM:
         self._stepper.sampler = Sampler(sampling, e.device)
         loop = GenerationLoop(self._stepper, stops, e.max_batch, e.max_seq_len,
                               e.cache.max_tokens, ignore_eos=ignore_eos,
-                              dedicated_prefill=self.use_dedicated_prefill)
+                              dedicated_prefill=self.use_dedicated_prefill, prefill_chunk=self.prefill_chunk)
         out = loop.run(prompts, max_new_tokens)
         self.last_stats = loop.stats
         if e.device.type == "cuda":

@@ -73,6 +73,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max_batch", type=int, default=64)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--ignore_eos", type=_flag, default=False)
+    ap.add_argument("--prefill_chunk", type=int, default=0,
+                    help="feed prompts in pieces of at most this many tokens per step (0: whole prompts)")
     return ap
 
 
@@ -122,7 +124,7 @@ def main(argv=None) -> int:
 
     common = dict(dtype=args.dtype, max_seq_len=args.max_seq_len or None, max_batch=args.max_batch,
                   enable_cuda_graph=args.enable_cuda_graph, use_dedicated_prefill=args.use_dedicated_prefill,
-                  detail_time=args.detail_time)
+                  detail_time=args.detail_time, prefill_chunk=args.prefill_chunk or None)
     if args.random:
         with open(args.random) as f:
             llm = LLM(config=json.load(f), seed=args.seed, **common)

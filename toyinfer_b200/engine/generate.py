@@ -8,6 +8,12 @@ reference, src/engine_runtime.cpp:448-450), after ``max_new_tokens``, or when it
 step and its slot goes back to the cache.  No request joins a running batch; the next
 batch starts when the last sequence of this one has ended.
 
+With ``prefill_chunk`` the prompts of a batch are fed in pieces: a step takes at most that
+many prompt tokens in all, dealt out in request order, so the activations of a step stay
+bounded however long the prompts are; sequences whose prompt is done decode in the same
+steps meanwhile (the step function takes any mix of the two; the reference can do
+neither).
+
 The loop only decides; it runs steps and draws tokens through a ``stepper`` with
 ``new_sequence()``, ``end_sequence(slot)``, ``step(entries, want) -> logits`` and
 ``sample(logits, keys, steps) -> list of ints``, so its decisions can be tested
@@ -78,7 +84,8 @@ def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_batch: int
 
 class GenerationLoop:
     def __init__(self, stepper, stop_ids: Sequence[int], max_batch: int, max_seq_len: int,
-                 capacity_tokens: int, ignore_eos: bool = False, dedicated_prefill: bool = True):
+                 capacity_tokens: int, ignore_eos: bool = False, dedicated_prefill: bool = True,
+                 prefill_chunk: Optional[int] = None):
         self.stepper = stepper
         self.stop_ids = frozenset(int(s) for s in stop_ids)
         self.max_batch = max_batch
@@ -88,6 +95,9 @@ class GenerationLoop:
         # False: prompts are fed one token per step through the decode path, the
         # reference's --use_dedicated_prefill=0 (src/engine_runtime.cpp:314-322)
         self.dedicated_prefill = dedicated_prefill
+        if prefill_chunk is not None and prefill_chunk <= 0:
+            raise ValueError(f"prefill_chunk must be positive, got {prefill_chunk}")
+        self.prefill_chunk = prefill_chunk      # most prompt tokens one step takes (None: whole prompts)
         self.stats = GenerationStats()
 
     def _accept(self, res: GenerationResult, prompt_len: int, token: int, max_new: int) -> bool:
@@ -146,23 +156,36 @@ class GenerationLoop:
                         alive = {i for i, _ in live}
                         logits = st.rows(logits, [r for r, (i, _) in enumerate(started) if i in alive])
                     want = [[0] for _ in live]
-                    n_run = len(started)
+                    n_prompt = 0
+                    stepping = live
                 else:
-                    entries, want = [], []
+                    entries, want, stepping = [], [], []
+                    n_prompt = 0
+                    budget = self.prefill_chunk if self.prefill_chunk is not None else None
                     for i, slot in live:
                         p = prompts[i]
                         if fed[i] < len(p):
                             in_prompt = True
-                            toks = list(p) if (self.dedicated_prefill and fed[i] == 0) else [p[fed[i]]]
-                            fed[i] += len(toks)
-                            want.append([len(toks) - 1] if fed[i] == len(p) else [])
+                            if not self.dedicated_prefill:
+                                n = 1
+                            elif budget is None:
+                                n = len(p) - fed[i]
+                            else:
+                                n = min(len(p) - fed[i], budget)
+                                budget -= n
+                            if n == 0:
+                                continue              # this step's prompt tokens are dealt out: the sequence waits
+                            toks = list(p[fed[i]:fed[i] + n])
+                            fed[i] += n
+                            n_prompt += n
+                            want.append([n - 1] if fed[i] == len(p) else [])
                         else:
                             toks = [last[i]]
                             want.append([0])
                         entries.append((slot, toks))
+                        stepping.append((i, slot))
                     logits = st.step(entries, want)
-                    n_run = sum(len(t) for _, t in entries)
-                drawing = [(i, slot) for (i, slot), w in zip(live, want) if w]
+                drawing = [(i, slot) for (i, slot), w in zip(stepping, want) if w]
                 draw_keys = [keys[i] for i, _ in drawing]
                 draw_steps = [len(results[i].tokens) for i, _ in drawing]
                 if not drawing:
@@ -189,7 +212,7 @@ class GenerationLoop:
                 dt = time.perf_counter() - t0
                 if in_prompt:
                     self.stats.prefill_seconds += dt
-                    self.stats.prompt_tokens += n_run
+                    self.stats.prompt_tokens += n_prompt
                 else:
                     self.stats.decode_seconds += dt
                     self.stats.decode_steps += 1

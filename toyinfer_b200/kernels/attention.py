@@ -44,6 +44,9 @@ def prefill(q, k, v, out, scale, window, batch) -> None:
           _code(q, "attention_prefill"), _stream())
 
 
+MAX_CLUSTER = 16     # splits that the tensor-core decode kernel merges itself, as one thread-block cluster
+
+
 def chunk(q, k, v, mem, out, scale, window, batch) -> None:
     """New tokens after positions that the cache holds: keys below a sequence's start come from
     ``mem``'s pages, the rest from k and v."""
@@ -67,11 +70,14 @@ def chunk(q, k, v, mem, out, scale, window, batch) -> None:
 
 def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int) -> int:
     """Splits along the keys so that the grid has about two blocks per SM, but no split
-    shorter than four pages.  Depends only on the batch's padded size and the longest
-    length the step was planned for, so that a captured launch stays valid."""
+    shorter than two pages and no more than the 16 blocks one cluster holds (the tensor-core
+    kernel merges the splits of a cluster itself; measured at one sequence of 2,176 positions:
+    16 splits of two pages 2.11 ms per step, 8 of four 2.14, 4 of eight 2.23).  Depends only on
+    the batch's padded size and the longest length the step was planned for, so that a captured
+    launch stays valid."""
     tiles = max(1, (max_len + page - 1) // page)
     want = max(1, (2 * sms) // max(1, n_seq * n_kv_heads))
-    return max(1, min(want, (tiles + 3) // 4, 64))
+    return max(1, min(want, (tiles + 1) // 2, MAX_CLUSTER))
 
 
 # A decode attention kernel with large shared memory leaves the SMs without an L1 for kernels that
@@ -87,13 +93,15 @@ def _combine_late(n_seq: int) -> bool:
     return n_seq <= max(gemm.SKINNY_MAX_TOKENS, gemm.GEMV_MAX_TOKENS)
 
 
-MAX_CLUSTER = 16     # splits that the tensor-core decode kernel merges itself, as one thread-block cluster
+force_merge_mode = None      # tests set 0 or 1 here to run the tensor-core kernel's splits through global scratch
 
 
 def _merge_mode(n_seq: int, splits: int, tensor_cores: bool) -> int:
     """How the splits' partial results meet (csrc/attn_decode_mma.cu): 2 the splits of a kv head are
     one cluster and merge through distributed shared memory (no scratch, no second kernel); else
     through global scratch and a combine kernel, started late (1) or like every kernel (0)."""
+    if force_merge_mode is not None:
+        return force_merge_mode
     if tensor_cores and 2 <= splits <= MAX_CLUSTER:
         return 2
     return 1 if _combine_late(n_seq) else 0
