@@ -449,8 +449,8 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             batch = fill_batch(BatchBuffers(B, B, dev), "extend", list(range(B)), [ctx - 1] * B, [[0]] * B, B, ctx)
             q = rnd(B, nh, hd)
             return (lambda: K.attention_decode(q, mem, 1 / math.sqrt(hd), 0, batch)), 2 * B * ctx * nkv * hd * 2, 4.0 * B * ctx * nh * hd
-        if name == "attn_prefill":
-            T, nh, nkv, hd = PREFILL_TOKENS, 32, 8, 128
+        if name.startswith("attn_prefill"):               # attn_prefill or attn_prefill:TOKENS
+            T, nh, nkv, hd = (int(name.split(":")[1]) if ":" in name else PREFILL_TOKENS), 32, 8, 128
             qkv = rnd(T, (nh + 2 * nkv) * hd)
             q = qkv[:, :nh * hd].view(T, nh, hd)
             k = qkv[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
@@ -458,6 +458,20 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             batch = fill_batch(BatchBuffers(1, T, dev), "start", [0], [0], [[0] * T], 1, T)
             return (lambda: K.attention_prefill(q, k, v, 1 / math.sqrt(hd), 0, batch)), qkv.numel() * 2 + T * nh * hd * 2, \
                 4.0 * nh * hd * T * (T + 1) / 2
+        if name.startswith("attn_chunk"):                 # attn_chunk or attn_chunk:CACHED,NEW
+            cached, new = (int(v) for v in name.split(":")[1].split(",")) if ":" in name else (2048, 2048)
+            nh, nkv, hd = 32, 8, 128
+            pages = (cached + new + 63) // 64
+            table = torch.zeros(2, pages, dtype=torch.int32, device=dev)
+            table[0] = torch.arange(1, pages + 1, dtype=torch.int32, device=dev)
+            mem = KVView(rnd(pages + 1, nkv, 64, hd), rnd(pages + 1, nkv, 64, hd), table, nkv, hd, 0, 0)
+            qkv = rnd(new, (nh + 2 * nkv) * hd)
+            q = qkv[:, :nh * hd].view(new, nh, hd)
+            k = qkv[:, nh * hd:(nh + nkv) * hd].view(new, nkv, hd)
+            v = qkv[:, (nh + nkv) * hd:].view(new, nkv, hd)
+            batch = fill_batch(BatchBuffers(1, new, dev), "mixed", [0], [cached], [[0] * new], 1, cached + new)
+            return (lambda: K.attention_chunk(q, k, v, mem, 1 / math.sqrt(hd), 0, batch)), \
+                qkv.numel() * 2 + new * nh * hd * 2 + 2 * cached * nkv * hd * 2, 4.0 * nh * hd * new * (cached + (new + 1) / 2)
         raise SystemExit(f"unknown kernel case {name!r}")
 
     fn, nbytes, flops = make()
@@ -508,7 +522,8 @@ def main() -> int:
     ap.add_argument("--range", action="store_true",
                     help="also the mean decode rate while the batch grows from 2,048 positions to --context (some 20 s more)")
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
-                    "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K, attn_decode, attn_decode_b64, attn_decode_b1, attn_prefill; "
+                    "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K, attn_decode, attn_decode_b64, attn_decode_b1, "
+                    "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW]; "
                     "ref:all or ref:<case> times the reference's kernel recompiled for sm_100a beside this library's")
     ap.add_argument("--workload", default="", choices=["", "8b", "32b"],
                     help="run one of the larger described workloads end to end instead (8B or 32B shape)")
