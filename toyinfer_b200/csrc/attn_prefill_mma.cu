@@ -6,7 +6,7 @@
 // is 64 positions x head_dim of one kv head, one tile) and then the step's own keys and values;
 // one online softmax runs over both.
 //
-// Grid (heads, query tiles of 64 taken from the last to the first, sequences), 128 threads,
+// Grid (heads, sequences, query tiles of 64 taken from the last to the first), 128 threads,
 // two blocks per SM.  q, k and v are strided views of the projection's output
 // [tokens, heads * head_dim]; tensor maps with the 128-byte swizzle cut 64 x 64 boxes out of
 // them.  The query tile is loaded once; key/value tiles of 64 positions run through a ring
@@ -63,15 +63,16 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
     __syncthreads();
     ti_pdl_sync();      // everything above touched only this block's shared memory
 
-    // Blocks are handed out with x running fastest: the heads are x and the query tiles, from the
-    // last to the first, y, so that the long rows of the causal triangle of every head start
-    // before any short one (with the tiles as x a head's short rows started before the next
-    // head's long ones, and the last heads' long rows ended the kernel alone: 2,048 tokens of
-    // 32 heads took 71 us where the work, evenly spread, takes 41).
-    const int b = blockIdx.z, h = blockIdx.x;
+    // Blocks are handed out with x running fastest, then y, then z: the heads are x, the sequences y
+    // and the query tiles, from the last to the first, z, so that the long rows of the causal
+    // triangle of every head and every sequence start before any short one (with the tiles as x a
+    // head's short rows started before the next head's long ones, and the last heads' long rows
+    // ended the kernel alone: 2,048 tokens of 32 heads took 71 us where the work, evenly spread,
+    // takes 41).  A sequence shorter than the longest has nothing at the highest tile numbers.
+    const int b = blockIdx.y, h = blockIdx.x;
     const int tok0 = a.cu_new[b];
     const int n = a.cu_new[b + 1] - tok0;
-    const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * BQ;
+    const int q0 = ((int)gridDim.z - 1 - (int)blockIdx.z) * BQ;
     if (q0 >= n) return;
     const int kvh = h / (a.n_heads / a.n_kv_heads);
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -314,7 +315,7 @@ int launch(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, 
     }
     int* status = ti_status_ptr();
     TI_REQUIRE(status != nullptr, "attention_prefill: no status word");
-    dim3 grid(a.n_heads, (max_new + BQ - 1) / BQ, n_seq);
+    dim3 grid(a.n_heads, n_seq, (max_new + BQ - 1) / BQ);
     TI_CUDA(ti_launch(attn_prefill_mma_kernel<HD, PAGED>, grid, dim3(THREADS), smem, stream, qm, km, vm, kpm, vpm, a, status));
     TI_CHECK_LAUNCH(PAGED ? "attention_chunk (tensor cores)" : "attention_prefill (tensor cores)");
     return 0;

@@ -3,8 +3,8 @@
 // accumulators in tensor memory.  Same contract and formulas as attn_prefill_simt.cu
 // (reference: src/prefill.cu:224-379); head_dim 128, bfloat16.
 //
-// A block owns 128 queries of one head (grid: heads, query tiles from the last to the first,
-// sequences) and walks over key/value tiles of 64 positions; tiles that the causal mask or the
+// A block owns 128 queries of one head (grid: heads, sequences, query tiles from the last to
+// the first) and walks over key/value tiles of 64 positions; tiles that the causal mask or the
 // window excludes entirely are never loaded.  Roles, 320 threads:
 //   warp 0     TMA: the query tile once, then key tiles and value tiles, each into a ring of two
 //              buffers of its own: a key buffer is free as soon as the first product has read it, so
@@ -141,15 +141,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const uint32_t tmem = *tmem_slot;
     ti_pdl_sync();
 
-    // Blocks are handed out with x running fastest: the heads are x and the query tiles, from the
-    // last to the first, y, so that the long rows of the causal triangle of every head start
-    // before any short one (with the tiles as x a head's short rows started before the next
-    // head's long ones, and the last heads' long rows ended the kernel alone: 2,048 tokens of
-    // 32 heads took 71 us where the work, evenly spread, takes 41).
-    const int b = blockIdx.z, h = blockIdx.x;
+    // Blocks are handed out with x running fastest, then y, then z: the heads are x, the sequences y
+    // and the query tiles, from the last to the first, z, so that the long rows of the causal
+    // triangle of every head and every sequence start before any short one (with the tiles as x a
+    // head's short rows started before the next head's long ones, and the last heads' long rows
+    // ended the kernel alone: 2,048 tokens of 32 heads took 71 us where the work, evenly spread,
+    // takes 41).  A sequence shorter than the longest has nothing at the highest tile numbers.
+    const int b = blockIdx.y, h = blockIdx.x;
     const int tok0 = a.cu_new[b];
     const int n = a.cu_new[b + 1] - tok0;
-    const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * BQ;
+    const int q0 = ((int)gridDim.z - 1 - (int)blockIdx.z) * BQ;
     const bool active = q0 < n;
     const int kvh = h / (a.n_heads / a.n_kv_heads);
     const int last_q = min(q0 + BQ, n) - 1;
@@ -437,7 +438,7 @@ extern "C" int ti_attn_prefill_tc(const void* q, const void* k, const void* v, v
     }
     int* status = ti_status_ptr();
     TI_REQUIRE(status != nullptr, "attention_prefill: no status word");
-    dim3 grid(n_heads, (max_new + BQ - 1) / BQ, n_seq);
+    dim3 grid(n_heads, n_seq, (max_new + BQ - 1) / BQ);
     TI_CUDA(ti_launch(attn_prefill_tc_kernel<HD>, grid, dim3(THREADS), smem, stream, qm, km, vm, a, status));
     TI_CHECK_LAUNCH("attention_prefill (tcgen05)");
     return 0;
