@@ -69,8 +69,13 @@ def test_every_step_once_and_pieces_meet(M, N, K):
     _check(M, N, K, 148)
 
 
-def test_the_layer_shapes_with_2560_columns_are_shared_out():
+def test_tiles_for_a_round_and_a_bit():
+    """2,048 x 2,560 outputs are 80 tiles of 256 x 256 for 74 pairs: they run as 72 tiles of 256 x 288 in one
+    round (whole tiles, nothing shared); 4,096 tokens x 2,560 (2.2 rounds) and a one-SM shape are shared out."""
     shared, pair = _check(2048, 2560, 4096, 148)
+    assert pair and shared == 0
+    assert _plan(2048, 2560, 4096, 148)[1] == 288 and _plan(2048, 4096, 12288, 148)[1] == 512
+    shared, pair = _check(4096, 2560, 4096, 148)
     assert pair and shared > 0
     shared, pair = _check(1300, 3600, 264, 148)
     assert not pair and shared > 0
@@ -92,7 +97,7 @@ def test_the_plan_asks_for_the_workspace_and_tickets_the_walk_uses(sms):
         N = rng.choice([128, 520, 2560, 3600, 6144, 19456])
         K = rng.choice([64, 264, 2560, 4096, 9728])
         swap, bn, splits, ws, tickets = _plan(M, N, K, sms)
-        assert bn % 16 == 0 and 16 <= bn <= 256 and splits >= 1
+        assert bn % 16 == 0 and 16 <= bn <= 512 and splits >= 1
         rows, units, tiles, pair = _trace(M, N, K, sms)
         if splits > 1:
             assert not rows                                   # a split contraction runs one block per tile

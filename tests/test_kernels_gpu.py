@@ -164,8 +164,11 @@ def _planned_shared_tiles(M, N, K_):
 
 @pytest.mark.parametrize("M,N,K_,f32", [
     (2048, 6144, 2560, False),     # prefill, q/k/v rows of a 4B-shaped layer
-    (2048, 2560, 9728, False),     # prefill, down projection (long contraction)
-    (2048, 2560, 4096, False),     # prefill, output projection (tile width chosen to fill the SMs)
+    (2048, 2560, 9728, False),     # prefill, down projection (long contraction): one round of tiles 288 wide on pairs of SMs
+    (2048, 2560, 4096, False),     # prefill, output projection
+    (4096, 2560, 4096, False),     # 2.2 rounds of pairs: tiles shared out by contraction steps
+    (2304, 2500, 520, True),       # tiles 320 wide, ragged on both sides (9 x 256 tokens, 8 x 320 > 2,500 columns)
+    (2048, 4096, 1032, False),     # tiles 512 wide: two MMAs of 256 columns into one accumulator
     (1000, 1536, 512, False), (777, 3000, 328, True),
     (4741, 520, 264, False),       # more token tiles than one panel of the tile order, the last panel short
     (300, 2560, 4096, False),      # few tiles: the contraction is split
@@ -186,7 +189,7 @@ def test_linear_tensor_cores_at_model_sizes(K, monkeypatch, M, N, K_, f32):
     w = (torch.randn(N, K_, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
     got = K.linear(x, w, out_dtype=torch.float32 if f32 else None)
     K.check_status()
-    if (M, N) in ((2048, 2560), (1300, 3600)):
+    if (M, N) in ((4096, 2560), (1300, 3600)):
         assert _planned_shared_tiles(M, N, K_) > 0      # these are here for the tiles that two blocks share
     want = x.float() @ w.float().T
     if f32:
@@ -199,7 +202,8 @@ def test_linear_tensor_cores_at_model_sizes(K, monkeypatch, M, N, K_, f32):
 
 
 @pytest.mark.parametrize("M,N,K_,f32", [
-    (2048, 2560, 4096, False),     # 80 tiles of 256 x 256 for 74 pairs: all shared out by contraction steps
+    (4096, 2560, 4096, False),     # 160 tiles of 256 x 256 for 74 pairs: the last rounds shared out by contraction steps
+    (2048, 2560, 4096, False),     # one round of tiles 288 wide on pairs
     (2048, 6144, 2560, False),     # whole tiles in both forms
     (1100, 3000, 328, True),       # ragged on every side; rows past the end in the pair's second block
     (512, 19456, 264, False),      # two token tiles

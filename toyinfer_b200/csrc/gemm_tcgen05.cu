@@ -131,7 +131,28 @@ Plan make_plan(int M, int N, int K, int sms) {
         const int pairs = sms / 2;
         const long long tiles_a2 = (rows_a + 2 * BM - 1) / (2 * BM), tiles_b2 = (rows_b + 255) / 256;
         const double useful = ((double)rows_a / (tiles_a2 * 2 * BM)) * ((double)rows_b / (tiles_b2 * 256));
-        if (g_pair_mode != 1 && pairs > 0 && tiles_a2 * tiles_b2 >= pairs && (useful >= 0.93 || g_pair_mode == 2)) {
+        // A product whose tiles of 256 x 256 are between one and two rounds of pairs takes wider
+        // tiles that fit one round where such a width exists: all pairs then walk the contraction in
+        // step (see gemm_tcgen05_walk.cuh).  Measured at 2,048 tokens, shared out by steps against one
+        // round of wide tiles: 4,096 x 12,288 (512 wide) 201 -> 138 us, 4,096 x 4,096 53 -> 50;
+        // 3,072 tokens x 2,560 x 9,728 133 -> 108; 2,048 x 2,560 x 9,728 (288 wide: two MMAs of 144
+        // columns) 87.0 -> 85.3, x 4,096 41.7 -> 40.4.
+        int fit = 0;
+        if (g_pair_mode != 1 && pairs > 0 && tiles_a2 <= pairs && tiles_a2 * tiles_b2 > pairs && tiles_a2 * tiles_b2 < 2 * pairs &&
+            (double)rows_a / (tiles_a2 * 2 * BM) >= 0.93) {      // the tokens fill their tiles of 256, as for any pair
+            const int cols = (int)(pairs / tiles_a2);                       // column tiles of one round
+            const int need = (rows_b + cols - 1) / cols;                    // weight rows each must hold
+            const int widths[4] = {288, 320, 384, 512};
+            for (int w = 0; w < 4 && !fit; w++)
+                if (widths[w] >= need) fit = widths[w];
+            // one round of wide tiles against the steps of the shared-out form, which run about 1.3 times slower each
+            if (fit && (double)fit / 256.0 > 0.95 * 1.3 * (double)(tiles_a2 * tiles_b2) / pairs) fit = 0;
+        }
+        if (fit) {
+            p.pair = true;
+            b = fit;
+        }
+        else if (g_pair_mode != 1 && pairs > 0 && tiles_a2 * tiles_b2 >= pairs && (useful >= 0.93 || g_pair_mode == 2)) {
             p.pair = true;
             b = 256;
             // Sharing costs about as much as a dozen steps of the contraction (measured at 2,048
@@ -217,7 +238,9 @@ extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int 
     TI_REQUIRE(!gated || (N % 2 == 0 && !out_f32), "linear (tcgen05): a gated product needs an even number of weight rows and a bfloat16 result");
     CUtensorMap am, bm;
     if (int rc = operand_map(swap ? w : x, g.rows_a, K, swap ? ldw : ldx, BM, &am)) return rc;
-    if (int rc = operand_map(swap ? x : w, g.rows_b, K, swap ? ldx : ldw, p.pair ? bn / 2 : bn, &bm)) return rc;
+    // the other operand's box: a whole tile's rows; a pair's block loads half of them, or, where the
+    // tile takes two MMAs per step, a quarter at a time
+    if (int rc = operand_map(swap ? x : w, g.rows_b, K, swap ? ldx : ldw, p.pair ? (bn > 256 ? bn / 4 : bn / 2) : bn, &bm)) return rc;
     if (p.pair) return launch_walk_pair(bn, am, bm, g, sms, stream);
     if (p.walk) return launch_walk_single(bn, am, bm, g, sms, stream);
     return launch_tile(bn, am, bm, g, stream);

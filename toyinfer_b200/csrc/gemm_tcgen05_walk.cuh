@@ -21,6 +21,16 @@ namespace {
 // the accumulator, in both blocks at once; the epilogue warps of both report a drained
 // accumulator to rank 0.  Each block reads its own 128 rows of the result from its own tensor
 // memory.  "Unit" below is what works on a tile: a block, or a pair of them.
+//
+// A pair also takes tiles wider than 256 weight rows (up to 512, BN a multiple of 32): two MMAs per
+// step of the contraction, each BN / 2 columns wide, into one accumulator that fills the tensor
+// memory; each block loads its quarter of the tile's weight rows for either MMA as a box of its
+// own, so that the accumulator's columns follow the weight rows in order.  With one accumulator
+// a tile's epilogue no longer runs under the next tile's MMAs: the form is for products whose
+// tiles then fit the pairs in one round (2,048 x 2,560 outputs are 80 tiles of 256 x 256 for 74
+// pairs but 72 of 256 x 288), where every pair walks the contraction from the same step at the
+// same time and what one brings into L2 the others use: shared out by contraction steps instead,
+// each pair starts at a step of its own and the L2 hit rate falls from 82 % to 62 %.
 // ---------------------------------------------------------------------------
 template <int BN, bool PAIR> constexpr int walk_stages() {
     constexpr int per = BM * BK * 2 + (PAIR ? BN / 2 : BN) * BK * 2;
@@ -50,12 +60,17 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                     GemmArgs g, int* status) {
     ti_pdl_trigger();
+    static_assert(BN <= 256 || (PAIR && BN % 32 == 0 && BN <= 512), "tiles wider than 256 weight rows: pairs only, a multiple of 32 up to 512");
     constexpr int STAGES = walk_stages<BN, PAIR>();
     constexpr int B_ROWS = PAIR ? BN / 2 : BN;                  // weight rows this block loads
+    constexpr int N_MMA = BN > 256 ? 2 : 1;                     // MMAs per step of 16, each BN / N_MMA columns wide
+    constexpr int MMA_N = BN / N_MMA;
+    constexpr int B_BOX = B_ROWS / N_MMA;                       // weight rows per TMA box: this block's share of one MMA
+    constexpr int N_ACC = BN > 256 ? 1 : 2;                     // accumulators in tensor memory
     constexpr int TILE_ROWS = PAIR ? 2 * BM : BM;               // tokens of a tile
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = B_ROWS * BK * 2;
-    constexpr uint32_t ACC_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;   // columns of one accumulator
-    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
+    constexpr uint32_t ACC_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : BN <= 256 ? 256 : 512;   // columns of one accumulator
+    constexpr uint32_t TMEM_COLS = N_ACC * ACC_COLS;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
@@ -115,7 +130,10 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
                         if (rank == 0) mbar_expect_tx(&full[s], 2 * (A_BYTES + B_BYTES));
                         const uint32_t bar = cluster_addr(&full[s], 0);
                         tma_load_2d_pair(sa, &a_map, kb * BK, a0, bar);
-                        tma_load_2d_pair(sa + A_BYTES, &b_map, kb * BK, b0, bar);
+#pragma unroll
+                        for (int h = 0; h < N_MMA; h++)     // MMA h reads weight rows h * MMA_N ...: this block brings its half of them
+                            tma_load_2d_pair(sa + A_BYTES + h * (B_BOX * BK * 2), &b_map, kb * BK,
+                                             b0 - rank * B_ROWS + h * MMA_N + rank * B_BOX, bar);
                     } else {
                         mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
                         tma_load_2d(sa, &a_map, kb * BK, a0, &full[s]);
@@ -126,15 +144,15 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MMA_N >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
             int it = 0, n = 0;
             bool ok = true;
             TileWalk walk(g.shared_tiles, n_tiles, nkb, unit, units);
             Piece p;
             for (; ok && walk.next(p); n++) {
-                const int buf = n & 1;
-                // the epilogue must have drained this accumulator (its use before last)
-                if (!mbar_wait(&acc_empty[buf], (uint32_t)(((n >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); ok = false; break; }
+                const int buf = N_ACC == 2 ? n & 1 : 0, use = N_ACC == 2 ? n >> 1 : n;      // which accumulator, and its how-manieth use
+                // the epilogue must have drained this accumulator (its use before this one)
+                if (!mbar_wait(&acc_empty[buf], (uint32_t)((use & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); ok = false; break; }
                 tc_fence_after();
                 const uint32_t acc = tmem + buf * ACC_COLS;
                 for (int kb = p.kb0; kb < p.kb1; kb++, it++) {
@@ -146,7 +164,11 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++) {
                         const uint32_t accumulate = (kb > p.kb0 || k > 0) ? 1u : 0u;
-                        if (PAIR) tc_mma_bf16_pair(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accumulate);
+                        if (PAIR) {
+#pragma unroll
+                            for (int h = 0; h < N_MMA; h++)     // a box of B_BOX rows of 128 bytes: whole groups of 8 rows, 1024 bytes each
+                                tc_mma_bf16_pair(acc + h * MMA_N, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2 + ((h * B_BOX * BK * 2) >> 4)), idesc, accumulate);
+                        }
                         else tc_mma_bf16(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accumulate);
                     }
                     if (PAIR) tc_commit_pair(&empty[s]); else tc_commit(&empty[s]);
@@ -173,11 +195,11 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
             }
         };
         for (; walk.next(p); n++) {
-            const int buf = n & 1;
+            const int buf = N_ACC == 2 ? n & 1 : 0, use = N_ACC == 2 ? n >> 1 : n;
             int a0, b0;
             tile_origin(p.tile, tiles_a, tiles_b, TILE_ROWS, BN, a0, b0);
             const int i = a0 + rank * BM + q * 32 + lane;
-            if (!mbar_wait(&acc_full[buf], (uint32_t)((n >> 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            if (!mbar_wait(&acc_full[buf], (uint32_t)(use & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
