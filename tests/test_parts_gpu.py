@@ -381,13 +381,42 @@ def test_toy_parts_register_build_and_step(graph):
         assert eng.graph_replays > 0
 
 
+def test_toy_parts_in_pieces_and_beside_decoding_sequences():
+    """The same toy model (a mixer with a state, a routed feed-forward, two position encodings) under the
+    step function's general form: a prompt fed in pieces, and a prompt that starts while another sequence
+    decodes.  Nothing in the toy parts knows about these cuts: the state mixer scans whatever tokens a
+    step brings from the state its slot holds."""
+    from toyinfer_b200.engine import Engine
+    from toyinfer_b200.parts.model import DecoderModel
+    make_toy_parts()
+    model = DecoderModel(toy_spec(), torch.float32, DEV)
+    w = bind_random(model, 7, torch.float32)
+    eng = Engine(model, max_tokens=64 * 6, max_batch=4, max_seq_len=256)
+    g = torch.Generator().manual_seed(18)
+    a, b = (torch.randint(0, 90, (n,), generator=g).tolist() for n in (75, 40))
+    wa, wb = toy_plain_forward(w, a), toy_plain_forward(w, b)
+    sa = eng.new_sequence()
+    got = [eng.step([(sa, a[lo:hi])], [list(range(hi - lo))]).clone() for lo, hi in ((0, 9), (9, 10), (10, 50))]
+    torch.testing.assert_close(torch.cat(got).cpu().double(), wa[:50], rtol=1e-4, atol=1e-5)
+    sb = eng.new_sequence()
+    out = eng.step([(sa, [a[50]]), (sb, b[:30])], [[0], [0, 29]]).clone()          # b starts beside a
+    torch.testing.assert_close(out.cpu().double(), torch.stack([wa[50], wb[0], wb[29]]), rtol=1e-4, atol=1e-5)
+    out = eng.step([(sa, a[51:60]), (sb, [b[30]])], [[8], [0]]).clone()            # a goes on by nine, b by one
+    torch.testing.assert_close(out.cpu().double(), torch.stack([wa[59], wb[30]]), rtol=1e-4, atol=1e-5)
+    out = eng.step([(sa, [a[60]]), (sb, [b[31]])], None).clone()
+    torch.testing.assert_close(out.cpu().double(), torch.stack([wa[60], wb[31]]), rtol=1e-4, atol=1e-5)
+
+
 # ---------------------------------------------------------------------------
 # the order of layers is data
 # ---------------------------------------------------------------------------
+@pytest.mark.parametrize("window", [0, 40])
 @pytest.mark.parametrize("dtype", DT)
-def test_schedule_names_a_layer_twice_and_borrows_a_cache(dtype):
+def test_schedule_names_a_layer_twice_and_borrows_a_cache(dtype, window):
     """Layers A, B and C (C has no keys and values of its own).  Schedule: A, B, B again
-    (same weights, a cache of its own), C reading the cache of the first B."""
+    (same weights, a cache of its own), C reading the cache of the first B.  Whole prompts, single
+    tokens, and then pieces of several tokens: with a window the first B's new keys must not reach its
+    ring before C, which reads that ring, has run (the store waits in ``shared["deferred"]``)."""
     from toyinfer_b200.engine import Engine
     from toyinfer_b200.parts import PartSpec
     from toyinfer_b200.parts.model import DecoderModel, LayerSpec, ModelSpec, ScheduleEntry
@@ -395,7 +424,7 @@ def test_schedule_names_a_layer_twice_and_borrows_a_cache(dtype):
     norm = PartSpec("rmsnorm", {"size": H, "eps": eps})
     ffn = PartSpec("swiglu", {"intermediate_size": 72})
     att = lambda own: PartSpec("gqa_attention", {"n_heads": nh, "n_kv_heads": nkv, "head_dim": hd, "qk_norm_eps": eps,
-                                                 "position": "rope", "own_kv": own})
+                                                 "position": "rope", "own_kv": own, "window": window})
     layers = [LayerSpec(f"model.layers.{i}.", PartSpec("prenorm", {"norm": norm, "mixer": att(i < 2), "feed_forward": ffn}))
               for i in range(3)]
     schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1), ScheduleEntry(2, memory_of=1)]
@@ -416,13 +445,13 @@ def test_schedule_names_a_layer_twice_and_borrows_a_cache(dtype):
             p = f"model.layers.{ent.layer}."
             x = plain.rms_norm(h, w[p + "input_layernorm.weight"], eps, r)
             if ent.memory_of is None:
-                a, kept[e] = plain_attention_layer(x, w, p + "self_attn.", nh, nkv, hd, eps, theta, 0, r)
+                a, kept[e] = plain_attention_layer(x, w, p + "self_attn.", nh, nkv, hd, eps, theta, window, r)
             else:
                 T = x.shape[0]
                 q = plain.linear(x, w[p + "self_attn.q_proj.weight"], r).view(T, nh, hd)
                 q = plain.rope(plain.rms_norm(q, w[p + "self_attn.q_norm.weight"], eps, r), plain.rope_angles(hd, theta, range(T)), r)
                 k, v = kept[ent.memory_of]
-                a = plain.linear(plain.attention(q, k, v, 1 / math.sqrt(hd), 0, r).reshape(T, nh * hd), w[p + "self_attn.o_proj.weight"], r)
+                a = plain.linear(plain.attention(q, k, v, 1 / math.sqrt(hd), window, r).reshape(T, nh * hd), w[p + "self_attn.o_proj.weight"], r)
             h = plain.rnd(h + a, r)
             x = plain.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps, r)
             m = plain.linear(plain.swiglu(plain.linear(x, w[p + "mlp.gate_proj.weight"], r), plain.linear(x, w[p + "mlp.up_proj.weight"], r), r),
@@ -433,7 +462,7 @@ def test_schedule_names_a_layer_twice_and_borrows_a_cache(dtype):
     from helpers import assert_logits_close
     name = "float32" if dtype == torch.float32 else "bfloat16"
     g = torch.Generator().manual_seed(10)
-    seqs = [torch.randint(0, V, (n,), generator=g).tolist() for n in (40, 75)]
+    seqs = [torch.randint(0, V, (n,), generator=g).tolist() for n in (100, 120)]
     want = [plain_forward(s) for s in seqs]
     slots = [eng.new_sequence() for _ in seqs]
     heads = [30, 70]
@@ -442,6 +471,13 @@ def test_schedule_names_a_layer_twice_and_borrows_a_cache(dtype):
     for t in range(5):
         logits = eng.step([(slots[i], [seqs[i][heads[i] + t]]) for i in range(2)], None).clone()
         assert_logits_close(logits, torch.stack([want[i][heads[i] + t] for i in range(2)]), name, f"schedule, step {t}")
+    # pieces: the first sequence goes on by 50 tokens at once (more than the ring has slack), the second by one
+    at = [heads[0] + 5, heads[1] + 5]
+    logits = eng.step([(slots[0], seqs[0][at[0]:at[0] + 50]), (slots[1], [seqs[1][at[1]]])], [[0, 24, 49], [0]]).clone()
+    assert_logits_close(logits, torch.stack([want[0][at[0]], want[0][at[0] + 24], want[0][at[0] + 49], want[1][at[1]]]), name,
+                        "schedule, pieces")
+    logits = eng.step([(slots[0], [seqs[0][at[0] + 50]]), (slots[1], seqs[1][at[1] + 1:at[1] + 4])], [[0], [2]]).clone()
+    assert_logits_close(logits, torch.stack([want[0][at[0] + 50], want[1][at[1] + 3]]), name, "schedule, after the pieces")
 
 
 def test_unknown_part_and_bad_schedule_are_refused():
