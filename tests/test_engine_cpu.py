@@ -228,3 +228,25 @@ def test_default_cache_size_asks_the_cache_for_bytes_per_token():
     assert bytes_per_token(reqs, torch.bfloat16) == 2 * 2 * 16 * 2 + 2 * 8 * 128 * 2
     assert bytes_per_token(reqs, torch.float32) == 2 * (2 * 2 * 16 * 2 + 2 * 8 * 128 * 2)
     assert bytes_per_token([None, StateRequest((5,))], torch.float32) == 0
+
+
+def test_decode_attention_merges_as_clusters_only_when_all_find_room(monkeypatch):
+    """The plan of a decode step's attention: splits of two pages merged inside clusters when the
+    device holds all clusters at once with some to spare, else splits of four pages merged through
+    scratch memory; the same answer for the same padded batch and planned length."""
+    from toyinfer_b200.kernels import attention
+    room = {16: 14, 9: 30, 8: 33, 4: 71, 2: 148}
+    monkeypatch.setattr(attention, "cluster_room", lambda hd, fused, splits: room.get(splits, 296 // splits))
+    monkeypatch.setattr(attention, "_combine_late", lambda n_seq: n_seq <= 16)
+    plan = lambda n_seq, length, tc=True: attention.decode_plan(n_seq, 32, 8, 128, length, 64, 148, tc, True)
+    assert plan(1, 2112) == (16, 2)          # 8 clusters of 16, room for 14
+    assert plan(2, 2112) == (9, 1)           # 16 clusters of 16 do not fit: nine splits of four pages
+    assert plan(4, 2112) == (9, 1)           # 32 clusters of 9, room for 30
+    assert plan(8, 2112) == (4, 2)           # 64 of 4, room for 71
+    assert plan(8, 100) == (1, 1)            # two pages: nothing to split
+    assert plan(32, 2112) == (1, 0)          # a block per SM without splits
+    assert plan(1, 2112, tc=False) == (9, 1)   # the CUDA-core kernel knows no clusters
+    monkeypatch.setattr(attention, "force_merge_mode", 2)
+    assert plan(2, 2112) == (16, 2)
+    monkeypatch.setattr(attention, "force_merge_mode", 0)
+    assert plan(1, 2112) == (9, 0)

@@ -693,9 +693,9 @@ def test_attention_decode(K, dtype, nh, nkv, hd, window):
     scale = 1.0 / math.sqrt(hd)
     from toyinfer_b200.kernels import attention
     # different split counts must agree, and so must the two ways the tensor-core kernel's splits
-    # meet: as a cluster through distributed shared memory (the default) and through global scratch
-    # with the combine kernel (forced here)
-    for plan, mode in ((64, None), (4096, None), (40960, None), (4096, 1), (40960, 0)):
+    # meet: as a cluster through distributed shared memory (chosen when all clusters find room at
+    # once) and through global scratch with the combine kernel; each is forced here as well
+    for plan, mode in ((64, None), (4096, None), (40960, None), (4096, 1), (40960, 0), (4096, 2), (40960, 2)):
         batch = make_batch("extend", list(range(len(lens))), [n - 1 for n in lens], [1] * len(lens), plan_len=plan)
         attention.force_merge_mode = mode
         try:

@@ -510,6 +510,41 @@ int launch(const tiattn::DecodeArgs& a, const FuseArgs& f, int n_seq, int mode, 
 }
 }  // namespace
 
+namespace {
+template <int HD, bool FUSED>
+int cluster_room(int n_splits, int* room) {
+    constexpr size_t stage_bytes = 2 * TILE * HD * 2;
+    constexpr size_t merge_bytes = (4 * 16 * HD + 2 * 4 * 16 + 16 * HD + 2 * 16) * sizeof(float);
+    constexpr size_t smem = (STAGES * stage_bytes > merge_bytes ? STAGES * stage_bytes : merge_bytes) + 1024;
+    TI_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<HD, FUSED, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    TI_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<HD, FUSED, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, n_splits);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)n_splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TI_CUDA(cudaOccupancyMaxActiveClusters(room, attn_decode_mma_kernel<HD, FUSED, true>, &cfg));
+    return 0;
+}
+}  // namespace
+
+// How many clusters of n_splits blocks of the cluster form of the kernel the device holds at once
+// (0: such a cluster cannot be placed at all).  The host merges through a cluster only when all
+// clusters of a step find room together: a second round of clusters costs more than the merge
+// through global memory saves.
+extern "C" int ti_attn_decode_cluster_room(int head_dim, int fused, int n_splits, int* room) {
+    TI_REQUIRE(head_dim == 64 || head_dim == 128, "attention_decode (cluster): head size %d is not 64 or 128", head_dim);
+    TI_REQUIRE(n_splits >= 1 && n_splits <= MAX_CLUSTER && room != nullptr, "attention_decode (cluster): bad cluster size %d", n_splits);
+    if (head_dim == 64) return fused ? cluster_room<64, true>(n_splits, room) : cluster_room<64, false>(n_splits, room);
+    return fused ? cluster_room<128, true>(n_splits, room) : cluster_room<128, false>(n_splits, room);
+}
+
 // bfloat16 only; head_dim 64 or 128; pages of 64 positions.  Same arguments as
 // ti_attn_decode_simt, plus `mode`: how the splits' results are merged (see launch above; with
 // mode 2 no scratch is needed).

@@ -2,6 +2,8 @@
 decode kernel."""
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import KernelError, _call, _code, _ptr, _row_stride, _stream
@@ -68,16 +70,27 @@ def chunk(q, k, v, mem, out, scale, window, batch) -> None:
           k.shape[1], hd, scale, window, *cache, _code(q, "attention_chunk"), _stream())
 
 
-def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int) -> int:
+def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int, min_pages: int = 4, most: int = 64) -> int:
     """Splits along the keys so that the grid has about two blocks per SM, but no split
-    shorter than two pages and no more than the 16 blocks one cluster holds (the tensor-core
-    kernel merges the splits of a cluster itself; measured at one sequence of 2,176 positions:
-    16 splits of two pages 2.11 ms per step, 8 of four 2.14, 4 of eight 2.23).  Depends only on
-    the batch's padded size and the longest length the step was planned for, so that a captured
-    launch stays valid."""
+    shorter than ``min_pages`` pages and no more than ``most``.  Depends only on the batch's
+    padded size and the longest length the step was planned for, so that a captured launch
+    stays valid."""
     tiles = max(1, (max_len + page - 1) // page)
     want = max(1, (2 * sms) // max(1, n_seq * n_kv_heads))
-    return max(1, min(want, (tiles + 1) // 2, MAX_CLUSTER))
+    return max(1, min(want, (tiles + min_pages - 1) // min_pages, most))
+
+
+_cluster_room: dict = {}
+
+
+def cluster_room(hd: int, fused: bool, splits: int) -> int:
+    """Clusters of ``splits`` blocks of the tensor-core decode kernel that the device holds at once."""
+    key = (hd, bool(fused), splits)
+    if key not in _cluster_room:
+        room = ctypes.c_int(0)
+        _call(library().ti_attn_decode_cluster_room, hd, 1 if fused else 0, splits, ctypes.byref(room), launches=0)
+        _cluster_room[key] = room.value
+    return _cluster_room[key]
 
 
 # A decode attention kernel with large shared memory leaves the SMs without an L1 for kernels that
@@ -93,27 +106,39 @@ def _combine_late(n_seq: int) -> bool:
     return n_seq <= max(gemm.SKINNY_MAX_TOKENS, gemm.GEMV_MAX_TOKENS)
 
 
-force_merge_mode = None      # tests set 0 or 1 here to run the tensor-core kernel's splits through global scratch
+force_merge_mode = None      # tests set 0, 1 or 2 here to choose how the tensor-core kernel's splits meet
 
 
-def _merge_mode(n_seq: int, splits: int, tensor_cores: bool) -> int:
-    """How the splits' partial results meet (csrc/attn_decode_mma.cu): 2 the splits of a kv head are
-    one cluster and merge through distributed shared memory (no scratch, no second kernel); else
-    through global scratch and a combine kernel, started late (1) or like every kernel (0)."""
-    if force_merge_mode is not None:
-        return force_merge_mode
-    if tensor_cores and 2 <= splits <= MAX_CLUSTER:
-        return 2
-    return 1 if _combine_late(n_seq) else 0
+def decode_plan(n_seq: int, n_heads: int, n_kv_heads: int, hd: int, max_len: int, page: int, sms: int,
+                tensor_cores: bool, fused: bool) -> tuple:
+    """(splits, mode) of a decode step's attention.  mode (csrc/attn_decode_mma.cu): 2 the splits of a
+    kv head are one cluster and merge through distributed shared memory (no scratch, no second kernel);
+    else through global scratch and a combine kernel, started late (1) or like every kernel (0).
+
+    The cluster form takes splits of two pages and up to 16 blocks, but only when all of the step's
+    clusters find room on the device together with some to spare (clusters are placed whole, inside one
+    part of the chip: a second round of them costs far more than the merge saves).  Measured on 36 layers
+    of 32 heads over 8 at 2,112 positions, ms per step, cluster against scratch: one sequence (8 clusters
+    of 16, room for 14) 2.13 / 2.18; two (16 of 16) 2.63 / 2.28; four (32 of 9, room for 30) 2.70 / 2.35,
+    (32 of 8, room for 33) 2.73 / 2.35; eight (64 of 4, room for 71) ahead by 1 to 3 %."""
+    scratch_mode = 1 if _combine_late(n_seq) else 0
+    if tensor_cores and force_merge_mode in (None, 2):
+        splits = decode_splits(n_seq, n_kv_heads, max_len, page, sms, min_pages=2, most=MAX_CLUSTER)
+        clusters = n_seq * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
+        if splits >= 2 and (force_merge_mode == 2 or clusters * 1.08 <= cluster_room(hd, fused, splits)):
+            return splits, 2
+    splits = decode_splits(n_seq, n_kv_heads, max_len, page, sms)
+    if tensor_cores and force_merge_mode in (0, 1):
+        return splits, force_merge_mode
+    return splits, scratch_mode
 
 
 def decode(q, mem, out, scale, window, batch) -> None:
     B, nh, hd = q.shape
     nkv = mem.n_kv_heads
     span = batch.plan_len if window <= 0 else min(batch.plan_len, window + mem.page_size)
-    splits = decode_splits(B, nkv, span, mem.page_size, sm_count(q.device))
     tensor_cores = q.dtype == torch.bfloat16 and hd in (64, 128)
-    mode = _merge_mode(B, splits, tensor_cores)
+    splits, mode = decode_plan(B, nh, nkv, hd, span, mem.page_size, sm_count(q.device), tensor_cores, False)
     part_o = part_ml = None
     if splits > 1 and mode != 2:
         part_o = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device)
@@ -154,8 +179,7 @@ def decode_fused(q, k, v, q_w, k_w, eps, tables, mem, out, scale, window, batch)
     B, nh, hd = q.shape
     nkv = mem.n_kv_heads
     span = batch.plan_len if window <= 0 else min(batch.plan_len, window + mem.page_size)
-    splits = decode_splits(B, nkv, span, mem.page_size, sm_count(q.device))
-    mode = _merge_mode(B, splits, True)
+    splits, mode = decode_plan(B, nh, nkv, hd, span, mem.page_size, sm_count(q.device), True, True)
     part_o = part_ml = None
     if splits > 1 and mode != 2:
         part_o = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device)
