@@ -609,15 +609,15 @@ def fill_cache(mem, slot, pages, k, v):
 
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (5, 1, 48, 40), (8, 4, 64, 0), (8, 2, 128, 0), (4, 4, 128, 64),
-                                               (6, 2, 64, 100), (2, 1, 256, 0)])
+                                               (6, 2, 64, 100), (2, 1, 256, 0), (8, 1, 128, 100), (6, 3, 128, 300)])
 def test_attention_chunk(K, dtype, nh, nkv, hd, window):
     """New tokens after positions in the cache: (positions held, new tokens) per sequence covers a
     sequence that starts, single tokens, a start in the middle and at the end of a page, runs of
     new tokens longer than a window's ring, and a ring that has wrapped.  Cache lines that no
     query may read hold NaN; so do the lines where this step's own tokens will go."""
-    cases = [(0, 70), (64, 1), (65, 40), (300, 1), (129, 130), (1, 1), (200, 200), (127, 2)]
-    mem = make_mem(dtype, len(cases), nkv, hd, pages=40, window=window, dirty=float("nan"))
-    free = list(range(40, 0, -1))
+    cases = [(0, 70), (64, 1), (65, 40), (300, 1), (129, 130), (1, 1), (200, 200), (127, 2), (700, 300)]
+    mem = make_mem(dtype, len(cases), nkv, hd, pages=64, window=window, dirty=float("nan"))
+    free = list(range(64, 0, -1))
     scale = 1.0 / math.sqrt(hd)
     ks = [randn(st + n, nkv, hd, seed=130 + i).to(dtype) for i, (st, n) in enumerate(cases)]
     vs = [randn(st + n, nkv, hd, seed=140 + i).to(dtype) for i, (st, n) in enumerate(cases)]

@@ -1,7 +1,12 @@
 // Causal grouped-query attention over the tokens of one step on the 5th-generation tensor
 // cores: both products of a tile, S = Q K^T and O += P V, are tcgen05 MMAs with their
 // accumulators in tensor memory.  Same contract and formulas as attn_prefill_simt.cu
-// (reference: src/prefill.cu:224-379); head_dim 128, bfloat16.
+// (reference: src/prefill.cu:224-379); head_dim 128, bfloat16.  Two forms, as there: sequences
+// that start at position 0, and, PAGED, new tokens after `seq_start[b]` positions kept in the
+// paged cache: a block then first walks the sequence's pages below the start (a page is 64
+// positions x head_dim of one kv head: one key tile and one value tile, read with the same TMA
+// box as a tile of the step) and then the step's own keys and values; one online softmax runs
+// over both, and nothing but the source of a tile's loads and its mask knows the difference.
 //
 // A block owns 128 queries of one head (grid: heads, sequences, query tiles from the last to
 // the first) and walks over key/value tiles of 64 positions; tiles that the causal mask or the
@@ -42,6 +47,8 @@ constexpr int BQ = 128, BKV = 64, THREADS = 320;      // TMA warp, MMA warp, eig
 struct Args {
     const int* cu_new; int n_heads, n_kv_heads; float scale; int window;
     void* out; long long o_stride;
+    // PAGED form: where the positions before the step's tokens are kept
+    const int* seq_start; const int* seq_slot; const int* page_table; int table_width, ring_rows, n_pages;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -86,10 +93,11 @@ template <int HD> struct Smem {
     static constexpr int TOTAL = L_OFF + 2 * BQ * 4;
 };
 
-template <int HD>
+template <int HD, bool PAGED>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                       const __grid_constant__ CUtensorMap v_map, Args a, int* status) {
+                       const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap kp_map,
+                       const __grid_constant__ CUtensorMap vp_map, Args a, int* status) {
     ti_pdl_trigger();
     using L = Smem<HD>;
     constexpr int Q_BYTES = L::Q_BYTES, KV_BYTES = L::KV_BYTES;
@@ -155,7 +163,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const int kvh = h / (a.n_heads / a.n_kv_heads);
     const int last_q = min(q0 + BQ, n) - 1;
     const int kt_lo = a.window > 0 ? max(0, q0 - a.window + 1) / BKV : 0;
-    const int n_tiles = active ? last_q / BKV - kt_lo + 1 : 0;
+    // PAGED: the sequence's positions below `start`, one page a tile, pages pt_lo .. pt_lo + n_old - 1,
+    // before the step's own.  lo_blk is the oldest position any query of this block reads.  Key
+    // positions are counted from the step's first token of the sequence, so a page's are negative.
+    const int start = PAGED ? a.seq_start[b] : 0;
+    const int slot = PAGED ? a.seq_slot[b] : 0;
+    const int lo_blk = (PAGED && a.window > 0) ? max(0, start + q0 - a.window + 1) : 0;
+    const int pt_lo = lo_blk / BKV;
+    const int n_old = (PAGED && active && lo_blk < start) ? (start - 1) / BKV - pt_lo + 1 : 0;
+    const int n_tiles = active ? n_old + last_q / BKV - kt_lo + 1 : 0;
 
     if (active && warp == 0) {
         if (lane == 0) {
@@ -165,13 +181,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             // Keys run one tile ahead of values: the keys of tile j + 1 are asked for as soon as the
             // first product of tile j - 1 has read that buffer, the values of tile j once the second
             // product of tile j - 2 has read theirs.
+            // the first row, in the tensor map of the pages, of the page that holds tile j of the old positions
+            auto page_row = [&](int j) -> int {
+                const int p0 = (pt_lo + j) * BKV;
+                const int pidx = (a.ring_rows > 0 ? p0 % a.ring_rows : p0) / BKV;
+                int page = pidx < a.table_width ? a.page_table[(size_t)slot * a.table_width + pidx] : 0;
+                if (page < 0 || page >= a.n_pages) page = 0;
+                return (page * a.n_kv_heads + kvh) * BKV;
+            };
             auto load_k = [&](int j) -> bool {
                 const int s = j & 1;
                 if (!mbar_wait(&k_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); return false; }
                 unsigned char* ks = kv_s + (size_t)s * 2 * KV_BYTES;
                 mbar_expect_tx(&k_full[s], KV_BYTES);
+                if (PAGED && j < n_old) {
+                    const int y = page_row(j);
 #pragma unroll
-                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + bx * KBOX, &k_map, kvh * HD + bx * 64, tok0 + (kt_lo + j) * BKV, &k_full[s]);
+                    for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + bx * KBOX, &kp_map, bx * 64, y, &k_full[s]);
+                    return true;
+                }
+#pragma unroll
+                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + bx * KBOX, &k_map, kvh * HD + bx * 64, tok0 + (kt_lo + j - n_old) * BKV, &k_full[s]);
                 return true;
             };
             auto load_v = [&](int j) -> bool {
@@ -179,8 +209,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 if (!mbar_wait(&v_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); return false; }
                 unsigned char* vs = kv_s + (size_t)s * 2 * KV_BYTES + KV_BYTES;
                 mbar_expect_tx(&v_full[s], KV_BYTES);
+                if (PAGED && j < n_old) {
+                    const int y = page_row(j);
 #pragma unroll
-                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(vs + bx * KBOX, &v_map, kvh * HD + bx * 64, tok0 + (kt_lo + j) * BKV, &v_full[s]);
+                    for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(vs + bx * KBOX, &vp_map, bx * 64, y, &v_full[s]);
+                    return true;
+                }
+#pragma unroll
+                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(vs + bx * KBOX, &v_map, kvh * HD + bx * 64, tok0 + (kt_lo + j - n_old) * BKV, &v_full[s]);
                 return true;
             };
             bool ok = n_tiles > 0 && load_k(0);
@@ -262,8 +298,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             if (ok && !mbar_wait(&s_full[sb], (uint32_t)((j >> 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
-            const int k0 = (kt_lo + j) * BKV + half * HALF;
-            const bool edge = a.window > 0 || k0 + HALF - 1 > q0 + qd * 32 || k0 + HALF > n;
+            const bool old = PAGED && j < n_old;
+            const int tile0 = old ? (pt_lo + j) * BKV - start : (kt_lo + j - n_old) * BKV;   // the tile's first position
+            const int limit = old ? 0 : n;                                                  // where its valid keys end
+            const int k0 = tile0 + half * HALF;
+            const bool edge = a.window > 0 || k0 + HALF - 1 > q0 + qd * 32 || k0 + HALF > limit;
             const uint32_t s_addr = tmem + sb * S_COLS + lane_base;
             // this thread's 32 scores of the row, as the product left them (the scale comes later)
             float v[HALF];
@@ -277,7 +316,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #pragma unroll
                 for (int e = 0; e < HALF; e++) {
                     const int kj = k0 + e;
-                    const bool vis = kj <= qi && kj < n && (a.window <= 0 || kj > qi - a.window);
+                    const bool vis = kj <= qi && kj < limit && (a.window <= 0 || kj > qi - a.window);
                     v[e] = vis ? v[e] : -INFINITY;
                 }
             }
@@ -318,6 +357,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             float sum4[4];
             unpack2(sum2[0], sum4[0], sum4[1]);
             unpack2(sum2[1], sum4[2], sum4[3]);
+            if (old && (tile0 + BKV > 0 || tile0 + start < lo_blk)) {
+                // Lines of the page outside [lo_blk, start) may hold anything (this step's tokens, an
+                // older turn of the ring, a former owner's): their value rows are cleared, so that a
+                // probability of zero times whatever stands there cannot make a NaN.  A row of a box is
+                // 128 bytes whatever the swizzle does inside it; four threads clear a row of both boxes.
+                // The second product starts only after every softmax warp has arrived on p_full below,
+                // and the next load into this buffer only after that product.
+                if (ok && !mbar_wait(&v_full[sb], (uint32_t)((j >> 1) & 1))) { ti_report(status, TI_STATUS_TMA_WAIT); ok = false; }
+                if (ok) {
+                    const int st = (int)threadIdx.x - 64, row = st >> 2, part = st & 3;
+                    const int p = tile0 + start + row;
+                    if (p < lo_blk || p >= start) {
+                        uint4* dst = reinterpret_cast<uint4*>(kv_s + (size_t)sb * 2 * KV_BYTES + KV_BYTES + (part >> 1) * KBOX + row * 128 + (part & 1) * 64);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) dst[e] = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async();
+                }
+            }
             // Every tile's completion is waited for, in order (a parity wait can only tell one phase
             // from the next); by now the previous tile's second product has long been issued.
             if (ok && j > 0 && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
@@ -408,38 +466,85 @@ int view_map(const void* ptr, long long rows, long long cols, long long stride, 
 }
 }  // namespace
 
+namespace {
+int check_common(const char* what, const void* q, const void* k, const void* v, const void* out, long long q_stride,
+                 long long k_stride, long long v_stride, long long o_stride, int n_seq, int n_tokens, int n_heads,
+                 int n_kv_heads, int head_dim, CUtensorMap* qm, CUtensorMap* km, CUtensorMap* vm) {
+    TI_REQUIRE(head_dim == 128, "%s (tcgen05): head size %d is not 128", what, head_dim);
+    TI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "%s: bad head counts", what);
+    TI_REQUIRE(n_seq <= 65535 && n_heads <= 65535, "%s: too many sequences or heads for one launch", what);
+    TI_REQUIRE(n_tokens <= 65535 * BQ, "%s: %d tokens are too many for one launch", what, n_tokens);
+    TI_REQUIRE(q_stride % 8 == 0 && k_stride % 8 == 0 && v_stride % 8 == 0 && o_stride % 8 == 0,
+               "%s (tcgen05): token strides must be multiples of 8 elements", what);
+    TI_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                 reinterpret_cast<uintptr_t>(out)) & 15) == 0, "%s (tcgen05): misaligned operands", what);
+    if (int rc = view_map(q, n_tokens, (long long)n_heads * head_dim, q_stride, BQ, qm)) return rc;
+    if (int rc = view_map(k, n_tokens, (long long)n_kv_heads * head_dim, k_stride, BKV, km)) return rc;
+    if (int rc = view_map(v, n_tokens, (long long)n_kv_heads * head_dim, v_stride, BKV, vm)) return rc;
+    return 0;
+}
+
+template <bool PAGED>
+int launch(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const CUtensorMap& kpm, const CUtensorMap& vpm,
+           const Args& a, int n_seq, int max_new, cudaStream_t stream) {
+    constexpr int HD = 128;
+    constexpr size_t smem = Smem<HD>::TOTAL;
+    static bool configured = false;
+    if (!configured) {
+        TI_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    int* status = ti_status_ptr();
+    TI_REQUIRE(status != nullptr, "attention_prefill: no status word");
+    dim3 grid(a.n_heads, n_seq, (max_new + BQ - 1) / BQ);
+    TI_CUDA(ti_launch(attn_prefill_tc_kernel<HD, PAGED>, grid, dim3(THREADS), smem, stream, qm, km, vm, kpm, vpm, a, status));
+    TI_CHECK_LAUNCH(PAGED ? "attention_chunk (tcgen05)" : "attention_prefill (tcgen05)");
+    return 0;
+}
+}  // namespace
+
 // bfloat16, head_dim 128.  Same arguments as ti_attn_prefill_mma.
 extern "C" int ti_attn_prefill_tc(const void* q, const void* k, const void* v, void* out,
                                   long long q_stride, long long k_stride, long long v_stride, long long o_stride,
                                   const int* cu_new, int n_seq, int max_new, int n_tokens, int n_heads, int n_kv_heads,
                                   int head_dim, float scale, int window, cudaStream_t stream) {
     if (n_seq == 0 || max_new == 0) return 0;
-    TI_REQUIRE(head_dim == 128, "attention_prefill (tcgen05): head size %d is not 128", head_dim);
-    TI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_prefill: bad head counts");
-    TI_REQUIRE(n_seq <= 65535 && n_heads <= 65535, "attention_prefill: too many sequences or heads for one launch");
-    TI_REQUIRE(n_tokens <= 65535 * BQ, "attention_prefill: %d tokens are too many for one launch", n_tokens);
-    TI_REQUIRE(q_stride % 8 == 0 && k_stride % 8 == 0 && v_stride % 8 == 0 && o_stride % 8 == 0,
-               "attention_prefill (tcgen05): token strides must be multiples of 8 elements");
-    TI_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
-                 reinterpret_cast<uintptr_t>(out)) & 15) == 0, "attention_prefill (tcgen05): misaligned operands");
     CUtensorMap qm, km, vm;
-    if (int rc = view_map(q, n_tokens, (long long)n_heads * head_dim, q_stride, BQ, &qm)) return rc;
-    if (int rc = view_map(k, n_tokens, (long long)n_kv_heads * head_dim, k_stride, BKV, &km)) return rc;
-    if (int rc = view_map(v, n_tokens, (long long)n_kv_heads * head_dim, v_stride, BKV, &vm)) return rc;
-    Args a;
+    if (int rc = check_common("attention_prefill", q, k, v, out, q_stride, k_stride, v_stride, o_stride, n_seq, n_tokens,
+                              n_heads, n_kv_heads, head_dim, &qm, &km, &vm)) return rc;
+    Args a = {};
     a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = window;
     a.out = out; a.o_stride = o_stride;
-    constexpr int HD = 128;
-    constexpr size_t smem = Smem<HD>::TOTAL;
-    static bool configured = false;
-    if (!configured) {
-        TI_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
-    }
-    int* status = ti_status_ptr();
-    TI_REQUIRE(status != nullptr, "attention_prefill: no status word");
-    dim3 grid(n_heads, n_seq, (max_new + BQ - 1) / BQ);
-    TI_CUDA(ti_launch(attn_prefill_tc_kernel<HD>, grid, dim3(THREADS), smem, stream, qm, km, vm, a, status));
-    TI_CHECK_LAUNCH("attention_prefill (tcgen05)");
-    return 0;
+    return launch<false>(qm, km, vm, km, vm, a, n_seq, max_new, stream);
+}
+
+// The same for new tokens after `seq_start[b]` positions that the cache holds (pages of 64
+// positions, bfloat16); arguments as ti_attn_chunk_mma.
+extern "C" int ti_attn_chunk_tc(const void* q, const void* k, const void* v, void* out,
+                                long long q_stride, long long k_stride, long long v_stride, long long o_stride,
+                                const int* cu_new, const int* seq_start, const int* seq_slot, int n_seq, int max_new,
+                                int n_tokens, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                const void* k_pages, const void* v_pages, const int* page_table, int table_width,
+                                int page_size, int ring_rows, int n_pages, cudaStream_t stream) {
+    if (n_seq == 0 || max_new == 0) return 0;
+    TI_REQUIRE(k_pages && v_pages && page_table && seq_start && seq_slot && table_width > 0 && n_pages > 0,
+               "attention_chunk: incomplete cache description");
+    TI_REQUIRE(page_size == BKV, "attention_chunk (tcgen05): pages of %d positions, this kernel works on %d", page_size, BKV);
+    TI_REQUIRE(ring_rows % page_size == 0, "attention_chunk: ring of %d rows is not whole pages", ring_rows);
+    TI_REQUIRE(ring_rows == 0 || (window > 0 && ring_rows >= window),
+               "attention_chunk: a ring of %d rows needs a window of at most as many positions (got %d)", ring_rows, window);
+    TI_REQUIRE(((reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages)) & 15) == 0,
+               "attention_chunk (tcgen05): cache pages must be 16-byte aligned");
+    CUtensorMap qm, km, vm, kpm, vpm;
+    if (int rc = check_common("attention_chunk", q, k, v, out, q_stride, k_stride, v_stride, o_stride, n_seq, n_tokens,
+                              n_heads, n_kv_heads, head_dim, &qm, &km, &vm)) return rc;
+    const long long rows = (long long)n_pages * n_kv_heads * BKV;
+    if (int rc = view_map(k_pages, rows, head_dim, head_dim, BKV, &kpm)) return rc;
+    if (int rc = view_map(v_pages, rows, head_dim, head_dim, BKV, &vpm)) return rc;
+    Args a = {};
+    a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = window;
+    a.out = out; a.o_stride = o_stride;
+    a.seq_start = seq_start; a.seq_slot = seq_slot; a.page_table = page_table; a.table_width = table_width;
+    a.ring_rows = ring_rows; a.n_pages = n_pages;
+    return launch<true>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream);
 }

@@ -61,7 +61,9 @@ def chunk(q, k, v, mem, out, scale, window, batch) -> None:
     if (q.dtype == torch.bfloat16 and hd in (64, 128) and mem.page_size == 64 and qs % 8 == 0 and ks % 8 == 0 and vs % 8 == 0
             and out.stride(0) % 2 == 0 and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0
             and mem.k_pages.data_ptr() % 16 == 0 and mem.v_pages.data_ptr() % 16 == 0):
-        _call(library().ti_attn_chunk_mma, _ptr(q), _ptr(k), _ptr(v), _ptr(out), qs, ks, vs, out.stride(0),
+        tcgen05 = hd == 128 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
+        fn = library().ti_attn_chunk_tc if tcgen05 else library().ti_attn_chunk_mma
+        _call(fn, _ptr(q), _ptr(k), _ptr(v), _ptr(out), qs, ks, vs, out.stride(0),
               _ptr(batch.cu_new), _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seq, batch.max_new, M, nh,
               k.shape[1], hd, scale, window, *cache, _stream())
         return

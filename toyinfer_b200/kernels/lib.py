@@ -37,6 +37,7 @@ def _declare(lib) -> None:
         "ti_attn_prefill_tc": [P, P, P, P, L, L, L, L, P, I, I, I, I, I, I, F, I, P],
         "ti_attn_chunk_simt": [P, P, P, P, L, L, L, L, P, P, P, I, I, I, I, I, F, I, P, P, P, I, I, I, I, I, P],
         "ti_attn_chunk_mma": [P, P, P, P, L, L, L, L, P, P, P, I, I, I, I, I, I, F, I, P, P, P, I, I, I, I, P],
+        "ti_attn_chunk_tc": [P, P, P, P, L, L, L, L, P, P, P, I, I, I, I, I, I, F, I, P, P, P, I, I, I, I, P],
         "ti_linear_tc": [P, P, P, I, I, I, L, L, L, I, I, I, P, P, P],
         "ti_linear_gemv": [P, P, P, I, I, I, L, L, L, I, I, I, I, P],
         "ti_linear_skinny": [P, P, P, I, I, I, L, L, L, I, I, I, I, P],
