@@ -458,9 +458,10 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             batch = fill_batch(BatchBuffers(1, T, dev), "start", [0], [0], [[0] * T], 1, T)
             return (lambda: K.attention_prefill(q, k, v, 1 / math.sqrt(hd), 0, batch)), qkv.numel() * 2 + T * nh * hd * 2, \
                 4.0 * nh * hd * T * (T + 1) / 2
-        if name.startswith("attn_chunk"):                 # attn_chunk or attn_chunk:CACHED,NEW
-            cached, new = (int(v) for v in name.split(":")[1].split(",")) if ":" in name else (2048, 2048)
-            nh, nkv, hd = 32, 8, 128
+        if name.startswith("attn_chunk"):                 # attn_chunk or attn_chunk:CACHED,NEW[,HEAD_DIM]
+            sizes = [int(v) for v in name.split(":")[1].split(",")] if ":" in name else [2048, 2048]
+            cached, new = sizes[:2]
+            nh, nkv, hd = 32, 8, (sizes[2] if len(sizes) > 2 else 128)     # heads of 64 run the mma.sync kernel
             pages = (cached + new + 63) // 64
             table = torch.zeros(2, pages, dtype=torch.int32, device=dev)
             table[0] = torch.arange(1, pages + 1, dtype=torch.int32, device=dev)
@@ -523,7 +524,7 @@ def main() -> int:
                     help="also the mean decode rate while the batch grows from 2,048 positions to --context (some 20 s more)")
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
                     "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K, attn_decode, attn_decode_b64, attn_decode_b1, "
-                    "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW]; "
+                    "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW[,HEAD_DIM]]; "
                     "ref:all or ref:<case> times the reference's kernel recompiled for sm_100a beside this library's")
     ap.add_argument("--workload", default="", choices=["", "8b", "32b"],
                     help="run one of the larger described workloads end to end instead (8B or 32B shape)")
