@@ -173,8 +173,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const int n_old = (PAGED && active && lo_blk < start) ? (start - 1) / BKV - pt_lo + 1 : 0;
     const int n_tiles = active ? n_old + last_q / BKV - kt_lo + 1 : 0;
 
-    if (active && warp == 0) {
-        if (lane == 0) {
+    if (active && warp_uniform() == 0) {
+        if (elect_one()) {
             mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
             for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(q_s + bx * QBOX, &q_map, h * HD + bx * 64, tok0 + q0, q_full);
@@ -225,8 +225,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 if (ok) ok = load_v(j);
             }
         }
-    } else if (active && warp == 1) {
-        if (lane == 0) {
+    } else if (active && warp_uniform() == 1) {
+        if (elect_one()) {
             constexpr uint32_t idesc_s = instr_desc_bf16(BKV, false);    // S: N = positions, K tile K-major
             constexpr uint32_t idesc_o = instr_desc_bf16(HD, true);      // O: N = head elements, V tile MN-major
             // The one thread that issues the products is on the block's critical path: descriptors
@@ -254,9 +254,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             }
             for (int j = 0; j < n_tiles && ok; j++) {
                 if (j + 1 < n_tiles) {
-                    // its score buffer holds P of tile j-1: that tile's second product must have read it
+                    // Its score buffer holds P of tile j-1, which that tile's second product reads.  That
+                    // product was issued before this one, by this thread, and the tensor cores take a
+                    // block's products in the order of issue: no wait for its completion is needed here
+                    // (the softmax warps are done with the buffer since they arrived on p_full for j-1).
                     const int sb = (j + 1) & 1, u = (j + 1) >> 1;
-                    if (!mbar_wait(&k_full[sb], (uint32_t)(u & 1)) || (j > 0 && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1)))) {
+                    if (!mbar_wait(&k_full[sb], (uint32_t)(u & 1))) {
                         ti_report(status, TI_STATUS_TMA_WAIT); ok = false; break;
                     }
                     tc_fence_after();
@@ -329,7 +332,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             }
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
             mx_s[(sb * 2 + half) * BQ + r] = mx;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + qd) : "memory");      // the two warps that share these rows
             mx = fmaxf(mx, mx_s[(sb * 2 + (half ^ 1)) * BQ + r]);
             float alpha = 1.f, m_new = m_used;
             if (mx > m_used + 8.f || (m_used == -INFINITY && mx > -INFINITY)) {
@@ -376,14 +379,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     fence_proxy_async();
                 }
             }
-            // Every tile's completion is waited for, in order (a parity wait can only tell one phase
-            // from the next); by now the previous tile's second product has long been issued.
-            if (ok && j > 0 && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            // O is touched only when some row of the warp rescales, and only then the previous tile's
+            // second product has to be through.  (pv_done is never more than one phase ahead of a
+            // softmax thread, whose own arrival on p_full every second product waits for: the parity
+            // of tile j-1 tells "through" from "pending" whether or not earlier phases were waited for.)
+            const bool rescale = j > 0 && __any_sync(0xffffffffu, alpha != 1.f);
+            if (ok && rescale && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             if (ok) {
-                if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                    // O may be touched: the previous tile's second product has finished.  Each half
-                    // rescales its 64 of the row's 128 columns.
+                if (rescale) {
+                    // Each half rescales its 64 of the row's 128 columns.
                     tc_fence_after();
 #pragma unroll 1
                     for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); c++) {
@@ -409,7 +414,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         }
         // the row's sum: both halves'
         l_s[half * BQ + r] = l_run;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + qd) : "memory");      // the two warps that share these rows
         l_run += l_s[(half ^ 1) * BQ + r];
         if (ok) {
             tc_fence_after();

@@ -14,6 +14,19 @@ __device__ __forceinline__ void tmem_relinquish() {
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
+// One lane of a converged warp, chosen by the hardware.  The thread that issues tcgen05.mma is
+// chosen this way inside a branch on a warp-uniform warp index (`warp_uniform()`), not by
+// `lane == 0`: the compiler then keeps descriptors and addresses in uniform registers, and one
+// thread issues an MMA of 128 x 64 x 16 every 35 cycles instead of every 80 (measured with
+// back-to-back MMAs, A in tensor memory; the MMA itself takes 32).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t p;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(p));
+    return p != 0;
+}
+__device__ __forceinline__ int warp_uniform() {
+    return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
