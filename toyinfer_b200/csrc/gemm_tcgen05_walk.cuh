@@ -111,8 +111,11 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
     const uint32_t tmem = tmem_slot;
     ti_pdl_sync();
 
-    if (warp == 0) {
-        if (lane == 0) {
+    // The loading and the issuing thread are elected inside branches on a warp-uniform value: the
+    // compiler then keeps their descriptors in uniform registers (see elect_one in tcgen05.cuh).
+    const int warp_u = warp_uniform();
+    if (warp_u == 0) {
+        if (elect_one()) {
             int it = 0;
             bool ok = true;
             TileWalk walk(g.shared_tiles, n_tiles, nkb, unit, units);
@@ -142,8 +145,8 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
                 }
             }
         }
-    } else if (warp == 1) {
-        if (lane == 0 && rank == 0) {
+    } else if (warp_u == 1) {
+        if (rank == 0 && elect_one()) {
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MMA_N >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
             int it = 0, n = 0;
             bool ok = true;
