@@ -57,7 +57,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
     // the kernel before this one may still be running; only the activations have to wait.
     const int n_pre = min(STAGES, n_iter);
     const bool weights_are_a = g.transposed != 0;
-    if (warp == 0 && lane == 0) {
+    // the loading and the issuing thread are elected inside branches on a warp-uniform value
+    // (see elect_one in tcgen05.cuh)
+    const int warp_u = warp_uniform();
+    bool loader = false;
+    if (warp_u == 0) loader = elect_one();
+    if (loader) {
         for (int it = 0; it < n_pre; it++) {
             unsigned char* sa = smem + (size_t)it * (A_BYTES + B_BYTES);
             mbar_expect_tx(&full[it], A_BYTES + B_BYTES);
@@ -67,9 +72,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
     }
     ti_pdl_sync();      // from here on memory written by earlier kernels may be read
 
-    if (warp == 0) {
+    if (warp_u == 0) {
         // ---- TMA producer
-        if (lane == 0) {
+        if (loader) {
             for (int it = 0; it < n_pre; it++) {
                 unsigned char* sa = smem + (size_t)it * (A_BYTES + B_BYTES);
                 if (weights_are_a) tma_load_2d(sa + A_BYTES, &b_map, (kb0 + it) * BK, b0, &full[it]);
@@ -84,9 +89,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
                 tma_load_2d(sa + A_BYTES, &b_map, (kb0 + it) * BK, b0, &full[s]);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp_u == 1) {
         // ---- MMA issuer
-        if (lane == 0) {
+        if (elect_one()) {
             constexpr uint32_t idesc = instr_desc<BN>();
             bool ok = true;
             for (int it = 0; it < n_iter && ok; it++) {
