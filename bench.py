@@ -185,12 +185,15 @@ def time_decode_range(engine, batch, start, end, seed=0):
             engine.end_sequence(s)
 
 
-def time_decode_sampled_range(engine, batch, lo, hi, points=13, steps=16, warm=3, seed=0):
+def time_decode_sampled_range(engine, batch, lo, hi, points=13, steps=16, warm=32, seed=0):
     """Mean decode step time while ``batch`` sequences grow from ``lo`` to ``hi`` positions, sampled:
     at ``points`` evenly spaced lengths the step is timed over ``steps`` steps that end there (after
     ``warm`` untimed ones); between the samples the sequences are brought forward by whole pieces
     of tokens (a step that continues every sequence by several hundred tokens).  The mean weighs
-    the two ends half (trapezoid rule): step time is close to linear in the length."""
+    the two ends half (trapezoid rule): step time is close to linear in the length.  The warm-up is
+    long on purpose: for some tens of milliseconds after a many-token step the decode steps run up to
+    a tenth slower (the clocks come back slowly from the tensor cores' load), whichever kernels the
+    many-token step used; with 3 warm-up steps the figure measured that step's intensity instead."""
     import torch
     vocab = engine.spec.vocab_size
     slots = [engine.new_sequence() for _ in range(batch)]
@@ -328,7 +331,7 @@ def run_ours(args):
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
             "tied": True, "global_batch": batch, "seq_len": ctx, "context": ctx, "prefill_tokens": PREFILL_TOKENS,
             "points_context": PREFILL_TOKENS, "parallelism": "single GPU", "l2": "inputs larger than L2, no flush",
-            "cuda_graph": True, "peaks": pk["source"], "range_points": "13 lengths from 2048 to context, 16 steps each",
+            "cuda_graph": True, "peaks": pk["source"], "range_points": "13 lengths from 2048 to context, 16 steps each after 32 untimed",
         },
         "e2e": {"value": round(e2e_value, 2) if e2e_value else None, "unit": "tokens/s",
                 "steps": st.decode_steps, "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": batch * 4},
