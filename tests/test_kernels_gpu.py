@@ -539,11 +539,15 @@ def plain_attention_on_gpu(q, k, v, scale, window, dtype):
     return plain.attention(q.double().cuda(), k.double().cuda(), v.double().cuda(), scale, window, rnd_mode(dtype)).cpu()
 
 
-@pytest.mark.parametrize("news,window", [([2048], 0), ([1025, 4097], 0), ([3000, 70], 1000)])
-def test_attention_prefill_tcgen05_at_long_lengths(K, news, window):
+@pytest.mark.parametrize("news,window,nh,nkv", [([2048], 0, 4, 2), ([1025, 4097], 0, 4, 2), ([3000, 70], 1000, 4, 2),
+                                                ([1300, 600, 129], 0, 32, 8), ([1300, 600, 129], 0, 4, 1), ([257], 0, 2, 1)])
+def test_attention_prefill_tcgen05_at_long_lengths(K, news, window, nh, nkv):
     """The tcgen05 kernel (head size 128) at the lengths prompts have in practice: 16 to 65 key
-    tiles per query tile, lengths one past a tile's end, two sequences in one launch."""
-    dtype, nh, nkv, hd = torch.bfloat16, 4, 2, 128
+    tiles per query tile, lengths one past a tile's end, several sequences in one launch.  With few
+    heads a block takes two query tiles, one from each end of its sequence (an odd number of
+    tiles leaves the middle one alone); with 32 heads and three sequences there are more blocks
+    than places, and every block takes one tile."""
+    dtype, hd = torch.bfloat16, 128
     M = sum(news)
     qkv = randn(M, (nh + 2 * nkv) * hd, seed=27).to(dtype)
     g = dev(qkv)

@@ -254,12 +254,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             }
             for (int j = 0; j < n_tiles && ok; j++) {
                 if (j + 1 < n_tiles) {
-                    // Its score buffer holds P of tile j-1, which that tile's second product reads.  That
-                    // product was issued before this one, by this thread, and the tensor cores take a
-                    // block's products in the order of issue: no wait for its completion is needed here
-                    // (the softmax warps are done with the buffer since they arrived on p_full for j-1).
+                    // its score buffer holds P of tile j-1: that tile's second product must have read it.
+                    // (Products of different accumulators are not promised to run in the order of issue,
+                    // so the wait stays although this thread issued that product first.)
                     const int sb = (j + 1) & 1, u = (j + 1) >> 1;
-                    if (!mbar_wait(&k_full[sb], (uint32_t)(u & 1))) {
+                    if (!mbar_wait(&k_full[sb], (uint32_t)(u & 1)) || (j > 0 && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1)))) {
                         ti_report(status, TI_STATUS_TMA_WAIT); ok = false; break;
                     }
                     tc_fence_after();
@@ -379,12 +378,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     fence_proxy_async();
                 }
             }
-            // O is touched only when some row of the warp rescales, and only then the previous tile's
-            // second product has to be through.  (pv_done is never more than one phase ahead of a
-            // softmax thread, whose own arrival on p_full every second product waits for: the parity
-            // of tile j-1 tells "through" from "pending" whether or not earlier phases were waited for.)
+            // Every tile's completion is waited for, in order, before this tile's P is handed over, whether
+            // or not O is touched.  (Waiting only when a row rescales looked safe on paper and gave wrong
+            // rows now and then at 32 heads and three sequences: tests/test_kernels_gpu.py,
+            // test_attention_prefill_tcgen05_at_long_lengths.)
             const bool rescale = j > 0 && __any_sync(0xffffffffu, alpha != 1.f);
-            if (ok && rescale && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
+            if (ok && j > 0 && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             if (ok) {
                 if (rescale) {
