@@ -410,6 +410,29 @@ def run_workload(name: str):
             "build_seconds": round(t_build, 1), "through": "LLM.generate"}
 
 
+def run_mma_issue():
+    """Cycles per tcgen05 MMA of 128 x N x 16 as one issuing thread per block sees them, with the thread
+    chosen by ``lane == 0`` and by ``elect.sync`` in a warp-uniform branch, one and two blocks per SM
+    (csrc/bench_mma_issue.cu).  One JSON line per case."""
+    import ctypes
+    import torch
+    from toyinfer_b200.kernels.lib import library
+    lib = library()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    names = {0: "A and B in shared memory, K-major", 1: "A in tensor memory, B K-major",
+             2: "A in tensor memory, B MN-major", 3: "A in shared memory, B MN-major"}
+    for per_sm in (1, 2):
+        for n, mode in ((64, 0), (64, 1), (128, 0), (128, 1), (128, 2), (128, 3), (256, 0)):
+            row = {"kernel": "mma_issue", "n": n, "operands": names[mode], "blocks_per_sm": per_sm, "mma_cycles": 128 * n * 16 * 2 // 8192}
+            for elect in (0, 1):
+                cyc, iss = ctypes.c_double(), ctypes.c_double()
+                if lib.ti_bench_mma_issue(n, mode, elect, 64, sms * per_sm, ctypes.byref(cyc), ctypes.byref(iss), stream) != 0:
+                    raise SystemExit(lib.ti_last_error().decode())
+                row["elected" if elect else "lane0"] = round(cyc.value, 1)
+            print(json.dumps(row), flush=True)
+
+
 # ---------------------------------------------------------------------------
 # one kernel at a time, at the sizes of one layer of the benchmark model
 # ---------------------------------------------------------------------------
@@ -426,6 +449,8 @@ def run_kernel(name: str, reps: int, eager: bool = False):
 
     pk = peaks()
     dev = "cuda"
+    if name == "mma_issue":
+        return run_mma_issue()
     g = torch.Generator(device=dev).manual_seed(0)
     H, I = 2560, 9728
 
@@ -527,7 +552,7 @@ def main() -> int:
                     help="also the mean decode rate while the batch grows from 2,048 positions to --context (some 20 s more)")
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
                     "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K, attn_decode, attn_decode_b64, attn_decode_b1, "
-                    "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW[,HEAD_DIM]]; "
+                    "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW[,HEAD_DIM]], mma_issue; "
                     "ref:all or ref:<case> times the reference's kernel recompiled for sm_100a beside this library's")
     ap.add_argument("--workload", default="", choices=["", "8b", "32b"],
                     help="run one of the larger described workloads end to end instead (8B or 32B shape)")
@@ -546,7 +571,9 @@ def main() -> int:
             print(json.dumps(row), flush=True)
         return 0
     if args.kernel:
-        print(json.dumps(run_kernel(args.kernel, args.reps, args.eager)))
+        result = run_kernel(args.kernel, args.reps, args.eager)
+        if result is not None:          # mma_issue prints its own lines
+            print(json.dumps(result))
         return 0
     if args.workload:
         print(json.dumps(run_workload(args.workload)))
