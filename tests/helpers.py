@@ -39,3 +39,43 @@ def plain_logits(folder: str, ids, dtype: str) -> torch.Tensor:
         w, cfg = _cache[folder]
         _cache[key] = plain.forward(w, cfg, ids, rounding_of(dtype))
     return _cache[key]
+
+
+def run_random_schedule(eng, ids, rng, max_live=4):
+    """Feeds the requests ``ids`` (lists of tokens) through the engine as a random schedule decides:
+    a step takes a random subset of the live sequences, each with a random number of its next
+    tokens (one, a few, a long piece, all that is left); new sequences start beside them; a
+    finished one gives its slot and pages back at once.  Returns, per request, the logits of all
+    its positions in order."""
+    import torch
+    lens = [len(x) for x in ids]
+    waiting = list(range(len(ids)))
+    live = {}                    # request -> (slot, tokens fed)
+    got = {r: [] for r in range(len(ids))}
+    steps = 0
+    while waiting or live:
+        steps += 1
+        assert steps < 5000, "the schedule does not end"
+        while waiting and len(live) < max_live and (not live or rng.random() < 0.5):
+            live[waiting.pop(0)] = (eng.new_sequence(), 0)
+        chosen = [r for r in live if rng.random() < 0.7] or [rng.choice(list(live))]
+        entries, wants = [], []
+        for r in chosen:
+            slot, fed = live[r]
+            left = lens[r] - fed
+            take = min(left, rng.choice([1, 1, 1, 2, 5, 64, 70, left]))
+            entries.append((slot, ids[r][fed:fed + take]))
+            wants.append(list(range(take)))
+            live[r] = (slot, fed + take)
+        out = eng.step(entries, wants).clone()
+        o = 0
+        for r, w in zip(chosen, wants):
+            got[r].append(out[o:o + len(w)])
+            o += len(w)
+        for r in chosen:
+            slot, fed = live[r]
+            assert eng.length(slot) == fed
+            if fed == lens[r]:
+                eng.end_sequence(slot)
+                del live[r]
+    return [torch.cat(got[r]) for r in range(len(ids))]

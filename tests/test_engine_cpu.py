@@ -39,6 +39,25 @@ def test_whole_prompt_matches_plain(cpu_engine, model_folders, name):
     eng.end_sequence(slot)
 
 
+@pytest.mark.parametrize("seed", [1, 2])
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_random_schedules(cpu_engine, model_folders, name, seed):
+    """Requests come and go as a random schedule decides (helpers.run_random_schedule), in a cache
+    so small that slots and pages come around again: every position's logits are those of its
+    sequence alone and whole."""
+    import random
+    from helpers import run_random_schedule
+    rng = random.Random(77 * seed + ord(name))
+    longest = {"B": 150, "C": 200}[name]
+    eng = cpu_engine(name, max_batch=3, max_tokens=3 * (longest + 64))
+    lens = [rng.choice([1, 2, 63, 64, 65, rng.randint(66, longest)]) for _ in range(5)]
+    ids = prompts_for(name, lens, seed=50 + seed)
+    got = run_random_schedule(eng, ids, rng, max_live=3)
+    for r, x in enumerate(ids):
+        torch.testing.assert_close(got[r], _plain_logits(model_folders[name], x), rtol=1e-4, atol=1e-5,
+                                   msg=lambda m: f"{name} request {r} of {lens[r]} tokens, seed {seed}: {m}")
+
+
 @pytest.mark.parametrize("name", ["A", "C"])
 def test_last_tokens_one_by_one(cpu_engine, model_folders, name):
     eng = cpu_engine(name)

@@ -220,3 +220,25 @@ def test_step_refuses_what_it_cannot_run(model_folders):
     with pytest.raises(StepError):
         eng.step([(a, None), (b, [1, 2])], None, token_source=torch.zeros(2, dtype=torch.int32, device="cuda"))
     assert eng.length(a) == 3 and eng.length(b) == 0    # nothing was changed
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "C", "D", "E"])
+def test_random_schedules(model_folders, name, dtype, seed):
+    """Requests of random lengths come and go as a random schedule decides: a step takes a random
+    subset of the live sequences, each with a random number of its next tokens (one, a few, a long
+    piece), new sequences start beside them, finished ones give their slot and pages back, in a cache
+    so small that both come around again.  Every position's logits must be those of its sequence
+    alone and whole, whatever kept it company."""
+    import random
+    from helpers import run_random_schedule
+    rng = random.Random(1000 * seed + sum(map(ord, name + dtype)))
+    longest = {"B": 200, "C": 300, "D": 500, "E": 330}[name]
+    eng = make_engine(model_folders[name], dtype, max_batch=4, max_tokens=4 * (longest + 64))
+    lens = [rng.choice([1, 2, 17, 63, 64, 65, rng.randint(66, longest)]) for _ in range(7)]
+    ids = prompts_for(name, lens, seed=40 + seed)
+    got = run_random_schedule(eng, ids, rng)
+    for r, x in enumerate(ids):
+        assert_logits_close(got[r], plain_logits(model_folders[name], x, dtype), dtype,
+                            f"{name} request {r} of {lens[r]} tokens, seed {seed}")
