@@ -1033,3 +1033,51 @@ def test_embed_scale_and_logit_scale_cap(K, dtype):
     assert torch.all(g[:, 1003:].cpu() == 7.0)          # the rows' tails are untouched
     out = K.logit_scale_cap(dev(logits).clone(), 2.0, 0.0)
     torch.testing.assert_close(out.cpu(), logits * 2.0, rtol=0, atol=0)
+
+
+def test_kernels_give_the_same_bits_every_time(K):
+    """Races show as results that change from launch to launch.  The kernels whose blocks hand work
+    to one another (tensor-core attention with its pipelines, products whose tiles are shared or
+    split, decode attention with split keys) run a dozen times each on a device-filling case, and
+    every run must give the first run's bits."""
+    dtype = torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(77)
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, generator=g, device="cuda") * scale).to(dtype)
+
+    cases = []
+    nh, nkv, hd = 32, 8, 128
+    news = [1300, 600, 129]
+    M = sum(news)
+    qkv = rnd(M, (nh + 2 * nkv) * hd)
+    q, k, v = qkv[:, :nh * hd].view(M, nh, hd), qkv[:, nh * hd:(nh + nkv) * hd].view(M, nkv, hd), qkv[:, (nh + nkv) * hd:].view(M, nkv, hd)
+    batch = make_batch("start", [0, 1, 2], [0, 0, 0], news)
+    cases.append(("prompt attention", lambda: K.attention_prefill(q, k, v, 1 / math.sqrt(hd), 0, batch)))
+    # new tokens after cached positions
+    starts = [700, 64, 1000]
+    mem = make_mem(dtype, 3, nkv, hd, pages=80)
+    free = list(range(80, 0, -1))
+    for s, (st, n) in enumerate(zip(starts, news)):
+        pages = [free.pop() for _ in range((st + n + 63) // 64)]
+        fill_cache(mem, s, pages, rnd(st, nkv, hd), rnd(st, nkv, hd))
+    mixed = make_batch("mixed", [0, 1, 2], starts, news)
+    cases.append(("chunk attention", lambda: K.attention_chunk(q, k, v, mem, 1 / math.sqrt(hd), 0, mixed)))
+    # decode attention with split keys, eight sequences
+    lens = [2000, 1999, 64, 65, 1500, 700, 1, 1024]
+    dmem = make_mem(dtype, 8, nkv, hd, pages=160)
+    free = list(range(160, 0, -1))
+    for s, n in enumerate(lens):
+        fill_cache(dmem, s, [free.pop() for _ in range((n + 63) // 64)], rnd(n, nkv, hd), rnd(n, nkv, hd))
+    dq = rnd(8, nh, hd)
+    dbatch = make_batch("extend", list(range(8)), [n - 1 for n in lens], [1] * 8, plan_len=2048)
+    cases.append(("decode attention", lambda: K.attention_decode(dq, dmem, 1 / math.sqrt(hd), 0, dbatch)))
+    for Mx, N, Kd in ((4096, 2560, 4096), (2048, 2560, 4096), (1300, 3600, 264), (64, 2560, 9728), (8, 2560, 9728), (2048, 6144, 2560)):
+        x, w = rnd(Mx, Kd), rnd(N, Kd, scale=0.03)
+        cases.append((f"product {Mx} x {N} x {Kd}", lambda x=x, w=w: K.linear(x, w)))
+    for what, fn in cases:
+        first = fn().clone()
+        for i in range(12):
+            again = fn()
+            assert torch.equal(first, again), f"{what}: run {i + 2} differs from the first"
+        K.check_status()
