@@ -477,6 +477,28 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             batch = fill_batch(BatchBuffers(B, B, dev), "extend", list(range(B)), [ctx - 1] * B, [[0]] * B, B, ctx)
             q = rnd(B, nh, hd)
             return (lambda: K.attention_decode(q, mem, 1 / math.sqrt(hd), 0, batch)), 2 * B * ctx * nkv * hd * 2, 4.0 * B * ctx * nh * hd
+        if name.startswith("add_rmsnorm"):                # add_rmsnorm or add_rmsnorm:TOKENS
+            T = int(name.split(":")[1]) if ":" in name else PREFILL_TOKENS
+            h, d, w = rnd(T, H), rnd(T, H, scale=0.01), rnd(H)
+            return (lambda: K.add_rmsnorm(h, d, w, 1e-6)), 4 * T * H * 2, 0.0
+        if name.startswith("rope_store"):                 # rope_store or rope_store:TOKENS
+            from toyinfer_b200.parts.rope import rotary_tables
+            T, nh, nkv, hd = (int(name.split(":")[1]) if ":" in name else PREFILL_TOKENS), 32, 8, 128
+            pages = (T + 63) // 64
+            table = torch.zeros(2, pages, dtype=torch.int32, device=dev)
+            table[0] = torch.arange(1, pages + 1, dtype=torch.int32, device=dev)
+            mem = KVView(rnd(pages + 1, nkv, 64, hd), rnd(pages + 1, nkv, 64, hd), table, nkv, hd, 0, 0)
+            qkv = rnd(T, (nh + 2 * nkv) * hd)
+            q = qkv[:, :nh * hd].view(T, nh, hd)
+            k = qkv[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
+            v = qkv[:, (nh + nkv) * hd:].view(T, nkv, hd)
+            qw, kw = rnd(hd), rnd(hd)
+            cos, sin = rotary_tables(hd, 1e6, T + 64)
+            tables = (cos.to(dev), sin.to(dev), hd)
+            batch = fill_batch(BatchBuffers(1, T, dev), "start", [0], [0], [[0] * T], 1, T)
+            # q and k read and written in place, v read, k and v written to the pages
+            return (lambda: K.qk_norm_rope_store(q, k, v, qw, kw, 1e-6, tables, batch, mem)), \
+                (2 * nh + 2 * nkv + nkv + 2 * nkv) * T * hd * 2, 0.0
         if name.startswith("attn_prefill"):               # attn_prefill or attn_prefill:TOKENS
             T, nh, nkv, hd = (int(name.split(":")[1]) if ":" in name else PREFILL_TOKENS), 32, 8, 128
             qkv = rnd(T, (nh + 2 * nkv) * hd)
@@ -552,7 +574,7 @@ def main() -> int:
                     help="also the mean decode rate while the batch grows from 2,048 positions to --context (some 20 s more)")
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
                     "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K, attn_decode, attn_decode_b64, attn_decode_b1, "
-                    "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW[,HEAD_DIM]], mma_issue; "
+                    "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW[,HEAD_DIM]], add_rmsnorm[:TOKENS], rope_store[:TOKENS], mma_issue; "
                     "ref:all or ref:<case> times the reference's kernel recompiled for sm_100a beside this library's")
     ap.add_argument("--workload", default="", choices=["", "8b", "32b"],
                     help="run one of the larger described workloads end to end instead (8B or 32B shape)")
