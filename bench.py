@@ -413,11 +413,13 @@ def run_workload(name: str):
 def run_mma_issue():
     """Cycles per tcgen05 MMA of 128 x N x 16 as one issuing thread per block sees them, with the thread
     chosen by ``lane == 0`` and by ``elect.sync`` in a warp-uniform branch, one and two blocks per SM
-    (csrc/bench_mma_issue.cu).  One JSON line per case."""
+    (csrc/measure/mma_issue.cu).  One JSON line per case."""
     import ctypes
     import torch
-    from toyinfer_b200.kernels.lib import library
-    lib = library()
+    from toyinfer_b200.csrc.build import build
+    lib = ctypes.CDLL(build(measure=True))       # the measurement kernels have a library of their own
+    lib.ti_bench_mma_issue.argtypes = [ctypes.c_int] * 5 + [ctypes.c_void_p] * 3
+    lib.ti_last_error.restype = ctypes.c_char_p
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     names = {0: "A and B in shared memory, K-major", 1: "A in tensor memory, B K-major",

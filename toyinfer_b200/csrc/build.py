@@ -23,6 +23,7 @@ from typing import List
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libtoyinfer_kernels.so"
+MEASURE_LIB_NAME = "libtoyinfer_measure.so"      # measurement kernels (csrc/measure), built only when asked for
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "--expt-extended-lambda",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
@@ -53,9 +54,14 @@ def _headers() -> List[str]:
     return sorted(os.path.join(HERE, n) for n in os.listdir(HERE) if n.endswith((".cuh", ".h")))
 
 
-def source_hash() -> str:
+def measure_sources() -> List[str]:
+    d = os.path.join(HERE, "measure")
+    return sorted(os.path.join(d, n) for n in os.listdir(d) if n.endswith(".cu"))
+
+
+def source_hash(srcs=None) -> str:
     h = hashlib.sha256()
-    for p in sources() + _headers():
+    for p in (sources() if srcs is None else srcs) + _headers():
         h.update(os.path.basename(p).encode())
         with open(p, "rb") as f:
             h.update(f.read())
@@ -90,18 +96,21 @@ def _compile_one(nvcc: str, src: str, obj: str, verbose: bool) -> None:
         sys.stderr.write(r.stderr)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, measure: bool = False) -> str:
+    """Compiles the kernels (or, with ``measure``, the measurement kernels of csrc/measure) and
+    returns the library's path."""
     out_dir = _build_dir()
-    lib = os.path.join(out_dir, LIB_NAME)
-    stamp = os.path.join(out_dir, "source.hash")
-    want = source_hash()
+    name = MEASURE_LIB_NAME if measure else LIB_NAME
+    lib = os.path.join(out_dir, name)
+    stamp = os.path.join(out_dir, "measure.hash" if measure else "source.hash")
+    want = source_hash(measure_sources() if measure else None)
     if not force and os.path.isfile(lib) and os.path.isfile(stamp):
         with open(stamp) as f:
             if f.read().strip() == want:
                 return lib
     nvcc = find_nvcc()
-    srcs = sources()
-    objs = [os.path.join(out_dir, os.path.basename(s)[:-3] + ".o") for s in srcs]
+    srcs = measure_sources() if measure else sources()
+    objs = [os.path.join(out_dir, ("measure_" if measure else "") + os.path.basename(s)[:-3] + ".o") for s in srcs]
     t0 = time.time()
     done = threading.Event()
 
@@ -122,13 +131,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
         cmd = [nvcc, "-shared", "-o", tmp] + objs + ARCH_FLAGS + ["-cudart", "static"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
-            raise BuildError(f"linking {LIB_NAME} failed:\n{r.stdout}\n{r.stderr}")
+            raise BuildError(f"linking {name} failed:\n{r.stdout}\n{r.stderr}")
         os.replace(tmp, lib)
         with open(stamp, "w") as f:
             f.write(want)
     finally:
         done.set()
-    _say(f"built {LIB_NAME} in {time.time() - t0:.0f} s")
+    _say(f"built {name} in {time.time() - t0:.0f} s")
     return lib
 
 

@@ -1,10 +1,24 @@
-// A measurement, not a product kernel: what one issuing thread per block gets out of the tensor
+// A measurement, not a product kernel (built into a library of its own, libtoyinfer_measure.so,
+// only when asked for): what one issuing thread per block gets out of the tensor
 // cores.  Every block issues `batch` accumulating tcgen05 MMAs of 128 x N x 16 back to back, commits,
 // waits (bounded) and repeats; the result is cycles per MMA as the issuing thread of block 0 sees
 // them.  Operands are zeros in shared and tensor memory; nothing is read from or written to global
 // memory but the result.  `python bench.py --kernel mma_issue` prints the table that decided how the
 // kernels of this library choose their issuing thread (elect_one in tcgen05.cuh).
-#include "tcgen05.cuh"
+#include "../tcgen05.cuh"
+
+#include <cstdarg>
+#include <cstdio>
+
+// this library's own error text (the kernels' library keeps its own)
+static char g_error[512];
+void ti_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+extern "C" const char* ti_last_error() { return g_error; }
 
 namespace {
 // MODE 0: A and B in shared memory, both K-major (a first product Q K^T); 1: A in tensor memory, B

@@ -30,7 +30,6 @@ def _declare(lib) -> None:
         "ti_attn_prefill_simt": [P, P, P, P, L, L, L, L, P, I, I, I, I, I, F, I, I, P],
         "ti_attn_decode_simt": [P, L, P, P, P, I, I, I, I, P, P, I, I, I, I, F, I, I, P, L, P, P, I, P],
         "ti_attn_decode_cluster_room": [I, I, I, P],
-        "ti_bench_mma_issue": [I, I, I, I, I, P, P, P],
         "ti_attn_decode_mma": [P, L, P, P, P, I, I, I, I, P, P, I, I, I, I, F, I, I, P, L, P, P, I, I, P],
         "ti_attn_decode_fused": [P, P, P, L, L, L, P, P, I, F, P, P, I, P, P, P, I, I, I, I, P, P, I, I, I, I, F, I, I,
                                  P, L, P, P, I, I, P],
