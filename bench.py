@@ -513,7 +513,7 @@ def run_kernel(name: str, reps: int, eager: bool = False):
         if name.startswith("attn_chunk"):                 # attn_chunk or attn_chunk:CACHED,NEW[,HEAD_DIM]
             sizes = [int(v) for v in name.split(":")[1].split(",")] if ":" in name else [2048, 2048]
             cached, new = sizes[:2]
-            nh, nkv, hd = 32, 8, (sizes[2] if len(sizes) > 2 else 128)     # heads of 64 run the mma.sync kernel
+            nh, nkv, hd = 32, 8, (sizes[2] if len(sizes) > 2 else 128)
             pages = (cached + new + 63) // 64
             table = torch.zeros(2, pages, dtype=torch.int32, device=dev)
             table[0] = torch.arange(1, pages + 1, dtype=torch.int32, device=dev)

@@ -498,13 +498,19 @@ def test_attention_prefill_on_views_of_one_buffer(K, nh, nkv, hd, window):
     v = g[:, (nh + nkv) * hd:].view(M, nkv, hd)
     batch = make_batch("start", list(range(len(news))), [0] * len(news), news)
     scale = 1.0 / math.sqrt(hd)
-    got = K.attention_prefill(q, k, v, scale, window, batch).cpu().double()
-    K.check_status()
-    o = 0
-    for n in news:
-        want = plain_attention_seq(q[o:o + n].cpu(), k[o:o + n].cpu(), v[o:o + n].cpu(), scale, window, dtype)
-        torch.testing.assert_close(got[o:o + n], want, **ATT_TOL[dtype])
-        o += n
+    from toyinfer_b200.kernels import attention
+    for mma_sync in (False, True):          # the tcgen05 kernel, then the mma.sync kernel it replaced
+        attention.prefer_mma_sync = mma_sync
+        try:
+            got = K.attention_prefill(q, k, v, scale, window, batch).cpu().double()
+        finally:
+            attention.prefer_mma_sync = False
+        K.check_status()
+        o = 0
+        for n in news:
+            want = plain_attention_seq(q[o:o + n].cpu(), k[o:o + n].cpu(), v[o:o + n].cpu(), scale, window, dtype)
+            torch.testing.assert_close(got[o:o + n], want, **ATT_TOL[dtype])
+            o += n
 
 
 @pytest.mark.parametrize("dtype", DT)
@@ -541,13 +547,13 @@ def plain_attention_on_gpu(q, k, v, scale, window, dtype):
 
 @pytest.mark.parametrize("news,window,nh,nkv", [([2048], 0, 4, 2), ([1025, 4097], 0, 4, 2), ([3000, 70], 1000, 4, 2),
                                                 ([1300, 600, 129], 0, 32, 8), ([1300, 600, 129], 0, 4, 1), ([257], 0, 2, 1)])
-def test_attention_prefill_tcgen05_at_long_lengths(K, news, window, nh, nkv):
-    """The tcgen05 kernel (head size 128) at the lengths prompts have in practice: 16 to 65 key
-    tiles per query tile, lengths one past a tile's end, several sequences in one launch.  With few
-    heads a block takes two query tiles, one from each end of its sequence (an odd number of
-    tiles leaves the middle one alone); with 32 heads and three sequences there are more blocks
-    than places, and every block takes one tile."""
-    dtype, hd = torch.bfloat16, 128
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attention_prefill_tcgen05_at_long_lengths(K, news, window, nh, nkv, hd):
+    """The tcgen05 kernel (head sizes 128 and 64) at the lengths prompts have in practice: 16 to 65
+    key tiles per query tile, lengths one past a tile's end, several sequences in one launch; with 32
+    heads and three sequences there are more blocks than the device holds at once, so that blocks
+    start beside blocks in every stage of their work."""
+    dtype = torch.bfloat16
     M = sum(news)
     qkv = randn(M, (nh + 2 * nkv) * hd, seed=27).to(dtype)
     g = dev(qkv)
@@ -639,13 +645,19 @@ def test_attention_chunk(K, dtype, nh, nkv, hd, window):
     q = torch.cat([qs[s][st:] for s, (st, _) in enumerate(cases)])
     k = torch.cat([ks[s][st:] for s, (st, _) in enumerate(cases)])
     v = torch.cat([vs[s][st:] for s, (st, _) in enumerate(cases)])
-    got = K.attention_chunk(dev(q), dev(k), dev(v), mem, scale, window, batch).cpu().double()
-    K.check_status()
-    o = 0
-    for s, (st, n) in enumerate(cases):
-        want = plain_attention_seq(qs[s], ks[s], vs[s], scale, window, dtype)[st:]
-        torch.testing.assert_close(got[o:o + n], want, **ATT_TOL[dtype], msg=lambda m: f"sequence {s} {cases[s]}: {m}")
-        o += n
+    from toyinfer_b200.kernels import attention
+    for mma_sync in (False, True):          # heads of 64 and 128: the tcgen05 kernel, then the mma.sync kernel
+        attention.prefer_mma_sync = mma_sync
+        try:
+            got = K.attention_chunk(dev(q), dev(k), dev(v), mem, scale, window, batch).cpu().double()
+        finally:
+            attention.prefer_mma_sync = False
+        K.check_status()
+        o = 0
+        for s, (st, n) in enumerate(cases):
+            want = plain_attention_seq(qs[s], ks[s], vs[s], scale, window, dtype)[st:]
+            torch.testing.assert_close(got[o:o + n], want, **ATT_TOL[dtype], msg=lambda m: f"sequence {s} {cases[s]}: {m}")
+            o += n
 
 
 @pytest.mark.parametrize("dtype", DT)
@@ -1054,6 +1066,8 @@ def test_kernels_give_the_same_bits_every_time(K):
     q, k, v = qkv[:, :nh * hd].view(M, nh, hd), qkv[:, nh * hd:(nh + nkv) * hd].view(M, nkv, hd), qkv[:, (nh + nkv) * hd:].view(M, nkv, hd)
     batch = make_batch("start", [0, 1, 2], [0, 0, 0], news)
     cases.append(("prompt attention", lambda: K.attention_prefill(q, k, v, 1 / math.sqrt(hd), 0, batch)))
+    q64, k64, v64 = q.view(M, 2 * nh, 64), k.view(M, 2 * nkv, 64), v.view(M, 2 * nkv, 64)      # the same rows as heads of 64
+    cases.append(("prompt attention, heads of 64", lambda: K.attention_prefill(q64, k64, v64, 0.125, 0, batch)))
     # new tokens after cached positions
     starts = [700, 64, 1000]
     mem = make_mem(dtype, 3, nkv, hd, pages=80)

@@ -1,7 +1,7 @@
 // Causal grouped-query attention over the tokens of one step on the 5th-generation tensor
 // cores: both products of a tile, S = Q K^T and O += P V, are tcgen05 MMAs with their
 // accumulators in tensor memory.  Same contract and formulas as attn_prefill_simt.cu
-// (reference: src/prefill.cu:224-379); head_dim 128, bfloat16.  Two forms, as there: sequences
+// (reference: src/prefill.cu:224-379); head_dim 64 or 128, bfloat16.  Two forms, as there: sequences
 // that start at position 0, and, PAGED, new tokens after `seq_start[b]` positions kept in the
 // paged cache: a block then first walks the sequence's pages below the start (a page is 64
 // positions x head_dim of one kv head: one key tile and one value tile, read with the same TMA
@@ -363,7 +363,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 // Lines of the page outside [lo_blk, start) may hold anything (this step's tokens, an
                 // older turn of the ring, a former owner's): their value rows are cleared, so that a
                 // probability of zero times whatever stands there cannot make a NaN.  A row of a box is
-                // 128 bytes whatever the swizzle does inside it; four threads clear a row of both boxes.
+                // 128 bytes whatever the swizzle does inside it; four threads clear a row of all boxes.
                 // The second product starts only after every softmax warp has arrived on p_full below,
                 // and the next load into this buffer only after that product.
                 if (ok && !mbar_wait(&v_full[sb], (uint32_t)((j >> 1) & 1))) { ti_report(status, TI_STATUS_TMA_WAIT); ok = false; }
@@ -371,9 +371,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     const int st = (int)threadIdx.x - 64, row = st >> 2, part = st & 3;
                     const int p = tile0 + start + row;
                     if (p < lo_blk || p >= start) {
-                        uint4* dst = reinterpret_cast<uint4*>(kv_s + (size_t)sb * 2 * KV_BYTES + KV_BYTES + (part >> 1) * KBOX + row * 128 + (part & 1) * 64);
+                        constexpr int PART = HD / 2;        // bytes of a row's HD * 2 that one of its four threads clears
+                        uint4* dst = reinterpret_cast<uint4*>(kv_s + (size_t)sb * 2 * KV_BYTES + KV_BYTES + (part * PART / 128) * KBOX +
+                                                              row * 128 + (part * PART) % 128);
 #pragma unroll
-                        for (int e = 0; e < 4; e++) dst[e] = make_uint4(0, 0, 0, 0);
+                        for (int e = 0; e < PART / 16; e++) dst[e] = make_uint4(0, 0, 0, 0);
                     }
                     fence_proxy_async();
                 }
@@ -474,7 +476,7 @@ namespace {
 int check_common(const char* what, const void* q, const void* k, const void* v, const void* out, long long q_stride,
                  long long k_stride, long long v_stride, long long o_stride, int n_seq, int n_tokens, int n_heads,
                  int n_kv_heads, int head_dim, CUtensorMap* qm, CUtensorMap* km, CUtensorMap* vm) {
-    TI_REQUIRE(head_dim == 128, "%s (tcgen05): head size %d is not 128", what, head_dim);
+    TI_REQUIRE(head_dim == 64 || head_dim == 128, "%s (tcgen05): head size %d is not 64 or 128", what, head_dim);
     TI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "%s: bad head counts", what);
     TI_REQUIRE(n_seq <= 65535 && n_heads <= 65535, "%s: too many sequences or heads for one launch", what);
     TI_REQUIRE(n_tokens <= 65535 * BQ, "%s: %d tokens are too many for one launch", what, n_tokens);
@@ -488,10 +490,9 @@ int check_common(const char* what, const void* q, const void* k, const void* v, 
     return 0;
 }
 
-template <bool PAGED>
+template <int HD, bool PAGED>
 int launch(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const CUtensorMap& kpm, const CUtensorMap& vpm,
            const Args& a, int n_seq, int max_new, cudaStream_t stream) {
-    constexpr int HD = 128;
     constexpr size_t smem = Smem<HD>::TOTAL;
     static bool configured = false;
     if (!configured) {
@@ -507,7 +508,7 @@ int launch(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, 
 }
 }  // namespace
 
-// bfloat16, head_dim 128.  Same arguments as ti_attn_prefill_mma.
+// bfloat16, head_dim 64 or 128.  Same arguments as ti_attn_prefill_mma.
 extern "C" int ti_attn_prefill_tc(const void* q, const void* k, const void* v, void* out,
                                   long long q_stride, long long k_stride, long long v_stride, long long o_stride,
                                   const int* cu_new, int n_seq, int max_new, int n_tokens, int n_heads, int n_kv_heads,
@@ -519,7 +520,8 @@ extern "C" int ti_attn_prefill_tc(const void* q, const void* k, const void* v, v
     Args a = {};
     a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = window;
     a.out = out; a.o_stride = o_stride;
-    return launch<false>(qm, km, vm, km, vm, a, n_seq, max_new, stream);
+    return head_dim == 64 ? launch<64, false>(qm, km, vm, km, vm, a, n_seq, max_new, stream)
+                          : launch<128, false>(qm, km, vm, km, vm, a, n_seq, max_new, stream);
 }
 
 // The same for new tokens after `seq_start[b]` positions that the cache holds (pages of 64
@@ -550,5 +552,6 @@ extern "C" int ti_attn_chunk_tc(const void* q, const void* k, const void* v, voi
     a.out = out; a.o_stride = o_stride;
     a.seq_start = seq_start; a.seq_slot = seq_slot; a.page_table = page_table; a.table_width = table_width;
     a.ring_rows = ring_rows; a.n_pages = n_pages;
-    return launch<true>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream);
+    return head_dim == 64 ? launch<64, true>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream)
+                          : launch<128, true>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream);
 }

@@ -31,12 +31,17 @@ def check_supported(n_heads: int, n_kv_heads: int, head_dim: int, dtype) -> None
                               f"of shared memory")
 
 
+prefer_mma_sync = False      # tests set this to run the `mma.sync` prompt and chunk kernels, which heads of 64 and 128
+                             # otherwise reach only when the output's stride does not fit the tcgen05 kernel's stores
+
+
 def prefill(q, k, v, out, scale, window, batch) -> None:
     M, nh, hd = q.shape
     qs, ks, vs = _row_stride(q, "q"), _row_stride(k, "k"), _row_stride(v, "v")
     if (q.dtype == torch.bfloat16 and hd in (64, 128) and qs % 8 == 0 and ks % 8 == 0 and vs % 8 == 0
             and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0):
-        fn = library().ti_attn_prefill_tc if (hd == 128 and out.stride(0) % 8 == 0) else library().ti_attn_prefill_mma
+        tcgen05 = out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and not prefer_mma_sync
+        fn = library().ti_attn_prefill_tc if tcgen05 else library().ti_attn_prefill_mma
         _call(fn, _ptr(q), _ptr(k), _ptr(v), _ptr(out), qs, ks, vs, out.stride(0),
               _ptr(batch.cu_new), batch.n_seq, batch.max_new, M, nh, k.shape[1], hd, scale, window, _stream())
         return
@@ -61,7 +66,7 @@ def chunk(q, k, v, mem, out, scale, window, batch) -> None:
     if (q.dtype == torch.bfloat16 and hd in (64, 128) and mem.page_size == 64 and qs % 8 == 0 and ks % 8 == 0 and vs % 8 == 0
             and out.stride(0) % 2 == 0 and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0
             and mem.k_pages.data_ptr() % 16 == 0 and mem.v_pages.data_ptr() % 16 == 0):
-        tcgen05 = hd == 128 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
+        tcgen05 = out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and not prefer_mma_sync
         fn = library().ti_attn_chunk_tc if tcgen05 else library().ti_attn_chunk_mma
         _call(fn, _ptr(q), _ptr(k), _ptr(v), _ptr(out), qs, ks, vs, out.stride(0),
               _ptr(batch.cu_new), _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seq, batch.max_new, M, nh,
