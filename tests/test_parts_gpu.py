@@ -494,3 +494,46 @@ def test_unknown_part_and_bad_schedule_are_refused():
         DecoderModel(ModelSpec(10, 32, 64, [LayerSpec("l.", ok)], norm, schedule=[ScheduleEntry(0, memory_of=0)]), torch.float32, DEV)
     with pytest.raises(ValueError):
         DecoderModel(ModelSpec(10, 32, 64, [LayerSpec("l.", ok)], norm, schedule=[ScheduleEntry(3)]), torch.float32, DEV)
+
+
+def test_a_whole_toy_architecture_registered_from_here(tmp_path):
+    """An architecture of its own, added without touching the library: a configuration class with
+    its own keys, a description that arranges the toy parts above, registered under a name; then
+    the library's own paths carry it: a model folder with random weights, the loader, the entry
+    point's greedy generation, against the plain toy forward."""
+    from toyinfer_b200 import LLM, SamplingParams
+    from toyinfer_b200.config import register_architecture, unregister_architecture
+    from toyinfer_b200.config.base import Key, ModelConfig
+    from toyinfer_b200.weights import write_model_folder
+    make_toy_parts()
+
+    class ToyConfig(ModelConfig):
+        KEYS = {"architectures": Key("str_list"), "width": Key("int"), "words": Key("int"),
+                "stop_word": Key("int", required=False, default=None, nullable=True)}
+
+        def validate(self):
+            return [] if self.width % 16 == 0 else [f"width: {self.width} is not a multiple of 16"]
+
+    def describe(cfg):
+        spec = toy_spec(H=cfg.width, V=cfg.words)
+        if cfg.stop_word is not None:
+            spec.stop_token_ids = (cfg.stop_word,)
+        return spec
+
+    register_architecture("ToyForCausalLM", ToyConfig, describe)
+    try:
+        folder = write_model_folder({"architectures": ["ToyForCausalLM"], "width": 48, "words": 90}, 5, str(tmp_path),
+                                    store_dtype=torch.float32)
+        llm = LLM(folder, dtype="float32", max_seq_len=128, max_batch=2, max_tokens=512)
+        prompts = [[3, 14, 15, 9, 26], [5, 3], [58, 9, 7, 9, 3, 2, 38, 46]]
+        got = [r.tokens for r in llm.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=6)]
+        w = {k: v.double() for k, v in plain.read_weights(folder).items()}
+        for p, g in zip(prompts, got):
+            ids = list(p)
+            for _ in range(6):
+                ids.append(int(torch.argmax(toy_plain_forward(w, ids)[-1])))
+            assert g == ids[len(p):]
+        with pytest.raises(Exception, match="width"):
+            write_model_folder({"architectures": ["ToyForCausalLM"], "width": 50, "words": 90}, 5, str(tmp_path / "bad"))
+    finally:
+        unregister_architecture("ToyForCausalLM")
