@@ -177,9 +177,29 @@ def test_decoding_across_a_length_class(tmp_path, dtype):
         out = eng.step([(a, [long_ids[1000 + t]]), (b, [short_ids[30 + t]])], [[0], [0]])
         got_a.append(out[0:1].clone())
         got_b.append(out[1:2].clone())
-    assert len({cls for (_, cls) in eng._graphs}) == 2
+    assert len(eng._graphs) == 2        # the keys of 1,024 and of 2,048 positions are split differently here
     assert_logits_close(torch.cat(got_a), want_long[1000:1050], dtype, "across a length class, long")
     assert_logits_close(torch.cat(got_b), want_short[30:80], dtype, "across a length class, short")
+
+
+def test_length_classes_with_the_same_launches_share_a_captured_step(tmp_path):
+    """Where nothing in the model's launches tells two classes of lengths apart (heads of 128 in
+    bfloat16: sixteen splits of the keys from 2,048 positions on), a sequence that grows past the
+    class's end keeps replaying the same captured step, and stays right."""
+    from toyinfer_b200.weights import write_model_folder
+    dtype = "bfloat16"
+    cfg = dict(TINY["D"], max_position_embeddings=4608)
+    folder = write_model_folder(cfg, 19, str(tmp_path / "longer"))
+    eng = make_engine(folder, dtype, max_tokens=8192, max_batch=2)
+    assert eng.model.launch_plan(2, 2048) == eng.model.launch_plan(2, 4096) != eng.model.launch_plan(2, 1024)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, cfg["vocab_size"], (2070,), generator=g).tolist()
+    want = plain_logits(folder, ids, dtype)
+    a = eng.new_sequence()
+    eng.step([(a, ids[:2030])], [[]])
+    got = [eng.step([(a, [ids[2030 + t]])], [[0]]).clone() for t in range(40)]
+    assert len(eng._graphs) == 1 and eng.graph_replays >= 38
+    assert_logits_close(torch.cat(got), want[2030:2070], dtype, "across two length classes with one captured step")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -21,7 +21,7 @@ from __future__ import annotations
 import gc
 import os
 import weakref
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -78,7 +78,8 @@ class Engine:
         self.memories = self.cache.views(len(model.schedule))
         self.use_cuda_graph = bool(use_cuda_graph) and self.device.type == "cuda"
         self._eager_bufs: Dict[Tuple[int, int], BatchBuffers] = {}
-        self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}     # (batch bucket, length class) -> captured step
+        self._graphs: Dict[Tuple[int, Any], "_DecodeGraph"] = {}     # (batch bucket, launch plan of its length class) -> captured step
+        self._plans: Dict[Tuple[int, int], Any] = {}                 # (batch bucket, length class) -> the model's launch plan
         # All captured steps draw their intermediate buffers from one pool: steps run one at a time,
         # so what one graph freed during its capture another may use.  Each graph still keeps its
         # own [bucket, vocab] float32 logits (alive at the end of its capture).
@@ -259,9 +260,14 @@ class Engine:
         while cls < longest:
             cls <<= 1
         cls = min(cls, self.max_seq_len)
-        g = self._graphs.get((b, cls))
+        # ... unless nothing in the model's launches tells the two classes apart (with eight sequences of
+        # 32 heads over 8 the keys are split four ways from 512 positions on): one graph serves both
+        plan = self._plans.get((b, cls))
+        if plan is None:
+            plan = self._plans[(b, cls)] = self.model.launch_plan(b, cls)
+        g = self._graphs.get((b, plan))
         if g is None:
-            g = self._graphs[(b, cls)] = _DecodeGraph(self, b, cls)
+            g = self._graphs[(b, plan)] = _DecodeGraph(self, b, cls)
         return g.run(slots, starts, tokens, token_source)
 
 

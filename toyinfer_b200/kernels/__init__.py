@@ -363,6 +363,17 @@ def attention_chunk(q, k, v, mem, scale: float, window: int, batch) -> torch.Ten
     return out
 
 
+def attention_decode_plan(n_seq: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int, plan_len: int, dtype, device):
+    """(splits, way of merging them) that a decode step's attention launches with when it is
+    planned for ``plan_len`` positions: all of the launch that depends on that length."""
+    from . import attention
+    from .gemm import sm_count
+    from ..cache.allocators import PAGE
+    span = plan_len if window <= 0 else min(plan_len, window + PAGE)
+    tensor_cores = dtype == torch.bfloat16 and head_dim in (64, 128)
+    return attention.decode_plan(n_seq, n_heads, n_kv_heads, head_dim, span, PAGE, sm_count(device), tensor_cores, True)
+
+
 def attention_decode(q, mem, scale: float, window: int, batch) -> torch.Tensor:
     """One query per sequence over the cache (the new token's key already stored).
     q[B, heads, d] -> [B, heads, d]."""

@@ -116,6 +116,10 @@ class GQAAttention(Mixer):
             return None
         return KVRequest(self.n_kv_heads, self.head_dim, self.window)
 
+    def launch_plan(self, n_seq: int, plan_len: int, dtype, device):
+        # only the split of a sequence's keys over blocks looks at the planned length
+        return K.attention_decode_plan(n_seq, self.n_heads, self.n_kv_heads, self.head_dim, self.window, plan_len, dtype, device)
+
     # -- one step -----------------------------------------------------------
     def forward(self, x, batch, mem, shared) -> torch.Tensor:
         if mem is None or not hasattr(mem, "k_pages"):

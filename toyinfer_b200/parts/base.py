@@ -149,6 +149,13 @@ class PositionEncoding(Part):
 class Mixer(Part):
     takes_pending_norm = False      # forward() may be given a kernels.PendingNorm, used by K.linear first
 
+    def launch_plan(self, n_seq: int, plan_len: int, dtype, device):
+        """What, of a captured single-token step of ``n_seq`` sequences, depends on the length the
+        step is planned for (a hashable value).  Steps planned for different lengths share one
+        captured graph when every mixer answers the same for both.  The default, the length itself,
+        shares nothing."""
+        return plan_len
+
     def memory_request(self):
         return None
 
@@ -181,6 +188,10 @@ class Head(Part):
 
 class Block(Part):
     mixer: Mixer
+
+    def launch_plan(self, n_seq: int, plan_len: int, dtype, device):
+        """As Mixer.launch_plan, for the whole block."""
+        return self.mixer.launch_plan(n_seq, plan_len, dtype, device)
 
     def forward(self, h, delta, batch, mem, shared):
         raise NotImplementedError

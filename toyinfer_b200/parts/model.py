@@ -131,6 +131,11 @@ class DecoderModel(Part):
             out.append(None if e.memory_of is not None else self.blocks[e.layer].mixer.memory_request())
         return out
 
+    def launch_plan(self, n_seq: int, plan_len: int):
+        """What of a captured single-token step depends on the length it is planned for: the answers
+        of all scheduled blocks (see Mixer.launch_plan)."""
+        return tuple(self.blocks[e.layer].launch_plan(n_seq, plan_len, self.dtype, self.device) for e in self.schedule)
+
     # -- one step -------------------------------------------------------------
     def forward_hidden(self, batch, memories: Sequence[Any]):
         """Runs the given tokens through all scheduled blocks.  Returns (h, delta):
