@@ -901,7 +901,11 @@ def test_argmax_ties_across_blocks_and_odd_rows(K):
 @pytest.mark.parametrize("V,top_k,top_p,temp", [(300, 0, 1.0, 0.8), (300, 20, 0.95, 0.6), (5000, 50, 0.5, 1.3),
                                                 (151936, 20, 0.95, 0.6), (1000, 1000, 1.0, 0.7),
                                                 (2000, 1024, 0.9, 1.0)])
-def test_sample_matches_plain(K, V, top_k, top_p, temp):
+@pytest.mark.parametrize("two_kernels", [True, False])
+def test_sample_matches_plain(K, monkeypatch, V, top_k, top_p, temp, two_kernels):
+    """``two_kernels``: the usual settings (top_k up to 64; temperature alone) as two short kernels over
+    many blocks, or every setting in its one-block-per-row form."""
+    monkeypatch.setattr(K, "two_kernel_sampling", two_kernels)
     R = 6
     x = randn(R, V, seed=71, scale=3.0)
     x[2, 5] = x[2, 9] = x[2].max() + 1      # tied maxima
@@ -917,6 +921,31 @@ def test_sample_matches_plain(K, V, top_k, top_p, temp):
             # the two tokens' cumulative intervals
             alt = {plain.sample(x[r], temp, top_k, top_p, min(max(u + d, 0.0), 0.99999994)) for d in (-3e-6, 3e-6)}
             assert got[r] in alt, (r, got[r], want, alt)
+
+
+@pytest.mark.parametrize("V,top_k,top_p,temp", [(151936, 20, 0.95, 0.6), (151936, 64, 1.0, 1.0), (5000, 50, 0.5, 1.3), (4097, 1, 1.0, 0.7),
+                                                (300, 40, 0.9, 0.8), (9000, 33, 0.999, 2.0), (151936, 1000, 0.9, 1.0), (2000, 1024, 0.95, 0.7),
+                                                (151936, 200, 1.0, 0.8)])
+def test_sample_top_k_in_two_kernels_gives_the_one_kernel_picks(K, monkeypatch, V, top_k, top_p, temp):
+    """With top_k up to 1,024 the two-kernel form keeps the same entries in the same order and then does
+    the one-kernel form's arithmetic: the same token, draw by draw, also where many entries are equal
+    (quantised logits: the lowest indices among the equal ones are kept) and where the k-th value is
+    shared by entries of different chunks."""
+    R = 32
+    x = randn(R, V, seed=75, scale=3.0)
+    x[1] = torch.round(x[1] * 2) / 2                    # many equal values
+    x[2] = torch.round(x[2])
+    x[3, ::4096 // 3] = x[3].max() + 0.5                # the largest value many times, in several chunks
+    x[4] = 0.0                                          # all equal: the first top_k indices are kept
+    x[4, 1::2] = -0.0
+    keys = torch.arange(500, 500 + R, dtype=torch.int64)
+    picks = {}
+    for two in (True, False):
+        monkeypatch.setattr(K, "two_kernel_sampling", two)
+        picks[two] = [K.sample(dev(x), temp, top_k, top_p, 99, dev(keys), dev(torch.full((R,), st, dtype=torch.int32))).cpu().tolist()
+                      for st in range(6)]
+    assert picks[True] == picks[False]
+    assert all(p < top_k for st in picks[True] for p in [st[4]])      # row 4: only the first top_k indices can be drawn
 
 
 def exact_picks(x, temp, top_k, top_p, u, slack):
@@ -951,11 +980,15 @@ def exact_picks(x, temp, top_k, top_p, u, slack):
     (6000, 0, 0.9, 2.0, 3.0, 0.5),         # values on a grid of 0.5: ties everywhere, also across tier boundaries
     (6000, 2500, 0.8, 2.0, 3.0, 1.0),
 ])
-def test_sample_any_top_k_and_top_p(K, V, top_k, top_p, temp, scale, quantum):
+@pytest.mark.parametrize("two_kernels", [True, False])
+def test_sample_any_top_k_and_top_p(K, monkeypatch, V, top_k, top_p, temp, scale, quantum, two_kernels):
     """The settings beyond one shared-memory sort (top_p without top_k, top_k above 1,024), draw by
     draw: the token is the plain (float32) sampler's, or the exact rule's for a draw within the
     rounding of a float32 running sum over the kept entries (4 standard deviations of a random walk
-    of n roundings of 2^-25 each)."""
+    of n roundings of 2^-25 each).  ``two_kernels``: top_p without top_k first looks for the nucleus
+    among the row's 64 largest entries (found by many blocks) and leaves the row to the tiered kernel
+    only where it is larger; else the tiered kernel does every row."""
+    monkeypatch.setattr(K, "two_kernel_sampling", two_kernels)
     R = 4
     x = randn(R, V, seed=73, scale=scale)
     if quantum:
@@ -973,9 +1006,12 @@ def test_sample_any_top_k_and_top_p(K, V, top_k, top_p, temp, scale, quantum):
             assert got[r] in allowed, (seed, r, got[r], allowed)
 
 
-def test_sample_nucleus_over_a_large_vocabulary(K):
+@pytest.mark.parametrize("two_kernels", [True, False])
+def test_sample_nucleus_over_a_large_vocabulary(K, monkeypatch, two_kernels):
     """top_k off and top_p 0.95 at the vocabulary of the benchmark model: a peaked row (the nucleus is
-    a handful of tokens) and a flat one (tens of tiers)."""
+    a handful of tokens: drawn by the kernel that looks among the 64 largest, when that form is on)
+    and a flat one (tens of tiers)."""
+    monkeypatch.setattr(K, "two_kernel_sampling", two_kernels)
     V = 151936
     x = randn(2, V, seed=74, scale=1.5)
     x[0, 777] = 14.0

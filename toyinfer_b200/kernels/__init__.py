@@ -426,6 +426,9 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     return out
 
 
+two_kernel_sampling = True      # tests clear this to run every setting in its one-block-per-row form
+
+
 def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int,
            keys: torch.Tensor, steps: torch.Tensor) -> torch.Tensor:
     """One draw per row from softmax(logits / temperature) restricted by top_k and top_p.
@@ -437,8 +440,13 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
     if keys.dtype != torch.int64 or steps.dtype != torch.int32 or keys.numel() != R or steps.numel() != R:
         raise KernelError("sample: keys must be int64[rows] and steps int32[rows]")
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    _call(library().ti_sample, _ptr(logits), logits.stride(0), R, V, float(temperature), int(top_k), float(top_p),
-          ctypes.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), _ptr(keys), _ptr(steps), _ptr(out), _stream())
+    # the usual settings run as two short kernels over many blocks and need room between them
+    lib = library()
+    need = int(lib.ti_sample_scratch_bytes(R, V, int(top_k), float(top_p))) if two_kernel_sampling else 0
+    scratch = torch.empty((need // 8 + 1,), dtype=torch.int64, device=logits.device) if need > 0 else None
+    _call(lib.ti_sample, _ptr(logits), logits.stride(0), R, V, float(temperature), int(top_k), float(top_p),
+          ctypes.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), _ptr(keys), _ptr(steps), _ptr(out), _ptr(scratch), _stream(),
+          launches=1 if need == 0 else 3 if (top_p < 1.0 and not 0 < top_k < V) else 2)
     return out
 
 

@@ -45,7 +45,7 @@ def _declare(lib) -> None:
         "ti_linear_tc_plan": [I, I, I, I, P, P, P, P, P],
         "ti_read_status": [P],
         "ti_argmax": [P, L, I, I, I, P, P, P, P],
-        "ti_sample": [P, L, I, I, F, I, F, c_uint64, P, P, P, P],
+        "ti_sample": [P, L, I, I, F, I, F, c_uint64, P, P, P, P, P],
     }
     for name, args in sig.items():
         fn = getattr(lib, name)
@@ -53,6 +53,8 @@ def _declare(lib) -> None:
         fn.argtypes = args
     lib.ti_uniform_from.restype = c_float
     lib.ti_uniform_from.argtypes = [c_uint64, c_uint64, c_uint64]
+    lib.ti_sample_scratch_bytes.restype = ctypes.c_longlong
+    lib.ti_sample_scratch_bytes.argtypes = [c_int, c_int, c_int, c_float]
     # entry points that later kernels add are declared by their own modules (see declare())
 
 

@@ -6,8 +6,9 @@ two differences: the temperature divides the logits once (the reference divides 
 second time inside the exponent, :38), and the uniform number is a function of
 (seed, sequence key, number of tokens the sequence has drawn), not of the clock (:57-60),
 so a sequence gets the same tokens whatever batch it runs in.  Every combination of top_k
-and top_p runs on the device: up to 1,024 candidates in one shared-memory sort, more (or
-top_p over the whole vocabulary) tier by tier (csrc/sampling.cu).
+and top_p runs on the device: top_k up to 1,024, temperature alone, and top_p whose nucleus
+lies within the row's 64 largest entries as two short kernels over many blocks; more
+candidates (or a larger nucleus) tier by tier in one block per row (csrc/sampling.cu).
 """
 from __future__ import annotations
 
