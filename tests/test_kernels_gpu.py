@@ -211,14 +211,14 @@ def test_linear_tensor_cores_at_model_sizes(K, monkeypatch, M, N, K_, f32):
 def test_linear_many_tokens_on_one_and_on_two_sms_per_tile(K, M, N, K_, f32):
     """The many-token tcgen05 kernel in both forms, one block per tile of 128 tokens and a pair of blocks
     per tile of 256 (cta_group::2), against a float32 product of the same bfloat16 operands."""
-    from toyinfer_b200.kernels.lib import library
+    from toyinfer_b200.kernels import gemm
     g = torch.Generator(device="cuda").manual_seed(6)
     x = torch.randn(M, K_, generator=g, device="cuda").to(torch.bfloat16)
     w = (torch.randn(N, K_, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
     want = x.float() @ w.float().T
     try:
         for mode in (1, 2):
-            library().ti_set_gemm_pair_mode(mode)
+            gemm.set_pair_mode(mode)
             got = K.linear(x, w, out_dtype=torch.float32 if f32 else None)
             K.check_status()
             if f32:
@@ -227,7 +227,7 @@ def test_linear_many_tokens_on_one_and_on_two_sms_per_tile(K, M, N, K_, f32):
                 torch.testing.assert_close(got.float(), want.to(torch.bfloat16).float(), rtol=1.6e-2, atol=4e-3)
             assert torch.equal(got, K.linear(x, w, out_dtype=torch.float32 if f32 else None))
     finally:
-        library().ti_set_gemm_pair_mode(0)
+        gemm.set_pair_mode(0)
 
 
 @pytest.mark.parametrize("M", [1, 2])

@@ -28,12 +28,23 @@ def _code(t: torch.Tensor, what: str) -> int:
         raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)") from None
 
 
-def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
-    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+def _ptr(t: Optional[torch.Tensor]):
+    """The tensor's address as ctypes takes it for a pointer argument: an integer, or None for null
+    (no object is built: a prompt step passes 1,700 pointers)."""
+    return None if t is None else t.data_ptr()
 
 
-def _stream() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+# The current stream's handle, asked for at every launch: torch.cuda.current_stream() builds a Python
+# object on the way (a prompt step of 36 layers asks 290 times: 2 ms of its 8 ms on the host), the
+# raw query behind it does not.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
+def _stream():
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
 def _need_cuda(*tensors, what: str) -> None:

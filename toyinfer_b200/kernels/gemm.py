@@ -21,6 +21,7 @@ from .lib import library
 GEMV_MAX_TOKENS = 1      # one token: a plain read of the weights on the CUDA cores
 SKINNY_MAX_TOKENS = 8    # up to this many: mma.sync with both operands loaded straight from global memory
 _tickets = {}
+_plans = {}         # (M, N, K, sms) -> (workspace floats, tickets) as ti_linear_tc_plan answers
 _sm_counts = {}
 
 
@@ -37,6 +38,13 @@ def _tickets_for(device) -> torch.Tensor:
     if t is None:
         t = _tickets[device] = torch.zeros(4096, dtype=torch.int32, device=device)
     return t
+
+
+def set_pair_mode(mode: int) -> None:
+    """For tests and measurements: 0 the plan decides between one and two SMs per tile, 1 never two,
+    2 two wherever there is a tile per pair.  Plans kept from before are forgotten."""
+    library().ti_set_gemm_pair_mode(int(mode))
+    _plans.clear()
 
 
 def tc_eligible(x, w, K, ldx, ldw) -> bool:
@@ -58,18 +66,23 @@ def run(x, w, out, M, N, K, ldx, ldw, gated: bool = False, late_start: bool = Fa
               sm_count(x.device), 1 if late_start else 0, _stream())
         return
     if tc_eligible(x, w, K, ldx, ldw):
-        swap, bn, splits, n_tiles = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
-        ws = ctypes.c_longlong()
         sms = sm_count(x.device)
-        lib.ti_linear_tc_plan(M, N, K, sms, ctypes.byref(swap), ctypes.byref(bn), ctypes.byref(splits),
-                              ctypes.byref(ws), ctypes.byref(n_tiles))
+        plan = _plans.get((M, N, K, sms))
+        if plan is None:        # (workspace floats, tiles that need a ticket) of this shape: asked once
+            swap, bn, splits, n_tiles = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+            ws = ctypes.c_longlong()
+            lib.ti_linear_tc_plan(M, N, K, sms, ctypes.byref(swap), ctypes.byref(bn), ctypes.byref(splits),
+                                  ctypes.byref(ws), ctypes.byref(n_tiles))
+            if len(_plans) > 4096:
+                _plans.clear()
+            plan = _plans[(M, N, K, sms)] = (ws.value, n_tiles.value)
         workspace = tickets = None
-        if ws.value > 0:
-            workspace = torch.empty(ws.value, dtype=torch.float32, device=x.device)
+        if plan[0] > 0:
+            workspace = torch.empty(plan[0], dtype=torch.float32, device=x.device)
             # tickets let the last block of a tile add the partial tiles itself; measured faster
             # than the separate reduction kernel the library falls back to without them
             tickets = _tickets_for(x.device)
-            if n_tiles.value > tickets.numel():
+            if plan[1] > tickets.numel():
                 tickets = None
         _call(lib.ti_linear_tc, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, 1 if gated else 0, sms,
               _ptr(workspace), _ptr(tickets), _stream())
