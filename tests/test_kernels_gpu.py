@@ -387,10 +387,16 @@ def make_mem(dtype, n_slots, nkv, hd, pages, window=0, dirty=0.0):
     return KVView(k, v, table, nkv, hd, window, ring)
 
 
-def make_batch(mode, slots, starts, news, plan_len=4096):
+def make_batch(mode, slots, starts, news, plan_len=4096, spare_rows=0):
+    """With ``spare_rows``, that many token rows of nobody's follow, as in a captured step of fixed size."""
     from toyinfer_b200.engine.batch import BatchBuffers, fill_batch
-    buf = BatchBuffers(len(slots), sum(news), "cuda")
     toks = [[0] * n for n in news]
+    if spare_rows:
+        total = sum(news) + spare_rows
+        buf = BatchBuffers(len(slots) + 1, total, "cuda")
+        return fill_batch(buf, mode, slots, starts, toks, scratch_slot=max(slots) + 1, plan_len=plan_len,
+                          total_tok=total, new_bound=max(news) + 5)
+    buf = BatchBuffers(len(slots), sum(news), "cuda")
     return fill_batch(buf, mode, slots, starts, toks, scratch_slot=max(slots) + 1, plan_len=plan_len)
 
 
@@ -510,6 +516,46 @@ def test_attention_prefill_on_views_of_one_buffer(K, nh, nkv, hd, window):
         for n in news:
             want = plain_attention_seq(q[o:o + n].cpu(), k[o:o + n].cpu(), v[o:o + n].cpu(), scale, window, dtype)
             torch.testing.assert_close(got[o:o + n], want, **ATT_TOL[dtype])
+            o += n
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(5, 1, 48, 40), (8, 2, 128, 0), (4, 4, 64, 0), (6, 2, 128, 100), (2, 1, 64, 64)])
+def test_attention_prefill_beside_rows_of_nan(K, dtype, nh, nkv, hd, window):
+    """A sequence's result does not depend on what stands in the rows of other sequences, nor in rows
+    that are nobody's (the spare rows of a step of fixed size): those hold NaN here, and a key tile's
+    or a query tile's rows reach into them."""
+    news = [70, 100, 1, 33, 200, 64, 2]
+    bad = (1, 3, 5)
+    spare = 59
+    M = sum(news)
+    total = M + spare
+    q = randn(total, nh, hd, seed=27).to(dtype)
+    k = randn(total, nkv, hd, seed=28).to(dtype)
+    v = randn(total, nkv, hd, seed=29).to(dtype)
+    o = 0
+    for i, n in enumerate(news):
+        if i in bad:
+            for t in (q, k, v):
+                t[o:o + n] = float("nan")
+        o += n
+    for t in (q, k, v):
+        t[M:] = float("nan")
+    batch = make_batch("start", list(range(len(news))), [0] * len(news), news, spare_rows=spare)
+    scale = 1.0 / math.sqrt(hd)
+    from toyinfer_b200.kernels import attention
+    for mma_sync in (False, True):
+        attention.prefer_mma_sync = mma_sync
+        try:
+            got = K.attention_prefill(dev(q), dev(k), dev(v), scale, window, batch).cpu().double()
+        finally:
+            attention.prefer_mma_sync = False
+        K.check_status()
+        o = 0
+        for i, n in enumerate(news):
+            if i not in bad:
+                want = plain_attention_seq(q[o:o + n], k[o:o + n], v[o:o + n], scale, window, dtype)
+                torch.testing.assert_close(got[o:o + n], want, **ATT_TOL[dtype], msg=lambda m: f"sequence {i}: {m}")
             o += n
 
 
@@ -645,6 +691,11 @@ def test_attention_chunk(K, dtype, nh, nkv, hd, window):
     q = torch.cat([qs[s][st:] for s, (st, _) in enumerate(cases)])
     k = torch.cat([ks[s][st:] for s, (st, _) in enumerate(cases)])
     v = torch.cat([vs[s][st:] for s, (st, _) in enumerate(cases)])
+    # one sequence's new rows are NaN as well: its neighbours' tiles reach into them
+    bad = 2
+    o_bad = sum(n for _, n in cases[:bad])
+    for t in (q, k, v):
+        t[o_bad:o_bad + cases[bad][1]] = float("nan")
     from toyinfer_b200.kernels import attention
     for mma_sync in (False, True):          # heads of 64 and 128: the tcgen05 kernel, then the mma.sync kernel
         attention.prefer_mma_sync = mma_sync
@@ -655,8 +706,9 @@ def test_attention_chunk(K, dtype, nh, nkv, hd, window):
         K.check_status()
         o = 0
         for s, (st, n) in enumerate(cases):
-            want = plain_attention_seq(qs[s], ks[s], vs[s], scale, window, dtype)[st:]
-            torch.testing.assert_close(got[o:o + n], want, **ATT_TOL[dtype], msg=lambda m: f"sequence {s} {cases[s]}: {m}")
+            if s != bad:
+                want = plain_attention_seq(qs[s], ks[s], vs[s], scale, window, dtype)[st:]
+                torch.testing.assert_close(got[o:o + n], want, **ATT_TOL[dtype], msg=lambda m: f"sequence {s} {cases[s]}: {m}")
             o += n
 
 

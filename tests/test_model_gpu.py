@@ -224,6 +224,70 @@ def test_padding_and_company_change_nothing(model_folders, dtype):
         torch.testing.assert_close(outs[0], outs[2], rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_prompt_shapes_that_come_back_run_from_a_captured_step(model_folders, name, dtype):
+    """Batches of prompts whose rounded shape is the same: the first runs as it is, the second is
+    captured, the others are replayed.  Each prompt's logits and the tokens decoded after it (they read
+    what the prompt step left in the cache) are the plain implementation's, and slots are used again."""
+    eng = make_engine(model_folders[name], dtype, max_tokens=64 * 12, max_batch=4)
+    assert eng.prompt_graph_tokens > 0
+    # three sequences and 65-128 tokens each time (128 token rows), the longest prompt 33-64
+    rounds = [[40, 9, 33], [64, 1, 20], [35, 35, 35], [50, 2, 60], [33, 33, 1]]
+    for r, lens in enumerate(rounds):
+        seqs = prompts_for(name, [n + 3 for n in lens], seed=40 + r)
+        want = [plain_logits(model_folders[name], s, dtype) for s in seqs]
+        slots = [eng.new_sequence() for _ in seqs]
+        logits = eng.step([(sl, s[:n]) for sl, s, n in zip(slots, seqs, lens)], None).clone()
+        for i, n in enumerate(lens):
+            assert_logits_close(logits[i], want[i][n - 1], dtype, f"{name} round {r} prompt {i}")
+        for t in range(3):
+            logits = eng.step([(sl, [s[n + t]]) for sl, s, n in zip(slots, seqs, lens)], None).clone()
+            for i, n in enumerate(lens):
+                assert_logits_close(logits[i], want[i][n + t], dtype, f"{name} round {r} seq {i} step {t}")
+        for sl in slots:
+            eng.end_sequence(sl)
+    assert len(eng._prompt_graphs) == 1
+    assert eng.graph_replays >= 3 + 5 * 2          # prompt rounds 2-4, and every round's decode steps but its first
+    # other wanted places than each prompt's last are not the captured step's business
+    slot = eng.new_sequence()
+    ids = prompts_for(name, [40], seed=50)[0]
+    for _ in range(3):
+        got = eng.step([(slot, ids)], [[0, 39]])
+        assert_logits_close(got, plain_logits(model_folders[name], ids, dtype)[[0, 39]], dtype, "two wanted places")
+        eng.end_sequence(slot)
+        slot = eng.new_sequence()
+    assert len(eng._prompt_graphs) == 1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_captured_prompt_step_with_and_without_spare_rows(model_folders, dtype):
+    """One prompt of 33-64 tokens is one shape of 64 token rows: full, or with up to 31 rows of nobody's."""
+    eng = make_engine(model_folders["D"], dtype)
+    for i, n in enumerate((64, 50, 64, 33, 64)):
+        ids = prompts_for("D", [n + 2], seed=70 + i)[0]
+        want = plain_logits(model_folders["D"], ids, dtype)
+        slot = eng.new_sequence()
+        got = [eng.step([(slot, ids[:n])], None).clone()] + [eng.step([(slot, [t])], None).clone() for t in ids[n:]]
+        assert_logits_close(torch.cat(got), want[n - 1:], dtype, f"prompt of {n}")
+        eng.end_sequence(slot)
+    assert list(eng._prompt_graphs) == [(1, 64, 64)]
+
+
+def test_captured_prompt_steps_are_kept_to_a_number(model_folders):
+    eng = make_engine(model_folders["B"], "bfloat16", max_tokens=64 * 12, max_batch=4)
+    eng.max_prompt_graphs = 2
+    for n in (10, 70, 130, 10):                # three shapes (64, 128 and 192 token rows); the first comes back
+        ids = prompts_for("B", [n], seed=60)[0]
+        want = plain_logits(model_folders["B"], ids, "bfloat16")[-1]
+        for _ in range(3):
+            slot = eng.new_sequence()
+            assert_logits_close(eng.step([(slot, ids)], None)[0], want, "bfloat16", f"prompt of {n}")
+            eng.end_sequence(slot)
+        assert len(eng._prompt_graphs) <= 2
+    assert [k[1] for k in eng._prompt_graphs] == [192, 64]
+
+
 def test_step_refuses_what_it_cannot_run(model_folders):
     from toyinfer_b200.engine import StepError
     eng = make_engine(model_folders["A"], "float32")

@@ -164,14 +164,15 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
         const int k0 = old ? (pt_lo + i) * BKV - start : (kt_lo + i - n_old) * BKV;
         const int limit = old ? 0 : n;
         bool patched = false;
-        if (old && (k0 + BKV > 0 || k0 + start < lo_blk)) {
-            // lines of the page outside [lo_blk, start) may hold anything (this step's tokens, an
-            // older turn of the ring, a former owner's): their value rows are cleared, so that a
+        if (old ? (k0 + BKV > 0 || k0 + start < lo_blk) : (k0 + BKV > n)) {
+            // Lines of a page outside [lo_blk, start) may hold anything (this step's tokens, an
+            // older turn of the ring, a former owner's), and the rows after a sequence's last new
+            // token are another sequence's or nobody's: their value rows are cleared, so that a
             // probability of zero times whatever stands there cannot make a NaN
             unsigned char* vt = kv_s + (size_t)stage * 2 * TILE_BYTES + TILE_BYTES;
             for (int r = warp; r < BKV; r += THREADS / 32) {
                 const int p = k0 + start + r;
-                if (p < lo_blk || p >= start)
+                if (old ? (p < lo_blk || p >= start) : (k0 + r >= n))
                     for (int d = lane * 8; d < HD; d += 256)
                         *reinterpret_cast<uint4*>(vt + swizzled_offset<BKV>(r, d)) = make_uint4(0, 0, 0, 0);
             }

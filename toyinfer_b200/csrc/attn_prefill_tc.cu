@@ -359,9 +359,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             float sum4[4];
             unpack2(sum2[0], sum4[0], sum4[1]);
             unpack2(sum2[1], sum4[2], sum4[3]);
-            if (old && (tile0 + BKV > 0 || tile0 + start < lo_blk)) {
-                // Lines of the page outside [lo_blk, start) may hold anything (this step's tokens, an
-                // older turn of the ring, a former owner's): their value rows are cleared, so that a
+            if (old ? (tile0 + BKV > 0 || tile0 + start < lo_blk) : (tile0 + BKV > n)) {
+                // Lines of a page outside [lo_blk, start) may hold anything (this step's tokens, an
+                // older turn of the ring, a former owner's), and the rows after a sequence's last new
+                // token are another sequence's or nobody's: their value rows are cleared, so that a
                 // probability of zero times whatever stands there cannot make a NaN.  A row of a box is
                 // 128 bytes whatever the swizzle does inside it; four threads clear a row of all boxes.
                 // The second product starts only after every softmax warp has arrived on p_full below,
@@ -370,7 +371,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 if (ok) {
                     const int st = (int)threadIdx.x - 64, row = st >> 2, part = st & 3;
                     const int p = tile0 + start + row;
-                    if (p < lo_blk || p >= start) {
+                    if (old ? (p < lo_blk || p >= start) : (tile0 + row >= n)) {
                         constexpr int PART = HD / 2;        // bytes of a row's HD * 2 that one of its four threads clears
                         uint4* dst = reinterpret_cast<uint4*>(kv_s + (size_t)sb * 2 * KV_BYTES + KV_BYTES + (part * PART / 128) * KBOX +
                                                               row * 128 + (part * PART) % 128);

@@ -97,16 +97,25 @@ class StepBatch:
 
 def fill_batch(buf: BatchBuffers, mode: str, slots: Sequence[int], starts: Sequence[int],
                tokens: Sequence[Sequence[int]], scratch_slot: int, plan_len: int,
-               pad_seqs: int = 0) -> StepBatch:
+               pad_seqs: int = 0, total_tok: Optional[int] = None, new_bound: Optional[int] = None) -> StepBatch:
     """Writes a step into ``buf`` (host side), uploads it and returns the views.
-    ``pad_seqs`` extra sequences of one token each are appended as padding."""
+    ``pad_seqs`` extra sequences of one token each are appended as padding.  With ``total_tok``
+    the step has that many token rows whatever it holds (a captured step's launches are fixed):
+    the spare rows after the last sequence's are nobody's.  They hold token 0 at position 0 of a
+    stand-in sequence one past the step's own (index ``n_seq``: the scratch slot, no new tokens;
+    the views of the per-sequence arrays are one entry longer for it, and ``buf`` must have the
+    room), so that whatever is stored for them goes to the scratch slot; no sequence's count
+    includes them and their results are never read.  ``new_bound`` stands for the longest run of
+    new tokens and the longest length wherever launches are sized."""
     n_real = len(slots)
     n_seq = n_real + pad_seqs
     new = [len(t) for t in tokens]
     n_real_tok = sum(new)
-    n_tok = n_real_tok + pad_seqs
-    if n_seq > buf.n_seq or n_tok > buf.n_tok:
-        raise ValueError(f"step of {n_seq} sequences / {n_tok} tokens exceeds buffers for {buf.n_seq} / {buf.n_tok}")
+    n_used = n_real_tok + pad_seqs
+    n_tok = n_used if total_tok is None else int(total_tok)
+    spare = n_tok > n_used
+    if n_seq + spare > buf.n_seq or n_tok > buf.n_tok or n_used > n_tok:
+        raise ValueError(f"step of {n_seq + spare} sequences / {max(n_tok, n_used)} tokens exceeds buffers for {buf.n_seq} / {buf.n_tok}")
     buf.begin_fill()
     ids, pos, seq = buf.host_view("token_ids"), buf.host_view("tok_pos"), buf.host_view("tok_seq")
     sl, st, nw, ln, cu = (buf.host_view("seq_slot"), buf.host_view("seq_start"), buf.host_view("seq_new"),
@@ -127,7 +136,7 @@ def fill_batch(buf: BatchBuffers, mode: str, slots: Sequence[int], starts: Seque
     # entries past the used part keep harmless values for kernels launched over the full buffers
     ids[o:] = 0
     pos[o:] = 0
-    seq[o:] = max(n_seq - 1, 0)
+    seq[o:] = n_seq if spare else max(n_seq - 1, 0)
     sl[n_seq:] = scratch_slot
     st[n_seq:] = 0
     nw[n_seq:] = 0
@@ -136,13 +145,13 @@ def fill_batch(buf: BatchBuffers, mode: str, slots: Sequence[int], starts: Seque
     buf.upload()
     return StepBatch(
         mode=mode, n_seq=n_seq, n_tok=n_tok, n_real_seq=n_real, n_real_tok=n_real_tok,
-        max_new=max(new + [1 if pad_seqs else 0]),
-        max_pos_after=max([s + n for s, n in zip(starts, new)] + [1]),
+        max_new=new_bound if new_bound is not None else max(new + [1 if pad_seqs else 0]),
+        max_pos_after=new_bound if new_bound is not None else max([s + n for s, n in zip(starts, new)] + [1]),
         plan_len=plan_len,
         token_ids=buf.dev_view("token_ids")[:n_tok], tok_pos=buf.dev_view("tok_pos")[:n_tok],
-        tok_seq=buf.dev_view("tok_seq")[:n_tok], seq_slot=buf.dev_view("seq_slot")[:n_seq],
-        seq_start=buf.dev_view("seq_start")[:n_seq], seq_new=buf.dev_view("seq_new")[:n_seq],
-        seq_len=buf.dev_view("seq_len")[:n_seq], cu_new=buf.dev_view("cu_new")[:n_seq + 1],
+        tok_seq=buf.dev_view("tok_seq")[:n_tok], seq_slot=buf.dev_view("seq_slot")[:n_seq + spare],
+        seq_start=buf.dev_view("seq_start")[:n_seq + spare], seq_new=buf.dev_view("seq_new")[:n_seq + spare],
+        seq_len=buf.dev_view("seq_len")[:n_seq + spare], cu_new=buf.dev_view("cu_new")[:n_seq + 1 + spare],
         host_slots=list(slots) + [scratch_slot] * pad_seqs, host_starts=list(starts) + [0] * pad_seqs,
         host_new=new + [1] * pad_seqs,
     )

@@ -21,6 +21,7 @@ from __future__ import annotations
 import gc
 import os
 import weakref
+from collections import OrderedDict
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -48,6 +49,9 @@ def parse_dtype(name) -> torch.dtype:
 
 class StepError(ValueError):
     """A step that cannot be run as asked; nothing was changed."""
+
+
+PROMPT_GRAPH_TOKENS = 1024      # prompt steps of up to so many token rows may be captured; longer ones keep the device busy
 
 
 def _bucket(n: int, cap: int) -> int:
@@ -78,13 +82,20 @@ class Engine:
         self.memories = self.cache.views(len(model.schedule))
         self.use_cuda_graph = bool(use_cuda_graph) and self.device.type == "cuda"
         self._eager_bufs: Dict[Tuple[int, int], BatchBuffers] = {}
-        self._graphs: Dict[Tuple[int, Any], "_DecodeGraph"] = {}     # (batch bucket, launch plan of its length class) -> captured step
+        self._graphs: Dict[Tuple[int, Any], "_CapturedStep"] = {}     # (batch bucket, launch plan of its length class) -> captured step
         self._plans: Dict[Tuple[int, int], Any] = {}                 # (batch bucket, length class) -> the model's launch plan
         # All captured steps draw their intermediate buffers from one pool: steps run one at a time,
         # so what one graph freed during its capture another may use.  Each graph still keeps its
         # own [bucket, vocab] float32 logits (alive at the end of its capture).
         self._graph_pool = None
         self.graph_replays = 0
+        # Steps of whole prompts with few tokens are bound by the host's launches, not by the device:
+        # a shape that comes back (token rows and the longest prompt rounded up, see _prompt_graph) is captured when
+        # it is seen the second time, if the model's parts allow it.  The least recently used go first.
+        self.prompt_graph_tokens = PROMPT_GRAPH_TOKENS if self.use_cuda_graph and model.captures_start() else 0
+        self.max_prompt_graphs = 16
+        self._prompt_graphs: "OrderedDict[Tuple[int, int, int], _CapturedStep]" = OrderedDict()
+        self._prompt_shapes_seen: Dict[Tuple[int, int, int], int] = {}
 
     # -- construction -----------------------------------------------------------
     @classmethod
@@ -205,6 +216,12 @@ class Engine:
             if len(rows) == n:
                 return logits_all[:n]
             return logits_all[torch.tensor(rows, device=self.device)]
+        # (a prompt step whose stages are to be timed runs as plain launches: a replay has no stages)
+        if mode == "start" and self.prompt_graph_tokens and not self.tracer.timing \
+                and all(list(w) == [len(t) - 1] for w, t in zip(want, tokens)):
+            logits_all = self._prompt_graph(slots, starts, tokens)
+            if logits_all is not None:
+                return logits_all
         batch = self._eager_batch(mode, slots, starts, tokens)
         if token_source is not None:
             batch.token_ids[:n].copy_(token_source)
@@ -267,21 +284,51 @@ class Engine:
             plan = self._plans[(b, cls)] = self.model.launch_plan(b, cls)
         g = self._graphs.get((b, plan))
         if g is None:
-            g = self._graphs[(b, plan)] = _DecodeGraph(self, b, cls)
+            g = self._graphs[(b, plan)] = _CapturedStep(self, "extend", b, b, cls)
         return g.run(slots, starts, tokens, token_source)
 
 
-class _DecodeGraph:
-    """A decode step of ``bucket`` sequences captured into a CUDA graph.  It refers to its
-    engine weakly: engine and graphs then form no cycle, and both are released (with their
-    device memory) when the last reference to the engine goes, not at some later collection."""
+    def _prompt_graph(self, slots, starts, tokens) -> Optional[torch.Tensor]:
+        """Runs a step of whole prompts from a captured graph, or returns None (run it as it is).
+        Shapes are rounded up so that fewer graphs serve more steps: token rows to a multiple of 64
+        (the spare rows are nobody's, see fill_batch), the longest prompt to a power of two."""
+        n_seq = len(slots)
+        n_tok = -(-sum(len(t) for t in tokens) // 64) * 64
+        if n_tok > self.prompt_graph_tokens:
+            return None
+        bound = min(_bucket(max(len(t) for t in tokens), 1 << 30), n_tok, self.max_seq_len)
+        key = (n_seq, n_tok, bound)
+        g = self._prompt_graphs.get(key)
+        if g is None:
+            seen = self._prompt_shapes_seen[key] = self._prompt_shapes_seen.get(key, 0) + 1
+            if seen < 2:
+                return None
+            while len(self._prompt_graphs) >= self.max_prompt_graphs:
+                self._prompt_graphs.popitem(last=False)
+            g = self._prompt_graphs[key] = _CapturedStep(self, "start", n_seq, n_tok, self.max_seq_len, bound)
+        else:
+            self._prompt_graphs.move_to_end(key)
+        return g.run(slots, starts, tokens)
 
-    def __init__(self, engine: Engine, bucket: int, plan_len: int):
+
+class _CapturedStep:
+    """A step of fixed launches captured into a CUDA graph: ``n_seq`` sequences that go on by one
+    token each ("extend"), or that start with up to ``n_tok`` tokens altogether and at most
+    ``new_bound`` each ("start").  It refers to its engine weakly: engine and graphs then form
+    no cycle, and both are released (with their device memory) when the last reference to the
+    engine goes, not at some later collection."""
+
+    def __init__(self, engine: Engine, mode: str, n_seq: int, n_tok: int, plan_len: int,
+                 new_bound: Optional[int] = None):
         self._engine = weakref.ref(engine)
-        self.bucket = bucket
+        self.mode = mode
+        self.bucket = n_seq
+        self.n_tok = n_tok
         self.plan_len = plan_len
-        self.buf = BatchBuffers(bucket, bucket, engine.device)
-        self.rows = torch.arange(bucket, dtype=torch.int32, device=engine.device)
+        self.new_bound = new_bound
+        self.buf = BatchBuffers(n_seq + (mode == "start"), n_tok, engine.device)     # a prompt step's spare rows need a stand-in
+        # the rows whose logits are wanted: every row of single tokens, each sequence's last otherwise
+        self.rows = torch.arange(n_seq, dtype=torch.int32, device=engine.device) if mode == "extend" else None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.launches = 0
@@ -296,14 +343,20 @@ class _DecodeGraph:
     def _body(self, batch: StepBatch) -> torch.Tensor:
         e = self.engine
         h, delta = e.model.forward_hidden(batch, e.memories)
+        # each sequence's last row, found on the device: the graph is replayed with other lengths
+        rows = self.rows if self.rows is not None else batch.cu_new[1:batch.n_seq + 1] - 1
         with e.tracer.range("head"):
-            return e.model.logits(h, delta, self.rows)
+            return e.model.logits(h, delta, rows)
 
     def run(self, slots, starts, tokens, token_source=None) -> torch.Tensor:
         e = self.engine
-        pad = self.bucket - len(slots)
-        batch = fill_batch(self.buf, "extend", slots, starts, tokens, e.cache.scratch_slot,
-                           self.plan_len, pad_seqs=pad)
+        name = "decode" if self.mode == "extend" else "prefill"
+        if self.mode == "extend":
+            batch = fill_batch(self.buf, "extend", slots, starts, tokens, e.cache.scratch_slot,
+                               self.plan_len, pad_seqs=self.bucket - len(slots))
+        else:
+            batch = fill_batch(self.buf, "start", slots, starts, tokens, e.cache.scratch_slot,
+                               self.plan_len, total_tok=self.n_tok, new_bound=self.new_bound)
         batch.trace = e.tracer
         if token_source is not None:
             batch.token_ids[:len(slots)].copy_(token_source)      # after the upload, before the replay
@@ -314,7 +367,7 @@ class _DecodeGraph:
             before = K.launch_count
             # the stages inside this run and inside the capture are not timed: replays have none
             was_capturing = e.tracer.capturing
-            with e.tracer.step("decode"):
+            with e.tracer.step(name):
                 e.tracer.capturing = True
                 try:
                     out = self._body(batch)
@@ -341,7 +394,7 @@ class _DecodeGraph:
                     gc.enable()
             self.graph = g
             return out
-        with e.tracer.step("decode"):
+        with e.tracer.step(name):
             self.graph.replay()
         e.graph_replays += 1
         return self.logits

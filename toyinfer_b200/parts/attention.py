@@ -107,6 +107,12 @@ class GQAAttention(Mixer):
 
     takes_pending_norm = True       # x goes into K.linear first, and nowhere else
 
+    @property
+    def captures_start(self) -> bool:
+        # the kernels read the batch's device side only; a position encoding that works on q and k
+        # itself is somebody else's code
+        return self.pos is None or self.pos.rotary_tables() is not None
+
     def check_kernels(self, dtype) -> None:
         from ..kernels import attention
         attention.check_supported(self.n_heads, self.n_kv_heads, self.head_dim, dtype)

@@ -22,7 +22,10 @@ Families and what each must provide:
                     special cases a mixer may run faster: ``"start"`` (every start is
                     0) and ``"extend"`` (one token each; device tensors only, since
                     such a step may be captured into a CUDA graph); anything else is
-                    ``"mixed"``.  ``shared`` is a dict that lives for one
+                    ``"mixed"``.  A mixer whose ``"start"`` steps read device tensors
+                    only as well says so with ``captures_start = True``: repeated
+                    prompt shapes are then captured too, if every part of the model
+                    agrees.  ``shared`` is a dict that lives for one
                     step and belongs to the schedule entry that owns ``mem``; an
                     entry that borrows another entry's memory gets the owner's dict.
                     When it holds a list ``"deferred"``, later entries still read
@@ -148,6 +151,8 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     takes_pending_norm = False      # forward() may be given a kernels.PendingNorm, used by K.linear first
+    captures_start = False          # a "start" step reads nothing of the batch's host side and allocates through torch
+                                    # only: the engine may capture it (a class attribute or a property)
 
     def launch_plan(self, n_seq: int, plan_len: int, dtype, device):
         """What, of a captured single-token step of ``n_seq`` sequences, depends on the length the
@@ -165,6 +170,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     takes_pending_norm = False      # as for Mixer
+    captures_start = False          # as for Mixer
 
     def forward(self, x, batch) -> torch.Tensor:
         raise NotImplementedError
@@ -192,6 +198,11 @@ class Block(Part):
     def launch_plan(self, n_seq: int, plan_len: int, dtype, device):
         """As Mixer.launch_plan, for the whole block."""
         return self.mixer.launch_plan(n_seq, plan_len, dtype, device)
+
+    @property
+    def captures_start(self) -> bool:
+        """As Mixer.captures_start, for the whole block; a block that knows of a feed-forward asks it too."""
+        return bool(self.mixer.captures_start)
 
     def forward(self, h, delta, batch, mem, shared):
         raise NotImplementedError

@@ -42,6 +42,10 @@ class PreNormBlock(Block):
         for c in self._children:
             c.check_kernels(dtype)
 
+    @property
+    def captures_start(self) -> bool:
+        return bool(self.mixer.captures_start and self.feed_forward.captures_start)
+
     def forward(self, h, delta, batch, mem, shared):
         trace = getattr(batch, "trace", None)
         if trace is not None and trace.active:

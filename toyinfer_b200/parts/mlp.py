@@ -42,6 +42,7 @@ class SwiGLU(FeedForward):
         self.w_down = tensors.pop(self.names["down"]).contiguous()
 
     takes_pending_norm = True       # x goes into K.linear_swiglu, and nowhere else
+    captures_start = True
 
     def forward(self, x, batch) -> torch.Tensor:
         z = K.linear_swiglu(x, self.w_gate_up)    # [M, inter]

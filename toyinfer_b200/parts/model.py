@@ -136,6 +136,10 @@ class DecoderModel(Part):
         of all scheduled blocks (see Mixer.launch_plan)."""
         return tuple(self.blocks[e.layer].launch_plan(n_seq, plan_len, self.dtype, self.device) for e in self.schedule)
 
+    def captures_start(self) -> bool:
+        """Whether a step of whole prompts may be captured: every scheduled block says so."""
+        return all(self.blocks[e.layer].captures_start for e in self.schedule)
+
     # -- one step -------------------------------------------------------------
     def forward_hidden(self, batch, memories: Sequence[Any]):
         """Runs the given tokens through all scheduled blocks.  Returns (h, delta):
