@@ -460,8 +460,11 @@ def run_kernel(name: str, reps: int, eager: bool = False):
         return (torch.randn(*shape, generator=g, device=dev) * scale).to(torch.bfloat16)
 
     def make():
-        if name.startswith("gemm:"):                     # gemm:M,N,K
-            M, N, Kd = (int(v) for v in name[5:].split(","))
+        if name.startswith("gemm:"):                     # gemm:M,N,K or gemm:M,N,K,BN,SPLITS (tile width and splits forced)
+            M, N, Kd, *force = (int(v) for v in name[5:].split(","))
+            if force:
+                from toyinfer_b200.kernels import gemm
+                gemm.set_tile_force(force[0], force[1] if len(force) > 1 else 0)
             x, w = rnd(M, Kd), rnd(N, Kd, scale=0.02)
             return (lambda: K.linear(x, w)), (N * Kd + M * Kd + M * N) * 2, 2.0 * M * N * Kd
         if name in ("gemm_decode", "gemm_decode_b64", "gemm_prefill", "gemm_head", "gemm_down", "gemm_qkv", "gemm_o"):
@@ -575,7 +578,7 @@ def main() -> int:
     ap.add_argument("--range", action="store_true",
                     help="also the mean decode rate while the batch grows from 2,048 positions to --context (some 20 s more)")
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
-                    "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K, attn_decode, attn_decode_b64, attn_decode_b1, "
+                    "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K[,BN,SPLITS], attn_decode, attn_decode_b64, attn_decode_b1, "
                     "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW[,HEAD_DIM]], add_rmsnorm[:TOKENS], rope_store[:TOKENS], mma_issue; "
                     "ref:all or ref:<case> times the reference's kernel recompiled for sm_100a beside this library's")
     ap.add_argument("--workload", default="", choices=["", "8b", "32b"],

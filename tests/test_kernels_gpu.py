@@ -172,6 +172,10 @@ def _planned_shared_tiles(M, N, K_):
     (1000, 1536, 512, False), (777, 3000, 328, True),
     (4741, 520, 264, False),       # more token tiles than one panel of the tile order, the last panel short
     (300, 2560, 4096, False),      # few tiles: the contraction is split
+    (100, 2560, 9728, False),      # one row of 20 tiles, four splits
+    (256, 2560, 9728, False),      # 40 tiles, three splits: all blocks in one round
+    (256, 6144, 2560, False),      # 96 whole tiles, no split
+    (192, 19456, 2560, False),     # a pair's tile of 256 tokens a quarter empty, wide tiles in one round
     (1300, 3600, 264, False),      # tiles for a round and a bit, shared out by contraction steps; short parts, ragged K
     (8, 19456, 2560, False),       # decode at batch 8, gate and up rows
     (64, 2560, 9728, False),       # decode at batch 64, split contraction

@@ -91,6 +91,10 @@ int wide_tile(int rows_a, int rows_b, int sms, bool whole_rounds, double* score_
 // tile, 2 puts them on two wherever there are enough tiles.
 static int g_pair_mode = 0;
 extern "C" void ti_set_gemm_pair_mode(int mode) { g_pair_mode = mode; }
+// For measurements: with bn > 0, products of more than 64 tokens that do not run on pairs take tiles
+// of bn weight rows and split the contraction `splits` ways (0: as planned).
+static int g_force_bn = 0, g_force_splits = 0;
+extern "C" void ti_set_gemm_force(int bn, int splits) { g_force_bn = bn; g_force_splits = splits; }
 
 
 namespace {
@@ -139,7 +143,9 @@ Plan make_plan(int M, int N, int K, int sms) {
         // columns) 87.0 -> 85.3, x 4,096 41.7 -> 40.4.
         int fit = 0;
         if (g_pair_mode != 1 && pairs > 0 && tiles_a2 <= pairs && tiles_a2 * tiles_b2 > pairs && tiles_a2 * tiles_b2 < 2 * pairs &&
-            (double)rows_a / (tiles_a2 * 2 * BM) >= 0.93) {      // the tokens fill their tiles of 256, as for any pair
+            ((double)rows_a / (tiles_a2 * 2 * BM) >= 0.93 || (rows_a + BM - 1) / BM == 2 * tiles_a2)) {
+            // (the tokens fill their tiles of 256, as for any pair, or tiles of 128 would hold as many empty rows:
+            // 192 tokens x 19,456 x 2,560 35.3 -> 27 us)
             const int cols = (int)(pairs / tiles_a2);                       // column tiles of one round
             const int need = (rows_b + cols - 1) / cols;                    // weight rows each must hold
             const int widths[4] = {288, 320, 384, 512};
@@ -173,6 +179,7 @@ Plan make_plan(int M, int N, int K, int sms) {
         }
     }
     else b = rows_b > 64 ? 128 : rows_b > 32 ? 64 : rows_b > 16 ? 32 : 16;
+    if (g_force_bn > 0 && !p.swap && !p.pair) { b = g_force_bn; share = false; }
     const int tile_rows = p.pair ? 2 * BM : BM;
     const int tiles = ((rows_a + tile_rows - 1) / tile_rows) * ((rows_b + b - 1) / b);
     int sp = 1;
@@ -180,13 +187,31 @@ Plan make_plan(int M, int N, int K, int sms) {
     // layer): 1.5 blocks per SM are 2-4 % faster in sum than 1.0, 2.0 are 10 % slower
     const int want = p.swap ? sms + sms / 2 : sms;
     if (tiles < want && !p.pair) {
-        sp = (want + tiles / 2) / tiles;
-        if (sp < 1) sp = 1;
-        const int max_sp = nkb / 4 > 0 ? nkb / 4 : 1;       // at least four 64-wide blocks per split
-        if (sp > max_sp) sp = max_sp;
-        if (sp > 32) sp = 32;
+        if (p.swap) {
+            sp = (want + tiles / 2) / tiles;
+            if (sp < 1) sp = 1;
+            const int max_sp = nkb / 4 > 0 ? nkb / 4 : 1;       // at least four 64-wide blocks per split
+            if (sp > max_sp) sp = max_sp;
+            if (sp > 32) sp = 32;
+        } else {
+            // 65 to some hundred tokens: a block is alone on its SM, so the blocks must fit the SMs in
+            // one round; a block that adds up a tile reads each 64 KB piece through its one SM, and a
+            // part of the contraction shorter than 20 steps is not worth its ramp.  Measured (us, 4B
+            // shapes, splits as rounded before -> so): 256 tokens x 6,144 x 2,560 25.4 -> 15.0 (two
+            // rounds of 192 blocks -> 96 whole tiles), x 2,560 x 4,096 23.2 -> 16.9, x 2,560 x 9,728
+            // 33.7 -> 24.5 (160 blocks -> 120); 512 x 2,560 x 4,096 29.8 -> 20.0, x 9,728 50.7 -> 41.1;
+            // 128 x 2,560 x 4,096 19.2 -> 16.6 (7 splits -> 3), x 9,728 23.9 -> 21.6 (7 -> 4).
+            sp = sms / tiles;
+            if (sp > nkb / 20) sp = nkb / 20;
+            if (sp > 4) sp = 4;
+            if (sp < 1) sp = 1;
+        }
         // drop splits that would get no work
         const int per = (nkb + sp - 1) / sp;
+        sp = (nkb + per - 1) / per;
+    }
+    if (g_force_bn > 0 && g_force_splits > 0 && !p.swap && !p.pair) {
+        const int per = (nkb + g_force_splits - 1) / g_force_splits;
         sp = (nkb + per - 1) / per;
     }
     p.bn = b; p.splits = sp; p.tiles = tiles;

@@ -47,6 +47,14 @@ def set_pair_mode(mode: int) -> None:
     _plans.clear()
 
 
+def set_tile_force(bn: int, splits: int = 0) -> None:
+    """For measurements: products of more than 64 tokens that do not run on two SMs per tile take tiles of
+    ``bn`` weight rows (128 to 256 in steps of 16) and split the contraction ``splits`` ways (0: as planned);
+    ``bn = 0`` ends it.  Plans kept from before are forgotten."""
+    library().ti_set_gemm_force(int(bn), int(splits))
+    _plans.clear()
+
+
 def tc_eligible(x, w, K, ldx, ldw) -> bool:
     return (x.dtype == torch.bfloat16 and K % 8 == 0 and ldx % 8 == 0 and ldw % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
