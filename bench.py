@@ -410,6 +410,41 @@ def run_workload(name: str):
             "build_seconds": round(t_build, 1), "through": "LLM.generate"}
 
 
+def run_prompt_steps(lengths, layers: int):
+    """One prompt of each given length through ``Engine.step`` on the benchmark model, host ids in,
+    logits of the last place out: the mean of five steps after three untimed ones (a shape that comes
+    back runs from a captured graph from its third time on, where the engine captures prompt steps).
+    One JSON line per length."""
+    import torch
+    from toyinfer_b200 import LLM
+    cfg = dict(QWEN3_4B)
+    cfg["num_hidden_layers"] = layers
+    limit = max(max(lengths) + 64, 4096)
+    llm = LLM(config=cfg, seed=0, dtype="bfloat16", max_seq_len=limit, max_batch=8, max_tokens=2 * limit)
+    eng = llm.engine
+    for T in lengths:
+        toks = random_tokens(T, cfg["vocab_size"], 1)
+
+        def once():
+            slot = eng.new_sequence()
+            eng.step([(slot, toks)], None)
+            eng.end_sequence(slot)
+
+        for _ in range(3):
+            once()
+        torch.cuda.synchronize()
+        replays = eng.graph_replays
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(5):
+            once()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / 5
+        print(json.dumps({"prompt_tokens": T, "layers": layers, "ms": round(ms, 3), "tokens_per_s": round(T / ms * 1e3, 1),
+                          "captured": eng.graph_replays - replays == 5}), flush=True)
+
+
 def run_mma_issue():
     """Cycles per tcgen05 MMA of 128 x N x 16 as one issuing thread per block sees them, with the thread
     chosen by ``lane == 0`` and by ``elect.sync`` in a warp-uniform branch, one and two blocks per SM
@@ -583,6 +618,8 @@ def main() -> int:
                     "ref:all or ref:<case> times the reference's kernel recompiled for sm_100a beside this library's")
     ap.add_argument("--workload", default="", choices=["", "8b", "32b"],
                     help="run one of the larger described workloads end to end instead (8B or 32B shape)")
+    ap.add_argument("--prompt-steps", default="", help="time one prompt step of each of these lengths instead (comma-separated), "
+                    "with --layers layers")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--eager", action="store_true", help="with --kernel: plain launches instead of a graph replay")
     args = ap.parse_args()
@@ -604,6 +641,9 @@ def main() -> int:
         return 0
     if args.workload:
         print(json.dumps(run_workload(args.workload)))
+        return 0
+    if args.prompt_steps:
+        run_prompt_steps([int(v) for v in args.prompt_steps.split(",")], args.layers)
         return 0
     if args.impl == "reference":
         print(json.dumps({"impl": "reference",
