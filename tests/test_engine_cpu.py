@@ -269,3 +269,36 @@ def test_decode_attention_merges_as_clusters_only_when_all_find_room(monkeypatch
     assert plan(2, 2112) == (16, 2)
     monkeypatch.setattr(attention, "force_merge_mode", 0)
     assert plan(1, 2112) == (9, 0)
+
+
+def test_spare_token_rows_of_a_step_of_fixed_size_change_nothing(cpu_engine, model_folders):
+    """The form of a captured prompt step: more token rows than the sequences hold.  The spare rows stand at
+    position 0 of a stand-in sequence in the scratch slot; the sequences' logits and what they leave in
+    the cache are those of the plain implementation."""
+    from toyinfer_b200.engine.batch import BatchBuffers, fill_batch
+    name = "B"
+    eng = cpu_engine(name)
+    seqs = prompts_for(name, [21, 8, 34], seed=9)
+    heads = [s[:-1] for s in seqs]
+    slots = [eng.new_sequence() for _ in seqs]
+    for s, ids in zip(slots, heads):
+        eng.cache.reserve(s, len(ids))
+    eng.cache.flush()
+    buf = BatchBuffers(len(seqs) + 1, 128, "cpu")
+    batch = fill_batch(buf, "start", slots, [0] * 3, heads, eng.cache.scratch_slot, eng.max_seq_len, total_tok=128, new_bound=64)
+    used = sum(len(h) for h in heads)
+    assert (batch.n_seq, batch.n_tok, batch.n_real_tok, batch.max_new) == (3, 128, used, 64)
+    assert batch.seq_slot.tolist() == slots + [eng.cache.scratch_slot] and batch.seq_new.tolist() == [20, 7, 33, 0]
+    assert batch.tok_seq[used:].tolist() == [3] * (128 - used) and batch.tok_pos[used:].tolist() == [0] * (128 - used)
+    assert batch.cu_new.tolist() == [0, 20, 27, 60, 60]
+    h, delta = eng.model.forward_hidden(batch, eng.memories)
+    got = eng.model.logits(h, delta, batch.cu_new[1:4] - 1)
+    for s, ids in zip(slots, heads):
+        eng.cache.commit(s, len(ids))
+    for i, ids in enumerate(seqs):
+        want = _plain_logits(model_folders[name], ids)
+        torch.testing.assert_close(got[i], want[-2], rtol=1e-4, atol=1e-5)
+        nxt = eng.step([(slots[i], [ids[-1]])], None)         # reads what the padded step stored
+        torch.testing.assert_close(nxt[0], want[-1], rtol=1e-4, atol=1e-5)
+    with pytest.raises(ValueError):                            # spare rows need room for the stand-in sequence
+        fill_batch(BatchBuffers(3, 128, "cpu"), "start", slots, [0] * 3, heads, eng.cache.scratch_slot, eng.max_seq_len, total_tok=128)
