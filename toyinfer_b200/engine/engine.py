@@ -51,7 +51,39 @@ class StepError(ValueError):
     """A step that cannot be run as asked; nothing was changed."""
 
 
-PROMPT_GRAPH_TOKENS = 1024      # prompt steps of up to so many token rows may be captured; longer ones keep the device busy
+# A prompt step launched from Python costs the host about 20 us per kernel, some eight kernels a layer,
+# whatever its size; the device needs about 2 flops per weight and token at some 1e15 flop/s, and it
+# still waits for the host now and then while it has less than one and a half times the host's time to
+# do (measured on the 4B shape: 1,024 tokens 9.4 ms as launches, 8.6 replayed; the host alone 5.9).  Steps
+# of fewer token rows than that are worth capturing (4B shape: 1,152; 0.6B: 7,552; 32B: 192); longer ones
+# keep the device busy anyway.
+HOST_SECONDS_PER_LAUNCH = 20e-6
+LAUNCHES_PER_LAYER = 8
+DEVICE_FLOPS = 1.0e15
+MAX_PROMPT_GRAPH_TOKENS = 8192
+
+
+def prompt_graph_limit(n_layers: int, weights_per_token: int) -> int:
+    """Token rows up to which a step of whole prompts is held up by the host's launches (a multiple of 64)."""
+    host = n_layers * LAUNCHES_PER_LAYER * HOST_SECONDS_PER_LAUNCH
+    rows = int(1.5 * host * DEVICE_FLOPS / (2.0 * max(weights_per_token, 1)))
+    return max(64, min(MAX_PROMPT_GRAPH_TOKENS, rows // 64 * 64))
+
+
+def _row_bucket(n: int) -> int:
+    """Token rows of a captured prompt step: a multiple of 64 up to 1,024, then of 128, 256, 512 as the count
+    doubles, so that rounding wastes a sixteenth of the rows at most and the shapes stay few."""
+    unit = 64
+    while n > 16 * unit:
+        unit *= 2
+    return -(-n // unit) * unit
+
+
+def _numel(shape) -> int:
+    n = 1
+    for d in shape:
+        n *= int(d)
+    return n
 
 
 def _bucket(n: int, cap: int) -> int:
@@ -92,7 +124,13 @@ class Engine:
         # Steps of whole prompts with few tokens are bound by the host's launches, not by the device:
         # a shape that comes back (token rows and the longest prompt rounded up, see _prompt_graph) is captured when
         # it is seen the second time, if the model's parts allow it.  The least recently used go first.
-        self.prompt_graph_tokens = PROMPT_GRAPH_TOKENS if self.use_cuda_graph and model.captures_start() else 0
+        self.prompt_graph_tokens = 0
+        if self.use_cuda_graph and model.captures_start():
+            # the weights every token meets: the scheduled blocks' matrices (the embedding is looked up, and the
+            # head reads one row per sequence)
+            per_token = sum(_numel(sp.shape) for e in model.schedule for sp in model.blocks[e.layer].param_specs().values()
+                            if sp.role == "matrix")
+            self.prompt_graph_tokens = prompt_graph_limit(len(model.schedule), per_token)
         self.max_prompt_graphs = 16
         self._prompt_graphs: "OrderedDict[Tuple[int, int, int], _CapturedStep]" = OrderedDict()
         self._prompt_shapes_seen: Dict[Tuple[int, int, int], int] = {}
@@ -290,10 +328,10 @@ class Engine:
 
     def _prompt_graph(self, slots, starts, tokens) -> Optional[torch.Tensor]:
         """Runs a step of whole prompts from a captured graph, or returns None (run it as it is).
-        Shapes are rounded up so that fewer graphs serve more steps: token rows to a multiple of 64
+        Shapes are rounded up so that fewer graphs serve more steps: token rows as _row_bucket says
         (the spare rows are nobody's, see fill_batch), the longest prompt to a power of two."""
         n_seq = len(slots)
-        n_tok = -(-sum(len(t) for t in tokens) // 64) * 64
+        n_tok = _row_bucket(sum(len(t) for t in tokens))
         if n_tok > self.prompt_graph_tokens:
             return None
         bound = min(_bucket(max(len(t) for t in tokens), 1 << 30), n_tok, self.max_seq_len)
