@@ -379,6 +379,56 @@ def test_toy_parts_register_build_and_step(graph):
             live = [i for i in live if t < dec[i]]
     if graph:
         assert eng.graph_replays > 0
+    # the toy mixer walks the host's lists when sequences start, and does not say captures_start:
+    # this model's prompt steps stay plain launches
+    assert eng.prompt_graph_tokens == 0 and not eng._prompt_graphs
+
+
+def test_a_toy_part_that_says_so_is_captured_in_prompt_steps():
+    """The routed toy feed-forward uses device tensors only; a subclass that says ``captures_start``
+    beside the library's attention makes a model whose prompt shapes are captured when they come back."""
+    from toyinfer_b200.engine import Engine
+    from toyinfer_b200.parts import PartSpec, build_part, register_part
+    from toyinfer_b200.parts.model import DecoderModel, LayerSpec, ModelSpec
+    make_toy_parts()
+    routed = type(build_part("feed_forward", PartSpec("toy_routed", {"inner": 8}), ctx_for(torch.float32, 48), "x."))
+    register_part("feed_forward", "toy_routed_device_only", type("RoutedDeviceOnly", (routed,), {"captures_start": True}), replace=True)
+    H, V, eps = 48, 90, 1e-5
+    norm = PartSpec("rmsnorm", {"size": H, "eps": eps})
+    block = PartSpec("prenorm", {"norm": norm, "feed_forward": PartSpec("toy_routed_device_only", {"inner": 24}),
+                                 "mixer": PartSpec("gqa_attention", {"n_heads": 3, "n_kv_heads": 1, "head_dim": 16, "qk_norm_eps": eps,
+                                                                     "position": "halves"})})
+    spec = ModelSpec(vocab_size=V, hidden_size=H, max_positions=256, layers=[LayerSpec("model.layers.0.", block)], final_norm=norm,
+                     positions={"halves": PartSpec("rotary_half", {"dim": 16, "theta": 1e4, "max_positions": 256})}, tie_head=True)
+    model = DecoderModel(spec, torch.float32, DEV)
+    w = bind_random(model, 17, torch.float32)
+    eng = Engine(model, max_tokens=64 * 6, max_batch=4, max_seq_len=256)
+    assert eng.prompt_graph_tokens > 0
+
+    def plain_logits(ids):
+        p = "model.layers.0."
+        h = plain.embedding(w["model.embed_tokens.weight"], ids)
+        a, _ = plain_attention_layer(plain.rms_norm(h, w[p + "input_layernorm.weight"], eps), w, p + "self_attn.", 3, 1, 16, eps, 1e4, 0, None)
+        h = h + a
+        x = plain.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
+        pick = (x @ w[p + "mlp.router.weight"].double().T).float()
+        ys = [torch.relu(x @ w[f"{p}mlp.e{e}.up.weight"].double().T) @ w[f"{p}mlp.e{e}.down.weight"].double().T for e in range(2)]
+        h = h + torch.where((pick[:, 1] > pick[:, 0])[:, None], ys[1], ys[0])
+        return plain.linear(plain.rms_norm(h, w["model.norm.weight"], eps), w["model.embed_tokens.weight"])
+
+    g = torch.Generator().manual_seed(28)
+    for lens in ([20, 5], [9, 30], [31, 31], [2, 17]):          # one shape: two sequences, 64 token rows, at most 32 each
+        seqs = [torch.randint(0, V, (n + 1,), generator=g).tolist() for n in lens]
+        slots = [eng.new_sequence() for _ in seqs]
+        first = eng.step([(sl, s[:-1]) for sl, s in zip(slots, seqs)], None).clone()
+        second = eng.step([(sl, [s[-1]]) for sl, s in zip(slots, seqs)], None).clone()
+        for i, s in enumerate(seqs):
+            want = plain_logits(s)
+            torch.testing.assert_close(first[i].cpu().double(), want[-2], rtol=1e-4, atol=1e-5)
+            torch.testing.assert_close(second[i].cpu().double(), want[-1], rtol=1e-4, atol=1e-5)
+        for sl in slots:
+            eng.end_sequence(sl)
+    assert list(eng._prompt_graphs) == [(2, 64, 32)]
 
 
 def test_toy_parts_in_pieces_and_beside_decoding_sequences():
