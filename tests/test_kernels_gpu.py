@@ -333,6 +333,30 @@ def test_linear_small_batch(K, monkeypatch, M, N, K_):
         assert gated.shape == (M, N // 2)
 
 
+@pytest.mark.parametrize("rows", [8, 9, 11, 12, 15, 16])
+def test_linear_small_batch_with_every_size_of_row_group(K, rows):
+    """The product for 2 to 8 tokens takes its weights in groups of 8 to 16 rows, as many as fill the
+    device's SMs evenly; here every size is forced in turn, on matrices whose last group is short, plain
+    and gated (a gated product's groups are even)."""
+    from toyinfer_b200.kernels import gemm
+    g = torch.Generator(device="cuda").manual_seed(14)
+    try:
+        gemm.set_skinny_rows(rows)
+        for M, N, K_ in ((8, 2560, 4096), (3, 333, 200), (5, 70, 1032), (2, 16, 64), (7, 9, 72)):
+            x = torch.randn(M, K_, generator=g, device="cuda").to(torch.bfloat16)
+            w = (torch.randn(N, K_, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+            want = (x.float() @ w.float().T)
+            torch.testing.assert_close(K.linear(x, w).float(), want.to(torch.bfloat16).float(), rtol=1.6e-2, atol=4e-3)
+            torch.testing.assert_close(K.linear(x, w, out_dtype=torch.float32), want, rtol=1e-3, atol=1e-3)
+            if N % 2 == 0:
+                gate, up = want[:, 0::2], want[:, 1::2]
+                act = up * (gate / (1 + torch.exp(-gate)))
+                torch.testing.assert_close(K.linear_swiglu(x, w).float(), act.to(torch.bfloat16).float(), rtol=1.6e-2, atol=4e-3)
+            K.check_status()
+    finally:
+        gemm.set_skinny_rows(0)
+
+
 @pytest.mark.parametrize("M", [1, 2, 8])
 def test_products_back_to_back_read_what_the_kernel_before_wrote(K, M):
     """Kernels are launched so that each may start while the one before it still runs and must

@@ -46,6 +46,7 @@ struct Args {
     const bf16* x; const bf16* w; void* out;
     int M, N, K;
     long long ldx, ldw, ldo;
+    int rows;       // weight rows per group, 8 to 16 (even for a gated product): see rows_per_group
 };
 
 // NT: token tiles of 8 (1 or 2); WARPS per block; WPR: warps that share a group of 16 rows.
@@ -56,11 +57,14 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int group = warp / WPR, slice = warp % WPR;
-    const long long r0 = ((long long)blockIdx.x * (WARPS / WPR) + group) * 16;
+    const int R = a.rows;
+    const long long r0 = ((long long)blockIdx.x * (WARPS / WPR) + group) * R;
     const int steps = (a.K + 63) >> 6;
     const int per = (steps + WPR - 1) / WPR;
     const int s0 = slice * per, s1 = min(steps, s0 + per);
-    // rows past the end repeat the last row; their sums are never stored
+    // of the MMA's 16 rows the group has the first R; the others, and rows past the matrix's end, are
+    // not loaded (zeros), and their sums are never stored
+    const bool lo_ok = g < R && r0 + g < a.N, hi_ok = g + 8 < R && r0 + g + 8 < a.N;
     const bf16* w_lo = a.w + (size_t)min(r0 + g, (long long)a.N - 1) * a.ldw + 16 * t;
     const bf16* w_hi = a.w + (size_t)min(r0 + g + 8, (long long)a.N - 1) * a.ldw + 16 * t;
     const bf16* x = a.x;
@@ -77,8 +81,8 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel
             for (int h = 0; h < 2; h++) {
                 const int k = (s + u) * 64 + 16 * t + 8 * h;
                 const bool ok = s + u < s1 && k < a.K;          // K is a multiple of 8: a piece is whole or absent
-                wl[u][h] = ok ? load_stream(w_lo + (size_t)(s + u) * 64 + 8 * h) : make_uint4(0, 0, 0, 0);
-                wh[u][h] = ok ? load_stream(w_hi + (size_t)(s + u) * 64 + 8 * h) : make_uint4(0, 0, 0, 0);
+                wl[u][h] = ok && lo_ok ? load_stream(w_lo + (size_t)(s + u) * 64 + 8 * h) : make_uint4(0, 0, 0, 0);
+                wh[u][h] = ok && hi_ok ? load_stream(w_hi + (size_t)(s + u) * 64 + 8 * h) : make_uint4(0, 0, 0, 0);
             }
         if (!waited) { ti_pdl_sync(); x = ti_dependent(x); waited = true; }      // x is the work of the kernel before this one
         // every piece of x of these steps (for one tile of 8 tokens at a time) is asked for before
@@ -134,9 +138,10 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel
             if ((g & 1) == 0) {
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    const long long row = r0 + g + (e >> 1) * 8;
+                    const int in_group = g + (e >> 1) * 8;
+                    const long long row = r0 + in_group;
                     const int tok = n * 8 + 2 * t + (e & 1);
-                    if (row + 1 < a.N && tok < a.M) {
+                    if (in_group + 1 < R && row + 1 < a.N && tok < a.M) {
                         const float gate = c[n][e], up = other[e];
                         out[(size_t)tok * a.ldo + (size_t)(row >> 1)] = from_f32<OutT>(up * (gate / (1.f + expf(-gate))));
                     }
@@ -145,9 +150,10 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel
         } else {
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const long long row = r0 + g + (e >> 1) * 8;
+                const int in_group = g + (e >> 1) * 8;
+                const long long row = r0 + in_group;
                 const int tok = n * 8 + 2 * t + (e & 1);
-                if (row < a.N && tok < a.M) out[(size_t)tok * a.ldo + (size_t)row] = from_f32<OutT>(c[n][e]);
+                if (in_group < R && row < a.N && tok < a.M) out[(size_t)tok * a.ldo + (size_t)row] = from_f32<OutT>(c[n][e]);
             }
         }
     }
@@ -155,7 +161,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel
 
 template <int NT, int WARPS, int WPR, bool GATED, typename OutT>
 int launch(const Args& a, bool late_start, cudaStream_t stream) {
-    const long long groups = ((long long)a.N + 15) / 16;
+    const long long groups = ((long long)a.N + a.rows - 1) / a.rows;
     const long long blocks = (groups + WARPS / WPR - 1) / (WARPS / WPR);
     TI_REQUIRE(blocks <= 0x7FFFFFFFll, "linear (small batch): %d rows of weights are too many", a.N);
     if (late_start)
@@ -184,7 +190,27 @@ int launch_nt(const Args& a, int out_f32, int gated, int wpr, bool late_start, c
     return launch_wpr<NT, false, bf16>(a, wpr, late_start, stream);
 }
 
+// Weight rows per group.  What bounds a product whose blocks all fit the SMs at once is the SM that has
+// most to read: 2,560 rows in groups of 16 are 160 blocks for 148 SMs, twelve SMs read twice as much as
+// the others and the rest wait for them (measured at 8 tokens, contraction 9,728: 148 groups 9.8 us, 149
+// groups 11.8, 160 groups 12.0, 296 groups 17.1).  So where groups of 16 rows leave places free, the
+// groups shrink (down to 8 rows; the MMA's other rows stay empty) until the blocks fill the places
+// that the SMs offer: 285 groups of 9 rows for 296 places.
+int g_force_rows = 0;       // for tests: every group size on any device
+int rows_per_group(int N, int wpr, bool gated, int sms) {
+    if (g_force_rows) return gated && (g_force_rows & 1) ? g_force_rows + 1 : g_force_rows;
+    const int warps = wpr == 16 ? 16 : 8;
+    const long long places = (long long)(sms > 0 ? sms : 1) * (warps == 16 ? 2 : 3) * (warps / wpr);     // groups on the SMs at once
+    if (((long long)N + 15) / 16 > places) return 16;
+    int rows = (int)((N + places - 1) / places);
+    if (rows < 8) rows = 8;
+    if (gated && (rows & 1)) rows++;
+    return rows > 16 ? 16 : rows;
+}
 }  // namespace
+
+// For tests: 8 to 16 weight rows per group whatever the shape (0: chosen by shape and device again).
+extern "C" void ti_set_skinny_rows(int rows) { g_force_rows = rows >= 8 && rows <= 16 ? rows : 0; }
 
 // x[M, K] (row stride ldx), w[N, K] (row stride ldw), both bfloat16, M from 1 to 16; out[M, N]
 // bfloat16 or float32.  With `gated`, w's rows are (gate_0, up_0, gate_1, up_1, ...) and out is
@@ -210,6 +236,6 @@ extern "C" int ti_linear_skinny(const void* x, const void* w, void* out, int M, 
     int wpr = 1;
     while (wpr < 8 && steps >= (wpr * 2) * UNROLL) wpr *= 2;
     if (wpr == 8 && groups * 8 < target && steps >= 16 * UNROLL) wpr = 16;
-    Args a{(const bf16*)x, (const bf16*)w, out, M, N, K, ldx, ldw, ldo};
+    Args a{(const bf16*)x, (const bf16*)w, out, M, N, K, ldx, ldw, ldo, rows_per_group(N, wpr, gated != 0, sms)};
     return M <= 8 ? launch_nt<1>(a, out_f32, gated, wpr, late_start != 0, stream) : launch_nt<2>(a, out_f32, gated, wpr, late_start != 0, stream);
 }

@@ -55,6 +55,12 @@ def set_tile_force(bn: int, splits: int = 0) -> None:
     _plans.clear()
 
 
+def set_skinny_rows(rows: int) -> None:
+    """For tests: the products of 2 to 8 tokens take groups of ``rows`` weight rows (8 to 16) whatever the
+    shape; 0 lets shape and device decide again."""
+    library().ti_set_skinny_rows(int(rows))
+
+
 def tc_eligible(x, w, K, ldx, ldw) -> bool:
     return (x.dtype == torch.bfloat16 and K % 8 == 0 and ldx % 8 == 0 and ldw % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
