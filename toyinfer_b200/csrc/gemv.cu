@@ -296,10 +296,14 @@ int launch_m(const Args& a, int out_f32, int gated, int rows, int wpr, bool late
     if (out_f32) return launch_r<M, false, float>(a, rows, wpr, late_start);
     return launch_r<M, false, bf16>(a, rows, wpr, late_start);
 }
-// Measured on the shapes of 4B- and 32B-sized layers: with at least half of 32 warps per SM
+// Measured on the shapes of 0.6B- to 32B-sized layers: with at least half of 32 warps per SM
 // from two rows per warp, one warp per pair of rows is best.  With fewer rows, several warps
 // share a pair so that the device fills, as long as a lane keeps a full round of loads; and
-// when the contraction is still long then, four rows per warp halve the reads of x.
+// four rows per warp halve the reads of x when the contraction is still long then, or when a
+// lane keeps four loads per row and the warps still fill the device (2,560 x 4,096: 5.7 -> 5.0 us,
+// one sequence's decode step on the 4B shape 2.11 -> 2.09 ms).  Alone, small matrices run faster
+// with more warps per pair than this gives them (1,024 x 3,072: 4.15 -> 2.5 us with eight), but
+// in a decode step they do not: a 0.6B-shaped step 0.75 -> 0.81 ms, whose kernels overlap.
 void choose_shape(int M, int N, int K, int sms, int* rows_out, int* wpr_out) {
     const long long target = 32ll * (sms > 0 ? sms : 1);
     const long long pairs = ((long long)N + 1) / 2;
@@ -307,7 +311,7 @@ void choose_shape(int M, int N, int K, int sms, int* rows_out, int* wpr_out) {
     int rows = 2, wpr = 1;
     if (pairs * 2 < target) {
         while (wpr < WARPS && pairs * wpr < target && pieces >= 32 * (wpr * 2) * 4) wpr *= 2;
-        if (pieces >= 32 * wpr * 8) rows = 4;
+        if (pieces >= 32 * wpr * 8 || (pieces >= 32 * wpr * 4 && pairs * wpr >= target)) rows = 4;
     } else if (M == 2 && pairs >= 8 * target) {
         rows = 4;
     }
