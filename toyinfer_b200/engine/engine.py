@@ -14,7 +14,9 @@ more than one token (its prefill writes cache rows [0, n) at positions 0..n-1,
 src/transformer.cpp:393-398, src/prefill.cu:185-208).  Its decode body is captured once
 into a CUDA graph and replayed (src/transformer.cpp:647-669).  Here a step in which every
 sequence goes on by one token is captured per batch-size bucket; the graph reads slots,
-lengths and token ids from device buffers refreshed before each replay.
+lengths and token ids from device buffers refreshed before each replay.  Steps of whole
+prompts with few tokens, which the host's launches would hold up, are captured as well when
+their shape comes back (``Engine._prompt_graph``).
 """
 from __future__ import annotations
 
@@ -55,7 +57,7 @@ class StepError(ValueError):
 # whatever its size; the device needs about 2 flops per weight and token at some 1e15 flop/s, and it
 # still waits for the host now and then while it has less than one and a half times the host's time to
 # do (measured on the 4B shape: 1,024 tokens 9.4 ms as launches, 8.6 replayed; the host alone 5.9).  Steps
-# of fewer token rows than that are worth capturing (4B shape: 1,152; 0.6B: 7,552; 32B: 192); longer ones
+# of fewer token rows than that are worth capturing (4B shape: 1,152; 0.6B: 7,616; 32B: 192); longer ones
 # keep the device busy anyway.
 HOST_SECONDS_PER_LAUNCH = 20e-6
 LAUNCHES_PER_LAYER = 8
