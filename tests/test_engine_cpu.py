@@ -271,6 +271,20 @@ def test_decode_attention_merges_as_clusters_only_when_all_find_room(monkeypatch
     assert plan(1, 2112) == (9, 0)
 
 
+def test_decode_attention_splits_the_keys_of_a_batch_that_would_leave_a_thin_second_round():
+    """A padded batch whose real sequences give a few more long blocks than run at once (two per SM) has
+    its keys split after all; batches that fit one round, or fill two, are left whole."""
+    from toyinfer_b200.kernels import attention
+    splits = lambda n_live, length, n_seq=64: attention.decode_splits(n_seq, 8, length, 64, 148, n_live=n_live)
+    assert [splits(n, 8192) for n in (32, 37, 38, 44, 45, 48, 53, 54, 64)] == [1, 1, 4, 4, 2, 2, 2, 1, 1]
+    assert [splits(n, 2048) for n in (37, 38, 48, 53, 54, 64)] == [1, 2, 2, 2, 1, 1]
+    assert splits(40, 100) == 1                                  # two pages: nothing to split
+    assert attention.decode_splits(64, 8, 8192, 64, 148) == 1    # asked without the number of real sequences
+    assert splits(8, 8192, n_seq=8) == 4                         # a batch that fits: as before
+    plan = lambda n_live: attention.decode_plan(64, 32, 8, 128, 8192, 64, 148, True, True, n_live)
+    assert plan(64) == (1, 0) and plan(40) == (4, 0)             # merged through scratch memory: no room for 512 clusters
+
+
 def test_spare_token_rows_of_a_step_of_fixed_size_change_nothing(cpu_engine, model_folders):
     """The form of a captured prompt step: more token rows than the sequences hold.  The spare rows stand at
     position 0 of a stand-in sequence in the scratch slot; the sequences' logits and what they leave in

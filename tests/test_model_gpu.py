@@ -202,6 +202,34 @@ def test_length_classes_with_the_same_launches_share_a_captured_step(tmp_path):
     assert_logits_close(torch.cat(got), want[2030:2070], dtype, "across two length classes with one captured step")
 
 
+def test_a_partly_filled_batch_splits_its_keys_and_a_full_one_does_not(model_folders, monkeypatch):
+    """The decode attention's plan looks at how many sequences of the padded batch are real: five of eight
+    on a device of (here pretended) four SMs would leave a thin second round of blocks and are split
+    two ways, eight of eight are not; two captured steps for one batch size, the plain implementation's
+    logits from both, also when the batch shrinks from one to the other."""
+    from toyinfer_b200.kernels import attention, gemm
+    monkeypatch.setattr(attention, "sm_count", lambda device: 4)
+    monkeypatch.setattr(gemm, "sm_count", lambda device: 4)
+    name, dtype = "D", "bfloat16"
+    eng = make_engine(model_folders[name], dtype, max_batch=8, max_tokens=64 * 40)
+    assert eng.model.launch_plan(8, 1024, 5)[0][0] == 2 and eng.model.launch_plan(8, 1024, 8)[0][0] == 1
+    lens = [70, 9, 130, 33, 64, 5, 90, 17]
+    seqs = prompts_for(name, [n + 6 for n in lens], seed=80)
+    want = [plain_logits(model_folders[name], s, dtype) for s in seqs]
+    slots = [eng.new_sequence() for _ in seqs]
+    eng.step([(sl, s[:n]) for sl, s, n in zip(slots, seqs, lens)], [[] for _ in seqs])
+    live = list(range(8))
+    for t in range(6):
+        if t == 3:                                   # three sequences end: five of eight go on
+            for i in (1, 4, 6):
+                eng.end_sequence(slots[i])
+            live = [i for i in live if i not in (1, 4, 6)]
+        logits = eng.step([(slots[i], [seqs[i][lens[i] + t]]) for i in live], None).clone()
+        for row, i in enumerate(live):
+            assert_logits_close(logits[row], want[i][lens[i] + t], dtype, f"sequence {i} step {t} of {len(live)} live")
+    assert len(eng._graphs) == 2 and eng.graph_replays >= 2
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_padding_and_company_change_nothing(model_folders, dtype):
     """A request's logits are the same alone, in a batch of 3 (padded to 4 by the graph's

@@ -117,7 +117,7 @@ class Engine:
         self.use_cuda_graph = bool(use_cuda_graph) and self.device.type == "cuda"
         self._eager_bufs: Dict[Tuple[int, int], BatchBuffers] = {}
         self._graphs: Dict[Tuple[int, Any], "_CapturedStep"] = {}     # (batch bucket, launch plan of its length class) -> captured step
-        self._plans: Dict[Tuple[int, int], Any] = {}                 # (batch bucket, length class) -> the model's launch plan
+        self._plans: Dict[Tuple[int, int, int], Any] = {}            # (batch bucket, length class, real sequences) -> the model's launch plan
         # All captured steps draw their intermediate buffers from one pool: steps run one at a time,
         # so what one graph freed during its capture another may use.  Each graph still keeps its
         # own [bucket, vocab] float32 logits (alive at the end of its capture).
@@ -319,9 +319,9 @@ class Engine:
         cls = min(cls, self.max_seq_len)
         # ... unless nothing in the model's launches tells the two classes apart (with eight sequences of
         # 32 heads over 8 the keys are split four ways from 512 positions on): one graph serves both
-        plan = self._plans.get((b, cls))
+        plan = self._plans.get((b, cls, n))
         if plan is None:
-            plan = self._plans[(b, cls)] = self.model.launch_plan(b, cls)
+            plan = self._plans[(b, cls, n)] = self.model.launch_plan(b, cls, n)
         g = self._graphs.get((b, plan))
         if g is None:
             g = self._graphs[(b, plan)] = _CapturedStep(self, "extend", b, b, cls)

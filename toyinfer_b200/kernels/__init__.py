@@ -374,15 +374,17 @@ def attention_chunk(q, k, v, mem, scale: float, window: int, batch) -> torch.Ten
     return out
 
 
-def attention_decode_plan(n_seq: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int, plan_len: int, dtype, device):
+def attention_decode_plan(n_seq: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int, plan_len: int, dtype, device,
+                          n_live: Optional[int] = None):
     """(splits, way of merging them) that a decode step's attention launches with when it is
-    planned for ``plan_len`` positions: all of the launch that depends on that length."""
+    planned for ``plan_len`` positions and ``n_live`` of its ``n_seq`` sequences are real: all of
+    the launch that depends on those two."""
     from . import attention
     from .gemm import sm_count
     from ..cache.allocators import PAGE
     span = plan_len if window <= 0 else min(plan_len, window + PAGE)
     tensor_cores = dtype == torch.bfloat16 and head_dim in (64, 128)
-    return attention.decode_plan(n_seq, n_heads, n_kv_heads, head_dim, span, PAGE, sm_count(device), tensor_cores, True)
+    return attention.decode_plan(n_seq, n_heads, n_kv_heads, head_dim, span, PAGE, sm_count(device), tensor_cores, True, n_live)
 
 
 def attention_decode(q, mem, scale: float, window: int, batch) -> torch.Tensor:

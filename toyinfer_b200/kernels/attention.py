@@ -3,6 +3,7 @@ decode kernel."""
 from __future__ import annotations
 
 import ctypes
+from typing import Optional
 
 import torch
 
@@ -77,14 +78,29 @@ def chunk(q, k, v, mem, out, scale, window, batch) -> None:
           k.shape[1], hd, scale, window, *cache, _code(q, "attention_chunk"), _stream())
 
 
-def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int, min_pages: int = 4, most: int = 64) -> int:
+def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int, min_pages: int = 4, most: int = 64,
+                  n_live: Optional[int] = None) -> int:
     """Splits along the keys so that the grid has about two blocks per SM, but no split
     shorter than ``min_pages`` pages and no more than ``most``.  Depends only on the batch's
-    padded size and the longest length the step was planned for, so that a captured launch
-    stays valid."""
+    padded size, the number of its sequences that are real (``n_live``; the others hold one
+    position) and the longest length the step was planned for; a captured launch is valid for
+    steps that give the same answer.
+
+    A step whose long blocks (a real sequence's kv head each) are a few more than the two per SM
+    that run at once leaves most SMs idle while the rest works off a second round: 38 to 52
+    sequences of a batch padded to 64 at 8 kv heads.  Their keys are then split after all, into
+    blocks short enough to fill the rounds (measured alone, 40 of 64 sequences at 8,192 positions:
+    291 us unsplit, 241 in two, 222 in four, 208 at the copy bandwidth; at 2,048: 76, 68, 71, 52;
+    56 and more of 64 are best left whole)."""
     tiles = max(1, (max_len + page - 1) // page)
     want = max(1, (2 * sms) // max(1, n_seq * n_kv_heads))
-    return max(1, min(want, (tiles + min_pages - 1) // min_pages, most))
+    longest = (tiles + min_pages - 1) // min_pages
+    splits = max(1, min(want, longest, most))
+    if splits == 1 and n_live is not None and longest >= 2 and most >= 2:
+        places, long_blocks = 2 * sms, n_live * n_kv_heads
+        if places < long_blocks <= 1.45 * places:
+            splits = 4 if (tiles >= 128 and long_blocks <= 1.2 * places and min(longest, most) >= 4) else 2
+    return splits
 
 
 _cluster_room: dict = {}
@@ -117,7 +133,7 @@ force_merge_mode = None      # tests set 0, 1 or 2 here to choose how the tensor
 
 
 def decode_plan(n_seq: int, n_heads: int, n_kv_heads: int, hd: int, max_len: int, page: int, sms: int,
-                tensor_cores: bool, fused: bool) -> tuple:
+                tensor_cores: bool, fused: bool, n_live: Optional[int] = None) -> tuple:
     """(splits, mode) of a decode step's attention.  mode (csrc/attn_decode_mma.cu): 2 the splits of a
     kv head are one cluster and merge through distributed shared memory (no scratch, no second kernel);
     else through global scratch and a combine kernel, started late (1) or like every kernel (0).
@@ -134,7 +150,7 @@ def decode_plan(n_seq: int, n_heads: int, n_kv_heads: int, hd: int, max_len: int
         clusters = n_seq * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
         if splits >= 2 and (force_merge_mode == 2 or clusters * 1.08 <= cluster_room(hd, fused, splits)):
             return splits, 2
-    splits = decode_splits(n_seq, n_kv_heads, max_len, page, sms)
+    splits = decode_splits(n_seq, n_kv_heads, max_len, page, sms, n_live=n_live)
     if tensor_cores and force_merge_mode in (0, 1):
         return splits, force_merge_mode
     return splits, scratch_mode
@@ -145,7 +161,7 @@ def decode(q, mem, out, scale, window, batch) -> None:
     nkv = mem.n_kv_heads
     span = batch.plan_len if window <= 0 else min(batch.plan_len, window + mem.page_size)
     tensor_cores = q.dtype == torch.bfloat16 and hd in (64, 128)
-    splits, mode = decode_plan(B, nh, nkv, hd, span, mem.page_size, sm_count(q.device), tensor_cores, False)
+    splits, mode = decode_plan(B, nh, nkv, hd, span, mem.page_size, sm_count(q.device), tensor_cores, False, batch.n_real_seq)
     part_o = part_ml = None
     if splits > 1 and mode != 2:
         part_o = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device)
@@ -186,7 +202,7 @@ def decode_fused(q, k, v, q_w, k_w, eps, tables, mem, out, scale, window, batch)
     B, nh, hd = q.shape
     nkv = mem.n_kv_heads
     span = batch.plan_len if window <= 0 else min(batch.plan_len, window + mem.page_size)
-    splits, mode = decode_plan(B, nh, nkv, hd, span, mem.page_size, sm_count(q.device), True, True)
+    splits, mode = decode_plan(B, nh, nkv, hd, span, mem.page_size, sm_count(q.device), True, True, batch.n_real_seq)
     part_o = part_ml = None
     if splits > 1 and mode != 2:
         part_o = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device)

@@ -122,9 +122,9 @@ class GQAAttention(Mixer):
             return None
         return KVRequest(self.n_kv_heads, self.head_dim, self.window)
 
-    def launch_plan(self, n_seq: int, plan_len: int, dtype, device):
-        # only the split of a sequence's keys over blocks looks at the planned length
-        return K.attention_decode_plan(n_seq, self.n_heads, self.n_kv_heads, self.head_dim, self.window, plan_len, dtype, device)
+    def launch_plan(self, n_seq: int, plan_len: int, dtype, device, n_live=None):
+        # only the split of a sequence's keys over blocks looks at the planned length and at how many sequences are real
+        return K.attention_decode_plan(n_seq, self.n_heads, self.n_kv_heads, self.head_dim, self.window, plan_len, dtype, device, n_live)
 
     # -- one step -----------------------------------------------------------
     def forward(self, x, batch, mem, shared) -> torch.Tensor:

@@ -154,11 +154,12 @@ class Mixer(Part):
     captures_start = False          # a "start" step reads nothing of the batch's host side and allocates through torch
                                     # only: the engine may capture it (a class attribute or a property)
 
-    def launch_plan(self, n_seq: int, plan_len: int, dtype, device):
-        """What, of a captured single-token step of ``n_seq`` sequences, depends on the length the
-        step is planned for (a hashable value).  Steps planned for different lengths share one
-        captured graph when every mixer answers the same for both.  The default, the length itself,
-        shares nothing."""
+    def launch_plan(self, n_seq: int, plan_len: int, dtype, device, n_live=None):
+        """What, of a captured single-token step of ``n_seq`` sequences of which ``n_live`` are real
+        (the others are padding of one position), depends on the length the step is planned for and
+        on ``n_live`` (a hashable value).  Steps share one captured graph when every mixer answers the
+        same for them.  The default, the length itself, shares graphs between numbers of real
+        sequences only."""
         return plan_len
 
     def memory_request(self):
@@ -195,9 +196,9 @@ class Head(Part):
 class Block(Part):
     mixer: Mixer
 
-    def launch_plan(self, n_seq: int, plan_len: int, dtype, device):
+    def launch_plan(self, n_seq: int, plan_len: int, dtype, device, n_live=None):
         """As Mixer.launch_plan, for the whole block."""
-        return self.mixer.launch_plan(n_seq, plan_len, dtype, device)
+        return self.mixer.launch_plan(n_seq, plan_len, dtype, device, n_live)
 
     @property
     def captures_start(self) -> bool:

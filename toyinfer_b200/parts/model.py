@@ -131,10 +131,10 @@ class DecoderModel(Part):
             out.append(None if e.memory_of is not None else self.blocks[e.layer].mixer.memory_request())
         return out
 
-    def launch_plan(self, n_seq: int, plan_len: int):
-        """What of a captured single-token step depends on the length it is planned for: the answers
-        of all scheduled blocks (see Mixer.launch_plan)."""
-        return tuple(self.blocks[e.layer].launch_plan(n_seq, plan_len, self.dtype, self.device) for e in self.schedule)
+    def launch_plan(self, n_seq: int, plan_len: int, n_live: Optional[int] = None):
+        """What of a captured single-token step depends on the length it is planned for and on how many
+        of its sequences are real: the answers of all scheduled blocks (see Mixer.launch_plan)."""
+        return tuple(self.blocks[e.layer].launch_plan(n_seq, plan_len, self.dtype, self.device, n_live) for e in self.schedule)
 
     def captures_start(self) -> bool:
         """Whether a step of whole prompts may be captured: every scheduled block says so."""
