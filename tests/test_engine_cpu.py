@@ -271,7 +271,7 @@ def test_decode_attention_merges_as_clusters_only_when_all_find_room(monkeypatch
     assert plan(1, 2112) == (9, 0)
 
 
-def test_decode_attention_splits_the_keys_of_a_batch_that_would_leave_a_thin_second_round():
+def test_decode_attention_splits_the_keys_of_a_batch_that_would_leave_a_thin_second_round(monkeypatch):
     """A padded batch whose real sequences give a few more long blocks than run at once (two per SM) has
     its keys split after all; batches that fit one round, or fill two, are left whole."""
     from toyinfer_b200.kernels import attention
@@ -281,8 +281,11 @@ def test_decode_attention_splits_the_keys_of_a_batch_that_would_leave_a_thin_sec
     assert splits(40, 100) == 1                                  # two pages: nothing to split
     assert attention.decode_splits(64, 8, 8192, 64, 148) == 1    # asked without the number of real sequences
     assert splits(8, 8192, n_seq=8) == 4                         # a batch that fits: as before
-    plan = lambda n_live: attention.decode_plan(64, 32, 8, 128, 8192, 64, 148, True, True, n_live)
+    places = {128: 296, 64: 592}
+    monkeypatch.setattr(attention, "cluster_room", lambda hd, fused, splits: places[hd] // splits)
+    plan = lambda n_live, hd=128: attention.decode_plan(64, 32, 8, hd, 8192, 64, 148, True, True, n_live)
     assert plan(64) == (1, 0) and plan(40) == (4, 0)             # merged through scratch memory: no room for 512 clusters
+    assert plan(40, hd=64) == (1, 0)                             # smaller blocks, four per SM: 320 of them run at once
 
 
 def test_spare_token_rows_of_a_step_of_fixed_size_change_nothing(cpu_engine, model_folders):

@@ -210,6 +210,7 @@ def test_a_partly_filled_batch_splits_its_keys_and_a_full_one_does_not(model_fol
     from toyinfer_b200.kernels import attention, gemm
     monkeypatch.setattr(attention, "sm_count", lambda device: 4)
     monkeypatch.setattr(gemm, "sm_count", lambda device: 4)
+    monkeypatch.setattr(attention, "cluster_room", lambda hd, fused, splits: 8 // splits)      # two blocks on each of them
     name, dtype = "D", "bfloat16"
     eng = make_engine(model_folders[name], dtype, max_batch=8, max_tokens=64 * 40)
     assert eng.model.launch_plan(8, 1024, 5)[0][0] == 2 and eng.model.launch_plan(8, 1024, 8)[0][0] == 1

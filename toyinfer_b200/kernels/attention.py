@@ -79,15 +79,15 @@ def chunk(q, k, v, mem, out, scale, window, batch) -> None:
 
 
 def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int, min_pages: int = 4, most: int = 64,
-                  n_live: Optional[int] = None) -> int:
+                  n_live: Optional[int] = None, places: Optional[int] = None) -> int:
     """Splits along the keys so that the grid has about two blocks per SM, but no split
     shorter than ``min_pages`` pages and no more than ``most``.  Depends only on the batch's
     padded size, the number of its sequences that are real (``n_live``; the others hold one
     position) and the longest length the step was planned for; a captured launch is valid for
     steps that give the same answer.
 
-    A step whose long blocks (a real sequence's kv head each) are a few more than the two per SM
-    that run at once leaves most SMs idle while the rest works off a second round: 38 to 52
+    A step whose long blocks (a real sequence's kv head each) are a few more than the ``places``
+    (blocks that run at once; two per SM unless told) leaves most SMs idle while the rest works off a second round: 38 to 52
     sequences of a batch padded to 64 at 8 kv heads.  Their keys are then split after all, into
     blocks short enough to fill the rounds (measured alone, 40 of 64 sequences at 8,192 positions:
     291 us unsplit, 241 in two, 222 in four, 208 at the copy bandwidth; at 2,048: 76, 68, 71, 52;
@@ -97,7 +97,7 @@ def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, page: int, sms: int
     longest = (tiles + min_pages - 1) // min_pages
     splits = max(1, min(want, longest, most))
     if splits == 1 and n_live is not None and longest >= 2 and most >= 2:
-        places, long_blocks = 2 * sms, n_live * n_kv_heads
+        places, long_blocks = places or 2 * sms, n_live * n_kv_heads
         if places < long_blocks <= 1.45 * places:
             splits = 4 if (tiles >= 128 and long_blocks <= 1.2 * places and min(longest, most) >= 4) else 2
     return splits
@@ -150,7 +150,9 @@ def decode_plan(n_seq: int, n_heads: int, n_kv_heads: int, hd: int, max_len: int
         clusters = n_seq * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
         if splits >= 2 and (force_merge_mode == 2 or clusters * 1.08 <= cluster_room(hd, fused, splits)):
             return splits, 2
-    splits = decode_splits(n_seq, n_kv_heads, max_len, page, sms, n_live=n_live)
+    # (how many blocks of the tensor-core kernel the device holds at once: a cluster of one is a block)
+    places = cluster_room(hd, fused, 1) if tensor_cores and n_live is not None and n_live * n_kv_heads > 2 * sms else None
+    splits = decode_splits(n_seq, n_kv_heads, max_len, page, sms, n_live=n_live, places=places)
     if tensor_cores and force_merge_mode in (0, 1):
         return splits, force_merge_mode
     return splits, scratch_mode
