@@ -159,8 +159,17 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel
     }
 }
 
+int rows_per_group(int N, long long places, bool gated);
+
 template <int NT, int WARPS, int WPR, bool GATED, typename OutT>
-int launch(const Args& a, bool late_start, cudaStream_t stream) {
+int launch(Args a, int sms, bool late_start, cudaStream_t stream) {
+    // blocks of this kernel that an SM holds at once, as the runtime counts them (asked once)
+    static int per_sm = 0;
+    if (per_sm == 0) {
+        TI_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, skinny_kernel<NT, WARPS, WPR, GATED, OutT>, WARPS * 32, 0));
+        if (per_sm < 1) per_sm = 1;
+    }
+    a.rows = rows_per_group(a.N, (long long)(sms > 0 ? sms : 1) * per_sm * (WARPS / WPR), GATED);
     const long long groups = ((long long)a.N + a.rows - 1) / a.rows;
     const long long blocks = (groups + WARPS / WPR - 1) / (WARPS / WPR);
     TI_REQUIRE(blocks <= 0x7FFFFFFFll, "linear (small batch): %d rows of weights are too many", a.N);
@@ -173,21 +182,21 @@ int launch(const Args& a, bool late_start, cudaStream_t stream) {
 }
 
 template <int NT, bool GATED, typename OutT>
-int launch_wpr(const Args& a, int wpr, bool late_start, cudaStream_t stream) {
+int launch_wpr(const Args& a, int wpr, int sms, bool late_start, cudaStream_t stream) {
     switch (wpr) {
-        case 1: return launch<NT, 8, 1, GATED, OutT>(a, late_start, stream);
-        case 2: return launch<NT, 8, 2, GATED, OutT>(a, late_start, stream);
-        case 4: return launch<NT, 8, 4, GATED, OutT>(a, late_start, stream);
-        case 8: return launch<NT, 8, 8, GATED, OutT>(a, late_start, stream);
-        default: return launch<NT, 16, 16, GATED, OutT>(a, late_start, stream);
+        case 1: return launch<NT, 8, 1, GATED, OutT>(a, sms, late_start, stream);
+        case 2: return launch<NT, 8, 2, GATED, OutT>(a, sms, late_start, stream);
+        case 4: return launch<NT, 8, 4, GATED, OutT>(a, sms, late_start, stream);
+        case 8: return launch<NT, 8, 8, GATED, OutT>(a, sms, late_start, stream);
+        default: return launch<NT, 16, 16, GATED, OutT>(a, sms, late_start, stream);
     }
 }
 
 template <int NT>
-int launch_nt(const Args& a, int out_f32, int gated, int wpr, bool late_start, cudaStream_t stream) {
-    if (gated) return launch_wpr<NT, true, bf16>(a, wpr, late_start, stream);
-    if (out_f32) return launch_wpr<NT, false, float>(a, wpr, late_start, stream);
-    return launch_wpr<NT, false, bf16>(a, wpr, late_start, stream);
+int launch_nt(const Args& a, int out_f32, int gated, int wpr, int sms, bool late_start, cudaStream_t stream) {
+    if (gated) return launch_wpr<NT, true, bf16>(a, wpr, sms, late_start, stream);
+    if (out_f32) return launch_wpr<NT, false, float>(a, wpr, sms, late_start, stream);
+    return launch_wpr<NT, false, bf16>(a, wpr, sms, late_start, stream);
 }
 
 // Weight rows per group.  What bounds a product whose blocks all fit the SMs at once is the SM that has
@@ -195,12 +204,10 @@ int launch_nt(const Args& a, int out_f32, int gated, int wpr, bool late_start, c
 // the others and the rest wait for them (measured at 8 tokens, contraction 9,728: 148 groups 9.8 us, 149
 // groups 11.8, 160 groups 12.0, 296 groups 17.1).  So where groups of 16 rows leave places free, the
 // groups shrink (down to 8 rows; the MMA's other rows stay empty) until the blocks fill the places
-// that the SMs offer: 285 groups of 9 rows for 296 places.
+// that the SMs offer (`places`: groups on the SMs at once): 285 groups of 9 rows for 296 places.
 int g_force_rows = 0;       // for tests: every group size on any device
-int rows_per_group(int N, int wpr, bool gated, int sms) {
+int rows_per_group(int N, long long places, bool gated) {
     if (g_force_rows) return gated && (g_force_rows & 1) ? g_force_rows + 1 : g_force_rows;
-    const int warps = wpr == 16 ? 16 : 8;
-    const long long places = (long long)(sms > 0 ? sms : 1) * (warps == 16 ? 2 : 3) * (warps / wpr);     // groups on the SMs at once
     if (((long long)N + 15) / 16 > places) return 16;
     int rows = (int)((N + places - 1) / places);
     if (rows < 8) rows = 8;
@@ -236,6 +243,7 @@ extern "C" int ti_linear_skinny(const void* x, const void* w, void* out, int M, 
     int wpr = 1;
     while (wpr < 8 && steps >= (wpr * 2) * UNROLL) wpr *= 2;
     if (wpr == 8 && groups * 8 < target && steps >= 16 * UNROLL) wpr = 16;
-    Args a{(const bf16*)x, (const bf16*)w, out, M, N, K, ldx, ldw, ldo, rows_per_group(N, wpr, gated != 0, sms)};
-    return M <= 8 ? launch_nt<1>(a, out_f32, gated, wpr, late_start != 0, stream) : launch_nt<2>(a, out_f32, gated, wpr, late_start != 0, stream);
+    Args a{(const bf16*)x, (const bf16*)w, out, M, N, K, ldx, ldw, ldo, 16};
+    return M <= 8 ? launch_nt<1>(a, out_f32, gated, wpr, sms, late_start != 0, stream)
+                  : launch_nt<2>(a, out_f32, gated, wpr, sms, late_start != 0, stream);
 }
