@@ -1,8 +1,8 @@
 """Which matrix-product kernel runs a given shape.
 
 bfloat16 operands whose rows are 16-byte aligned go to the tcgen05 kernel (the weights play
-the 128-row operand when there are at most 64 tokens), or, for up to 8 tokens, to kernels
-that only stream the weights (CUDA cores for one token, mma.sync beyond); everything else,
+the 128-row operand when there are at most 64 tokens), or, for up to 8 tokens (16 for small
+matrices), to kernels that only stream the weights (CUDA cores for one token, mma.sync beyond); everything else,
 and the whole 32-bit engine, runs on the CUDA-core kernels.
 """
 from __future__ import annotations
@@ -20,6 +20,16 @@ from .lib import library
 # 2.63 / 2.88; at 16 sequences the tcgen05 kernel 3.37 against 3.58.
 GEMV_MAX_TOKENS = 1      # one token: a plain read of the weights on the CUDA cores
 SKINNY_MAX_TOKENS = 8    # up to this many: mma.sync with both operands loaded straight from global memory
+# ... and up to 16 tokens where the matrix is small: the tcgen05 kernel's fixed costs (tensor memory,
+# barriers, a split contraction to add up) then weigh more than the second tile of tokens does here.
+# Measured alone at 12 and 16 tokens, us, this kernel against tcgen05: 4,096 x 1,024 3.1 / 5.8, 2,048 x 2,048
+# 4.4 / 6.6, 6,144 x 2,560 7.2 / 9.1, 6,144 x 4,096 10.3 / 12.0, but 7,168 x 5,120 20.5 / 14.8, 2,560 x 9,728
+# 16.4 / 12.6.  In whole decode steps of 9 to 16 sequences only the small shapes keep the gain (0.6B-shaped
+# layers 1.53 -> 1.36 ms; with 4B's q/k/v and output projections here too 3.02 -> 3.12, 8B's 4.03 -> 4.24):
+# the limits are those of the small shapes.
+SKINNY_SMALL_MAX_TOKENS = 16
+SKINNY_SMALL_MAX_K = 3072
+SKINNY_SMALL_MAX_WEIGHTS = 8_500_000
 _tickets = {}
 _plans = {}         # (M, N, K, sms) -> (workspace floats, tickets) as ti_linear_tc_plan answers
 _sm_counts = {}
@@ -75,7 +85,8 @@ def run(x, w, out, M, N, K, ldx, ldw, gated: bool = False, late_start: bool = Fa
         _call(lib.ti_linear_gemv, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, 1 if gated else 0,
               sm_count(x.device), 1 if late_start else 0, _stream())
         return
-    if tc_eligible(x, w, K, ldx, ldw) and M <= SKINNY_MAX_TOKENS:
+    if tc_eligible(x, w, K, ldx, ldw) and (M <= SKINNY_MAX_TOKENS or (
+            M <= SKINNY_SMALL_MAX_TOKENS and SKINNY_MAX_TOKENS >= 8 and K <= SKINNY_SMALL_MAX_K and N * K <= SKINNY_SMALL_MAX_WEIGHTS)):
         _call(lib.ti_linear_skinny, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, 1 if gated else 0,
               sm_count(x.device), 1 if late_start else 0, _stream())
         return
