@@ -126,3 +126,28 @@ def test_random_shapes_and_device_sizes():
         if _check(M, N, K, sms) is not None:
             walked += 1
     assert walked > 100
+
+
+def test_row_groups_of_the_few_token_product_fill_the_places_and_never_overflow_them():
+    """The few-token product's weight rows per group (8 to 16, even when gated): whenever groups of 16 rows
+    fit the places that the SMs offer at once, the groups are the smallest (down to 8 rows) that still fit."""
+    from toyinfer_b200.kernels.lib import library
+    fn = library().ti_skinny_rows_per_group
+    fn.argtypes = [ctypes.c_int, ctypes.c_longlong, ctypes.c_int]
+    fn.restype = ctypes.c_int
+    assert fn(2560, 296, 0) == 9 and fn(6144, 444, 0) == 14 and fn(19456, 444, 1) == 16 and fn(2560, 296, 1) == 10
+    rng = random.Random(3)
+    for _ in range(3000):
+        places = rng.choice([1, 2, 60, 148, 264, 296, 444, 592, 1184])
+        n = rng.randint(1, 20 * places + 40)
+        for gated in (0, 1):
+            rows = fn(n, places, gated)
+            assert 8 <= rows <= 16 and (not gated or rows % 2 == 0)
+            groups = -(-n // rows)
+            if -(-n // 16) > places:
+                assert rows == 16                       # more than one round anyway: whole groups
+            else:
+                assert groups <= places
+                smaller = rows - (2 if gated else 1)
+                if smaller >= 8:
+                    assert -(-n // smaller) > places    # the next smaller group would overflow the places

@@ -216,6 +216,9 @@ int rows_per_group(int N, long long places, bool gated) {
 }
 }  // namespace
 
+// For tests on the host: the rows per group that a product of N weight rows takes when the SMs hold `places` groups at once.
+extern "C" int ti_skinny_rows_per_group(int N, long long places, int gated) { return rows_per_group(N, places, gated != 0); }
+
 // For tests: 8 to 16 weight rows per group whatever the shape (0: chosen by shape and device again).
 extern "C" void ti_set_skinny_rows(int rows) { g_force_rows = rows >= 8 && rows <= 16 ? rows : 0; }
 
